@@ -1,0 +1,487 @@
+// Attention kernels: head norm + rotation + cache write, prefill attention over the step's
+// own keys, decode attention over the paged cache (split over fixed chunks, ordered merge).
+//
+// Masks: a key at position k is visible to a query at position p when k <= p and, for a
+// window W > 0, k + W > p.  Scores, softmax and the probability-value sums are float.
+#include "common.cuh"
+#include <math.h>
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float* out);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* out) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<bf16>(const bf16* p, float* out) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+
+// =========================================================================================
+// Head norm, rotation, cache write.  One warp per (token, head); q heads first, then k heads.
+//   qkv row: [ q: QH*HD | k: KVH*HD | v: KVH*HD | ... ]  (row stride ld)
+//   u = T((x * inv_rms(x)) * w)           when w is given (w_q for q heads, w_k for k heads)
+//   o_i       = u_i cos a - u_{i+HD/2} sin a
+//   o_{i+HD/2}= u_{i+HD/2} cos a + u_i sin a,   a = float(pos) * rate[i]      when rate is given
+// q and k are overwritten in place; k and the raw v also go to the cache entry of (slot, pos):
+// entry = pos (growing group) or pos % ring (ring group; during a prompt longer than the ring
+// only the last `ring` positions are stored, so that no two rows meet in one entry).
+// =========================================================================================
+template <typename T>
+__global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float* __restrict__ wq,
+                                  const float* __restrict__ wk, const float* __restrict__ rate,
+                                  const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                  const int* __restrict__ seq_slot, const int* __restrict__ seq_end,
+                                  T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
+                                  int ptab_stride, int ring, int QH, int KVH, int HD, float eps) {
+    extern __shared__ float ubuf[];              // [warps][HD]
+    const int lane = threadIdx.x, warp = threadIdx.y;
+    const int head = blockIdx.x * blockDim.y + warp;
+    const int t = blockIdx.y;
+    if (head >= QH + KVH) return;
+    const bool is_q = head < QH;
+    const int kvh = head - QH;
+    T* x = qkv + (long long)t * ld + (is_q ? (long long)head * HD : (long long)QH * HD + (long long)kvh * HD);
+    float* u = ubuf + warp * HD;
+    const float* w = is_q ? wq : wk;
+    const int pos = tok_pos[t];
+    const int half = HD >> 1;
+
+    float ss = 0.f;
+    for (int d = lane; d < HD; d += 32) {
+        const float v = to_f32(x[d]);
+        u[d] = v;
+        ss += v * v;
+    }
+    if (w) {
+        ss = warp_sum(ss);
+        const float inv = 1.f / sqrtf(ss / (float)HD + eps);
+        for (int d = lane; d < HD; d += 32) u[d] = rounded<T>((u[d] * inv) * w[d]);
+    }
+    __syncwarp();
+
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (!is_q && pool) {
+        const int b = tok_seq[t];
+        const int end = seq_end[b];
+        const bool keep = ring == 0 || pos + ring >= end;
+        if (keep) {
+            const int entry = ring ? pos % ring : pos;
+            const int page = ptab[(long long)seq_slot[b] * ptab_stride + entry / PAGE_TOKENS];
+            const int row = entry % PAGE_TOKENS;
+            kdst = kv_tile(pool, 0, pages, page, kvh, KVH, HD) + (long long)row * HD;
+            vdst = kv_tile(pool, 1, pages, page, kvh, KVH, HD) + (long long)row * HD;
+        }
+    }
+    for (int d = lane; d < HD; d += 32) {
+        float o = u[d];
+        if (rate) {
+            const int i = d < half ? d : d - half;
+            const float a = (float)pos * rate[i];
+            float s, c;
+            sincosf(a, &s, &c);
+            o = d < half ? u[d] * c - u[d + half] * s : u[d] * c + u[d - half] * s;
+        }
+        const T ot = from_f32<T>(o);
+        x[d] = ot;
+        if (kdst) kdst[d] = ot;
+    }
+    if (vdst) {
+        const T* v = x + (long long)KVH * HD;
+        for (int d = lane; d < HD; d += 32) vdst[d] = v[d];
+    }
+}
+
+extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, const float* wk,
+                             const float* rate, const int* tok_pos, const int* tok_seq,
+                             const int* seq_slot, const int* seq_end, void* pool, long long pages,
+                             const int* ptab, int ptab_stride, int ring, int T, int QH, int KVH,
+                             int HD, float eps, cudaStream_t st) {
+    if (T <= 0) return CM_OK;
+    if (HD % 2 || HD <= 0) CM_REFUSE("qk_prepare: head size %d is not even", HD);
+    if (ring % PAGE_TOKENS) CM_REFUSE("qk_prepare: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
+    dim3 block(32, 4), grid((QH + KVH + 3) / 4, T);
+    const size_t smem = 4 * (size_t)HD * sizeof(float);
+    if (smem > 48 * 1024) CM_REFUSE("qk_prepare: head size %d too large", HD);
+    if (dt == DT_F32)
+        qk_prepare_kernel<float><<<grid, block, smem, st>>>((float*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
+                                                            seq_slot, seq_end, (float*)pool, pages, ptab,
+                                                            ptab_stride, ring, QH, KVH, HD, eps);
+    else if (dt == DT_BF16)
+        qk_prepare_kernel<bf16><<<grid, block, smem, st>>>((bf16*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
+                                                           seq_slot, seq_end, (bf16*)pool, pages, ptab,
+                                                           ptab_stride, ring, QH, KVH, HD, eps);
+    else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// =========================================================================================
+// Prefill attention on the CUDA cores (the 32-bit path, and any head size).
+// One block = 32 queries of one head of one sequence; keys come in tiles of 32 from the
+// step's own rows (all sequences of a prefill step start at position 0).
+// Warp w owns queries 8w..8w+7; a lane is a key for the scores and a set of channels for PV.
+// =========================================================================================
+#define AP_BQ 32
+#define AP_BK 32
+#define AP_MAXJ 8        // head_dim <= 32 * AP_MAXJ
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict__ q,
+                         const T* __restrict__ k, const T* __restrict__ v, long long ld,
+                         const T* __restrict__ gate, long long ldg,
+                         const int* __restrict__ seq_start, int QH, int KVH, int HD, int window,
+                         float scale) {
+    extern __shared__ float smem[];
+    const int ldq = HD + 1;
+    float* Qs = smem;                       // [AP_BQ][HD+1]
+    float* Ks = Qs + AP_BQ * ldq;           // [AP_BK][HD+1]
+    float* Vs = Ks + AP_BK * ldq;           // [AP_BK][HD]
+    float* Ps = Vs + AP_BK * HD;            // [AP_BQ][AP_BK+1]
+    const int b = blockIdx.z, hq = blockIdx.y, hk = hq / (QH / KVH);
+    const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
+    const int q0 = blockIdx.x * AP_BQ;
+    if (q0 >= len) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nq = min(AP_BQ, len - q0);
+
+    for (int e = threadIdx.x; e < AP_BQ * HD; e += blockDim.x) {
+        const int r = e / HD, d = e - r * HD;
+        Qs[r * ldq + d] = r < nq ? to_f32(q[(long long)(s0 + q0 + r) * ld + (long long)hq * HD + d]) : 0.f;
+    }
+    float m[8], l[8], acc[8][AP_MAXJ];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        m[i] = -INFINITY;
+        l[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < AP_MAXJ; ++j) acc[i][j] = 0.f;
+    }
+    const int q_last = q0 + nq - 1;
+    int k_begin = 0;
+    if (window > 0) k_begin = max(0, q0 - window + 1) / AP_BK * AP_BK;
+    const int nj = (HD + 31) / 32;
+
+    for (int k0 = k_begin; k0 <= q_last; k0 += AP_BK) {
+        __syncthreads();
+        for (int e = threadIdx.x; e < AP_BK * HD; e += blockDim.x) {
+            const int r = e / HD, d = e - r * HD;
+            const bool in = k0 + r < len;
+            const long long row = (long long)(s0 + k0 + r) * ld + (long long)hk * HD + d;
+            Ks[r * ldq + d] = in ? to_f32(k[row]) : 0.f;
+            Vs[r * HD + d] = in ? to_f32(v[row]) : 0.f;
+        }
+        __syncthreads();
+        const int kpos = k0 + lane;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int qi = warp * 8 + i;
+            const int qpos = q0 + qi;
+            const float* qr = Qs + qi * ldq;
+            const float* kr = Ks + lane * ldq;
+            float s = 0.f;
+            for (int d = 0; d < HD; ++d) s = fmaf(qr[d], kr[d], s);
+            s *= scale;
+            const bool vis = qi < nq && kpos <= qpos && kpos < len && (window <= 0 || kpos + window > qpos);
+            s = vis ? s : -INFINITY;
+            const float mx = fmaxf(m[i], warp_max(s));
+            float p = 0.f, alpha = 1.f;
+            if (mx != -INFINITY) {
+                p = vis ? expf(s - mx) : 0.f;
+                alpha = expf(m[i] - mx);         // exp(-inf) = 0 on the first visible tile
+            }
+            l[i] = l[i] * alpha + warp_sum(p);
+            m[i] = mx;
+#pragma unroll
+            for (int j = 0; j < AP_MAXJ; ++j) acc[i][j] *= alpha;
+            Ps[qi * (AP_BK + 1) + lane] = p;
+        }
+        __syncwarp();
+        for (int kk = 0; kk < AP_BK; ++kk) {
+            float vv[AP_MAXJ];
+#pragma unroll
+            for (int j = 0; j < AP_MAXJ; ++j) vv[j] = (j < nj && lane + 32 * j < HD) ? Vs[kk * HD + lane + 32 * j] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float p = Ps[(warp * 8 + i) * (AP_BK + 1) + kk];
+#pragma unroll
+                for (int j = 0; j < AP_MAXJ; ++j) acc[i][j] = fmaf(p, vv[j], acc[i][j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int qi = warp * 8 + i;
+        if (qi >= nq) continue;
+        const long long t = s0 + q0 + qi;
+        float g = 1.f;
+        if (gate) g = sigmoid_f32(to_f32(gate[t * ldg + hq]));
+        const float inv = 1.f / l[i];
+#pragma unroll
+        for (int j = 0; j < AP_MAXJ; ++j) {
+            const int d = lane + 32 * j;
+            if (j < nj && d < HD) ctx[t * ldc + (long long)hq * HD + d] = from_f32<T>(acc[i][j] * inv * g);
+        }
+    }
+}
+
+extern "C" int cm_attn_prefill_simt(int dt, void* ctx, long long ldc, const void* q, const void* k,
+                                    const void* v, long long ld, const void* gate, long long ldg,
+                                    const int* seq_start, int B, int max_len, int QH, int KVH, int HD,
+                                    int window, float scale, cudaStream_t st) {
+    if (B <= 0 || max_len <= 0) return CM_OK;
+    if (HD > 32 * AP_MAXJ) CM_REFUSE("attn_prefill: head size %d above %d", HD, 32 * AP_MAXJ);
+    if (QH % KVH) CM_REFUSE("attn_prefill: %d query heads over %d key heads", QH, KVH);
+    const size_t smem = ((size_t)(AP_BQ + AP_BK) * (HD + 1) + (size_t)AP_BK * HD + AP_BQ * (AP_BK + 1)) * sizeof(float);
+    dim3 grid((max_len + AP_BQ - 1) / AP_BQ, QH, B);
+    if (dt == DT_F32) {
+        cudaFuncSetAttribute(attn_prefill_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_prefill_simt_kernel<float><<<grid, 128, smem, st>>>((float*)ctx, ldc, (const float*)q, (const float*)k,
+                                                                 (const float*)v, ld, (const float*)gate, ldg,
+                                                                 seq_start, QH, KVH, HD, window, scale);
+    } else if (dt == DT_BF16) {
+        cudaFuncSetAttribute(attn_prefill_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_prefill_simt_kernel<bf16><<<grid, 128, smem, st>>>((bf16*)ctx, ldc, (const bf16*)q, (const bf16*)k,
+                                                                (const bf16*)v, ld, (const bf16*)gate, ldg,
+                                                                seq_start, QH, KVH, HD, window, scale);
+    } else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// =========================================================================================
+// Decode attention over the paged cache.  One new query token per sequence.
+// Grid (chunk, kv head, sequence); a chunk is AD_CHUNK cache entries (4 pages), one page per
+// warp.  The G = QH/KVH query heads of the kv head share every key and value that is read;
+// they are taken AD_GB at a time.  Each block leaves (max, sum, unnormalised output) per head
+// in scratch; cm_attn_decode's second kernel merges the chunks in index order and applies the
+// head gate.  Chunk borders are fixed, so a sequence's result does not depend on its
+// batch-mates.
+//   growing group: entry e holds position e;          entries 0..pos
+//   ring group:    entry e holds the latest position <= pos that is congruent to e (mod ring)
+// =========================================================================================
+#define AD_CHUNK 256
+#define AD_GB 8
+#define AD_THREADS 128
+
+template <typename T>
+__global__ void __launch_bounds__(AD_THREADS)
+attn_decode_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, const T* __restrict__ q,
+                   long long ldq, const int* __restrict__ seq_pos, const int* __restrict__ seq_slot,
+                   const T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
+                   int ptab_stride, int ring, int window, int QH, int KVH, int HD, int n_chunks,
+                   float scale) {
+    extern __shared__ float smem[];
+    float* qs = smem;                               // [AD_GB][HD]
+    float* ss = qs + AD_GB * HD;                    // [AD_GB][AD_CHUNK]
+    float* red = ss + AD_GB * AD_CHUNK;             // [groups][AD_GB][HD] partial outputs
+    __shared__ float ml[AD_GB][2];
+    const int c = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int G = QH / KVH;
+    const int pos = seq_pos[b];                     // position of the query token
+    const int n_entries = ring ? min(pos + 1, ring) : pos + 1;
+    const int e0 = c * AD_CHUNK;
+    if (e0 >= n_entries) return;
+    const int slot = seq_slot[b];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tpr = HD / 8;                         // threads per value row (8 channels each)
+    const int groups = AD_THREADS / tpr;
+    const int vg = threadIdx.x / tpr, vc = (threadIdx.x - vg * tpr) * 8;
+
+    // page of this warp
+    const int page_idx = e0 / PAGE_TOKENS + warp;
+    const bool page_live = page_idx * PAGE_TOKENS < n_entries;
+    const int page = page_live ? ptab[(long long)slot * ptab_stride + page_idx] : 0;
+
+    for (int g0 = 0; g0 < G; g0 += AD_GB) {
+        const int ng = min(AD_GB, G - g0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < AD_GB * HD; e += AD_THREADS) {
+            const int g = e / HD, d = e - g * HD;
+            qs[e] = g < ng ? to_f32(q[(long long)b * ldq + (long long)(hk * G + g0 + g) * HD + d]) : 0.f;
+        }
+        __syncthreads();
+        // ---- scores: a lane owns entries lane and lane+32 of its warp's page
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = lane + 32 * r;
+            const int e = page_idx * PAGE_TOKENS + row;
+            float s[AD_GB];
+#pragma unroll
+            for (int g = 0; g < AD_GB; ++g) s[g] = 0.f;
+            bool vis = false;
+            if (page_live && e < n_entries) {
+                int kpos = e;
+                if (ring) {
+                    int back = (pos - e) % ring;      // pos >= 0, e < ring: C remainder may be negative
+                    if (back < 0) back += ring;
+                    kpos = pos - back;
+                }
+                vis = kpos >= 0 && kpos <= pos && (window <= 0 || kpos + window > pos);
+                if (vis) {
+                    const T* kr = kv_tile(pool, 0, pages, page, hk, KVH, HD) + (long long)row * HD;
+                    for (int d = 0; d < HD; d += 8) {
+                        float kv8[8];
+                        load8<T>(kr + d, kv8);
+#pragma unroll
+                        for (int g = 0; g < AD_GB; ++g) {
+                            const float* qg = qs + g * HD + d;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) s[g] = fmaf(qg[i], kv8[i], s[g]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < AD_GB; ++g)
+                ss[g * AD_CHUNK + warp * PAGE_TOKENS + row] = vis ? s[g] * scale : -INFINITY;
+        }
+        __syncthreads();
+        // ---- softmax pieces per head: warp w takes heads w, w+4
+        for (int g = warp; g < AD_GB; g += AD_THREADS / 32) {
+            float mx = -INFINITY;
+            for (int e = lane; e < AD_CHUNK; e += 32) mx = fmaxf(mx, ss[g * AD_CHUNK + e]);
+            mx = warp_max(mx);
+            float sum = 0.f;
+            for (int e = lane; e < AD_CHUNK; e += 32) {
+                const float sv = ss[g * AD_CHUNK + e];
+                const float p = (mx == -INFINITY || sv == -INFINITY) ? 0.f : expf(sv - mx);
+                ss[g * AD_CHUNK + e] = p;
+                sum += p;
+            }
+            sum = warp_sum(sum);
+            if (lane == 0) {
+                ml[g][0] = mx;
+                ml[g][1] = sum;
+            }
+        }
+        __syncthreads();
+        // ---- PV: thread (vg, vc) sums entries vg, vg+groups, ... for 8 channels of every head
+        float acc[AD_GB][8];
+#pragma unroll
+        for (int g = 0; g < AD_GB; ++g)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+        if (vg < groups) {
+            const int n_here = min(AD_CHUNK, n_entries - e0);
+            for (int e = vg; e < n_here; e += groups) {
+                const int pidx = (e0 + e) / PAGE_TOKENS;
+                const int pg = ptab[(long long)slot * ptab_stride + pidx];
+                const T* vr = kv_tile(pool, 1, pages, pg, hk, KVH, HD) + (long long)((e0 + e) % PAGE_TOKENS) * HD + vc;
+                float vv[8];
+                load8<T>(vr, vv);
+#pragma unroll
+                for (int g = 0; g < AD_GB; ++g) {
+                    const float p = ss[g * AD_CHUNK + e];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(p, vv[i], acc[g][i]);
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < AD_GB; ++g)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) red[((long long)vg * AD_GB + g) * HD + vc + i] = acc[g][i];
+        }
+        __syncthreads();
+        // ---- fold the entry groups in index order and leave the chunk's partial result
+        for (int e = threadIdx.x; e < ng * HD; e += AD_THREADS) {
+            const int g = e / HD, d = e - g * HD;
+            float o = 0.f;
+            for (int x = 0; x < groups; ++x) o += red[((long long)x * AD_GB + g) * HD + d];
+            const long long idx = ((long long)b * QH + hk * G + g0 + g) * n_chunks + c;
+            part_o[idx * HD + d] = o;
+            if (d == 0) {
+                part_ml[idx * 2] = ml[g][0];
+                part_ml[idx * 2 + 1] = ml[g][1];
+            }
+        }
+    }
+}
+
+// Merge of the chunks of one (sequence, head), in chunk order; gate; store.
+template <typename T>
+__global__ void attn_decode_merge_kernel(T* __restrict__ ctx, long long ldc,
+                                         const float* __restrict__ part_o,
+                                         const float* __restrict__ part_ml,
+                                         const T* __restrict__ gate, long long ldg,
+                                         const int* __restrict__ seq_pos, int ring, int QH, int HD,
+                                         int n_chunks) {
+    const int hq = blockIdx.x, b = blockIdx.y;
+    const int pos = seq_pos[b];
+    const int n_entries = ring ? min(pos + 1, ring) : pos + 1;
+    const int nc = min(n_chunks, (n_entries + AD_CHUNK - 1) / AD_CHUNK);
+    const long long base = ((long long)b * QH + hq) * n_chunks;
+    float mx = -INFINITY;
+    for (int c = 0; c < nc; ++c) mx = fmaxf(mx, part_ml[(base + c) * 2]);
+    float den = 0.f;
+    for (int c = 0; c < nc; ++c) {
+        const float mc = part_ml[(base + c) * 2];
+        den += mc == -INFINITY ? 0.f : part_ml[(base + c) * 2 + 1] * expf(mc - mx);
+    }
+    float g = 1.f;
+    if (gate) g = sigmoid_f32(to_f32(gate[(long long)b * ldg + hq]));
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float o = 0.f;
+        for (int c = 0; c < nc; ++c) {
+            const float mc = part_ml[(base + c) * 2];
+            if (mc != -INFINITY) o += part_o[(base + c) * HD + d] * expf(mc - mx);
+        }
+        ctx[(long long)b * ldc + (long long)hq * HD + d] = from_f32<T>(o / den * g);
+    }
+}
+
+// Scratch: part_o holds B*QH*n_chunks*HD floats, part_ml B*QH*n_chunks*2 floats.
+extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, long long ldq,
+                              const void* gate, long long ldg, const int* seq_pos, const int* seq_slot,
+                              const void* pool, long long pages, const int* ptab, int ptab_stride,
+                              int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
+                              float scale, float* part_o, float* part_ml, cudaStream_t st) {
+    if (B <= 0) return CM_OK;
+    if (HD % 8 || HD < 8 || HD > 256) CM_REFUSE("attn_decode: head size %d (multiples of 8 up to 256)", HD);
+    if (QH % KVH) CM_REFUSE("attn_decode: %d query heads over %d key heads", QH, KVH);
+    if (ring % PAGE_TOKENS) CM_REFUSE("attn_decode: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
+    if (n_chunks <= 0) CM_REFUSE("attn_decode: %d chunks", n_chunks);
+    const int groups = AD_THREADS / (HD / 8);
+    const size_t smem = ((size_t)AD_GB * HD + (size_t)AD_GB * AD_CHUNK + (size_t)groups * AD_GB * HD) * sizeof(float);
+    dim3 grid(n_chunks, KVH, B);
+    dim3 mgrid(QH, B);
+    const int mthreads = HD <= 64 ? 64 : 128;
+    if (dt == DT_F32) {
+        cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_decode_kernel<float><<<grid, AD_THREADS, smem, st>>>(part_o, part_ml, (const float*)q, ldq, seq_pos,
+                                                                  seq_slot, (const float*)pool, pages, ptab,
+                                                                  ptab_stride, ring, window, QH, KVH, HD,
+                                                                  n_chunks, scale);
+        CM_CHECK_LAUNCH();
+        attn_decode_merge_kernel<float><<<mgrid, mthreads, 0, st>>>((float*)ctx, ldc, part_o, part_ml,
+                                                                    (const float*)gate, ldg, seq_pos, ring, QH,
+                                                                    HD, n_chunks);
+    } else if (dt == DT_BF16) {
+        cudaFuncSetAttribute(attn_decode_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_decode_kernel<bf16><<<grid, AD_THREADS, smem, st>>>(part_o, part_ml, (const bf16*)q, ldq, seq_pos,
+                                                                 seq_slot, (const bf16*)pool, pages, ptab,
+                                                                 ptab_stride, ring, window, QH, KVH, HD,
+                                                                 n_chunks, scale);
+        CM_CHECK_LAUNCH();
+        attn_decode_merge_kernel<bf16><<<mgrid, mthreads, 0, st>>>((bf16*)ctx, ldc, part_o, part_ml,
+                                                                   (const bf16*)gate, ldg, seq_pos, ring, QH,
+                                                                   HD, n_chunks);
+    } else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}

@@ -1,0 +1,94 @@
+// Shared device helpers for the sm_100a kernels of this library.
+//
+// Every kernel is templated on the storage type of activations and matrices (float for
+// the true 32-bit path, __nv_bfloat16 for the serving path) and does its reductions,
+// norms, softmax, rotation angles and residual sums in float.  The C entry points take
+// a dtype code (DT_F32 / DT_BF16), raw device pointers and the stream to launch on;
+// they return 0 or a negative code and never allocate.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define DT_F32 0
+#define DT_BF16 1
+
+#define CM_OK 0
+#define CM_ERR_DTYPE -1      // unknown dtype code
+#define CM_ERR_SHAPE -2      // a size this kernel refuses (message via cm_last_error)
+#define CM_ERR_LAUNCH -3     // cudaGetLastError() after the launch was not cudaSuccess
+#define CM_ERR_DRIVER -4     // a driver entry point (tensor map encode) failed
+
+typedef __nv_bfloat16 bf16;
+
+// Set by the entry points when they refuse a call; read through cm_last_error().
+void cm_set_error(const char* fmt, ...);
+
+#define CM_REFUSE(...)            \
+    do {                          \
+        cm_set_error(__VA_ARGS__); \
+        return CM_ERR_SHAPE;      \
+    } while (0)
+
+#define CM_CHECK_LAUNCH()                                              \
+    do {                                                               \
+        cudaError_t e_ = cudaGetLastError();                           \
+        if (e_ != cudaSuccess) {                                       \
+            cm_set_error("%s:%d launch failed: %s", __FILE__, __LINE__, \
+                         cudaGetErrorString(e_));                      \
+            return CM_ERR_LAUNCH;                                      \
+        }                                                              \
+    } while (0)
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+// Value as it will read back after a store in T: identity for float, a bf16 round trip else.
+template <typename T>
+__device__ __forceinline__ float rounded(float x) { return to_f32(from_f32<T>(x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block in a fixed order (lane tree, then warp 0 over the per-warp sums), so
+// that a row's result never depends on how many other rows the launch carries.
+// `scratch` holds at least 32 floats.  Every thread gets the total.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();                 // scratch may still be read from a previous call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+
+__device__ __forceinline__ float sigmoid_f32(float x) { return 1.f / (1.f + expf(-x)); }
+
+// Page-table geometry shared by the cache kernels: a page holds PAGE_TOKENS consecutive
+// cache entries of one sequence for every layer of a group.
+#define PAGE_TOKENS 64
+
+// Storage of one layer group: [layer][k|v][page][kv_head][PAGE_TOKENS][head_dim].
+template <typename T>
+__device__ __forceinline__ T* kv_tile(T* layer_base, int kv, long long pages, int page, int kvh,
+                                      int KVH, int HD) {
+    return layer_base + ((((long long)kv * pages + page) * KVH + kvh) * PAGE_TOKENS) * (long long)HD;
+}

@@ -1,0 +1,79 @@
+// Gated short convolution between in_proj and out_proj, with its per-sequence state.
+//
+//   bcx row: [ B: H | C: H | X: H ]         bx = B * X               (float, never rounded)
+//   s = concat(state[K-1, H], bx[T_b, H])    z[i,c] = sum_j w[c,j] * s[i+j, c]   (j = 0..K-1)
+//   y = T(z * C)                             state <- s[T_b : T_b + K-1]           (float)
+// One thread per (token, channel).  A prompt step starts every sequence from an empty state
+// (from_zero = 1: the stored state is not read, so a slot that is used again needs no
+// clearing); a decode step has one token per sequence and shifts the state in place.
+#include "common.cuh"
+
+#define SC_MAXK 16
+
+template <typename T>
+__global__ void shortconv_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld,
+                                 const float* __restrict__ w, float* __restrict__ state,
+                                 const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                                 const int* __restrict__ seq_slot, int H, int K, int from_zero) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = blockIdx.y;
+    if (c >= H) return;
+    const int b = tok_seq[t];
+    const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
+    const int i = t - s0;
+    float* st = state + (long long)seq_slot[b] * (K - 1) * H + c;     // [K-1] entries, stride H
+    const float* wc = w + (long long)c * K;
+
+    float z = 0.f;
+    float cur = 0.f;
+    for (int j = 0; j < K; ++j) {
+        const int r = i + j - (K - 1);            // row of bx; negative rows lie in the state
+        float sv;
+        if (r >= 0) {
+            const T* row = bcx + (long long)(s0 + r) * ld;
+            sv = to_f32(row[c]) * to_f32(row[2 * H + c]);
+            if (j == K - 1) cur = sv;
+        } else {
+            sv = from_zero ? 0.f : st[(long long)(K - 1 + r) * H];
+        }
+        z += wc[j] * sv;
+    }
+    const float cc = to_f32(bcx[(long long)t * ld + H + c]);
+    y[(long long)t * H + c] = from_f32<T>(z * cc);
+
+    if (i == len - 1) {
+        // new state entry j = s[len + j]; s index below K-1 is an old state entry
+        for (int j = 0; j < K - 1; ++j) {
+            const int r = len + j - (K - 1);
+            float sv;
+            if (r == len - 1)
+                sv = cur;
+            else if (r >= 0) {
+                const T* row = bcx + (long long)(s0 + r) * ld;
+                sv = to_f32(row[c]) * to_f32(row[2 * H + c]);
+            } else
+                sv = from_zero ? 0.f : st[(long long)(len + j) * H];   // len + j > j: not yet overwritten
+            st[(long long)j * H] = sv;
+        }
+    }
+}
+
+extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, const float* w, float* state,
+                            const int* tok_seq, const int* seq_start, const int* seq_slot, int T, int H,
+                            int K, int from_zero, int one_token_each, cudaStream_t st) {
+    if (T <= 0) return CM_OK;
+    if (K < 2 || K > SC_MAXK) CM_REFUSE("shortconv: %d taps (2..%d)", K, SC_MAXK);
+    if (!from_zero && !one_token_each)
+        CM_REFUSE("shortconv: several tokens of a sequence on top of a stored state are not supported");
+    dim3 grid((H + 127) / 128, T);
+    if (dt == DT_F32)
+        shortconv_kernel<float><<<grid, 128, 0, st>>>((float*)y, (const float*)bcx, ld, w, state, tok_seq,
+                                                      seq_start, seq_slot, H, K, from_zero);
+    else if (dt == DT_BF16)
+        shortconv_kernel<bf16><<<grid, 128, 0, st>>>((bf16*)y, (const bf16*)bcx, ld, w, state, tok_seq,
+                                                     seq_start, seq_slot, H, K, from_zero);
+    else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}

@@ -1,0 +1,88 @@
+"""One step's batch as the kernels see it: packed tokens and their sequence geometry.
+
+A step is either a prompt step (every sequence starts at position 0 and brings its whole
+prompt) or a decode step (every sequence brings one token).  All integer metadata travels in
+one int32 buffer, filled on the host in pinned memory and copied once:
+
+    tokens[T] tok_seq[T] tok_pos[T] seq_slot[B] seq_start[B+1] seq_pos0[B] seq_end[B]
+    want_rows[W] upd_count[1] upd_index[U] upd_value[U]
+
+`want_rows` are rows of the packed batch whose logits are asked for; `upd_*` are page-table
+entries that the cache allocated for this step (applied on the device before any layer runs).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..cache.spec import PAGE_TOKENS
+from ..kernels import ATTN_DECODE_CHUNK
+
+
+class BatchLayout:
+    """Offsets of the fields in the int32 buffer for given capacities."""
+
+    def __init__(self, T, B, W, U):
+        self.T, self.B, self.W, self.U = T, B, W, U
+        fields = [("tokens", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B + 1),
+                  ("seq_pos0", B), ("seq_end", B), ("want_rows", W), ("upd_count", 1), ("upd_index", U),
+                  ("upd_value", U)]
+        self.offsets, off = {}, 0
+        for name, n in fields:
+            self.offsets[name] = (off, n)
+            off += (n + 3) // 4 * 4                     # 16-byte aligned fields
+        self.size = max(4, off)
+
+    def views(self, buf):
+        return {name: buf[off:off + n] for name, (off, n) in self.offsets.items()}
+
+
+class StepBatch:
+    """Device-side views plus the host-side facts a part may need to size a launch."""
+
+    def __init__(self, layout, device_buf, prefill, lengths, positions, n_want, n_updates):
+        self.layout = layout
+        self.buf = device_buf
+        v = layout.views(device_buf)
+        self.tokens, self.tok_seq, self.tok_pos = v["tokens"], v["tok_seq"], v["tok_pos"]
+        self.seq_slot, self.seq_start = v["seq_slot"], v["seq_start"]
+        self.seq_pos0, self.seq_end = v["seq_pos0"], v["seq_end"]
+        self.want_rows = v["want_rows"][:n_want]
+        self.upd_count, self.upd_index, self.upd_value = v["upd_count"], v["upd_index"], v["upd_value"]
+        self.prefill = prefill
+        self.B, self.T = layout.B, layout.T
+        self.max_len = max(lengths) if lengths else 0          # longest run of new tokens
+        self.max_end = max((p + n for p, n in zip(positions, lengths)), default=0)
+        self.n_want, self.n_updates = n_want, n_updates
+        self.chunk_bucket = None                               # set by a captured decode graph
+
+    def decode_chunks(self, kv_spec):
+        """Chunks of cache entries the decode attention walks for this state spec."""
+        entries = kv_spec.entries(self.chunk_bucket or self.max_end)
+        return max(1, (entries + ATTN_DECODE_CHUNK - 1) // ATTN_DECODE_CHUNK)
+
+
+def fill_host(layout, host, slots, token_lists, positions, want, updates):
+    """Write one step into the pinned int32 array `host` (numpy view).  Returns n_want."""
+    v = layout.views(host)
+    t = 0
+    rows = []
+    for b, (slot, toks, pos) in enumerate(zip(slots, token_lists, positions)):
+        n = len(toks)
+        v["tokens"][t:t + n] = toks
+        v["tok_seq"][t:t + n] = b
+        v["tok_pos"][t:t + n] = np.arange(pos, pos + n, dtype=np.int32)
+        v["seq_slot"][b] = slot
+        v["seq_start"][b] = t
+        v["seq_pos0"][b] = pos
+        v["seq_end"][b] = pos + n
+        for w in want[b]:
+            rows.append(t + w)
+        t += n
+    v["seq_start"][len(slots)] = t
+    v["want_rows"][:len(rows)] = rows
+    v["upd_count"][0] = len(updates)
+    for i, (idx, page) in enumerate(updates):
+        v["upd_index"][i] = idx
+        v["upd_value"][i] = page
+    return len(rows)

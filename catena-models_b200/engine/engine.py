@@ -1,0 +1,200 @@
+"""The step function and the cache it runs on.
+
+`Engine.step(slots, tokens, want)` runs one batch of sequences that started together: their
+whole prompts in the first step (unequal lengths, packed without padding), then one token
+each.  It runs only the tokens it is given, reads everything older from the cache, and
+returns float32 logits at the wanted places.  catena-models has the one-sequence form of
+this (`Session::forward`, src/model.rs:692-731, with its errors: empty input, capacity
+exceeded, token id outside the vocabulary, src/model.rs:697-710).
+
+Decode steps of a given batch size replay a captured CUDA graph: positions, slots and new
+page-table entries live in a fixed device buffer that is refreshed by one host-to-device
+copy before each replay.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..cache.cache import Cache
+from ..cache.allocators import CacheError, CacheFull
+from ..kernels import ATTN_DECODE_CHUNK
+from .batch import BatchLayout, StepBatch, fill_host
+
+
+class StepError(ValueError):
+    """A step was refused before anything ran (bad token id, unknown slot, mixed batch...)."""
+
+
+class _Staging:
+    """A few pinned host buffers used in turn, each guarded by an event of its last copy."""
+
+    def __init__(self, n=4):
+        self.bufs = [None] * n
+        self.events = [None] * n
+        self.i = 0
+
+    def take(self, size):
+        self.i = (self.i + 1) % len(self.bufs)
+        if self.events[self.i] is not None:
+            self.events[self.i].synchronize()
+        buf = self.bufs[self.i]
+        if buf is None or buf.numel() < size:
+            buf = torch.empty(max(1024, size * 2), dtype=torch.int32, pin_memory=True)
+            self.bufs[self.i] = buf
+        return buf, self.i
+
+    def mark(self, i):
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
+class _DecodeGraph:
+    def __init__(self, layout, device_buf, graph, logits, batch):
+        self.layout, self.device_buf, self.graph, self.logits, self.batch = layout, device_buf, graph, logits, batch
+
+
+class Engine:
+    def __init__(self, model, max_tokens, max_seqs=None, use_graphs=True):
+        self.model, self.rt = model, model.rt
+        max_len = model.definition.max_positions or None
+        self.cache = Cache(model.state_specs, max_tokens, self.rt.dtype, self.rt.device, max_seqs, max_len)
+        self.n_kv_groups = len(self.cache.kv_specs)
+        self.use_graphs = use_graphs
+        self._staging = _Staging()
+        self._graphs = {}
+        self.steps_run = 0
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ slots
+    def admit(self, count=1):
+        """Slots for `count` new sequences (all or none)."""
+        if count > self.cache.book.slots.free_count:
+            raise CacheFull(f"{count} slot(s) wanted, {self.cache.book.slots.free_count} free")
+        return [self.cache.admit() for _ in range(count)]
+
+    def release(self, slots):
+        for s in slots:
+            self.cache.release(s)
+
+    def length(self, slot):
+        return self.cache.book.length[slot]
+
+    # ------------------------------------------------------------------ the step
+    def _check(self, slots, tokens, want):
+        book = self.cache.book
+        if not slots:
+            raise StepError("a step needs at least one sequence")
+        if len(set(slots)) != len(slots):
+            raise StepError("a slot appears twice in one step")
+        if len(tokens) != len(slots):
+            raise StepError("one token list per slot")
+        for s in slots:
+            if s not in book.length:
+                raise StepError(f"slot {s} is not live")
+        positions = [book.length[s] for s in slots]
+        if any(len(t) == 0 for t in tokens):
+            raise StepError("a sequence brought no tokens")
+        prefill = all(p == 0 for p in positions)
+        if not prefill and not all(len(t) == 1 for t in tokens):
+            raise StepError("sequences either all start at their first token or all go on by one token")
+        V = self.model.vocab_size
+        for t in tokens:
+            arr = np.asarray(t)
+            if arr.min() < 0 or arr.max() >= V:
+                raise StepError(f"token id outside the vocabulary of {V}")
+        if want is None:
+            want = [[len(t) - 1] for t in tokens]
+        if len(want) != len(slots):
+            raise StepError("one list of wanted places per slot")
+        for w, t in zip(want, tokens):
+            if any(i < 0 or i >= len(t) for i in w):
+                raise StepError("a wanted place lies outside the sequence's tokens of this step")
+        return positions, prefill, want
+
+    def _reserve(self, slots, positions, tokens):
+        """Pages for the new tokens of every sequence; undone as a whole if one does not fit."""
+        book = self.cache.book
+        updates, done = [], []
+        try:
+            for s, p, t in zip(slots, positions, tokens):
+                ups = book.reserve(s, p + len(t))
+                done.append((s, ups))
+                updates.extend(self.cache.flat_updates(s, ups))
+        except CacheError:
+            for s, ups in done:                                  # give the pages of this step back
+                for g, j, page in reversed(ups):
+                    book.pages[s][g].pop()
+                    book.page_alloc[g].give_back([page])
+            raise
+        return updates
+
+    def step(self, slots, tokens, want=None):
+        """Run one step.  `tokens[i]` are the next tokens of the sequence in `slots[i]`;
+        `want[i]` the places among them whose logits are returned (default: the last).
+        Returns float32 logits [sum(len(want[i])), vocab] on the device, in the order of
+        `slots` and of `want`.  The tensor is valid until the next step of the same size."""
+        positions, prefill, want = self._check(slots, tokens, want)
+        updates = self._reserve(slots, positions, tokens)
+        book = self.cache.book
+        B, T = len(slots), sum(len(t) for t in tokens)
+        if prefill or not self.use_graphs:
+            n_want = sum(len(w) for w in want)
+            layout = BatchLayout(T, B, n_want, len(updates))
+            host, idx = self._staging.take(layout.size)
+            fill_host(layout, host.numpy(), slots, tokens, positions, want, updates)
+            dev = host[:layout.size].to(self.rt.device, non_blocking=True)
+            self._staging.mark(idx)
+            batch = StepBatch(layout, dev, prefill, [len(t) for t in tokens], positions, n_want, len(updates))
+            logits = self.model.forward(batch, self.cache)
+        else:
+            logits = self._decode_graph_step(slots, tokens, positions, want, updates)
+        for s, p, t in zip(slots, positions, tokens):
+            book.advance(s, p + len(t))
+        self.steps_run += 1
+        return logits
+
+    # ------------------------------------------------------------------ captured decode
+    @staticmethod
+    def _bucket(n):
+        b = ATTN_DECODE_CHUNK
+        while b < n:
+            b *= 2
+        return b
+
+    def _decode_graph_step(self, slots, tokens, positions, want, updates):
+        B = len(slots)
+        bucket = self._bucket(max(positions) + 1)
+        key = (B, bucket)
+        all_rows = [[0]] * B
+        entry = self._graphs.get(key)
+        if entry is None:
+            layout = BatchLayout(B, B, B, B * max(1, self.n_kv_groups))
+            device_buf = torch.zeros(layout.size, dtype=torch.int32, device=self.rt.device)
+            entry = _DecodeGraph(layout, device_buf, None, None, None)
+            self._graphs[key] = entry
+        layout = entry.layout
+        host, idx = self._staging.take(layout.size)
+        fill_host(layout, host.numpy(), slots, tokens, positions, all_rows, updates)
+        entry.device_buf.copy_(host[:layout.size], non_blocking=True)
+        self._staging.mark(idx)
+        if entry.graph is None:
+            # First step of this size: run it eagerly (this is the step's result; it also loads
+            # every kernel, which must not happen inside a capture), then record the same
+            # launches into a graph for the steps that follow.  A capture executes nothing, so
+            # the cache and the fixed-size states advance exactly once.
+            batch = StepBatch(layout, entry.device_buf, False, [1] * B, positions, B, len(updates))
+            batch.chunk_bucket = bucket
+            logits = self.model.forward(batch, self.cache)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                entry.logits = self.model.forward(batch, self.cache)
+            entry.graph, entry.batch = graph, batch
+        else:
+            entry.graph.replay()
+            logits = entry.logits
+        if all(w == [0] for w in want):
+            return logits
+        rows = [b for b, w in enumerate(want) for _ in w]
+        return logits[rows]

@@ -1,0 +1,103 @@
+"""The generation loop above the step function.
+
+Requests are cut into batches that start together; a batch's prompts (of unequal lengths)
+run in one step, then every live sequence gets one token per step; a sequence ends at a stop
+token or at its budget and gives its slot back at once, the others go on; the next batch
+starts when the last sequence of this one has ended, on the slots and pages just freed.
+catena-models has the one-sequence loop (src/main.rs:311-347: the first new token comes from
+the prompt step, stop at eos unless --ignore-eos, at most -n tokens) and the server's
+finish reasons "stop" / "length" (src/server/engine.rs:516-522).
+
+The loop's decisions are plain Python over an engine-like object (`admit`, `release`, `step`)
+and a sampler-like object (`sample`), so they can be tested without a device.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+PAGE = 64
+
+
+@dataclasses.dataclass
+class Generation:
+    prompt: list
+    tokens: list = dataclasses.field(default_factory=list)
+    finish_reason: str = None         # "stop" | "length"
+
+
+def plan_batches(prompt_lens, max_new_tokens, max_batch, max_tokens, page=PAGE):
+    """Cut requests, in order, into batches of at most `max_batch` sequences whose worst-case
+    footprint (prompt + budget, each rounded up to whole pages) fits `max_tokens`."""
+    batches, cur, used = [], [], 0
+    for i, n in enumerate(prompt_lens):
+        need = (n + max_new_tokens + page - 1) // page * page
+        if need > max_tokens:
+            raise ValueError(f"request {i} needs {need} cache tokens, the cache holds {max_tokens}")
+        if cur and (len(cur) >= max_batch or used + need > max_tokens):
+            batches.append(cur)
+            cur, used = [], 0
+        cur.append(i)
+        used += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+def finish_reason(token, n_generated, max_new_tokens, stop_token_ids, ignore_eos):
+    """Why a sequence ends after `token`, its `n_generated`-th new token; None if it goes on.
+    A stop token is kept in the output, as the reference keeps it (src/main.rs:332-346)."""
+    if not ignore_eos and token in stop_token_ids:
+        return "stop"
+    if n_generated >= max_new_tokens:
+        return "length"
+    return None
+
+
+def run_batch(engine, sampler, requests, ids, max_new_tokens, stop_token_ids, ignore_eos, on_step=None):
+    """One batch from admission to its last sequence's end.  `requests`: Generation objects,
+    `ids`: their sequence ids (the sampler's key)."""
+    if max_new_tokens <= 0:
+        for r in requests:
+            r.finish_reason = "length"
+        return
+    slots = engine.admit(len(requests))
+    live = list(range(len(requests)))
+    try:
+        logits = engine.step(slots, [r.prompt for r in requests])
+        step = 0
+        while True:
+            tokens = sampler.sample(logits, [ids[i] for i in live], [step] * len(live))
+            still = []
+            for i, tok in zip(live, tokens):
+                r = requests[i]
+                r.tokens.append(int(tok))
+                r.finish_reason = finish_reason(int(tok), len(r.tokens), max_new_tokens, stop_token_ids, ignore_eos)
+                if r.finish_reason is None:
+                    still.append(i)
+                else:
+                    engine.release([slots[i]])
+                    slots[i] = None
+            if on_step:
+                on_step(step, len(live))
+            live = still
+            if not live:
+                break
+            step += 1
+            logits = engine.step([slots[i] for i in live], [[requests[i].tokens[-1]] for i in live])
+    finally:
+        engine.release([s for s in slots if s is not None])
+
+
+def generate(engine, sampler, prompts, max_new_tokens, stop_token_ids=(), ignore_eos=False, max_batch=64,
+             max_tokens=None, on_step=None):
+    """Generate for every prompt (lists of token ids); returns a Generation per prompt."""
+    for i, p in enumerate(prompts):
+        if len(p) == 0:
+            raise ValueError(f"prompt {i} is empty")
+    requests = [Generation(list(p)) for p in prompts]
+    max_tokens = max_tokens or engine.cache.book.page_budget * PAGE
+    max_batch = min(max_batch, engine.cache.book.max_seqs) if hasattr(engine, "cache") else max_batch
+    stop = frozenset(stop_token_ids)
+    for batch in plan_batches([len(p) for p in prompts], max_new_tokens, max_batch, max_tokens):
+        run_batch(engine, sampler, [requests[i] for i in batch], batch, max_new_tokens, stop, ignore_eos, on_step)
+    return requests

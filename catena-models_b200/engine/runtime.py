@@ -1,0 +1,61 @@
+"""The engine's view of the device: activation dtype, kernel choice, scratch memory.
+
+Parts ask the runtime for a matrix product or an attention pass and the runtime picks the
+kernel from the dtype and the number of rows: the 32-bit engine runs plain FMA kernels only
+(no tensor-core mode of reduced precision), the bfloat16 engine runs the tensor-core and
+weight-streaming kernels.  Kernel choice never depends on which model or layer is running.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+
+
+class Runtime:
+    def __init__(self, dtype, device):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"engine dtype must be float32 or bfloat16, got {dtype}")
+        self.dtype = dtype
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
+        kernels.lib()                       # build and load now: fail loudly before any model work
+        self._scratch = {}
+        self._retired = []
+
+    # ------------------------------------------------------------------ scratch
+    def scratch(self, key, numel, dtype=torch.float32):
+        """A grow-only device buffer shared by the kernels that run one after another."""
+        buf = self._scratch.get(key)
+        if buf is None or buf.numel() < numel or buf.dtype != dtype:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(f"scratch '{key}' would be allocated during graph capture")
+            if buf is not None:
+                self._retired.append(buf)      # captured graphs may still launch kernels on it
+            buf = torch.empty(numel, dtype=dtype, device=self.device)
+            self._scratch[key] = buf
+        return buf
+
+    def scratch_attn_decode(self, B, QH, HD, n_chunks):
+        return (self.scratch("attn_decode_o", B * QH * n_chunks * HD),
+                self.scratch("attn_decode_ml", B * QH * n_chunks * 2))
+
+    # ------------------------------------------------------------------ matrix products
+    def linear(self, x, w, out_dtype=None):
+        """y = x @ w^T; y in the activation dtype unless `out_dtype` says float32."""
+        y = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+        kernels.gemm_simt(y, x, w)
+        return y
+
+    def gate_up_swiglu(self, x, w_gate_up, F):
+        """a = silu(x Wgate^T) * (x Wup^T) for the row-packed [Wgate; Wup]."""
+        gu = self.linear(x, w_gate_up)
+        a = torch.empty((x.shape[0], F), dtype=x.dtype, device=x.device)
+        kernels.swiglu(a, gu)
+        return a
+
+    # ------------------------------------------------------------------ attention
+    def attention_prefill(self, ctx, q, k, v, gate, batch, QH, KVH, HD, window, scale):
+        kernels.attn_prefill_simt(ctx, q, k, v, gate, batch.seq_start, batch.B, batch.max_len, QH, KVH, HD,
+                                  window, scale)

@@ -1,0 +1,196 @@
+"""Python face of the CUDA library: one function per entry point, taking torch tensors.
+
+Every call launches on torch's current stream, checks the entry point's return code and
+raises `KernelError` with the library's message.  There is no fallback: if the library
+cannot be built or loaded, importing a kernel raises.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .csrc import build as _build
+
+DT_F32, DT_BF16 = 0, 1
+PAGE_TOKENS = 64
+ATTN_DECODE_CHUNK = 256
+
+_vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+_SIGNATURES = {
+    "cm_embed_gather": [_i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],
+    "cm_rmsnorm": [_i, _vp, _vp, _vp, _i, _i, _f, _ll, _ll, _vp],
+    "cm_add_norm": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
+    "cm_swiglu": [_i, _vp, _vp, _i, _i, _vp],
+    "cm_gather_rows": [_i, _vp, _vp, _vp, _i, _i, _vp],
+    "cm_gemm_simt": [_i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
+    "cm_qk_prepare": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i,
+                      _i, _f, _vp],
+    "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "cm_attn_decode": [_i, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _i,
+                       _i, _f, _vp, _vp, _vp],
+    "cm_shortconv": [_i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "cm_sample": [_vp, _vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp],
+    "cm_scatter_i32": [_vp, _vp, _vp, _vp, _i, _vp],
+    "cm_zero_rows_f32": [_vp, _vp, _i, _ll, _vp],
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    """The loaded CUDA library, with argument types set."""
+    global _lib
+    if _lib is None:
+        handle = _build.load()
+        handle.cm_last_error.restype = ctypes.c_char_p
+        for name, args in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = args
+            fn.restype = _i
+        _lib = handle
+    return _lib
+
+
+def library_path():
+    return lib()._name
+
+
+def dtype_code(dtype):
+    if dtype == torch.float32:
+        return DT_F32
+    if dtype == torch.bfloat16:
+        return DT_BF16
+    raise KernelError(f"no kernels for dtype {dtype}")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code, name):
+    if code != 0:
+        raise KernelError(f"{name} returned {code}: {lib().cm_last_error().decode(errors='replace')}")
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels take CUDA tensors only; there is no CPU path")
+
+
+# ---------------------------------------------------------------------------- row-wise
+def embed_gather(out, table, tokens, err=None):
+    _need_cuda(out, table, tokens)
+    T, H = out.shape
+    _check(lib().cm_embed_gather(dtype_code(out.dtype), _ptr(out), _ptr(table), _ptr(tokens), T, H,
+                                 table.shape[0], _ptr(err), _stream()), "embed_gather")
+
+
+def rmsnorm(out, x, w, eps):
+    _need_cuda(out, x, w)
+    rows, H = x.shape
+    _check(lib().cm_rmsnorm(dtype_code(x.dtype), _ptr(out), _ptr(x), _ptr(w), rows, H, eps, x.stride(0),
+                            out.stride(0), _stream()), "rmsnorm")
+
+
+def add_norm(h_out, n_out, m, h_in, w_post, w_next, eps_post, eps_next):
+    """h_out = h_in + (norm(m; w_post) or m); n_out = norm(h_out; w_next) when w_next is given."""
+    _need_cuda(h_out, m, h_in)
+    rows, H = m.shape
+    _check(lib().cm_add_norm(dtype_code(m.dtype), _ptr(h_out), _ptr(n_out), _ptr(m), _ptr(h_in), _ptr(w_post),
+                             _ptr(w_next), rows, H, eps_post, eps_next, _stream()), "add_norm")
+
+
+def swiglu(out, gate_up):
+    rows, F = out.shape
+    _check(lib().cm_swiglu(dtype_code(out.dtype), _ptr(out), _ptr(gate_up), rows, F, _stream()), "swiglu")
+
+
+def gather_rows(out, x, rows):
+    n, H = out.shape
+    _check(lib().cm_gather_rows(dtype_code(x.dtype), _ptr(out), _ptr(x), _ptr(rows), n, H, _stream()),
+           "gather_rows")
+
+
+# ------------------------------------------------------------------------------- gemm
+def gemm_simt(y, x, w):
+    """y[M,N] = x[M,K] @ w[N,K]^T on the CUDA cores (float accumulation)."""
+    _need_cuda(y, x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(y.shape) != (M, N):
+        raise KernelError(f"gemm shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    _check(lib().cm_gemm_simt(dtype_code(x.dtype), dtype_code(w.dtype), dtype_code(y.dtype), _ptr(y), _ptr(x),
+                              _ptr(w), M, N, K, x.stride(0), w.stride(0), y.stride(0), _stream()), "gemm_simt")
+
+
+# -------------------------------------------------------------------------- attention
+def qk_prepare(qkv, wq, wk, rate, tok_pos, tok_seq, seq_slot, seq_end, pool, pages, ptab, ring,
+               QH, KVH, HD, eps):
+    """Head norm + rotation in place on the q and k columns of qkv; k and v go to the cache
+    (pool: this layer's [2, pages, KVH, 64, HD] storage, or None to write no cache)."""
+    T = qkv.shape[0]
+    _check(lib().cm_qk_prepare(dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(wq), _ptr(wk), _ptr(rate),
+                               _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(seq_end), _ptr(pool), pages,
+                               _ptr(ptab), 0 if ptab is None else ptab.stride(0), ring, T, QH, KVH, HD, eps,
+                               _stream()), "qk_prepare")
+
+
+def attn_prefill_simt(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale):
+    """q, k, v, gate are column views of one packed row-major buffer (same row stride)."""
+    if not (q.stride(0) == k.stride(0) == v.stride(0)):
+        raise KernelError("attn_prefill: q, k and v must share a row stride")
+    _check(lib().cm_attn_prefill_simt(dtype_code(q.dtype), _ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v),
+                                      q.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0),
+                                      _ptr(seq_start), B, max_len, QH, KVH, HD, window, scale, _stream()),
+           "attn_prefill_simt")
+
+
+def attn_decode_scratch(B, QH, HD, n_chunks, device):
+    return (torch.empty(B * QH * n_chunks * HD, dtype=torch.float32, device=device),
+            torch.empty(B * QH * n_chunks * 2, dtype=torch.float32, device=device))
+
+
+def attn_decode(ctx, q, gate, seq_pos, seq_slot, pool, pages, ptab, ring, window, QH, KVH, HD, n_chunks,
+                scale, part_o, part_ml):
+    B = q.shape[0]
+    _check(lib().cm_attn_decode(dtype_code(q.dtype), _ptr(ctx), ctx.stride(0), _ptr(q), q.stride(0), _ptr(gate),
+                                0 if gate is None else gate.stride(0), _ptr(seq_pos), _ptr(seq_slot), _ptr(pool),
+                                pages, _ptr(ptab), ptab.stride(0), ring, window, B, QH, KVH, HD, n_chunks, scale,
+                                _ptr(part_o), _ptr(part_ml), _stream()), "attn_decode")
+
+
+# -------------------------------------------------------------------------- short conv
+def shortconv(y, bcx, w, state, tok_seq, seq_start, seq_slot, K, from_zero, one_token_each):
+    T, H = y.shape
+    _check(lib().cm_shortconv(dtype_code(y.dtype), _ptr(y), _ptr(bcx), bcx.stride(0), _ptr(w), _ptr(state),
+                              _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slot), T, H, K, int(from_zero),
+                              int(one_token_each), _stream()), "shortconv")
+
+
+# ---------------------------------------------------------------------------- sampling
+def sample(out, logits, temperature, sequence, step, seed_words):
+    n, V = logits.shape
+    _check(lib().cm_sample(_ptr(out), _ptr(logits), logits.stride(0), n, V, _ptr(temperature), _ptr(sequence),
+                           _ptr(step), _ptr(seed_words), _stream()), "sample")
+
+
+# ------------------------------------------------------------------------------- cache
+def scatter_i32(table, index, value, count, max_count):
+    _check(lib().cm_scatter_i32(_ptr(table), _ptr(index), _ptr(value), _ptr(count), max_count, _stream()),
+           "scatter_i32")
+
+
+def zero_rows_f32(x, rows, n, width):
+    _check(lib().cm_zero_rows_f32(_ptr(x), _ptr(rows), n, width, _stream()), "zero_rows_f32")

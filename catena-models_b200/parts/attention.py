@@ -1,0 +1,89 @@
+"""Grouped-query attention mixer with head RMSNorm on q and k, a position encoding, a full or
+sliding causal mask and an optional per-head sigmoid gate on the output.
+
+Order of operations (src/lfm3.rs:390-464): one matrix product over the packed rows
+[Wq; Wk; Wv; Wgate] (src/lfm3.rs:1159-1262); head norm and rotation of q and k, k and the raw v
+written to the cache (src/catena/lfm3.hex:622-781); scores scaled by 1/sqrt(head_dim), keys
+hidden when k > p or, with a window W, when k + W <= p (src/catena/lfm3.hex:48-57); softmax and
+the value sum in float; context times sigmoid(gate) per head (src/catena/lfm3.hex:25-46);
+output projection.
+
+A prompt step attends over the step's own keys and values (every sequence of such a step
+starts at position 0); a decode step attends over the cache.  All sizes and switches are
+constructor parameters; the part knows neither its layer index nor its model.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import kernels
+from ..cache.spec import KVStateSpec
+from ..weights.loader import TensorSpec
+from .base import Mixer, register_part
+from .linear import Linear
+
+
+class GQAttention(Mixer):
+    def __init__(self, prefix, hidden, heads, kv_heads, head_dim, window, position, qk_norm_eps,
+                 output_gate, names=None):
+        names = names or {}
+        n = lambda key, default: prefix + names.get(key, default)
+        self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, head_dim
+        self.window = int(window or 0)
+        self.position = position
+        self.qk_norm_eps = qk_norm_eps           # None: no head norm
+        self.output_gate = bool(output_gate)
+        self.q_size, self.kv_size = heads * head_dim, kv_heads * head_dim
+        mats = [n("q", "attn_q.weight"), n("k", "attn_k.weight"), n("v", "attn_v.weight")]
+        rows = [self.q_size, self.kv_size, self.kv_size]
+        if self.output_gate:
+            mats.append(n("gate", "attn_gate.weight"))
+            rows.append(heads)
+        self.qkvg = Linear(mats, rows, hidden)
+        self.out = Linear(n("out", "attn_output.weight"), hidden, self.q_size)
+        self.q_norm_name, self.k_norm_name = n("q_norm", "attn_q_norm.weight"), n("k_norm", "attn_k_norm.weight")
+        self.q_norm_w = self.k_norm_w = None
+        # 1/sqrt(head_dim) in float32, as the reference bakes it (src/catena/qwen35_wmma_attention.hex:3-22)
+        self.scale = float(torch.tensor(1.0, dtype=torch.float32) / torch.sqrt(torch.tensor(float(head_dim), dtype=torch.float32)))
+
+    def children(self):
+        return [self.qkvg, self.out, self.position]
+
+    def tensor_specs(self):
+        if self.qk_norm_eps is None:
+            return []
+        return [TensorSpec(self.q_norm_name, (self.head_dim,), "norm"),
+                TensorSpec(self.k_norm_name, (self.head_dim,), "norm")]
+
+    def bind(self, tensors, rt):
+        if self.qk_norm_eps is not None:
+            self.q_norm_w = tensors[self.q_norm_name].to(torch.float32).contiguous()
+            self.k_norm_w = tensors[self.k_norm_name].to(torch.float32).contiguous()
+            self._bound = [self.q_norm_w, self.k_norm_w]
+
+    def state_spec(self):
+        return KVStateSpec(self.kv_heads, self.head_dim, self.window)
+
+    def forward(self, rt, batch, x, state):
+        QS, KVS, QH, KVH, HD = self.q_size, self.kv_size, self.heads, self.kv_heads, self.head_dim
+        qkvg = self.qkvg.apply(rt, x)                                   # [T, QS + 2 KVS (+ QH)]
+        kernels.qk_prepare(qkvg, self.q_norm_w, self.k_norm_w, self.position.rate_table(), batch.tok_pos,
+                           batch.tok_seq, batch.seq_slot, batch.seq_end, state.pool, state.pages, state.ptab,
+                           state.ring, QH, KVH, HD, self.qk_norm_eps or 0.0)
+        q = qkvg[:, :QS]
+        gate = qkvg[:, QS + 2 * KVS:] if self.output_gate else None
+        ctx = torch.empty((batch.T, QS), dtype=x.dtype, device=x.device)
+        if batch.prefill:
+            k, v = qkvg[:, QS:QS + KVS], qkvg[:, QS + KVS:QS + 2 * KVS]
+            rt.attention_prefill(ctx, q, k, v, gate, batch, QH, KVH, HD, self.window, self.scale)
+        else:
+            n_chunks = batch.decode_chunks(state.spec)
+            part_o, part_ml = rt.scratch_attn_decode(batch.B, QH, HD, n_chunks)
+            kernels.attn_decode(ctx, q, gate, batch.seq_pos0, batch.seq_slot, state.pool, state.pages, state.ptab,
+                                state.ring, self.window, QH, KVH, HD, n_chunks, self.scale, part_o, part_ml)
+        return self.out.apply(rt, ctx)
+
+
+register_part("mixer", "gqa_attention", GQAttention)

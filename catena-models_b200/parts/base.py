@@ -1,0 +1,114 @@
+"""Interfaces of the parts that layers are put together from, and their registries.
+
+Five kinds of part exist: `mixer` (attention, short convolution, ...), `feed_forward`,
+`norm`, `position` (position encoding) and `block` (the arrangement of the others in one
+layer).  A part is built from parameters only (sizes and constants come from a configuration
+through the model definition, never from this package's code) and does not know which model
+or which layer it is in.  A part that needs tensors lists them with full names in
+`tensor_specs()` and receives them, on the device and in their kept dtype, in `bind()`.
+
+    register_part("mixer", "my_mixer", MyMixer)     # open to tests and later architectures
+    build_part("mixer", "my_mixer", **params)
+
+Interfaces (x, h, n are [tokens, width] activations of the step's packed batch):
+
+    Norm.apply(rt, x) -> y                      weight, eps: attributes the fused kernels read
+    Position.rate_table() -> float32 [head_dim/2] or None    (angle = position * rate[i])
+    Mixer.state_spec() -> KVStateSpec | FixedStateSpec | None
+    Mixer.forward(rt, batch, x, state) -> y     state: the cache's view for this layer
+    FeedForward.forward(rt, batch, x) -> y
+    Block.input_norm                            the norm applied to h before the block runs
+    Block.forward(rt, batch, h, n, state, next_norm) -> (h, n_next)
+        n = input_norm(h) was made by whoever ran before; n_next = next_norm(h) is made
+        here (fused with the last residual sum) when next_norm is given, else None.
+
+`rt` is the engine's Runtime (dtype, device, scratch), `batch` the StepBatch (token
+positions, sequence boundaries, slots, prefill or decode).
+"""
+from __future__ import annotations
+
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block")
+_PARTS = {c: {} for c in CATEGORIES}
+
+
+def register_part(category, kind, cls, replace=False):
+    if category not in _PARTS:
+        raise ValueError(f"unknown part category '{category}'; one of {CATEGORIES}")
+    if kind in _PARTS[category] and not replace:
+        raise ValueError(f"{category} '{kind}' is already registered")
+    _PARTS[category][kind] = cls
+
+
+def part_kinds(category):
+    return sorted(_PARTS[category])
+
+
+def build_part(category, kind, **params):
+    try:
+        cls = _PARTS[category][kind]
+    except KeyError:
+        raise ValueError(f"unknown {category} '{kind}'; registered: {part_kinds(category)}") from None
+    return cls(**params)
+
+
+class Part:
+    """Base of every part: no tensors, nothing to bind."""
+
+    def tensor_specs(self):
+        return []
+
+    def bind(self, tensors, rt):
+        """Take this part's tensors out of {name: device tensor}."""
+
+    def children(self):
+        """Parts nested in this one (their tensors are listed and bound with it)."""
+        return []
+
+    def all_tensor_specs(self):
+        out = list(self.tensor_specs())
+        for child in self.children():
+            out.extend(child.all_tensor_specs())
+        return out
+
+    def bind_all(self, tensors, rt):
+        for child in self.children():
+            child.bind_all(tensors, rt)
+        self.bind(tensors, rt)
+
+    def weight_bytes(self):
+        """Bytes of weights a step reads from this part (each tensor once)."""
+        own = sum(t.numel() * t.element_size() for t in getattr(self, "_bound", ()))
+        return own + sum(c.weight_bytes() for c in self.children())
+
+
+class Mixer(Part):
+    def state_spec(self):
+        return None
+
+    def forward(self, rt, batch, x, state):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, rt, batch, x):
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def apply(self, rt, x):
+        raise NotImplementedError
+
+
+class Position(Part):
+    def rate_table(self):
+        return None
+
+
+class Block(Part):
+    input_norm = None
+
+    def state_spec(self):
+        return None
+
+    def forward(self, rt, batch, h, n, state, next_norm):
+        raise NotImplementedError
