@@ -18,6 +18,7 @@ import torch
 
 from ..cache.cache import Cache
 from ..cache.allocators import CacheError, CacheFull
+from .. import kernels as _kernels
 from ..kernels import ATTN_DECODE_CHUNK
 from .batch import BatchLayout, StepBatch, fill_host
 
@@ -53,6 +54,7 @@ class _Staging:
 class _DecodeGraph:
     def __init__(self, layout, device_buf, graph, logits, batch):
         self.layout, self.device_buf, self.graph, self.logits, self.batch = layout, device_buf, graph, logits, batch
+        self.launches = 0
 
 
 class Engine:
@@ -188,11 +190,15 @@ class Engine:
             batch.chunk_bucket = bucket
             logits = self.model.forward(batch, self.cache)
             graph = torch.cuda.CUDAGraph()
+            before = _kernels.launches
             with torch.cuda.graph(graph):
                 entry.logits = self.model.forward(batch, self.cache)
+            entry.launches = _kernels.launches - before       # kernels one replay runs
+            _kernels.launches = before                         # the capture itself ran nothing
             entry.graph, entry.batch = graph, batch
         else:
             entry.graph.replay()
+            _kernels.launches += entry.launches
             logits = entry.logits
         if all(w == [0] for w in want):
             return logits

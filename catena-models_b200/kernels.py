@@ -78,7 +78,12 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check(code, name):
+launches = 0          # kernels launched (or recorded into a graph) by this process, counted per call
+
+
+def _check(code, name, n=1):
+    global launches
+    launches += n
     if code != 0:
         raise KernelError(f"{name} returned {code}: {lib().cm_last_error().decode(errors='replace')}")
 
@@ -168,7 +173,7 @@ def attn_decode(ctx, q, gate, seq_pos, seq_slot, pool, pages, ptab, ring, window
     _check(lib().cm_attn_decode(dtype_code(q.dtype), _ptr(ctx), ctx.stride(0), _ptr(q), q.stride(0), _ptr(gate),
                                 0 if gate is None else gate.stride(0), _ptr(seq_pos), _ptr(seq_slot), _ptr(pool),
                                 pages, _ptr(ptab), ptab.stride(0), ring, window, B, QH, KVH, HD, n_chunks, scale,
-                                _ptr(part_o), _ptr(part_ml), _stream()), "attn_decode")
+                                _ptr(part_o), _ptr(part_ml), _stream()), "attn_decode", 2)
 
 
 # -------------------------------------------------------------------------- short conv

@@ -24,6 +24,11 @@ class Sampler:
         self.temperature, self.seed = float(temperature), int(seed)
         self._cap = 0
 
+    @staticmethod
+    def staging_ints(n):
+        """int32 words copied to the device per call for n rows (ids, steps, temperatures, seed)."""
+        return 3 * max(64, 2 * n) + 2
+
     def _buffers(self, n):
         if n > self._cap:
             cap = max(64, 2 * n)
