@@ -1,0 +1,151 @@
+// Y[M,N] = X[M,K] * W[N,K]^T for a handful of rows (decode steps): the weights are streamed
+// once from HBM and are the 16-row operand of mma.sync.m16n8k16, the M <= 8*NT activation
+// rows are its 8-wide operand ("swap A and B"), accumulation is float.
+//
+// A block owns 16 consecutive rows of W; its 8 warps split K between them and their partial
+// sums are added through shared memory in warp order, so the result does not depend on the
+// grid or on what else runs.  Every thread loads 16 contiguous bytes (8 values of k) per row
+// and k-block of 32; the two mma steps of a k-block use those 8 values in an order that is
+// the same for the W and the X fragment, so the sum over k is complete and each product is
+// formed once (the instruction's own k order is irrelevant to a dot product).
+//
+// MODE_SWIGLU: W is the row-packed [Wgate; Wup] (2F rows); a block computes 16 gate rows with
+// warps 0-3 and the matching 16 up rows with warps 4-7 and stores
+// a = T(silu(T(g)) * T(u)) -- the reference's rounding points (lfm3_wmma.hex:10790-10815).
+#include "common.cuh"
+
+#define SK_WARPS 8
+#define SK_MODE_PLAIN 0
+#define SK_MODE_SWIGLU 1
+
+__device__ __forceinline__ void mma_bf16_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream16(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <int NT, typename TY, int MODE, int UNROLL>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* __restrict__ W, int M, int N,
+                   int K, long long ldx, long long ldw, long long ldy) {
+    __shared__ float red[SK_WARPS][NT][32][4];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = blockIdx.x * 16;
+    // plain: all 8 warps split K; swiglu: warps 0-3 take the gate rows, 4-7 the up rows
+    const int splits = MODE == SK_MODE_SWIGLU ? SK_WARPS / 2 : SK_WARPS;
+    const int part = MODE == SK_MODE_SWIGLU ? (warp & 3) : warp;
+    const int row_base = (MODE == SK_MODE_SWIGLU && warp >= 4) ? N + r0 : r0;     // N = F in swiglu mode
+    const int row_limit = (MODE == SK_MODE_SWIGLU && warp >= 4) ? 2 * N : N;
+    const int nblk = (K + 31) >> 5;
+    const int per = (nblk + splits - 1) / splits;
+    const int b0 = part * per, b1 = min(nblk, b0 + per);
+    const bool v0 = row_base + g < row_limit, v1 = row_base + g + 8 < row_limit;
+    const bf16* w0 = W + (long long)(row_base + g) * ldw;
+    const bf16* w1 = W + (long long)(row_base + g + 8) * ldw;
+
+    float acc[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[n][j] = 0.f;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+    for (int blk = b0; blk < b1; blk += UNROLL) {
+        uint4 wa[UNROLL], wb[UNROLL], xv[UNROLL][NT];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (blk + u) * 32 + t * 8;
+            const bool kv = blk + u < b1 && k < K;
+            wa[u] = (kv && v0) ? ld_stream16(w0 + k) : zero;
+            wb[u] = (kv && v1) ? ld_stream16(w1 + k) : zero;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const int m = n * 8 + g;
+                xv[u][n] = (kv && m < M) ? __ldg(reinterpret_cast<const uint4*>(X + (long long)m * ldx + k)) : zero;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                mma_bf16_16816(acc[n], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv[u][n].x, xv[u][n].y);
+                mma_bf16_16816(acc[n], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv[u][n].z, xv[u][n].w);
+            }
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) red[warp][n][lane][j] = acc[n][j];
+    __syncthreads();
+    // element (n, lane, j): W row r0 + g (+8 for j >= 2), batch row 8n + 2t + (j & 1)
+    for (int e = threadIdx.x; e < NT * 128; e += SK_WARPS * 32) {
+        const int n = e >> 7, l = (e >> 2) & 31, j = e & 3;
+        const int row = r0 + (l >> 2) + (j >= 2 ? 8 : 0);
+        const int m = n * 8 + (l & 3) * 2 + (j & 1);
+        if (row >= N || m >= M) continue;
+        if (MODE == SK_MODE_SWIGLU) {
+            float gsum = 0.f, usum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) gsum += red[w][n][l][j];
+#pragma unroll
+            for (int w = 4; w < 8; ++w) usum += red[w][n][l][j];
+            const float gr = rounded<TY>(gsum), ur = rounded<TY>(usum);
+            Y[(long long)m * ldy + row] = from_f32<TY>((gr * sigmoid_f32(gr)) * ur);
+        } else {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < SK_WARPS; ++w) s += red[w][n][l][j];
+            Y[(long long)m * ldy + row] = from_f32<TY>(s);
+        }
+    }
+}
+
+template <int NT, typename TY, int MODE>
+static int launch_skinny(void* Y, const void* X, const void* W, int M, int N, int K, long long ldx, long long ldw,
+                         long long ldy, cudaStream_t st) {
+    const int blocks = (N + 15) / 16;
+    constexpr int UNROLL = NT == 1 ? 8 : (NT == 2 ? 4 : 2);
+    gemm_skinny_kernel<NT, TY, MODE, UNROLL><<<blocks, SK_WARPS * 32, 0, st>>>(
+        (TY*)Y, (const bf16*)X, (const bf16*)W, M, N, K, ldx, ldw, ldy);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+template <typename TY, int MODE>
+static int dispatch_skinny(void* Y, const void* X, const void* W, int M, int N, int K, long long ldx, long long ldw,
+                           long long ldy, cudaStream_t st) {
+    if (M <= 8) return launch_skinny<1, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+    if (M <= 16) return launch_skinny<2, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+    if (M <= 32) return launch_skinny<4, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+    if (M <= 64) return launch_skinny<8, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+    CM_REFUSE("gemm_skinny: %d rows (at most 64)", M);
+}
+
+// X and W bfloat16; Y bfloat16 (dty = DT_BF16) or float (DT_F32).  swiglu: W has 2N rows
+// ([gate; up]) and Y is [M, N].  K, ldx and ldw must be multiples of 8 (16-byte loads).
+extern "C" int cm_gemm_skinny(int dty, void* Y, const void* X, const void* W, int M, int N, int K, long long ldx,
+                              long long ldw, long long ldy, int swiglu, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return CM_OK;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8)
+        CM_REFUSE("gemm_skinny: inner size %d and row strides %lld, %lld must be multiples of 8", K, ldx, ldw);
+    if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W)) & 15)
+        CM_REFUSE("gemm_skinny: operands must be 16-byte aligned");
+    if (swiglu) {
+        if (dty != DT_BF16) return CM_ERR_DTYPE;
+        return dispatch_skinny<bf16, SK_MODE_SWIGLU>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+    }
+    if (dty == DT_BF16) return dispatch_skinny<bf16, SK_MODE_PLAIN>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+    if (dty == DT_F32) return dispatch_skinny<float, SK_MODE_PLAIN>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+    return CM_ERR_DTYPE;
+}

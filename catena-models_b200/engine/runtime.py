@@ -45,13 +45,26 @@ class Runtime:
     def linear(self, x, w, out_dtype=None):
         """y = x @ w^T; y in the activation dtype unless `out_dtype` says float32."""
         y = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
-        kernels.gemm_simt(y, x, w)
+        if self._skinny(x, w):
+            kernels.gemm_skinny(y, x, w)
+        else:
+            kernels.gemm_simt(y, x, w)
         return y
+
+    SKINNY_ROWS = 64
+
+    def _skinny(self, x, w):
+        """Few bfloat16 rows: the weight-streaming kernel (decode steps, wanted rows of the head)."""
+        return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= self.SKINNY_ROWS
+                and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
 
     def gate_up_swiglu(self, x, w_gate_up, F):
         """a = silu(x Wgate^T) * (x Wup^T) for the row-packed [Wgate; Wup]."""
-        gu = self.linear(x, w_gate_up)
         a = torch.empty((x.shape[0], F), dtype=x.dtype, device=x.device)
+        if self._skinny(x, w_gate_up):
+            kernels.gemm_skinny(a, x, w_gate_up, swiglu=True)
+            return a
+        gu = self.linear(x, w_gate_up)
         kernels.swiglu(a, gu)
         return a
 

@@ -25,6 +25,7 @@ _SIGNATURES = {
     "cm_swiglu": [_i, _vp, _vp, _i, _i, _vp],
     "cm_gather_rows": [_i, _vp, _vp, _vp, _i, _i, _vp],
     "cm_gemm_simt": [_i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
+    "cm_gemm_skinny": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp],
     "cm_qk_prepare": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i,
                       _i, _f, _vp],
     "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
@@ -138,6 +139,20 @@ def gemm_simt(y, x, w):
         raise KernelError(f"gemm shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
     _check(lib().cm_gemm_simt(dtype_code(x.dtype), dtype_code(w.dtype), dtype_code(y.dtype), _ptr(y), _ptr(x),
                               _ptr(w), M, N, K, x.stride(0), w.stride(0), y.stride(0), _stream()), "gemm_simt")
+
+
+def gemm_skinny(y, x, w, swiglu=False):
+    """y = x @ w^T for at most 64 bfloat16 rows, weights streamed once (mma.sync, float sums).
+    swiglu: w is [gate; up] with 2F rows and y[M, F] = silu(x Wgate^T) * (x Wup^T)."""
+    _need_cuda(y, x, w)
+    M, K = x.shape
+    N = y.shape[1]
+    if w.shape[1] != K or w.shape[0] != (2 * N if swiglu else N) or y.shape[0] != M:
+        raise KernelError(f"gemm_skinny shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny takes bfloat16 operands")
+    _check(lib().cm_gemm_skinny(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
+                                y.stride(0), int(swiglu), _stream()), "gemm_skinny")
 
 
 # -------------------------------------------------------------------------- attention

@@ -1,0 +1,409 @@
+"""Each CUDA kernel alone against a plain PyTorch float32/float64 statement of the same
+operation, at sizes other than the engine's (odd widths, row counts that fill no tile)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-2)
+
+
+def close(got, ref, dtype, **kw):
+    t = tol(dtype)
+    t.update(kw)
+    torch.testing.assert_close(got.float().cpu(), ref.float().cpu(), **t)
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.fixture(scope="module")
+def K():
+    from catena_models_b200 import kernels
+    kernels.lib()
+    return kernels
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather_and_bad_token(K, dtype):
+    table = rnd(37, 24, dtype=dtype)
+    tokens = torch.tensor([0, 36, 5, 5, 99, -1], dtype=torch.int32, device=DEV)
+    out = torch.empty(6, 24, dtype=dtype, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.embed_gather(out, table, tokens, err)
+    assert torch.equal(out[:4], table[[0, 36, 5, 5]])
+    assert int(err) == 1 and float(out[4:].abs().sum()) == 0.0          # refused ids: zeros and a flag, no fault
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,H", [(1, 8), (5, 200), (3, 1000), (2, 2056)])
+def test_rmsnorm(K, dtype, rows, H):
+    x, w = rnd(rows, H, dtype=dtype, scale=3.0), 1 + 0.1 * rnd(H)
+    y = torch.empty_like(x)
+    K.rmsnorm(y, x, w, 1e-3)
+    xf = x.double()
+    ref = xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + 1e-3) * w.double()
+    close(y, ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("post,nxt", [(True, True), (False, True), (True, False), (False, False)])
+def test_add_norm(K, dtype, post, nxt):
+    rows, H = 7, 328
+    m, h = rnd(rows, H, dtype=dtype, scale=2.0, seed=1), rnd(rows, H, dtype=dtype, seed=2)
+    wp, wn = 1 + 0.1 * rnd(H, seed=3), 1 + 0.1 * rnd(H, seed=4)
+    h_out, n_out = torch.empty_like(h), torch.empty_like(h)
+    K.add_norm(h_out, n_out if nxt else None, m, h, wp if post else None, wn if nxt else None, 1e-5, 1e-6)
+
+    def rms(v, w, eps):
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * w.double()
+
+    d = rms(m.double(), wp, 1e-5) if post else m.double()
+    if dtype == torch.bfloat16 and post:
+        d = d.to(torch.bfloat16).double()
+    href = h.double() + d
+    close(h_out, href, dtype)
+    if nxt:
+        close(n_out, rms(h_out.double(), wn, 1e-6), dtype)            # over the stored sum, as the kernel does
+    # in place on the residual stream
+    h2 = h.clone()
+    K.add_norm(h2, None, m, h2, wp if post else None, None, 1e-5, 0.0)
+    assert torch.equal(h2, h_out)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_and_gather(K, dtype):
+    gu = rnd(5, 2 * 72, dtype=dtype, scale=2.0)
+    a = torch.empty(5, 72, dtype=dtype, device=DEV)
+    K.swiglu(a, gu)
+    g, u = gu[:, :72].double(), gu[:, 72:].double()
+    close(a, g * torch.sigmoid(g) * u, dtype)
+    x = rnd(9, 40, dtype=dtype)
+    rows = torch.tensor([8, 0, 3, 3], dtype=torch.int32, device=DEV)
+    out = torch.empty(4, 40, dtype=dtype, device=DEV)
+    K.gather_rows(out, x, rows)
+    assert torch.equal(out, x[[8, 0, 3, 3]])
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 64, 256), (17, 67, 256), (65, 128, 2048), (3, 5, 8), (130, 70, 24)])
+@pytest.mark.parametrize("dtx,dtw,dty", [
+    (torch.float32, torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+    (torch.bfloat16, torch.bfloat16, torch.float32), (torch.bfloat16, torch.float32, torch.bfloat16)])
+def test_gemm_simt(K, M, N, Kd, dtx, dtw, dty):
+    x, w = rnd(M, Kd, dtype=dtx, seed=1), rnd(N, Kd, dtype=dtw, scale=0.1, seed=2)
+    y = torch.empty(M, N, dtype=dty, device=DEV)
+    K.gemm_simt(y, x, w)
+    ref = x.double() @ w.double().T
+    if dty == torch.float32:
+        torch.testing.assert_close(y.double().cpu(), ref.cpu(), rtol=1e-5, atol=1e-5 * math.sqrt(Kd))
+    else:
+        close(y, ref, torch.bfloat16)
+
+
+def test_gemm_simt_rows_do_not_depend_on_their_neighbours(K):
+    x, w = rnd(70, 96, seed=5), rnd(50, 96, seed=6)
+    y = torch.empty(70, 50, device=DEV)
+    K.gemm_simt(y, x, w)
+    y1 = torch.empty(1, 50, device=DEV)
+    K.gemm_simt(y1, x[69:70].contiguous(), w)
+    assert torch.equal(y1[0], y[69])                                   # bit-equal: fixed k order per element
+
+
+@pytest.mark.parametrize("M", [1, 2, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("N,Kd", [(16, 32), (100, 72), (2048, 2048), (24, 8), (515, 1000)])
+@pytest.mark.parametrize("dty", [torch.bfloat16, torch.float32])
+def test_gemm_skinny(K, M, N, Kd, dty):
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=1), rnd(N, Kd, dtype=torch.bfloat16, scale=0.1, seed=2)
+    y = torch.full((M, N), float("nan"), dtype=dty, device=DEV)
+    K.gemm_skinny(y, x, w)
+    ref = x.double() @ w.double().T
+    if dty == torch.float32:
+        torch.testing.assert_close(y.double().cpu(), ref.cpu(), rtol=2e-5, atol=2e-5 * math.sqrt(Kd))
+    else:
+        close(y, ref, torch.bfloat16)
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 64])
+@pytest.mark.parametrize("F,Kd", [(16, 32), (100, 72), (1000, 520)])
+def test_gemm_skinny_swiglu(K, M, F, Kd):
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=1), rnd(2 * F, Kd, dtype=torch.bfloat16, scale=0.2, seed=2)
+    a = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.gemm_skinny(a, x, w, swiglu=True)
+    # the scalar form of the reference's own check (tests/lfm3_projections.rs:139-158)
+    g = (x.double() @ w[:F].double().T).to(torch.bfloat16).double()
+    u = (x.double() @ w[F:].double().T).to(torch.bfloat16).double()
+    close(a, g / (1 + torch.exp(-g)) * u, torch.bfloat16, rtol=2e-2)
+
+
+def test_gemm_skinny_batch_mates_change_nothing(K):
+    x, w = rnd(8, 520, dtype=torch.bfloat16, seed=3), rnd(70, 520, dtype=torch.bfloat16, seed=4)
+    y8 = torch.empty(8, 70, dtype=torch.float32, device=DEV)
+    K.gemm_skinny(y8, x, w)
+    y1 = torch.empty(1, 70, dtype=torch.float32, device=DEV)
+    K.gemm_skinny(y1, x[5:6].contiguous(), w)
+    assert torch.equal(y1[0], y8[5])
+
+
+def _ref_attention(q, k, v, window, scale, gate=None):
+    """float64 softmax attention with GQA, causal or sliding mask and the head gate
+    (the form of the reference's own check, tests/lfm3_online_attention.rs:145-181)."""
+    T, QH, HD = q.shape
+    KVH = k.shape[1]
+    out = torch.zeros(T, QH, HD, dtype=torch.float64)
+    pos = torch.arange(T)
+    hidden = pos[None, :] > pos[:, None]
+    if window > 0:
+        hidden |= pos[None, :] + window <= pos[:, None]
+    for h in range(QH):
+        s = (q[:, h].double() @ k[:, h // (QH // KVH)].double().T) * scale
+        s = s.masked_fill(hidden, float("-inf"))
+        out[:, h] = torch.softmax(s, -1) @ v[:, h // (QH // KVH)].double()
+    if gate is not None:
+        out = out * torch.sigmoid(gate.double())[:, :, None]
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("QH,KVH,HD,window,gated", [(4, 2, 16, 0, True), (6, 1, 24, 5, False), (2, 2, 128, 40, True),
+                                                    (3, 3, 256, 0, False), (8, 2, 64, 256, True)])
+def test_attn_prefill_varlen(K, dtype, QH, KVH, HD, window, gated):
+    lens = [17, 65, 1, 100]
+    T = sum(lens)
+    width = QH * HD + 2 * KVH * HD + (QH if gated else 0)
+    buf = rnd(T, width, dtype=dtype, seed=HD)
+    q, k = buf[:, :QH * HD], buf[:, QH * HD:QH * HD + KVH * HD]
+    v = buf[:, QH * HD + KVH * HD:QH * HD + 2 * KVH * HD]
+    gate = buf[:, QH * HD + 2 * KVH * HD:] if gated else None
+    starts = torch.tensor([0, 17, 82, 83, 183], dtype=torch.int32, device=DEV)
+    ctx = torch.full((T, QH * HD), float("nan"), dtype=dtype, device=DEV)
+    scale = HD ** -0.5
+    K.attn_prefill_simt(ctx, q, k, v, gate, starts, len(lens), max(lens), QH, KVH, HD, window, scale)
+    off = 0
+    for n in lens:
+        sl = slice(off, off + n)
+        ref = _ref_attention(q[sl].cpu().view(n, QH, HD), k[sl].cpu().view(n, KVH, HD), v[sl].cpu().view(n, KVH, HD),
+                             window, scale, None if gate is None else gate[sl].cpu())
+        close(ctx[sl].view(n, QH, HD), ref, dtype)
+        off += n
+
+
+def _paged_cache(K, kv, KVH, HD, dtype, lens, ring, scramble_seed=0):
+    """Put per-sequence keys/values kv[b]: [len, 2, KVH, HD] into a paged pool with shuffled page
+    ids the way the engine would (entry = pos, or pos % ring)."""
+    pages_per_seq = [((min(n, ring) if ring else n) + 63) // 64 for n in lens]
+    total = sum(pages_per_seq) + 3
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(scramble_seed)).tolist()
+    pool = torch.full((2, total, KVH, 64, HD), float("nan"), dtype=dtype, device=DEV)
+    stride = max(pages_per_seq)
+    ptab = torch.full((len(lens) + 2, stride), -1, dtype=torch.int32)
+    nxt = 0
+    for b, n in enumerate(lens):
+        slot = b + 1                                   # slot ids differ from batch order
+        for j in range(pages_per_seq[b]):
+            ptab[slot, j] = perm[nxt]
+            nxt += 1
+        first = max(0, n - ring) if ring else 0
+        for p in range(first, n):
+            e = p % ring if ring else p
+            page = int(ptab[slot, e // 64])
+            pool[0, page, :, e % 64] = kv[b][p, 0].to(dtype)
+            pool[1, page, :, e % 64] = kv[b][p, 1].to(dtype)
+    return pool, total, ptab.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("QH,KVH,HD,window", [(4, 2, 16, 0), (4, 1, 24, 8), (5, 5, 32, 70), (32, 8, 64, 0),
+                                              (16, 1, 128, 300), (2, 1, 256, 0)])
+def test_attn_decode_paged(K, dtype, QH, KVH, HD, window):
+    ring = (window + 63) // 64 * 64 if window else 0
+    lens = [1, 64, 65, 300, 700]                      # tokens held including the new one
+    B = len(lens)
+    g = torch.Generator().manual_seed(HD + window)
+    kv = [torch.randn(n, 2, KVH, HD, generator=g) for n in lens]
+    pool, pages, ptab = _paged_cache(K, kv, KVH, HD, dtype, lens, ring)
+    q = rnd(B, QH * HD, dtype=dtype, seed=7)
+    gate = rnd(B, QH, dtype=dtype, seed=8)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    slots = torch.arange(1, B + 1, dtype=torch.int32, device=DEV)
+    n_chunks = 4                                       # more chunks than the short sequences have
+    part_o, part_ml = K.attn_decode_scratch(B, QH, HD, n_chunks, DEV)
+    ctx = torch.full((B, QH * HD), float("nan"), dtype=dtype, device=DEV)
+    scale = HD ** -0.5
+    K.attn_decode(ctx, q, gate, pos, slots, pool, pages, ptab, ring, window, QH, KVH, HD, n_chunks, scale, part_o, part_ml)
+    for b, n in enumerate(lens):
+        kk, vv = kv[b][:, 0].to(dtype), kv[b][:, 1].to(dtype)
+        qq = torch.zeros(n, QH, HD)
+        qq[-1] = q[b].float().cpu().view(QH, HD)
+        gg = torch.zeros(n, QH)
+        gg[-1] = gate[b].float().cpu()
+        ref = _ref_attention(qq, kk, vv, window, scale, gg)[-1]
+        close(ctx[b].view(QH, HD), ref, dtype)
+
+
+def test_attn_decode_finds_a_far_key_and_respects_the_window_edge(K):
+    """One key far back is made to dominate; it must be found among hundreds when it is inside
+    the window and be invisible one step after it leaves."""
+    QH = KVH = 1
+    HD, n = 16, 500
+    for window, far, seen in [(0, 3, True), (200, n - 200, True), (200, n - 201, False)]:
+        ring = (window + 63) // 64 * 64 if window else 0
+        kv = [torch.randn(n, 2, KVH, HD, generator=torch.Generator().manual_seed(1)) * 0.1]
+        kv[0][far, 0, 0] = 0.0
+        kv[0][far, 0, 0, 0] = 40.0                     # the key that stands out
+        kv[0][far, 1, 0] = 7.0                         # its value
+        pool, pages, ptab = _paged_cache(K, kv, KVH, HD, torch.float32, [n], ring)
+        q = torch.zeros(1, HD, device=DEV)
+        q[0, 0] = 40.0
+        pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+        slots = torch.tensor([1], dtype=torch.int32, device=DEV)
+        part_o, part_ml = K.attn_decode_scratch(1, QH, HD, 2, DEV)
+        ctx = torch.empty(1, HD, device=DEV)
+        K.attn_decode(ctx, q, None, pos, slots, pool, pages, ptab, ring, window, QH, KVH, HD, 2, HD ** -0.5, part_o, part_ml)
+        if seen:
+            assert torch.allclose(ctx.cpu(), torch.full((1, HD), 7.0), atol=1e-3)
+        else:
+            assert float(ctx.abs().max()) < 1.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("QH,KVH,HD,ring,normed,rotated", [(4, 2, 16, 0, True, True), (3, 1, 24, 64, True, False),
+                                                          (2, 2, 128, 0, False, True), (5, 5, 32, 128, True, True)])
+def test_qk_prepare(K, dtype, QH, KVH, HD, ring, normed, rotated):
+    lens, pos0 = [5, 150, 1], [0, 0, 0]
+    T = sum(lens)
+    width = QH * HD + 2 * KVH * HD + 3
+    qkv = rnd(T, width, dtype=dtype, seed=ring + HD)
+    orig = qkv.clone()
+    wq, wk = 1 + 0.1 * rnd(HD, seed=1), 1 + 0.1 * rnd(HD, seed=2)
+    rate = (torch.rand(HD // 2, generator=torch.Generator().manual_seed(3)) * 0.5).to(DEV)
+    tok_seq = torch.tensor(sum([[b] * n for b, n in enumerate(lens)], []), dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(sum([list(range(n)) for n in lens], []), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, 0, 1], dtype=torch.int32, device=DEV)
+    seq_end = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    pages = 8
+    pool = torch.zeros(2, pages, KVH, 64, HD, dtype=dtype, device=DEV)
+    ptab = torch.tensor([[3, 1, 6], [0, 7, 7], [5, 7, 7]], dtype=torch.int32, device=DEV)   # by slot
+    eps = 1e-5
+    K.qk_prepare(qkv, wq if normed else None, wk if normed else None, rate if rotated else None, tok_pos, tok_seq,
+                 slots, seq_end, pool, pages, ptab, ring, QH, KVH, HD, eps)
+
+    def prepared(x, w):
+        x = x.double()
+        if normed:
+            x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w.double().cpu()
+            if dtype == torch.bfloat16:
+                x = x.to(torch.bfloat16).double()
+        if rotated:
+            ang = tok_pos.cpu().double()[:, None] * rate.cpu().double()[None, :]
+            c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            lo, hi = x[..., :HD // 2], x[..., HD // 2:]
+            x = torch.cat([lo * c - hi * s, hi * c + lo * s], -1)
+        return x
+
+    o = orig.cpu()
+    q_ref = prepared(o[:, :QH * HD].view(T, QH, HD), wq)
+    k_ref = prepared(o[:, QH * HD:QH * HD + KVH * HD].view(T, KVH, HD), wk)
+    close(qkv[:, :QH * HD].view(T, QH, HD), q_ref, dtype)
+    close(qkv[:, QH * HD:QH * HD + KVH * HD].view(T, KVH, HD), k_ref, dtype)
+    assert torch.equal(qkv[:, QH * HD + KVH * HD:], orig[:, QH * HD + KVH * HD:])       # v and the rest untouched
+    # cache entries of the middle sequence (slot 0: pages 3, 1, 6)
+    v_ref = o[:, QH * HD + KVH * HD:QH * HD + 2 * KVH * HD].view(T, KVH, HD)
+    first = max(0, 150 - ring) if ring else 0
+    for p in (first, 63 if first <= 63 else first, 64 if first <= 64 else first, 149):
+        e = p % ring if ring else p
+        page = [3, 1, 6][e // 64]
+        t = 5 + p
+        close(pool[0, page, :, e % 64], k_ref[t], dtype)
+        assert torch.equal(pool[1, page, :, e % 64].cpu(), v_ref[t])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,taps", [(8, 2), (72, 3), (200, 4), (136, 7)])
+def test_shortconv_prompt_then_decode(K, dtype, H, taps):
+    lens = [1, 2, 9, 30]
+    extra = 5
+    g = torch.Generator().manual_seed(H)
+    w = (torch.randn(H, taps, generator=g) * 0.5).to(DEV)
+    seqs = [torch.randn(n + extra, 3 * H, generator=g).to(dtype) for n in lens]
+    slots = torch.tensor([3, 0, 2, 1], dtype=torch.int32, device=DEV)
+    state = torch.full((5, taps - 1, H), float("nan"), device=DEV)         # stale contents must not matter
+
+    def reference(s):
+        s = s.double()
+        B_, C_, X_ = s[:, :H], s[:, H:2 * H], s[:, 2 * H:]
+        bx = torch.cat([torch.zeros(taps - 1, H, dtype=torch.float64), B_ * X_])
+        z = sum(w.cpu().double()[:, j][None, :] * bx[j:j + s.shape[0]] for j in range(taps))
+        return z * C_
+
+    bcx = torch.cat([s[:n] for s, n in zip(seqs, lens)]).to(DEV)
+    T = bcx.shape[0]
+    tok_seq = torch.tensor(sum([[b] * n for b, n in enumerate(lens)], []), dtype=torch.int32, device=DEV)
+    starts = torch.tensor([0, 1, 3, 12, 42], dtype=torch.int32, device=DEV)
+    y = torch.empty(T, H, dtype=dtype, device=DEV)
+    K.shortconv(y, bcx, w, state, tok_seq, starts, slots, taps, from_zero=True, one_token_each=False)
+    got = [[y[a:b]] for a, b in zip(starts.tolist()[:-1], starts.tolist()[1:])]
+    dec_seq = torch.arange(4, dtype=torch.int32, device=DEV)
+    dec_start = torch.arange(5, dtype=torch.int32, device=DEV)
+    for t in range(extra):
+        bcx = torch.stack([s[n + t] for s, n in zip(seqs, lens)]).to(DEV)
+        y = torch.empty(4, H, dtype=dtype, device=DEV)
+        K.shortconv(y, bcx, w, state, dec_seq, dec_start, slots, taps, from_zero=False, one_token_each=True)
+        for b in range(4):
+            got[b].append(y[b:b + 1].clone())
+    for b, s in enumerate(seqs):
+        close(torch.cat(got[b]), reference(s), dtype)
+    with pytest.raises(K.KernelError):
+        K.shortconv(y, bcx, w, state, dec_seq, dec_start, slots, taps, from_zero=False, one_token_each=False)
+
+
+def test_sample_greedy_ties_and_temperature(K):
+    import plain_lfm3 as P
+
+    V = 1000
+    logits = rnd(6, V, scale=2.0, seed=4)
+    logits[0, 17] = logits[0, 400] = logits[0].max() + 1.0                 # a tie: the lower index wins
+    logits[1, V - 1] = 50.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    temp = torch.tensor([0.0, 0.0, 0.8, 0.8, 1.5, 0.8], device=DEV)
+    seq = torch.tensor([0, 1, 2, 3, 4, 2], dtype=torch.int32, device=DEV)
+    step = torch.tensor([0, 0, 5, 5, 9, 5], dtype=torch.int32, device=DEV)
+    seed = 0x1234567890ABCDEF
+    words = torch.tensor([seed & 0xFFFFFFFF, seed >> 32], dtype=torch.int64).to(torch.int32).to(DEV)
+    K.sample(out, logits, temp, seq, step, words)
+    got = out.tolist()
+    assert got[0] == 17 and got[1] == V - 1
+    for r in (2, 3, 4):
+        u = P.uniform_draw(seed, int(seq[r]), int(step[r]))
+        x = logits[r].double().cpu() / float(temp[r])
+        cdf = torch.cumsum(torch.exp(x - x.max()), 0)
+        target = u * float(cdf[-1])
+        lo = float(cdf[got[r] - 1]) if got[r] > 0 else 0.0
+        slack = 1e-4 * float(cdf[-1])
+        assert lo - slack <= target <= float(cdf[got[r]]) + slack           # the drawn index holds u
+    # rows 2 and 5 differ only in their logits' row: same key -> same uniform
+    many = torch.empty(4000, dtype=torch.int32, device=DEV)
+    flat = torch.log(torch.tensor([0.1, 0.2, 0.3, 0.4], device=DEV)).repeat(4000, 1).contiguous()
+    K.sample(many, flat, torch.full((4000,), 1.0, device=DEV), torch.arange(4000, dtype=torch.int32, device=DEV),
+             torch.zeros(4000, dtype=torch.int32, device=DEV), words)
+    freq = torch.bincount(many.cpu().long(), minlength=4).double() / 4000
+    assert torch.allclose(freq, torch.tensor([0.1, 0.2, 0.3, 0.4], dtype=torch.float64), atol=0.03)
+
+
+def test_refusals_are_errors_not_wrong_results(K):
+    x = torch.zeros(2, 12, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(K.KernelError):
+        K.gemm_skinny(torch.empty(2, 4, dtype=torch.bfloat16, device=DEV), x, torch.zeros(4, 12, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(K.KernelError):
+        K.gemm_skinny(torch.empty(70, 4, dtype=torch.bfloat16, device=DEV), torch.zeros(70, 16, dtype=torch.bfloat16, device=DEV),
+                      torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(K.KernelError):
+        K.rmsnorm(torch.empty(2, 4), torch.empty(2, 4), torch.ones(4), 1e-5)     # CPU tensors
