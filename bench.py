@@ -229,6 +229,8 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run one part only (small captures under a profiler); prints that part's facts")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -251,11 +253,17 @@ def main():
     pk = peaks()
     cfg = model_config(args.layers)
     vocab = cfg["vocab_size"]
-    big = 64 if not args.no_points else args.batch
+    big = 64 if not (args.no_points or args.only != "all") else args.batch
     model = Model.random(cfg, seed=0, std=0.02, dtype="bfloat16", device="cuda:0",
                          max_tokens=max(big, args.batch) * args.context, max_seqs=max(big, args.batch))
     weight_bytes = model.decoder.weight_bytes_per_step()
 
+    if args.only == "decode":
+        print(json.dumps(decode_run(model, args.batch, args.prompt_len, args.steps, args.warmup, vocab)))
+        return 0
+    if args.only == "prefill":
+        print(json.dumps(prefill_run(model, 2048, vocab, cfg, pk["bf16_tflops"])))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     main_run = decode_run(model, args.batch, args.prompt_len, args.steps, args.warmup, vocab)

@@ -44,6 +44,8 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
                                   const int* __restrict__ seq_slot, const int* __restrict__ seq_end,
                                   T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
                                   int ptab_stride, int ring, int QH, int KVH, int HD, float eps) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float ubuf[];              // [warps][HD]
     const int lane = threadIdx.x, warp = threadIdx.y;
     const int head = blockIdx.x * blockDim.y + warp;
@@ -115,11 +117,11 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
     const size_t smem = 4 * (size_t)HD * sizeof(float);
     if (smem > 48 * 1024) CM_REFUSE("qk_prepare: head size %d too large", HD);
     if (dt == DT_F32)
-        qk_prepare_kernel<float><<<grid, block, smem, st>>>((float*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
+        cm_launch(qk_prepare_kernel<float>, grid, block, smem, st, (float*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
                                                             seq_slot, seq_end, (float*)pool, pages, ptab,
                                                             ptab_stride, ring, QH, KVH, HD, eps);
     else if (dt == DT_BF16)
-        qk_prepare_kernel<bf16><<<grid, block, smem, st>>>((bf16*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
+        cm_launch(qk_prepare_kernel<bf16>, grid, block, smem, st, (bf16*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
                                                            seq_slot, seq_end, (bf16*)pool, pages, ptab,
                                                            ptab_stride, ring, QH, KVH, HD, eps);
     else
@@ -145,6 +147,8 @@ attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict
                          const T* __restrict__ gate, long long ldg,
                          const int* __restrict__ seq_start, int QH, int KVH, int HD, int window,
                          float scale) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     const int ldq = HD + 1;
     float* Qs = smem;                       // [AP_BQ][HD+1]
@@ -249,12 +253,12 @@ extern "C" int cm_attn_prefill_simt(int dt, void* ctx, long long ldc, const void
     dim3 grid((max_len + AP_BQ - 1) / AP_BQ, QH, B);
     if (dt == DT_F32) {
         cudaFuncSetAttribute(attn_prefill_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_prefill_simt_kernel<float><<<grid, 128, smem, st>>>((float*)ctx, ldc, (const float*)q, (const float*)k,
+        cm_launch(attn_prefill_simt_kernel<float>, grid, 128, smem, st, (float*)ctx, ldc, (const float*)q, (const float*)k,
                                                                  (const float*)v, ld, (const float*)gate, ldg,
                                                                  seq_start, QH, KVH, HD, window, scale);
     } else if (dt == DT_BF16) {
         cudaFuncSetAttribute(attn_prefill_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_prefill_simt_kernel<bf16><<<grid, 128, smem, st>>>((bf16*)ctx, ldc, (const bf16*)q, (const bf16*)k,
+        cm_launch(attn_prefill_simt_kernel<bf16>, grid, 128, smem, st, (bf16*)ctx, ldc, (const bf16*)q, (const bf16*)k,
                                                                 (const bf16*)v, ld, (const bf16*)gate, ldg,
                                                                 seq_start, QH, KVH, HD, window, scale);
     } else
@@ -285,6 +289,8 @@ attn_decode_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, cons
                    const T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
                    int ptab_stride, int ring, int window, int QH, int KVH, int HD, int n_chunks,
                    float scale) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     float* qs = smem;                               // [AD_GB][HD]
     float* ss = qs + AD_GB * HD;                    // [AD_GB][AD_CHUNK]
@@ -420,6 +426,8 @@ __global__ void attn_decode_merge_kernel(T* __restrict__ ctx, long long ldc,
                                          const T* __restrict__ gate, long long ldg,
                                          const int* __restrict__ seq_pos, int ring, int QH, int HD,
                                          int n_chunks) {
+    pdl_trigger();
+    pdl_wait();
     const int hq = blockIdx.x, b = blockIdx.y;
     const int pos = seq_pos[b];
     const int n_entries = ring ? min(pos + 1, ring) : pos + 1;
@@ -462,22 +470,22 @@ extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, l
     const int mthreads = HD <= 64 ? 64 : 128;
     if (dt == DT_F32) {
         cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_decode_kernel<float><<<grid, AD_THREADS, smem, st>>>(part_o, part_ml, (const float*)q, ldq, seq_pos,
+        cm_launch(attn_decode_kernel<float>, grid, AD_THREADS, smem, st, part_o, part_ml, (const float*)q, ldq, seq_pos,
                                                                   seq_slot, (const float*)pool, pages, ptab,
                                                                   ptab_stride, ring, window, QH, KVH, HD,
                                                                   n_chunks, scale);
         CM_CHECK_LAUNCH();
-        attn_decode_merge_kernel<float><<<mgrid, mthreads, 0, st>>>((float*)ctx, ldc, part_o, part_ml,
+        cm_launch(attn_decode_merge_kernel<float>, mgrid, mthreads, 0, st, (float*)ctx, ldc, part_o, part_ml,
                                                                     (const float*)gate, ldg, seq_pos, ring, QH,
                                                                     HD, n_chunks);
     } else if (dt == DT_BF16) {
         cudaFuncSetAttribute(attn_decode_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attn_decode_kernel<bf16><<<grid, AD_THREADS, smem, st>>>(part_o, part_ml, (const bf16*)q, ldq, seq_pos,
+        cm_launch(attn_decode_kernel<bf16>, grid, AD_THREADS, smem, st, part_o, part_ml, (const bf16*)q, ldq, seq_pos,
                                                                  seq_slot, (const bf16*)pool, pages, ptab,
                                                                  ptab_stride, ring, window, QH, KVH, HD,
                                                                  n_chunks, scale);
         CM_CHECK_LAUNCH();
-        attn_decode_merge_kernel<bf16><<<mgrid, mthreads, 0, st>>>((bf16*)ctx, ldc, part_o, part_ml,
+        cm_launch(attn_decode_merge_kernel<bf16>, mgrid, mthreads, 0, st, (bf16*)ctx, ldc, part_o, part_ml,
                                                                    (const bf16*)gate, ldg, seq_pos, ring, QH,
                                                                    HD, n_chunks);
     } else

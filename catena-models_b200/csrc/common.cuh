@@ -30,6 +30,62 @@ void cm_set_error(const char* fmt, ...);
         return CM_ERR_SHAPE;      \
     } while (0)
 
+// ---- programmatic dependent launch --------------------------------------------------
+// Every kernel of this library is launched with the "programmatic stream serialization"
+// attribute (unless cm_set_pdl(0)): the next kernel of the stream may be scheduled while this
+// one still runs, and blocks in pdl_wait() until this one has finished and its writes are
+// visible.  A kernel may read constants (weights) before pdl_wait(), and nothing else; every
+// block calls pdl_wait() before it reads an activation, writes anything, or exits, so that
+// completion of a kernel implies completion of all kernels before it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+int cm_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t cm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = cm_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// The same, for a grid whose blocks form clusters of (1, cluster_y, 1).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t cm_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t st, int cluster_y, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster_y > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = cluster_y;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (cm_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define CM_CHECK_LAUNCH()                                              \
     do {                                                               \
         cudaError_t e_ = cudaGetLastError();                           \

@@ -14,6 +14,8 @@ template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(TY* __restrict__ Y, const TX* __restrict__ X, const TW* __restrict__ W, int M,
                  int N, int K, long long ldx, long long ldw, long long ldy) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float xs[GS_BK][GS_BM + 1];
     __shared__ float ws[GS_BK][GS_BN + 1];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // 16 x 16 threads, 4 x 4 outputs each
@@ -65,7 +67,7 @@ template <typename TX, typename TW, typename TY>
 static int launch_simt(void* Y, const void* X, const void* W, int M, int N, int K, long long ldx,
                        long long ldw, long long ldy, cudaStream_t st) {
     dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
-    gemm_simt_kernel<TX, TW, TY><<<grid, 256, 0, st>>>((TY*)Y, (const TX*)X, (const TW*)W, M, N, K,
+    cm_launch(gemm_simt_kernel<TX, TW, TY>, grid, 256, 0, st, (TY*)Y, (const TX*)X, (const TW*)W, M, N, K,
                                                        ldx, ldw, ldy);
     CM_CHECK_LAUNCH();
     return CM_OK;

@@ -8,6 +8,8 @@ template <typename T>
 __global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ table,
                                     const int* __restrict__ tokens, int H, int V,
                                     int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     const bool ok = tok >= 0 && tok < V;
@@ -22,47 +24,121 @@ extern "C" int cm_embed_gather(int dt, void* out, const void* table, const int* 
     if (T <= 0) return CM_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (dt == DT_F32)
-        embed_gather_kernel<float><<<T, threads, 0, st>>>((float*)out, (const float*)table, tokens, H, V, err);
+        cm_launch(embed_gather_kernel<float>, T, threads, 0, st, (float*)out, (const float*)table, tokens, H, V, err);
     else if (dt == DT_BF16)
-        embed_gather_kernel<bf16><<<T, threads, 0, st>>>((bf16*)out, (const bf16*)table, tokens, H, V, err);
+        cm_launch(embed_gather_kernel<bf16>, T, threads, 0, st, (bf16*)out, (const bf16*)table, tokens, H, V, err);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
 
+// ---------------------------------------------------------------- rows in registers
+// The norm kernels keep a row in registers: a thread owns chunks of 8 consecutive elements,
+// chunk c of thread t starts at (c * blockDim.x + t) * 8.  All global loads of a row are
+// issued before the first reduction.  H must be a multiple of 8 and at most 8 * 256 * NV_MAXC.
+#define NV_THREADS 256
+#define NV_MAXC 4
+
+template <typename T>
+__device__ __forceinline__ void load8f(const T* p, float* out);
+template <>
+__device__ __forceinline__ void load8f<float>(const float* p, float* out) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8f<bf16>(const bf16* p, float* out) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+template <typename T>
+__device__ __forceinline__ void store8f(T* p, const float* v);
+template <>
+__device__ __forceinline__ void store8f<float>(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8f<bf16>(bf16* p, const float* v) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
 // -------------------------------------------------------------------------- RMSNorm
 // y = T((x * inv) * w), inv = 1/sqrt(mean(x^2) + eps); w is float.
-template <typename T>
-__global__ void rmsnorm_kernel(T* __restrict__ y, const T* __restrict__ x,
-                               const float* __restrict__ w, int H, float eps, long long ldx,
-                               long long ldy) {
+template <typename T, int C>
+__global__ void __launch_bounds__(NV_THREADS)
+rmsnorm_kernel(T* __restrict__ y, const T* __restrict__ x, const float* __restrict__ w, int H, float eps,
+               long long ldx, long long ldy) {
     __shared__ float scratch[32];
+    pdl_trigger();
+    float wv[C][8], xv[C][8];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int e = (c * NV_THREADS + threadIdx.x) * 8;
+        if (e < H) load8f<float>(w + e, wv[c]);
+    }
+    pdl_wait();
     const T* xr = x + (long long)blockIdx.x * ldx;
     T* yr = y + (long long)blockIdx.x * ldy;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        const float v = to_f32(xr[c]);
-        ss += v * v;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int e = (c * NV_THREADS + threadIdx.x) * 8;
+        if (e < H) {
+            load8f<T>(xr + e, xv[c]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += xv[c][i] * xv[c][i];
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)H + eps);
-    for (int c = threadIdx.x; c < H; c += blockDim.x)
-        yr[c] = from_f32<T>((to_f32(xr[c]) * inv) * w[c]);
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int e = (c * NV_THREADS + threadIdx.x) * 8;
+        if (e < H) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = (xv[c][i] * inv) * wv[c][i];
+            store8f<T>(yr + e, o);
+        }
+    }
+}
+
+template <typename T>
+static int launch_rmsnorm(void* y, const void* x, const float* w, int rows, int H, float eps, long long ldx,
+                          long long ldy, cudaStream_t st) {
+    const int chunks = (H / 8 + NV_THREADS - 1) / NV_THREADS;
+    if (chunks <= 1)
+        cm_launch(rmsnorm_kernel<T, 1>, rows, NV_THREADS, 0, st, (T*)y, (const T*)x, w, H, eps, ldx, ldy);
+    else if (chunks <= 2)
+        cm_launch(rmsnorm_kernel<T, 2>, rows, NV_THREADS, 0, st, (T*)y, (const T*)x, w, H, eps, ldx, ldy);
+    else
+        cm_launch(rmsnorm_kernel<T, NV_MAXC>, rows, NV_THREADS, 0, st, (T*)y, (const T*)x, w, H, eps, ldx, ldy);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
 }
 
 extern "C" int cm_rmsnorm(int dt, void* y, const void* x, const float* w, int rows, int H,
                           float eps, long long ldx, long long ldy, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
-    const int threads = H >= 1024 ? 256 : 128;
-    if (dt == DT_F32)
-        rmsnorm_kernel<float><<<rows, threads, 0, st>>>((float*)y, (const float*)x, w, H, eps, ldx, ldy);
-    else if (dt == DT_BF16)
-        rmsnorm_kernel<bf16><<<rows, threads, 0, st>>>((bf16*)y, (const bf16*)x, w, H, eps, ldx, ldy);
-    else
-        return CM_ERR_DTYPE;
-    CM_CHECK_LAUNCH();
-    return CM_OK;
+    if (H % 8 || H > 8 * NV_THREADS * NV_MAXC || ldx % 8 || ldy % 8)
+        CM_REFUSE("rmsnorm: width %d (strides %lld, %lld) must be a multiple of 8, at most %d", H, ldx, ldy,
+                  8 * NV_THREADS * NV_MAXC);
+    if (((uintptr_t)y | (uintptr_t)x | (uintptr_t)w) & 15) CM_REFUSE("rmsnorm: operands must be 16-byte aligned");
+    if (dt == DT_F32) return launch_rmsnorm<float>(y, x, w, rows, H, eps, ldx, ldy, st);
+    if (dt == DT_BF16) return launch_rmsnorm<bf16>(y, x, w, rows, H, eps, ldx, ldy, st);
+    return CM_ERR_DTYPE;
 }
 
 // ------------------------------------------------- residual add with both norms fused
@@ -70,75 +146,109 @@ extern "C" int cm_rmsnorm(int dt, void* y, const void* x, const float* w, int ro
 // h_out  = T(h_in + d)                                    (sum in float)
 // n_out  = w_next ? T((h_out * inv(h_out)) * w_next)      (pre-norm of whatever runs next,
 //                                                          taken over the stored h_out)
-// h_out may alias h_in.  Row stays in shared memory as float between the passes.
-template <typename T>
-__global__ void add_norm_kernel(T* __restrict__ h_out, T* __restrict__ n_out,
-                                const T* __restrict__ m, const T* __restrict__ h_in,
-                                const float* __restrict__ w_post,
-                                const float* __restrict__ w_next, int H, float eps_post,
-                                float eps_next) {
-    extern __shared__ float row[];   // H floats
+// h_out may alias h_in.  The row stays in registers between the passes.
+template <typename T, int C>
+__global__ void __launch_bounds__(NV_THREADS)
+add_norm_kernel(T* __restrict__ h_out, T* __restrict__ n_out, const T* __restrict__ m,
+                const T* __restrict__ h_in, const float* __restrict__ w_post,
+                const float* __restrict__ w_next, int H, float eps_post, float eps_next) {
     __shared__ float scratch[32];
+    pdl_trigger();
+    float wp[C][8], wn[C][8], mv[C][8], hv[C][8];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int e = (c * NV_THREADS + threadIdx.x) * 8;
+        if (e < H) {
+            if (w_post) load8f<float>(w_post + e, wp[c]);
+            if (w_next) load8f<float>(w_next + e, wn[c]);
+        }
+    }
+    pdl_wait();
     const long long off = (long long)blockIdx.x * H;
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int e = (c * NV_THREADS + threadIdx.x) * 8;
+        if (e < H) {
+            load8f<T>(m + off + e, mv[c]);
+            load8f<T>(h_in + off + e, hv[c]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += mv[c][i] * mv[c][i];
+        }
+    }
     float inv_post = 1.f;
     if (w_post) {
-        float ss = 0.f;
-        for (int c = threadIdx.x; c < H; c += blockDim.x) {
-            const float v = to_f32(m[off + c]);
-            row[c] = v;
-            ss += v * v;
-        }
         ss = block_sum(ss, scratch);
         inv_post = 1.f / sqrtf(ss / (float)H + eps_post);
     }
     float ss2 = 0.f;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float d;
-        if (w_post)
-            d = rounded<T>((row[c] * inv_post) * w_post[c]);
-        else
-            d = to_f32(m[off + c]);
-        const float hn = rounded<T>(to_f32(h_in[off + c]) + d);
-        h_out[off + c] = from_f32<T>(hn);
-        row[c] = hn;
-        ss2 += hn * hn;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int e = (c * NV_THREADS + threadIdx.x) * 8;
+        if (e < H) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float d = w_post ? rounded<T>((mv[c][i] * inv_post) * wp[c][i]) : mv[c][i];
+                const float hn = rounded<T>(hv[c][i] + d);
+                hv[c][i] = hn;
+                ss2 += hn * hn;
+            }
+            store8f<T>(h_out + off + e, hv[c]);
+        }
     }
     if (!w_next) return;
     ss2 = block_sum(ss2, scratch);
     const float inv_next = 1.f / sqrtf(ss2 / (float)H + eps_next);
-    for (int c = threadIdx.x; c < H; c += blockDim.x)
-        n_out[off + c] = from_f32<T>((row[c] * inv_next) * w_next[c]);
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int e = (c * NV_THREADS + threadIdx.x) * 8;
+        if (e < H) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = (hv[c][i] * inv_next) * wn[c][i];
+            store8f<T>(n_out + off + e, o);
+        }
+    }
+}
+
+template <typename T>
+static int launch_add_norm(void* h_out, void* n_out, const void* m, const void* h_in, const float* w_post,
+                           const float* w_next, int rows, int H, float eps_post, float eps_next, cudaStream_t st) {
+    const int chunks = (H / 8 + NV_THREADS - 1) / NV_THREADS;
+    if (chunks <= 1)
+        cm_launch(add_norm_kernel<T, 1>, rows, NV_THREADS, 0, st, (T*)h_out, (T*)n_out, (const T*)m, (const T*)h_in,
+                  w_post, w_next, H, eps_post, eps_next);
+    else if (chunks <= 2)
+        cm_launch(add_norm_kernel<T, 2>, rows, NV_THREADS, 0, st, (T*)h_out, (T*)n_out, (const T*)m, (const T*)h_in,
+                  w_post, w_next, H, eps_post, eps_next);
+    else
+        cm_launch(add_norm_kernel<T, NV_MAXC>, rows, NV_THREADS, 0, st, (T*)h_out, (T*)n_out, (const T*)m,
+                  (const T*)h_in, w_post, w_next, H, eps_post, eps_next);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
 }
 
 extern "C" int cm_add_norm(int dt, void* h_out, void* n_out, const void* m, const void* h_in,
                            const float* w_post, const float* w_next, int rows, int H,
                            float eps_post, float eps_next, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
-    const size_t smem = (size_t)H * sizeof(float);
-    if (smem > 160 * 1024) CM_REFUSE("add_norm: hidden size %d needs %zu bytes of shared memory", H, smem);
-    const int threads = H >= 1024 ? 256 : 128;
-    if (dt == DT_F32) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_norm_kernel<float><<<rows, threads, smem, st>>>((float*)h_out, (float*)n_out, (const float*)m,
-                                                            (const float*)h_in, w_post, w_next, H,
-                                                            eps_post, eps_next);
-    } else if (dt == DT_BF16) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_norm_kernel<bf16><<<rows, threads, smem, st>>>((bf16*)h_out, (bf16*)n_out, (const bf16*)m,
-                                                           (const bf16*)h_in, w_post, w_next, H,
-                                                           eps_post, eps_next);
-    } else
-        return CM_ERR_DTYPE;
-    CM_CHECK_LAUNCH();
-    return CM_OK;
+    if (H % 8 || H > 8 * NV_THREADS * NV_MAXC)
+        CM_REFUSE("add_norm: width %d must be a multiple of 8, at most %d", H, 8 * NV_THREADS * NV_MAXC);
+    if (((uintptr_t)h_out | (uintptr_t)n_out | (uintptr_t)m | (uintptr_t)h_in | (uintptr_t)w_post | (uintptr_t)w_next) & 15)
+        CM_REFUSE("add_norm: operands must be 16-byte aligned");
+    if (dt == DT_F32)
+        return launch_add_norm<float>(h_out, n_out, m, h_in, w_post, w_next, rows, H, eps_post, eps_next, st);
+    if (dt == DT_BF16)
+        return launch_add_norm<bf16>(h_out, n_out, m, h_in, w_post, w_next, rows, H, eps_post, eps_next, st);
+    return CM_ERR_DTYPE;
 }
 
 // --------------------------------------------------------------------------- SwiGLU
 // a[t,f] = T((g * sigmoid(g)) * u), g = gu[t, f], u = gu[t, F + f]  (gate | up packed rows).
 template <typename T>
 __global__ void swiglu_kernel(T* __restrict__ a, const T* __restrict__ gu, long long total, int F) {
+    pdl_trigger();
+    pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long t = i / F;
@@ -154,9 +264,9 @@ extern "C" int cm_swiglu(int dt, void* a, const void* gu, int rows, int F, cudaS
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dt == DT_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, st>>>((float*)a, (const float*)gu, total, F);
+        cm_launch(swiglu_kernel<float>, blocks, threads, 0, st, (float*)a, (const float*)gu, total, F);
     else if (dt == DT_BF16)
-        swiglu_kernel<bf16><<<blocks, threads, 0, st>>>((bf16*)a, (const bf16*)gu, total, F);
+        cm_launch(swiglu_kernel<bf16>, blocks, threads, 0, st, (bf16*)a, (const bf16*)gu, total, F);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
@@ -167,6 +277,8 @@ extern "C" int cm_swiglu(int dt, void* a, const void* gu, int rows, int F, cudaS
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x,
                                    const int* __restrict__ rows, int H) {
+    pdl_trigger();
+    pdl_wait();
     const T* src = x + (long long)rows[blockIdx.x] * H;
     T* dst = out + (long long)blockIdx.x * H;
     for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = src[c];
@@ -176,9 +288,9 @@ extern "C" int cm_gather_rows(int dt, void* out, const void* x, const int* rows,
                               cudaStream_t st) {
     if (n <= 0) return CM_OK;
     if (dt == DT_F32)
-        gather_rows_kernel<float><<<n, 128, 0, st>>>((float*)out, (const float*)x, rows, H);
+        cm_launch(gather_rows_kernel<float>, n, 128, 0, st, (float*)out, (const float*)x, rows, H);
     else if (dt == DT_BF16)
-        gather_rows_kernel<bf16><<<n, 128, 0, st>>>((bf16*)out, (const bf16*)x, rows, H);
+        cm_launch(gather_rows_kernel<bf16>, n, 128, 0, st, (bf16*)out, (const bf16*)x, rows, H);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();

@@ -14,13 +14,21 @@ void cm_set_error(const char* fmt, ...) {
 
 extern "C" const char* cm_last_error() { return g_last_error; }
 
-extern "C" int cm_abi_version() { return 1; }
+extern "C" int cm_abi_version() { return 2; }
+
+static int g_pdl = 1;
+int cm_pdl_enabled() { return g_pdl; }
+// 1 (default): kernels are launched so that the next one may start while they run (see
+// common.cuh); 0: plain stream order.
+extern "C" void cm_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 // table[index[i]] = value[i] for i < *count (count lives on the device so that a captured
 // graph can carry a different number of page-table updates on every replay).
 __global__ void scatter_i32_kernel(int* __restrict__ table, const int* __restrict__ index,
                                    const int* __restrict__ value, const int* __restrict__ count,
                                    int max_count) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int n = min(*count, max_count);
     if (i < n) table[index[i]] = value[i];
@@ -29,20 +37,22 @@ __global__ void scatter_i32_kernel(int* __restrict__ table, const int* __restric
 extern "C" int cm_scatter_i32(int* table, const int* index, const int* value, const int* count,
                               int max_count, cudaStream_t st) {
     if (max_count <= 0) return CM_OK;
-    scatter_i32_kernel<<<(max_count + 127) / 128, 128, 0, st>>>(table, index, value, count, max_count);
+    cm_launch(scatter_i32_kernel, (max_count + 127) / 128, 128, 0, st, table, index, value, count, max_count);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
 
 // x[rows[i], :] = 0 for float rows of `width` elements (fixed-size state of admitted slots).
 __global__ void zero_rows_kernel(float* __restrict__ x, const int* __restrict__ rows, long long width) {
+    pdl_trigger();
+    pdl_wait();
     float* dst = x + (long long)rows[blockIdx.x] * width;
     for (long long c = threadIdx.x; c < width; c += blockDim.x) dst[c] = 0.f;
 }
 
 extern "C" int cm_zero_rows_f32(float* x, const int* rows, int n, long long width, cudaStream_t st) {
     if (n <= 0 || width <= 0) return CM_OK;
-    zero_rows_kernel<<<n, 256, 0, st>>>(x, rows, width);
+    cm_launch(zero_rows_kernel, n, 256, 0, st, x, rows, width);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }

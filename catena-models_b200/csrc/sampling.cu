@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(SM_THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long ld, int V,
               const float* __restrict__ temperature, const int* __restrict__ sequence,
               const int* __restrict__ step, const int* __restrict__ seed_words) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sval[SM_THREADS];
     __shared__ int sidx[SM_THREADS];
     __shared__ float scratch[32];
@@ -114,7 +116,7 @@ extern "C" int cm_sample(int* out, const float* logits, long long ld, int n, int
                          const int* seed_words, cudaStream_t st) {
     if (n <= 0) return CM_OK;
     if (V <= 0) CM_REFUSE("sample: vocabulary of %d", V);
-    sample_kernel<<<n, SM_THREADS, 0, st>>>(out, logits, ld, V, temperature, sequence, step, seed_words);
+    cm_launch(sample_kernel, n, SM_THREADS, 0, st, out, logits, ld, V, temperature, sequence, step, seed_words);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }

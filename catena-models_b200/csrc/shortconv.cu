@@ -15,6 +15,8 @@ __global__ void shortconv_kernel(T* __restrict__ y, const T* __restrict__ bcx, l
                                  const float* __restrict__ w, float* __restrict__ state,
                                  const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
                                  const int* __restrict__ seq_slot, int H, int K, int from_zero) {
+    pdl_trigger();
+    pdl_wait();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int t = blockIdx.y;
     if (c >= H) return;
@@ -67,10 +69,10 @@ extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, cons
         CM_REFUSE("shortconv: several tokens of a sequence on top of a stored state are not supported");
     dim3 grid((H + 127) / 128, T);
     if (dt == DT_F32)
-        shortconv_kernel<float><<<grid, 128, 0, st>>>((float*)y, (const float*)bcx, ld, w, state, tok_seq,
+        cm_launch(shortconv_kernel<float>, grid, 128, 0, st, (float*)y, (const float*)bcx, ld, w, state, tok_seq,
                                                       seq_start, seq_slot, H, K, from_zero);
     else if (dt == DT_BF16)
-        shortconv_kernel<bf16><<<grid, 128, 0, st>>>((bf16*)y, (const bf16*)bcx, ld, w, state, tok_seq,
+        cm_launch(shortconv_kernel<bf16>, grid, 128, 0, st, (bf16*)y, (const bf16*)bcx, ld, w, state, tok_seq,
                                                      seq_start, seq_slot, H, K, from_zero);
     else
         return CM_ERR_DTYPE;

@@ -7,6 +7,7 @@ cannot be built or loaded, importing a kernel raises.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -55,8 +56,18 @@ def lib():
             fn = getattr(handle, name)
             fn.argtypes = args
             fn.restype = _i
+        handle.cm_set_pdl.argtypes = [_i]
+        handle.cm_set_pdl.restype = None
+        if os.environ.get("CATENA_B200_PDL", "1") == "0":
+            handle.cm_set_pdl(0)
         _lib = handle
     return _lib
+
+
+def set_pdl(on):
+    """Programmatic dependent launch for every kernel of the library (on by default; the
+    environment variable CATENA_B200_PDL=0 turns it off at load)."""
+    lib().cm_set_pdl(1 if on else 0)
 
 
 def library_path():
