@@ -1,0 +1,352 @@
+// C[M,N] = A[M,K] * B[N,K]^T in bfloat16 on the 5th-generation tensor cores (prompt steps).
+//
+// One block computes a 128 x BLOCK_N tile of C.  Roles (one warp each, six warps):
+//   warp 0  one thread: TMA loads of the A and B k-slices (128 x 64 and BLOCK_N x 64 bf16,
+//           128-byte swizzle) into a ring of STAGES shared-memory stages;
+//   warp 1  allocates the tensor-memory columns of the accumulator; one thread issues
+//           tcgen05.mma (128 x BLOCK_N x 16 per instruction, float accumulation in tensor
+//           memory) and commits each stage back to the loader and the finished tile to the
+//           epilogue through mbarriers;
+//   warps 2-5  epilogue: tcgen05.ld of the accumulator (a warp reaches the 32 lanes
+//           32*(warp%4)..), conversion, bounds-checked stores to C.
+// Rows or columns beyond M, N, K are zero-filled by TMA on load and masked on store, so any
+// M and N and any K that is a multiple of 8 (16-byte row pitch) is taken.
+//
+// MODE_SWIGLU: B is the row-packed [Wgate; Wup] with 2N rows; the B stage is two 64-row boxes
+// (gate rows n0.., up rows N+n0..), so columns 0-63 of the accumulator are g and 64-127 are u,
+// and the epilogue stores C = T(silu(T(g)) * T(u)) (catena-models' fused gate epilogue,
+// src/catena/lfm3_wmma.hex:10790-10815).
+//
+// Every wait on an mbarrier is bounded.  A wait that runs out raises *err, every role leaves
+// its loop, copies still in flight are awaited (bounded again), tensor memory is freed and the
+// block returns.
+#include "common.cuh"
+#include <cuda.h>
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_MODE_PLAIN 0
+#define TC_MODE_SWIGLU 1
+#define TC_SPIN_LIMIT (1 << 24)
+
+#define TC_ERR_TIMEOUT_LOAD 101
+#define TC_ERR_TIMEOUT_MMA 102
+#define TC_ERR_TIMEOUT_EPILOGUE 103
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Waits for the phase of `parity` to complete.  Gives up after TC_SPIN_LIMIT polls or when
+// another role has raised *abort; on its own timeout it raises *abort and *err itself.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, int* err, int code) {
+    for (int i = 0; i < TC_SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255) == 255 && *abort) return false;
+    }
+    *abort = 1;
+    if (err) atomicCAS(err, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle:
+// 8-row groups 1024 bytes apart (SBO), descriptor version 1 (sm_100), layout type 2.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <typename TC>
+__device__ __forceinline__ void store_cols(TC* dst, const float* v, int n_valid, bool aligned);
+template <>
+__device__ __forceinline__ void store_cols<bf16>(bf16* dst, const float* v, int n_valid, bool aligned) {
+    if (n_valid >= 32 && aligned) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 raw;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+            *reinterpret_cast<uint4*>(dst + 8 * i) = raw;
+        }
+    } else {
+        for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+    }
+}
+template <>
+__device__ __forceinline__ void store_cols<float>(float* dst, const float* v, int n_valid, bool aligned) {
+    if (n_valid >= 32 && aligned) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+        for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = v[i];
+    }
+}
+
+template <int BLOCK_N, int STAGES, typename TC, int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               TC* __restrict__ C, int M, int N, int K, long long ldc, int* err) {
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
+    constexpr uint32_t B_BYTES = BLOCK_N * TC_BK * 2;
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bars[2 * STAGES + 1];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ int issued_kb;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM;
+    const int n0 = blockIdx.x * (MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N);   // first output column
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;                    // swizzle atoms need 1024-byte alignment
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), done = smem_u32(&bars[2 * STAGES]);
+
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(done, 1);
+        abort_flag = 0;
+        issued_kb = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"((uint32_t)BLOCK_N)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    pdl_wait();                                   // A is the previous kernel's output
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------- TMA loader
+        for (int kb = 0; kb < num_kb; ++kb) {
+            const int s = kb % STAGES;
+            const uint32_t ph = (kb / STAGES) & 1;
+            if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, err, TC_ERR_TIMEOUT_LOAD)) break;
+            const uint32_t a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+            tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * TC_BK, m0);
+            if (MODE == TC_MODE_SWIGLU) {
+                tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, n0);
+                tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * TC_BK, N + n0);
+            } else {
+                tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, n0);
+            }
+            issued_kb = kb + 1;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------- MMA issuer
+        // instruction descriptor: float accumulator, bf16 A and B, both K-major, N/8 and M/16
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_N >> 3) << 17) |
+                                   ((uint32_t)(TC_BM >> 4) << 24);
+        bool ok = true;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+            const int s = kb % STAGES;
+            const uint32_t ph = (kb / STAGES) & 1;
+            ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, err, TC_ERR_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t adesc = umma_desc(tiles + s * STAGE_BYTES);
+            const uint64_t bdesc = umma_desc(tiles + s * STAGE_BYTES + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k)          // 16 values of k = 32 bytes further in the row
+                umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+            umma_commit(empty0 + 8 * s);                  // stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(done);                        // accumulator complete
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------- epilogue
+        const int q = warp & 3;                           // tensor-memory lane quarter of this warp
+        const int row = m0 + q * 32 + lane;
+        if (mbar_wait(done, 0, &abort_flag, err, TC_ERR_TIMEOUT_EPILOGUE)) {
+            tc_fence_after();
+            const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+            constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+#pragma unroll 1
+            for (int c = 0; c < OUT_COLS / 32; ++c) {
+                float v[32];
+                tmem_load32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+                if (MODE == TC_MODE_SWIGLU) {
+                    float u[32];
+                    tmem_load32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(OUT_COLS + c * 32), u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float g = rounded<TC>(v[i]), uu = rounded<TC>(u[i]);
+                        v[i] = (g * sigmoid_f32(g)) * uu;
+                    }
+                }
+                const int col = n0 + c * 32;
+                if (row < M && col < N) store_cols<TC>(C + (long long)row * ldc + col, v, N - col, vec_ok);
+            }
+        }
+    }
+    // ------------------------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag && threadIdx.x == 0) {
+        // copies that were issued but never consumed must land before shared memory is given up
+        const int issued = issued_kb;
+        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+            const int s = kb % STAGES;
+            for (int i = 0; i < TC_SPIN_LIMIT; ++i)
+                if (mbar_try_wait(full0 + 8 * s, (kb / STAGES) & 1)) break;
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BLOCK_N)
+                     : "memory");
+    }
+}
+
+// --------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with row pitch ld (elements): boxes of
+// box_rows x 64 columns, 128-byte swizzle, zero fill outside.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        cm_set_error("gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+        return CM_ERR_DRIVER;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        cm_set_error("gemm_tc: tensor map for [%lld, %lld] pitch %lld refused (CUresult %d)", rows, cols, ld, (int)r);
+        return CM_ERR_DRIVER;
+    }
+    return CM_OK;
+}
+
+template <int BLOCK_N, int STAGES, typename TC, int MODE>
+static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                     long long ldc, int* err, cudaStream_t st) {
+    CUtensorMap map_a, map_b;
+    const long long b_rows = MODE == TC_MODE_SWIGLU ? 2LL * N : N;
+    const int b_box = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+    int rc = make_map(&map_a, A, M, K, lda, TC_BM);
+    if (rc != CM_OK) return rc;
+    rc = make_map(&map_b, B, b_rows, K, ldb, b_box);
+    if (rc != CM_OK) return rc;
+    constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+    const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BLOCK_N * TC_BK * 2) + 1024;
+    auto kernel = gemm_tc_kernel<BLOCK_N, STAGES, TC, MODE>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cm_set_error("gemm_tc: %zu bytes of shared memory refused", smem);
+            cudaGetLastError();
+            return CM_ERR_LAUNCH;
+        }
+        configured = true;
+    }
+    dim3 grid((N + OUT_COLS - 1) / OUT_COLS, (M + TC_BM - 1) / TC_BM);
+    cm_launch(kernel, grid, TC_THREADS, smem, st, map_a, map_b, (TC*)C, M, N, K, ldc, err);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// A [M,K] and B [N,K] (2N rows when swiglu) bfloat16, row pitches lda/ldb multiples of 8
+// elements, bases 16-byte aligned; C bfloat16 or float.  err: device int, raised by a block
+// whose pipeline wait ran out (0 otherwise); may be null.
+extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M, int N, int K, long long lda,
+                          long long ldb, long long ldc, int swiglu, int* err, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return CM_OK;
+    if (K <= 0 || K % 8 || lda % 8 || ldb % 8)
+        CM_REFUSE("gemm_tc: inner size %d and row pitches %lld, %lld must be multiples of 8", K, lda, ldb);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15)
+        CM_REFUSE("gemm_tc: operands must be 16-byte aligned");
+    if (swiglu) {
+        if (dtc != DT_BF16) return CM_ERR_DTYPE;
+        return launch_tc<128, 6, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
+    }
+    if (dtc == DT_BF16) return launch_tc<128, 6, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
+    if (dtc == DT_F32) return launch_tc<128, 6, float, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
+    return CM_ERR_DTYPE;
+}

@@ -23,6 +23,18 @@ class Runtime:
         kernels.lib()                       # build and load now: fail loudly before any model work
         self._scratch = {}
         self._retired = []
+        # raised by a kernel whose bounded pipeline wait ran out (0 otherwise); see check_errors
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def check_errors(self):
+        """Read the device error flag (synchronises); raises if a kernel gave up on a wait."""
+        code = int(self.error_flag.item())
+        if code:
+            self.error_flag.zero_()
+            raise RuntimeError(f"a kernel's pipeline wait ran out (code {code}); its output is not valid")
+
+    def _unused(self):
+        pass
 
     # ------------------------------------------------------------------ scratch
     def scratch(self, key, numel, dtype=torch.float32):
@@ -47,9 +59,16 @@ class Runtime:
         y = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
         if self._skinny(x, w):
             kernels.gemm_skinny(y, x, w)
+        elif self._tensor_core(x, w):
+            kernels.gemm_tc(y, x, w, err=self.error_flag)
         else:
             kernels.gemm_simt(y, x, w)
         return y
+
+    def _tensor_core(self, x, w):
+        """Many bfloat16 rows: the TMA-fed tcgen05 kernel (prompt steps)."""
+        return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+                and x.stride(0) % 8 == 0 and x.stride(1) == 1 and x.data_ptr() % 16 == 0 and w.stride(0) % 8 == 0)
 
     SKINNY_ROWS = 64
 
@@ -63,6 +82,9 @@ class Runtime:
         a = torch.empty((x.shape[0], F), dtype=x.dtype, device=x.device)
         if self._skinny(x, w_gate_up):
             kernels.gemm_skinny(a, x, w_gate_up, swiglu=True)
+            return a
+        if self._tensor_core(x, w_gate_up):
+            kernels.gemm_tc(a, x, w_gate_up, swiglu=True, err=self.error_flag)
             return a
         gu = self.linear(x, w_gate_up)
         kernels.swiglu(a, gu)

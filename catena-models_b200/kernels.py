@@ -27,6 +27,7 @@ _SIGNATURES = {
     "cm_gather_rows": [_i, _vp, _vp, _vp, _i, _i, _vp],
     "cm_gemm_simt": [_i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
     "cm_gemm_skinny": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp],
+    "cm_gemm_tc": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp],
     "cm_qk_prepare": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i,
                       _i, _f, _vp],
     "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
@@ -164,6 +165,23 @@ def gemm_skinny(y, x, w, swiglu=False):
         raise KernelError("gemm_skinny takes bfloat16 operands")
     _check(lib().cm_gemm_skinny(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
                                 y.stride(0), int(swiglu), _stream()), "gemm_skinny")
+
+
+def gemm_tc(y, x, w, swiglu=False, err=None):
+    """y = x @ w^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory), any
+    number of bfloat16 rows.  swiglu: w is [gate; up] with 2F rows and y[M, F] = silu(g) * u.
+    err: device int32 that a block raises if one of its bounded pipeline waits runs out."""
+    _need_cuda(y, x, w)
+    M, K = x.shape
+    N = y.shape[1]
+    if w.shape[1] != K or w.shape[0] != (2 * N if swiglu else N) or y.shape[0] != M:
+        raise KernelError(f"gemm_tc shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc takes bfloat16 operands")
+    if x.stride(1) != 1 or w.stride(1) != 1 or y.stride(1) != 1:
+        raise KernelError("gemm_tc takes row-major operands")
+    _check(lib().cm_gemm_tc(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
+                            y.stride(0), int(swiglu), _ptr(err), _stream()), "gemm_tc")
 
 
 # -------------------------------------------------------------------------- attention

@@ -407,3 +407,44 @@ def test_refusals_are_errors_not_wrong_results(K):
                       torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV))
     with pytest.raises(K.KernelError):
         K.rmsnorm(torch.empty(2, 4), torch.empty(2, 4), torch.ones(4), 1e-5)     # CPU tensors
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 128, 64), (100, 70, 72), (1, 8, 8), (257, 384, 520), (2048, 2048, 2048),
+                                     (65, 3104, 2048), (300, 200, 1000)])
+@pytest.mark.parametrize("dty", [torch.bfloat16, torch.float32])
+def test_gemm_tc(K, M, N, Kd, dty):
+    """tcgen05/TMA GEMM: shapes that fill no tile in any dimension, K with a ragged last k-slice."""
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=1), rnd(N, Kd, dtype=torch.bfloat16, scale=0.1, seed=2)
+    y = torch.full((M, N), float("nan"), dtype=dty, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.gemm_tc(y, x, w, err=err)
+    ref = x.double() @ w.double().T
+    assert int(err) == 0
+    if dty == torch.float32:
+        torch.testing.assert_close(y.double().cpu(), ref.cpu(), rtol=2e-5, atol=2e-5 * math.sqrt(Kd))
+    else:
+        close(y, ref, torch.bfloat16)
+
+
+@pytest.mark.parametrize("M,F,Kd", [(128, 64, 64), (200, 136, 520), (70, 1000, 264)])
+def test_gemm_tc_swiglu(K, M, F, Kd):
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=1), rnd(2 * F, Kd, dtype=torch.bfloat16, scale=0.2, seed=2)
+    a = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.gemm_tc(a, x, w, swiglu=True, err=err)
+    g = (x.double() @ w[:F].double().T).to(torch.bfloat16).double()
+    u = (x.double() @ w[F:].double().T).to(torch.bfloat16).double()
+    assert int(err) == 0
+    close(a, g / (1 + torch.exp(-g)) * u, torch.bfloat16, rtol=2e-2)
+
+
+def test_gemm_tc_strided_operands(K):
+    """A is a column block of a wider buffer (the attention context inside qkv-sized rows)."""
+    buf = rnd(150, 96 + 40, dtype=torch.bfloat16, seed=3)
+    x = buf[:, 8:8 + 96]
+    w = rnd(50, 96, dtype=torch.bfloat16, scale=0.1, seed=4)
+    ybuf = torch.zeros(150, 64, dtype=torch.bfloat16, device=DEV)
+    y = ybuf[:, :50]
+    K.gemm_tc(y, x, w)
+    close(y, x.double() @ w.double().T, torch.bfloat16)
+    assert float(ybuf[:, 50:].abs().sum()) == 0.0
