@@ -1,0 +1,249 @@
+// Prefill attention on the tensor cores (bfloat16, head sizes that are multiples of 16 up to
+// 128): online-softmax attention over the step's own keys and values with causal or sliding
+// mask, grouped-query heads, unequal sequence lengths and the per-head sigmoid gate.
+//
+// One block = 64 queries of one head of one sequence, 4 warps of 16 query rows.  Keys and
+// values come in tiles of 64 through a two-stage cp.async ring in shared memory (rows padded
+// by 16 bytes so that ldmatrix reads without bank conflicts).  S = Q K^T and O += P V run on
+// mma.sync.m16n8k16 with float accumulation; the score accumulators are re-used as the
+// probability operand of the second product.  Maximum, sum, rescaling and the final division
+// are float; exp is taken as exp2 of log2(e)-prescaled scores.
+#include "common.cuh"
+#include <math.h>
+
+#define FA_BQ 64
+#define FA_BK 64
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = valid ? 16 : 0;                 // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128)
+attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __restrict__ q,
+                        const bf16* __restrict__ k, const bf16* __restrict__ v, long long ld,
+                        const bf16* __restrict__ gate, long long ldg, const int* __restrict__ seq_start, int QH,
+                        int KVH, int window, float scale_log2) {
+    constexpr int LDS = HD + 8;                   // padded row, elements
+    constexpr int CH = HD / 8;                    // 16-byte chunks per row
+    extern __shared__ __align__(16) uint8_t fa_smem[];
+    bf16* Qs = reinterpret_cast<bf16*>(fa_smem);              // [FA_BQ][LDS]
+    bf16* Ks = Qs + FA_BQ * LDS;                              // [2][FA_BK][LDS]
+    bf16* Vs = Ks + 2 * FA_BK * LDS;                          // [2][FA_BK][LDS]
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.z, hq = blockIdx.y, hk = hq / (QH / KVH);
+    const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
+    const int q0 = (gridDim.x - 1 - blockIdx.x) * FA_BQ;      // long rows first
+    if (q0 >= len) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+
+    const int kt_begin = window > 0 ? max(0, q0 - window + 1) / FA_BK : 0;
+    const int kt_end = min(q0 + FA_BQ - 1, len - 1) / FA_BK;  // inclusive
+
+    auto load_tile = [&](bf16* dst, const bf16* src, int row0) {
+        for (int e = tid; e < FA_BK * CH; e += 128) {
+            const int r = e / CH, c = e - r * CH;
+            const bool in = row0 + r < len;
+            const long long row = (long long)(s0 + (in ? row0 + r : 0));
+            cp_async16(dst + r * LDS + c * 8, src + row * ld + c * 8, in);
+        }
+    };
+    load_tile(Qs, q + (long long)hq * HD, q0);
+    cp_async_commit();
+    load_tile(Ks, k + (long long)hk * HD, kt_begin * FA_BK);
+    load_tile(Vs, v + (long long)hk * HD, kt_begin * FA_BK);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    // Q fragments of this warp's 16 rows
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk)
+        ldmatrix_x4(qf[kk], Qs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int row_lo = q0 + warp * 16 + g;        // this thread's rows: row_lo and row_lo + 8
+
+    for (int kt = kt_begin; kt <= kt_end; ++kt) {
+        const int buf = (kt - kt_begin) & 1;
+        if (kt + 1 <= kt_end) {
+            load_tile(Ks + (buf ^ 1) * FA_BK * LDS, k + (long long)hk * HD, (kt + 1) * FA_BK);
+            load_tile(Vs + (buf ^ 1) * FA_BK * LDS, v + (long long)hk * HD, (kt + 1) * FA_BK);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* Kt = Ks + buf * FA_BK * LDS;
+        const bf16* Vt = Vs + buf * FA_BK * LDS;
+
+        // ---- S = Q K^T : 16 x 64 per warp, 8 tiles of 8 keys
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {      // key tiles 2jp, 2jp+1
+                uint32_t kb[4];
+                ldmatrix_x4(kb, Kt + (jp * 16 + (lane & 7) + 8 * (lane >> 4)) * LDS + kk * 16 + 8 * ((lane >> 3) & 1));
+                mma16816(s[2 * jp], qf[kk], kb[0], kb[1]);
+                mma16816(s[2 * jp + 1], qf[kk], kb[2], kb[3]);
+            }
+        }
+        // ---- mask, running maximum
+        const int key0 = kt * FA_BK;
+        const bool edge = key0 + FA_BK - 1 > q0 + warp * 16 || key0 + FA_BK > len ||
+                          (window > 0 && key0 + window <= q0 + warp * 16 + 15);
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float x = s[j][i] * scale_log2;
+                if (edge) {
+                    const int key = key0 + 8 * j + 2 * t + (i & 1);
+                    const int row = row_lo + (i >> 1) * 8;
+                    const bool vis = key <= row && key < len && (window <= 0 || key + window > row);
+                    x = vis ? x : -INFINITY;
+                }
+                s[j][i] = x;
+                mx[i >> 1] = fmaxf(mx[i >> 1], x);
+            }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m_run[h], mx[h]);
+            m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+            alpha[h] = exp2f(m_run[h] - m_use[h]);            // exp2(-inf) = 0 on the first visible tile
+            m_run[h] = m_new;
+        }
+        float rs[2] = {0.f, 0.f};
+        uint32_t pf[4][4];                                     // P as the A operand, 4 steps of 16 keys
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
+            const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+            rs[0] += p0 + p1;
+            rs[1] += p2 + p3;
+            pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);       // rows g
+            pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);   // rows g + 8
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * alpha[h] + rs[h];
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) {
+            o[j][0] *= alpha[0];
+            o[j][1] *= alpha[0];
+            o[j][2] *= alpha[1];
+            o[j][3] *= alpha[1];
+        }
+        // ---- O += P V
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {                       // keys 16kk .. 16kk+15
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {             // channel tiles 2dp, 2dp+1
+                uint32_t vb[4];
+                ldmatrix_x4_trans(vb, Vt + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+                mma16816(o[2 * dp], pf[kk], vb[0], vb[1]);
+                mma16816(o[2 * dp + 1], pf[kk], vb[2], vb[3]);
+            }
+        }
+        __syncthreads();                                       // the other buffer is refilled next round
+    }
+    cp_async_wait<0>();
+
+    // ---- normalise, gate, store
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = row_lo + 8 * h;
+        if (row >= len) continue;
+        const long long tok = s0 + row;
+        float f = 1.f / l_run[h];
+        if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + hq]));
+        bf16* dst = ctx + tok * ldc + (long long)hq * HD;
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j)
+            *reinterpret_cast<uint32_t*>(dst + 8 * j + 2 * t) = pack_bf16(o[j][2 * h] * f, o[j][2 * h + 1] * f);
+    }
+}
+
+template <int HD>
+static int launch_fa(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
+                     const void* gate, long long ldg, const int* seq_start, int B, int max_len, int QH, int KVH,
+                     int window, float scale, cudaStream_t st) {
+    const size_t smem = (size_t)(FA_BQ + 4 * FA_BK) * (HD + 8) * sizeof(bf16);
+    auto kernel = attn_prefill_mma_kernel<HD>;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            CM_REFUSE("attn_prefill_mma: %zu bytes of shared memory refused", smem);
+        }
+        configured = true;
+    }
+    dim3 grid((max_len + FA_BQ - 1) / FA_BQ, QH, B);
+    cm_launch(kernel, grid, 128, smem, st, (bf16*)ctx, ldc, (const bf16*)q, (const bf16*)k, (const bf16*)v, ld,
+              (const bf16*)gate, ldg, seq_start, QH, KVH, window, scale * 1.4426950408889634f);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// bfloat16 only; head size a multiple of 16 up to 128; q, k, v column blocks of one row-major
+// buffer with a row pitch that is a multiple of 8 elements and 16-byte aligned bases.
+extern "C" int cm_attn_prefill_mma(void* ctx, long long ldc, const void* q, const void* k, const void* v,
+                                   long long ld, const void* gate, long long ldg, const int* seq_start, int B,
+                                   int max_len, int QH, int KVH, int HD, int window, float scale, cudaStream_t st) {
+    if (B <= 0 || max_len <= 0) return CM_OK;
+    if (QH % KVH) CM_REFUSE("attn_prefill_mma: %d query heads over %d key heads", QH, KVH);
+    if (ld % 8 || ldc % 2 || ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15 || (uintptr_t)ctx & 3)
+        CM_REFUSE("attn_prefill_mma: row pitch %lld must be a multiple of 8 and the operands 16-byte aligned", ld);
+#define FA_CASE(D) \
+    case D: return launch_fa<D>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, window, scale, st);
+    switch (HD) {
+        FA_CASE(16) FA_CASE(32) FA_CASE(48) FA_CASE(64) FA_CASE(80) FA_CASE(96) FA_CASE(112) FA_CASE(128)
+        default: CM_REFUSE("attn_prefill_mma: head size %d (multiples of 16 up to 128)", HD);
+    }
+#undef FA_CASE
+}

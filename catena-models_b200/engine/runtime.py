@@ -92,5 +92,7 @@ class Runtime:
 
     # ------------------------------------------------------------------ attention
     def attention_prefill(self, ctx, q, k, v, gate, batch, QH, KVH, HD, window, scale):
-        kernels.attn_prefill_simt(ctx, q, k, v, gate, batch.seq_start, batch.B, batch.max_len, QH, KVH, HD,
-                                  window, scale)
+        tensor_cores = (q.dtype == torch.bfloat16 and HD % 16 == 0 and HD <= 128 and q.stride(0) % 8 == 0
+                        and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
+        fn = kernels.attn_prefill_mma if tensor_cores else kernels.attn_prefill_simt
+        fn(ctx, q, k, v, gate, batch.seq_start, batch.B, batch.max_len, QH, KVH, HD, window, scale)

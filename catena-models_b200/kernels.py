@@ -31,6 +31,7 @@ _SIGNATURES = {
     "cm_qk_prepare": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i,
                       _i, _f, _vp],
     "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "cm_attn_prefill_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "cm_attn_decode": [_i, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _i,
                        _i, _f, _vp, _vp, _vp],
     "cm_shortconv": [_i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
@@ -204,6 +205,15 @@ def attn_prefill_simt(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, wi
                                       q.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0),
                                       _ptr(seq_start), B, max_len, QH, KVH, HD, window, scale, _stream()),
            "attn_prefill_simt")
+
+
+def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale):
+    """The same on the tensor cores: bfloat16, head sizes that are multiples of 16 up to 128."""
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.dtype != torch.bfloat16:
+        raise KernelError("attn_prefill_mma: bfloat16 q, k and v that share a row stride")
+    _check(lib().cm_attn_prefill_mma(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
+                                     0 if gate is None else gate.stride(0), _ptr(seq_start), B, max_len, QH, KVH,
+                                     HD, window, scale, _stream()), "attn_prefill_mma")
 
 
 def attn_decode_scratch(B, QH, HD, n_chunks, device):

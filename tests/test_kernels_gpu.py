@@ -172,21 +172,28 @@ def _ref_attention(q, k, v, window, scale, gate=None):
     return out
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype,impl", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma")])
 @pytest.mark.parametrize("QH,KVH,HD,window,gated", [(4, 2, 16, 0, True), (6, 1, 24, 5, False), (2, 2, 128, 40, True),
-                                                    (3, 3, 256, 0, False), (8, 2, 64, 256, True)])
-def test_attn_prefill_varlen(K, dtype, QH, KVH, HD, window, gated):
+                                                    (3, 3, 256, 0, False), (8, 2, 64, 256, True), (4, 4, 48, 70, True),
+                                                    (2, 1, 112, 0, False)])
+def test_attn_prefill_varlen(K, dtype, impl, QH, KVH, HD, window, gated):
+    if impl == "mma" and (HD % 16 or HD > 128):
+        with pytest.raises(K.KernelError):                              # refused, not computed wrongly
+            K.attn_prefill_mma(torch.empty(1, QH * HD, dtype=dtype, device=DEV), *(torch.empty(1, QH * HD, dtype=dtype, device=DEV),) * 3,
+                               None, torch.zeros(2, dtype=torch.int32, device=DEV), 1, 1, QH, KVH, HD, window, 1.0)
+        return
     lens = [17, 65, 1, 100]
     T = sum(lens)
-    width = QH * HD + 2 * KVH * HD + (QH if gated else 0)
+    width = (QH * HD + 2 * KVH * HD + (QH if gated else 0) + 7) // 8 * 8
     buf = rnd(T, width, dtype=dtype, seed=HD)
     q, k = buf[:, :QH * HD], buf[:, QH * HD:QH * HD + KVH * HD]
     v = buf[:, QH * HD + KVH * HD:QH * HD + 2 * KVH * HD]
-    gate = buf[:, QH * HD + 2 * KVH * HD:] if gated else None
+    gate = buf[:, QH * HD + 2 * KVH * HD:QH * HD + 2 * KVH * HD + QH] if gated else None
     starts = torch.tensor([0, 17, 82, 83, 183], dtype=torch.int32, device=DEV)
     ctx = torch.full((T, QH * HD), float("nan"), dtype=dtype, device=DEV)
     scale = HD ** -0.5
-    K.attn_prefill_simt(ctx, q, k, v, gate, starts, len(lens), max(lens), QH, KVH, HD, window, scale)
+    fn = K.attn_prefill_mma if impl == "mma" else K.attn_prefill_simt
+    fn(ctx, q, k, v, gate, starts, len(lens), max(lens), QH, KVH, HD, window, scale)
     off = 0
     for n in lens:
         sl = slice(off, off + n)
@@ -448,3 +455,26 @@ def test_gemm_tc_strided_operands(K):
     K.gemm_tc(y, x, w)
     close(y, x.double() @ w.double().T, torch.bfloat16)
     assert float(ybuf[:, 50:].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("window", [0, 100])
+def test_attn_prefill_mma_long_and_window_edge(K, window):
+    """700 queries (many key tiles, first and last tiles ragged); one key is made to dominate and
+    must be seen by exactly the queries whose window holds it."""
+    QH, KVH, HD, T = 2, 1, 64, 700
+    buf = rnd(T, QH * HD + 2 * KVH * HD, dtype=torch.bfloat16, scale=0.3, seed=11)
+    far = 250
+    buf[far, QH * HD:QH * HD + HD] = 0
+    buf[far, QH * HD] = 30.0                       # the key
+    buf[:, 0] = 30.0                               # every query of head 0 looks for it
+    q, k, v = buf[:, :QH * HD], buf[:, QH * HD:QH * HD + HD], buf[:, QH * HD + HD:]
+    starts = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    ctx = torch.empty(T, QH * HD, dtype=torch.bfloat16, device=DEV)
+    K.attn_prefill_mma(ctx, q, k, v, None, starts, 1, T, QH, KVH, HD, window, HD ** -0.5)
+    ref = _ref_attention(q.cpu().view(T, QH, HD), k.cpu().view(T, KVH, HD), v.cpu().view(T, KVH, HD), window, HD ** -0.5)
+    close(ctx.view(T, QH, HD), ref, torch.bfloat16)
+    hit = (ctx.view(T, QH, HD)[:, 0].float() - v[far].float()).abs().max(dim=-1).values < 0.05
+    expect = torch.arange(T, device=DEV) >= far
+    if window:
+        expect &= torch.arange(T, device=DEV) < far + window
+    assert torch.equal(hit, expect)
