@@ -493,3 +493,62 @@ extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, l
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
+
+// =========================================================================================
+// The same decode attention for callers that cannot allocate (see attention_noalloc.h).
+// The per-chunk partial results live in this file-scope device array instead of in buffers
+// the caller provides.  In host code `noalloc_scratch` is only a handle for the runtime, not
+// a device address: the address a kernel can use comes from cudaGetSymbolAddress, looked up
+// once per device with that device current.
+// =========================================================================================
+#include "attention_noalloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float noalloc_scratch[CM_NOALLOC_SCRATCH_FLOATS];
+
+#define CM_NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_ptr[CM_NOALLOC_MAX_DEVICES] = {nullptr};
+static std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device (set up at the first call there).
+static int noalloc_scratch_address(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= CM_NOALLOC_MAX_DEVICES) {
+        cm_set_error("attn_decode_noalloc: cannot tell the current device (%s)", cudaGetErrorString(e));
+        return CM_ERR_DRIVER;
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            cm_set_error("attn_decode_noalloc: cudaGetSymbolAddress failed on device %d (%s)", dev,
+                         cudaGetErrorString(e));
+            return CM_ERR_DRIVER;
+        }
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return CM_OK;
+}
+
+extern "C" int cm_attn_decode_noalloc(int dt, void* ctx, long long ldc, const void* q, long long ldq,
+                                      const void* gate, long long ldg, const int* seq_pos, const int* seq_slot,
+                                      const void* pool, long long pages, const int* ptab, int ptab_stride,
+                                      int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
+                                      float scale, cudaStream_t st) {
+    if (B <= 0) return CM_OK;
+    if (QH <= 0 || HD <= 0 || n_chunks <= 0) CM_REFUSE("attn_decode_noalloc: %d heads, head size %d, %d chunks", QH, HD, n_chunks);
+    const long long o_floats = (long long)B * QH * n_chunks * HD;       // unnormalised outputs per chunk
+    const long long ml_floats = (long long)B * QH * n_chunks * 2;       // maximum and sum per chunk
+    if (o_floats + ml_floats > CM_NOALLOC_SCRATCH_FLOATS)
+        CM_REFUSE("attn_decode_noalloc: %lld floats of scratch wanted (B=%d, heads=%d, chunks=%d, head size=%d), "
+                  "the built-in array holds %d", o_floats + ml_floats, B, QH, n_chunks, HD, CM_NOALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch_address(&scratch);
+    if (rc != CM_OK) return rc;
+    // part_o first (16-byte aligned for any size since HD is a multiple of 8), then part_ml
+    return cm_attn_decode(dt, ctx, ldc, q, ldq, gate, ldg, seq_pos, seq_slot, pool, pages, ptab, ptab_stride, ring,
+                          window, B, QH, KVH, HD, n_chunks, scale, scratch, scratch + o_floats, st);
+}
