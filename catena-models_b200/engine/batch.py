@@ -50,6 +50,7 @@ class StepBatch:
         self.want_rows = v["want_rows"][:n_want]
         self.upd_count, self.upd_index, self.upd_value = v["upd_count"], v["upd_index"], v["upd_value"]
         self.prefill = prefill
+        self.lengths, self.positions = list(lengths), list(positions)    # host copies, per sequence
         self.B, self.T = layout.B, layout.T
         self.max_len = max(lengths) if lengths else 0          # longest run of new tokens
         self.max_end = max((p + n for p, n in zip(positions, lengths)), default=0)

@@ -1,0 +1,302 @@
+"""Each part alone (norm, position encoding, attention mixer, short-conv mixer, feed-forward,
+block), built from parameters at sizes of its own and compared with the plain functions; and a
+toy architecture with a toy mixer that keeps state of its own, registered from this file."""
+import dataclasses
+
+import pytest
+import torch
+
+import plain_lfm3 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _runtime(dtype):
+    from catena_models_b200.engine.runtime import Runtime
+    return Runtime(dtype, DEV)
+
+
+def _batch(rt, cache, slots, token_lists, positions):
+    """A StepBatch for parts that are stepped outside an Engine."""
+    from catena_models_b200.engine.batch import BatchLayout, StepBatch, fill_host
+
+    updates = []
+    for s, p, t in zip(slots, positions, token_lists):
+        updates += cache.flat_updates(s, cache.book.reserve(s, p + len(t)))
+        cache.book.advance(s, p + len(t))
+    T = sum(len(t) for t in token_lists)
+    layout = BatchLayout(T, len(slots), 0, len(updates))
+    host = torch.zeros(layout.size, dtype=torch.int32)
+    fill_host(layout, host.numpy(), slots, token_lists, positions, [[] for _ in slots], updates)
+    batch = StepBatch(layout, host.to(DEV), all(p == 0 for p in positions), [len(t) for t in token_lists], positions, 0, len(updates))
+    from catena_models_b200 import kernels
+    if updates:
+        kernels.scatter_i32(cache.ptab_all, batch.upd_index, batch.upd_value, batch.upd_count, layout.U)
+    return batch
+
+
+def _bind(part, rt, seed, std=0.3):
+    from catena_models_b200.weights.random_init import random_tensors
+    from catena_models_b200.weights.loader import adopt_tensors
+
+    specs = part.all_tensor_specs()
+    raw = random_tensors(specs, seed, std=std, norm_weights="random", rope_factors="uniform")
+    tensors = adopt_tensors(raw, specs, rt.device, widen=rt.dtype == torch.float32)
+    part.bind_all(tensors, rt)
+    return {k: v.double() for k, v in raw.items()}
+
+
+def _close(got, ref, dtype, same=None):
+    """float32: close to the exact result.  bfloat16 with `same` (the plain part run with the
+    reference's bfloat16 rounding points on the same inputs): the part's largest error is at most
+    twice the largest error that the rounding points alone cause."""
+    got = got.double().cpu()
+    if dtype == torch.float32:
+        torch.testing.assert_close(got, ref, rtol=2e-5, atol=2e-5)
+    elif same is None:
+        torch.testing.assert_close(got, ref, rtol=3e-2, atol=3e-2)
+    else:
+        assert float((got - ref).abs().max()) <= 2.0 * float((same - ref).abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_and_rotary_alone(dtype):
+    from catena_models_b200.parts import build_part
+
+    rt = _runtime(dtype)
+    norm = build_part("norm", "rms", name="n.weight", width=136, eps=3e-4)
+    raw = _bind(norm, rt, 1)
+    x = torch.randn(9, 136).to(dtype)
+    _close(norm.apply(rt, x.to(DEV)), P.rms_norm(x.double(), raw["n.weight"], 3e-4), dtype)
+    rot = build_part("position", "rotary", head_dim=48, theta=12345.0, factors_name="f.weight")
+    raw = _bind(rot, rt, 2)
+    want = P.rope_frequencies(12345.0, 48, torch.float32) / raw["f.weight"].float()
+    assert torch.equal(rot.rate_table().cpu(), want)
+    assert build_part("position", "none").rate_table() is None
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window,gate,qk_norm", [(0, True, True), (20, False, True), (70, True, False)])
+def test_attention_mixer_alone(dtype, window, gate, qk_norm):
+    """Prompt step over three sequences, then decode steps, against the plain mixer."""
+    from catena_models_b200.cache.cache import Cache
+    from catena_models_b200.parts import build_part
+
+    H, QH, KVH, HD = 72, 6, 2, 32
+    rt = _runtime(dtype)
+    pos_part = build_part("position", "rotary", head_dim=HD, theta=5000.0, factors_name=None if window else "rope_freqs.weight")
+    mixer = build_part("mixer", "gqa_attention", prefix="L.", hidden=H, heads=QH, kv_heads=KVH, head_dim=HD,
+                       window=window, position=pos_part, qk_norm_eps=1e-5 if qk_norm else None, output_gate=gate)
+    raw = _bind(mixer, rt, 3, std=0.2)
+    w = {k[2:] if k.startswith("L.") else k: v for k, v in raw.items()}
+    if not qk_norm:
+        w["attn_q_norm.weight"] = w["attn_k_norm.weight"] = None
+    if window:
+        w["rope_freqs.weight"] = torch.ones(HD // 2, dtype=torch.float64)
+    cfg = dict(num_attention_heads=QH, num_key_value_heads=KVH, head_dim=HD, norm_eps=1e-5, sliding_window=window,
+               rope_theta=5000.0, rope_theta_sliding=5000.0, attn_output_gate=gate)
+    cache = Cache([mixer.state_spec()], 1024, dtype, DEV)
+    lens, extra = [5, 90, 33], 6
+    seqs = [torch.randn(n + extra, H).to(dtype) for n in lens]
+    slots = [cache.admit() for _ in lens]
+    batch = _batch(rt, cache, slots, [[0] * n for n in lens], [0, 0, 0])
+    y = mixer.forward(rt, batch, torch.cat([s[:n] for s, n in zip(seqs, lens)]).to(DEV), cache.view(0))
+    outs = [[y[a:a + n]] for a, n in zip([0, 5, 95], lens)]
+    for t in range(extra):
+        batch = _batch(rt, cache, slots, [[0]] * 3, [n + t for n in lens])
+        y = mixer.forward(rt, batch, torch.stack([s[n + t] for s, n in zip(seqs, lens)]).to(DEV), cache.view(0))
+        for b in range(3):
+            outs[b].append(y[b:b + 1])
+
+    def plain(n, r=P._identity):
+        kind = "sliding_attention" if window else "full_attention"
+        if qk_norm:
+            return P.attention_mixer(n, w, cfg, kind, r)
+        old = P.rms_norm                                  # no head norm: the plain mixer's norm becomes the identity
+        P.rms_norm = lambda x, ww, eps, rr=P._identity: x if ww is None else old(x, ww, eps, rr)
+        try:
+            return P.attention_mixer(n, w, cfg, kind, r)
+        finally:
+            P.rms_norm = old
+
+    for b, s in enumerate(seqs):
+        _close(torch.cat(outs[b]), plain(s.double()), dtype, plain(s.double(), P._round_bf16))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_shortconv_ffn_and_block_alone(dtype):
+    from catena_models_b200.cache.cache import Cache
+    from catena_models_b200.parts import build_part
+
+    H, F, taps = 88, 168, 5
+    rt = _runtime(dtype)
+    conv = build_part("mixer", "short_conv", prefix="L.", hidden=H, taps=taps)
+    ffn = build_part("feed_forward", "swiglu", prefix="L.", hidden=H, intermediate=F)
+    norms = {n: build_part("norm", "rms", name=f"L.{n}.weight", width=H, eps=1e-5)
+             for n in ("attn_norm", "post_attention_norm", "ffn_norm", "post_ffw_norm")}
+    block = build_part("block", "sandwich", mixer=conv, feed_forward=ffn, input_norm=norms["attn_norm"],
+                       ffn_norm=norms["ffn_norm"], post_mixer_norm=norms["post_attention_norm"],
+                       post_ffn_norm=norms["post_ffw_norm"])
+    raw = _bind(block, rt, 4, std=0.15)
+    w = {k[2:]: v for k, v in raw.items()}
+    cfg = dict(conv_L_cache=taps, norm_eps=1e-5, post_norm=True)
+    cache = Cache([block.state_spec()], 1024, dtype, DEV)
+    lens, extra = [3, 40], 4
+    seqs = [torch.randn(n + extra, H).to(dtype) for n in lens]
+    slots = [cache.admit() for _ in lens]
+    hs = torch.cat([s[:n] for s, n in zip(seqs, lens)]).to(DEV)
+    batch = _batch(rt, cache, slots, [[0] * n for n in lens], [0, 0])
+    # parts alone: the feed-forward and the mixer on the same rows
+    _close(ffn.forward(rt, batch, hs), P.swiglu_ffn(hs.double().cpu(), w), dtype,
+           P.swiglu_ffn(hs.double().cpu(), w, P._round_bf16))
+    h, n_next = block.forward(rt, batch, hs.clone(), norms["attn_norm"].apply(rt, hs), cache.view(0), norms["attn_norm"])
+    outs = [[h[a:a + n]] for a, n in zip([0, 3], lens)]
+    _close(n_next, P.rms_norm(h.double().cpu(), w["attn_norm.weight"], 1e-5), dtype)
+    for t in range(extra):
+        batch = _batch(rt, cache, slots, [[0]] * 2, [n + t for n in lens])
+        x = torch.stack([s[n + t] for s, n in zip(seqs, lens)]).to(DEV)
+        h, none = block.forward(rt, batch, x.clone(), norms["attn_norm"].apply(rt, x), cache.view(0), None)
+        assert none is None
+        for b in range(2):
+            outs[b].append(h[b:b + 1])
+    for b, s in enumerate(seqs):
+        _close(torch.cat(outs[b]), P.block(s.double(), w, cfg, "conv"), dtype, P.block(s.double(), w, cfg, "conv", P._round_bf16))
+
+
+# ----------------------------------------------------------------------------- toy parts
+def test_toy_mixer_with_its_own_state_registers_builds_and_steps():
+    """A mixer defined here (a per-channel leaky running sum, one float vector of state per
+    sequence), a layer-norm-free toy architecture around it, registered, built with random
+    weights and stepped through prompt and decode steps, without touching the library."""
+    from catena_models_b200 import register_architecture, register_part
+    from catena_models_b200.api import Model
+    from catena_models_b200.cache.spec import FixedStateSpec
+    from catena_models_b200.config.base import Reader
+    from catena_models_b200.engine.definition import ModelDefinition, PlanEntry
+    from catena_models_b200.parts import Mixer, build_part
+    from catena_models_b200.parts.linear import Linear
+    from catena_models_b200.weights.loader import TensorSpec
+
+    class LeakySum(Mixer):
+        """s_t = decay * s_{t-1} + x_t ; y_t = proj(s_t * scale).  State: s, float32 [hidden]."""
+
+        def __init__(self, prefix, hidden, decay):
+            self.hidden, self.decay = hidden, decay
+            self.scale_name = prefix + "scale"
+            self.proj = Linear(prefix + "proj.weight", hidden, hidden)
+
+        def children(self):
+            return [self.proj]
+
+        def tensor_specs(self):
+            return [TensorSpec(self.scale_name, (self.hidden,), "norm")]
+
+        def bind(self, tensors, rt):
+            self.scale = tensors[self.scale_name].float()
+
+        def state_spec(self):
+            return FixedStateSpec((self.hidden,), "float32")
+
+        def forward(self, rt, batch, x, state):
+            slots = batch.seq_slot.long()
+            out = torch.empty_like(x, dtype=torch.float32)
+            if batch.prefill:
+                start = 0
+                for b, n in enumerate(batch.lengths):
+                    s = torch.zeros(self.hidden, device=x.device)
+                    for t in range(start, start + n):
+                        s = self.decay * s + x[t].float()
+                        out[t] = s
+                    state.tensor[slots[b]] = s
+                    start += n
+            else:
+                s = self.decay * state.tensor[slots] + x.float()
+                state.tensor[slots] = s
+                out = s
+            return self.proj.apply(rt, (out * self.scale).to(x.dtype))
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig:
+        vocab_size: int
+        hidden_size: int
+        intermediate_size: int
+        layer_kinds: tuple
+        decay: float
+        norm_eps: float
+
+        @classmethod
+        def from_dict(cls, data, where="config.json"):
+            r = Reader(data, where)
+            cfg = cls(r.integer("vocab_size"), r.integer("hidden_size"), r.integer("intermediate_size"),
+                      r.string_list("layer_kinds"), r.number("decay"), r.number("norm_eps"))
+            r.finish()
+            return cfg
+
+    def define(cfg):
+        H = cfg.hidden_size
+        blocks = []
+        for l, kind in enumerate(cfg.layer_kinds):
+            pre = f"layers.{l}."
+            mixer = (build_part("mixer", "toy_leaky_sum", prefix=pre, hidden=H, decay=cfg.decay) if kind == "leaky"
+                     else build_part("mixer", "short_conv", prefix=pre, hidden=H, taps=2))
+            blocks.append(build_part(
+                "block", "sandwich", mixer=mixer,
+                feed_forward=build_part("feed_forward", "swiglu", prefix=pre, hidden=H, intermediate=cfg.intermediate_size),
+                input_norm=build_part("norm", "rms", name=pre + "in_norm.weight", width=H, eps=cfg.norm_eps),
+                ffn_norm=build_part("norm", "rms", name=pre + "ffn_norm.weight", width=H, eps=cfg.norm_eps)))
+        return ModelDefinition("toy", cfg.vocab_size, H, "embed.weight", blocks,
+                               [PlanEntry(i, i) for i in range(len(blocks))],
+                               build_part("norm", "rms", name="final_norm.weight", width=H, eps=cfg.norm_eps), None)
+
+    register_part("mixer", "toy_leaky_sum", LeakySum, replace=True)
+    register_architecture("toy", ToyConfig, define, replace=True)
+    config = dict(architecture="toy", vocab_size=50, hidden_size=32, intermediate_size=48,
+                  layer_kinds=["leaky", "conv", "leaky"], decay=0.75, norm_eps=1e-5)
+    from catena_models_b200.engine.model import DecoderModel
+    from catena_models_b200.weights.random_init import random_tensors
+
+    raw = random_tensors(define(ToyConfig.from_dict(config)).tensor_specs(), 5, std=0.3, norm_weights="random")
+    model = Model(DecoderModel.from_tensors(config, raw, torch.float32, DEV), max_tokens=512)
+    eng = model.engine
+    assert [type(s).__name__ for s in model.decoder.state_specs] == ["FixedStateSpec"] * 3
+    assert len(eng.cache.fixed_storage) == 2                       # two groups: [32] and [1, 32]
+
+    # the same toy model in plain torch on the CPU
+    w = {k: v.double() for k, v in raw.items()}
+
+    def plain(tokens):
+        h = w["embed.weight"][tokens]
+        for l, kind in enumerate(config["layer_kinds"]):
+            pre = f"layers.{l}."
+            n = P.rms_norm(h, w[pre + "in_norm.weight"], 1e-5)
+            if kind == "leaky":
+                s, rows = torch.zeros(32, dtype=torch.float64), []
+                for t in range(n.shape[0]):
+                    s = 0.75 * s + n[t]
+                    rows.append(s)
+                m = (torch.stack(rows) * w[pre + "scale"]) @ w[pre + "proj.weight"].T
+            else:
+                m = P.shortconv_mixer(n, {k[len(pre):]: v for k, v in w.items() if k.startswith(pre)}, dict(conv_L_cache=2))
+            h = h + m
+            n2 = P.rms_norm(h, w[pre + "ffn_norm.weight"], 1e-5)
+            h = h + P.swiglu_ffn(n2, {k[len(pre):]: v for k, v in w.items() if k.startswith(pre)})
+        return P.rms_norm(h, w["final_norm.weight"], 1e-5) @ w["embed.weight"].T
+
+    seqs = [[3, 9, 27, 31, 4, 1, 49, 0, 12], [7, 7, 8, 40]]
+    for round_ in range(2):                                         # twice: the slots are used again
+        slots = eng.admit(2)
+        got = [[], []]
+        out = eng.step(slots, [seqs[0][:5], seqs[1][:2]], [[0, 1, 2, 3, 4], [0, 1]])
+        got[0].append(out[:5].clone())
+        got[1].append(out[5:].clone())
+        for t in range(2):
+            out = eng.step(slots, [[seqs[0][5 + t]], [seqs[1][2 + t]]])
+            got[0].append(out[0:1].clone())
+            got[1].append(out[1:2].clone())
+        eng.release([slots[1]])
+        for t in range(7, 9):
+            got[0].append(eng.step([slots[0]], [[seqs[0][t]]]).clone())
+        eng.release([slots[0]])
+        for g, s in zip(got, seqs):
+            torch.testing.assert_close(torch.cat(g).double().cpu(), plain(s), rtol=2e-5, atol=2e-5)
