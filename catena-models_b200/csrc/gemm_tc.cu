@@ -1,6 +1,6 @@
 // C[M,N] = A[M,K] * B[N,K]^T in bfloat16 on the 5th-generation tensor cores (prompt steps).
 //
-// One block computes a 128 x BLOCK_N tile of C.  Roles (one warp each, six warps):
+// One block per SM computes 128 x BLOCK_N tiles of C, one after another.  Roles (six warps):
 //   warp 0  one thread: TMA loads of the A and B k-slices (128 x 64 and BLOCK_N x 64 bf16,
 //           128-byte swizzle) into a ring of STAGES shared-memory stages;
 //   warp 1  allocates the tensor-memory columns of the accumulator; one thread issues
@@ -12,8 +12,8 @@
 // Rows or columns beyond M, N, K are zero-filled by TMA on load and masked on store, so any
 // M and N and any K that is a multiple of 8 (16-byte row pitch) is taken.
 //
-// MODE_SWIGLU: B is the row-packed [Wgate; Wup] with 2N rows; the B stage is two 64-row boxes
-// (gate rows n0.., up rows N+n0..), so columns 0-63 of the accumulator are g and 64-127 are u,
+// MODE_SWIGLU: B is the row-packed [Wgate; Wup] with 2N rows; the B stage is two half-height boxes
+// (gate rows n0.., up rows N+n0..), so the first half of the accumulator's columns is g, the second u,
 // and the epilogue stores C = T(silu(T(g)) * T(u)) (catena-models' fused gate epilogue,
 // src/catena/lfm3_wmma.hex:10790-10815).
 //
@@ -139,6 +139,15 @@ __device__ __forceinline__ void store_cols<float>(float* dst, const float* v, in
     }
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Persistent form: gridDim.x blocks (one per SM) walk the output tiles t = blockIdx.x,
+// blockIdx.x + gridDim.x, ...; tile t covers rows (t / n_tiles) * 128 and output columns
+// (t % n_tiles) * OUT_COLS.  The accumulator is double-buffered in tensor memory (2 * BLOCK_N
+// columns), so the epilogue of one tile runs while the next tile's products are issued; the
+// shared-memory ring of k-slices keeps turning across tile borders.
 template <int BLOCK_N, int STAGES, typename TC, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -146,18 +155,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = BLOCK_N * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+    constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;                 // two accumulators
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[2 * STAGES + 1];
+    __shared__ uint64_t bars[2 * STAGES + 4];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ int issued_kb;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM;
-    const int n0 = blockIdx.x * (MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N);   // first output column
     const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int n_tiles = (N + OUT_COLS - 1) / OUT_COLS;
+    const int num_tiles = n_tiles * ((M + TC_BM - 1) / TC_BM);
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;                    // swizzle atoms need 1024-byte alignment
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), done = smem_u32(&bars[2 * STAGES]);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = smem_u32(&bars[2 * STAGES + 2]);
 
     pdl_trigger();
     if (threadIdx.x == 0) {
@@ -165,14 +177,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(done, 1);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full0 + 8 * a, 1);
+            mbar_init(acc_empty0 + 8 * a, 4);                   // one arrival per epilogue warp
+        }
         abort_flag = 0;
         issued_kb = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
-                     "r"((uint32_t)BLOCK_N)
+                     "r"(TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -184,65 +199,87 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------- TMA loader
-        for (int kb = 0; kb < num_kb; ++kb) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, err, TC_ERR_TIMEOUT_LOAD)) break;
-            const uint32_t a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
-            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-            tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * TC_BK, m0);
-            if (MODE == TC_MODE_SWIGLU) {
-                tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, n0);
-                tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * TC_BK, N + n0);
-            } else {
-                tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, n0);
+        int it = 0;                               // k-slices issued so far, over all tiles
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile / n_tiles) * TC_BM, n0 = (tile % n_tiles) * OUT_COLS;
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, err, TC_ERR_TIMEOUT_LOAD);
+                if (!ok) break;
+                const uint32_t a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * TC_BK, m0);
+                if (MODE == TC_MODE_SWIGLU) {
+                    tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, n0);
+                    tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * TC_BK, N + n0);
+                } else {
+                    tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, n0);
+                }
+                issued_kb = it + 1;
             }
-            issued_kb = kb + 1;
         }
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------- MMA issuer
         // instruction descriptor: float accumulator, bf16 A and B, both K-major, N/8 and M/16
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_N >> 3) << 17) |
                                    ((uint32_t)(TC_BM >> 4) << 24);
+        int it = 0, local = 0;
         bool ok = true;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, err, TC_ERR_TIMEOUT_MMA);
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            // the epilogue must have drained this accumulator (two tiles ago)
+            ok = mbar_wait(acc_empty0 + 8 * acc, ((local >> 1) & 1) ^ 1, &abort_flag, err, TC_ERR_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after();
-            const uint64_t adesc = umma_desc(tiles + s * STAGE_BYTES);
-            const uint64_t bdesc = umma_desc(tiles + s * STAGE_BYTES + A_BYTES);
+            const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, err, TC_ERR_TIMEOUT_MMA);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t adesc = umma_desc(tiles + s * STAGE_BYTES);
+                const uint64_t bdesc = umma_desc(tiles + s * STAGE_BYTES + A_BYTES);
 #pragma unroll
-            for (int k = 0; k < TC_BK / 16; ++k)          // 16 values of k = 32 bytes further in the row
-                umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
-            umma_commit(empty0 + 8 * s);                  // stage is free once these MMAs have read it
+                for (int k = 0; k < TC_BK / 16; ++k)      // 16 values of k = 32 bytes further in the row
+                    umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+                umma_commit(empty0 + 8 * s);              // stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(acc_full0 + 8 * acc);     // accumulator complete
         }
-        if (ok) umma_commit(done);                        // accumulator complete
     } else if (warp >= 2) {
         // ------------------------------------------------------------- epilogue
         const int q = warp & 3;                           // tensor-memory lane quarter of this warp
-        const int row = m0 + q * 32 + lane;
-        if (mbar_wait(done, 0, &abort_flag, err, TC_ERR_TIMEOUT_EPILOGUE)) {
+        const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        int local = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            const int m0 = (tile / n_tiles) * TC_BM, n0 = (tile % n_tiles) * OUT_COLS;
+            const int row = m0 + q * 32 + lane;
+            if (!mbar_wait(acc_full0 + 8 * acc, (local >> 1) & 1, &abort_flag, err, TC_ERR_TIMEOUT_EPILOGUE)) break;
             tc_fence_after();
-            const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
-            constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+            const uint32_t t_acc = tmem_base + (uint32_t)(acc * BLOCK_N) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < OUT_COLS / 32; ++c) {
                 float v[32];
-                tmem_load32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+                tmem_load32(t_acc + (uint32_t)(c * 32), v);
                 if (MODE == TC_MODE_SWIGLU) {
                     float u[32];
-                    tmem_load32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(OUT_COLS + c * 32), u);
+                    tmem_load32(t_acc + (uint32_t)(OUT_COLS + c * 32), u);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const float g = rounded<TC>(v[i]), uu = rounded<TC>(u[i]);
-                        v[i] = (g * sigmoid_f32(g)) * uu;
+                        v[i] = __fdividef(g, 1.f + __expf(-g)) * uu;
                     }
                 }
                 const int col = n0 + c * 32;
                 if (row < M && col < N) store_cols<TC>(C + (long long)row * ldc + col, v, N - col, vec_ok);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);    // this warp has read its quarter
         }
     }
     // ------------------------------------------------------------------ teardown
@@ -260,7 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BLOCK_N)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
                      : "memory");
     }
 }
@@ -326,7 +363,15 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
         }
         configured = true;
     }
-    dim3 grid((N + OUT_COLS - 1) / OUT_COLS, (M + TC_BM - 1) / TC_BM);
+    const int num_tiles = ((N + OUT_COLS - 1) / OUT_COLS) * ((M + TC_BM - 1) / TC_BM);
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 1;
+    }
+    dim3 grid(num_tiles < sm_count ? num_tiles : sm_count);
     cm_launch(kernel, grid, TC_THREADS, smem, st, map_a, map_b, (TC*)C, M, N, K, ldc, err);
     CM_CHECK_LAUNCH();
     return CM_OK;
@@ -335,6 +380,10 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
 // A [M,K] and B [N,K] (2N rows when swiglu) bfloat16, row pitches lda/ldb multiples of 8
 // elements, bases 16-byte aligned; C bfloat16 or float.  err: device int, raised by a block
 // whose pipeline wait ran out (0 otherwise); may be null.
+// Tile choice for experiments: 0 = 128 x 128 (6 stages), 1 = 128 x 256 (4 stages).
+static int g_tc_variant = 1;
+extern "C" void cm_gemm_tc_set_variant(int v) { g_tc_variant = v; }
+
 extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M, int N, int K, long long lda,
                           long long ldb, long long ldc, int swiglu, int* err, cudaStream_t st) {
     if (M <= 0 || N <= 0) return CM_OK;
@@ -344,8 +393,11 @@ extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M,
         CM_REFUSE("gemm_tc: operands must be 16-byte aligned");
     if (swiglu) {
         if (dtc != DT_BF16) return CM_ERR_DTYPE;
+        if (g_tc_variant == 1) return launch_tc<256, 4, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
         return launch_tc<128, 6, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     }
+    if (dtc == DT_BF16 && g_tc_variant == 1)
+        return launch_tc<256, 4, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     if (dtc == DT_BF16) return launch_tc<128, 6, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     if (dtc == DT_F32) return launch_tc<128, 6, float, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     return CM_ERR_DTYPE;
