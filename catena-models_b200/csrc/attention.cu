@@ -279,10 +279,10 @@ extern "C" int cm_attn_prefill_simt(int dt, void* ctx, long long ldc, const void
 //   ring group:    entry e holds the latest position <= pos that is congruent to e (mod ring)
 // =========================================================================================
 #define AD_CHUNK 256
-#define AD_GB 8
 #define AD_THREADS 128
 
-template <typename T>
+// AD_GB: query heads of a kv head that one pass handles (1, 2, 4 or 8; more heads take more passes)
+template <typename T, int AD_GB>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, const T* __restrict__ q,
                    long long ldq, const int* __restrict__ seq_pos, const int* __restrict__ seq_slot,
@@ -321,7 +321,61 @@ attn_decode_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, cons
             qs[e] = g < ng ? to_f32(q[(long long)b * ldq + (long long)(hk * G + g0 + g) * HD + d]) : 0.f;
         }
         __syncthreads();
-        // ---- scores: a lane owns entries lane and lane+32 of its warp's page
+        // ---- scores of this warp's page
+        if ((tpr & (tpr - 1)) == 0 && tpr <= 32) {
+            // head sizes 16, 32, 64, 128, 256: HD/8 lanes share a key row (16 bytes each), so a warp
+            // reads 32/tpr whole rows (512 contiguous bytes) per step; the partial dot products of a
+            // row are added over its lanes by xor shuffles
+            const int kq = lane / tpr, dq = lane - kq * tpr, kpw = 32 / tpr;
+            float qr[AD_GB][8];
+#pragma unroll
+            for (int g = 0; g < AD_GB; ++g)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) qr[g][i] = qs[g * HD + dq * 8 + i];
+            const T* kpage = kv_tile(pool, 0, pages, page, hk, KVH, HD);
+            constexpr int SU = 4;                          // key rows in flight per lane
+            for (int r0 = 0; r0 < PAGE_TOKENS; r0 += kpw * SU) {
+                float kv8[SU][8];
+                unsigned vis_mask = 0;
+#pragma unroll
+                for (int u = 0; u < SU; ++u) {
+                    const int row = r0 + u * kpw + kq;
+                    const int e = page_idx * PAGE_TOKENS + row;
+                    bool v_u = false;
+                    if (row < PAGE_TOKENS && page_live && e < n_entries) {
+                        int kpos = e;
+                        if (ring) {
+                            int back = (pos - e) % ring;
+                            if (back < 0) back += ring;
+                            kpos = pos - back;
+                        }
+                        v_u = kpos >= 0 && kpos <= pos && (window <= 0 || kpos + window > pos);
+                    }
+                    if (v_u) {
+                        vis_mask |= 1u << u;
+                        load8<T>(kpage + (long long)row * HD + dq * 8, kv8[u]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < SU; ++u) {
+                    const int row = r0 + u * kpw + kq;
+                    if (row >= PAGE_TOKENS) continue;      // uniform over the warp: kq < kpw, rows come in whole steps
+#pragma unroll
+                    const bool v_u = (vis_mask >> u) & 1u;
+#pragma unroll
+                    for (int g = 0; g < AD_GB; ++g) {
+                        float sg = 0.f;
+                        if (v_u) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) sg = fmaf(qr[g][i], kv8[u][i], sg);
+                        }
+                        for (int o = tpr >> 1; o > 0; o >>= 1) sg += __shfl_xor_sync(0xffffffffu, sg, o);
+                        if (dq == 0) ss[g * AD_CHUNK + warp * PAGE_TOKENS + row] = v_u ? sg * scale : -INFINITY;
+                    }
+                }
+            }
+        } else {
+        // ---- any other head size: a lane owns entries lane and lane+32 of its warp's page
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const int row = lane + 32 * r;
@@ -356,6 +410,7 @@ attn_decode_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, cons
             for (int g = 0; g < AD_GB; ++g)
                 ss[g * AD_CHUNK + warp * PAGE_TOKENS + row] = vis ? s[g] * scale : -INFINITY;
         }
+        }
         __syncthreads();
         // ---- softmax pieces per head: warp w takes heads w, w+4
         for (int g = warp; g < AD_GB; g += AD_THREADS / 32) {
@@ -384,17 +439,34 @@ attn_decode_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, cons
             for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
         if (vg < groups) {
             const int n_here = min(AD_CHUNK, n_entries - e0);
-            for (int e = vg; e < n_here; e += groups) {
-                const int pidx = (e0 + e) / PAGE_TOKENS;
-                const int pg = ptab[(long long)slot * ptab_stride + pidx];
-                const T* vr = kv_tile(pool, 1, pages, pg, hk, KVH, HD) + (long long)((e0 + e) % PAGE_TOKENS) * HD + vc;
-                float vv[8];
-                load8<T>(vr, vv);
+            // the chunk's four pages, looked up once
+            const int* prow = ptab + (long long)slot * ptab_stride + e0 / PAGE_TOKENS;
+            const T* vp0 = kv_tile(pool, 1, pages, prow[0], hk, KVH, HD) + vc;
+            const T* vp1 = kv_tile(pool, 1, pages, n_here > 64 ? prow[1] : 0, hk, KVH, HD) + vc;
+            const T* vp2 = kv_tile(pool, 1, pages, n_here > 128 ? prow[2] : 0, hk, KVH, HD) + vc;
+            const T* vp3 = kv_tile(pool, 1, pages, n_here > 192 ? prow[3] : 0, hk, KVH, HD) + vc;
+            constexpr int VU = 4;                          // value rows in flight per thread
+            for (int eb = vg; eb < n_here; eb += groups * VU) {
+                float vv[VU][8];
 #pragma unroll
-                for (int g = 0; g < AD_GB; ++g) {
-                    const float p = ss[g * AD_CHUNK + e];
+                for (int u = 0; u < VU; ++u) {
+                    const int e = eb + u * groups;
+                    if (e < n_here) {
+                        const int pi = e / PAGE_TOKENS;
+                        const T* base = pi == 0 ? vp0 : (pi == 1 ? vp1 : (pi == 2 ? vp2 : vp3));
+                        load8<T>(base + (long long)(e % PAGE_TOKENS) * HD, vv[u]);
+                    }
+                }
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(p, vv[i], acc[g][i]);
+                for (int u = 0; u < VU; ++u) {
+                    const int e = eb + u * groups;
+                    if (e >= n_here) continue;
+#pragma unroll
+                    for (int g = 0; g < AD_GB; ++g) {
+                        const float p = ss[g * AD_CHUNK + e];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(p, vv[u][i], acc[g][i]);
+                    }
                 }
             }
 #pragma unroll
@@ -452,7 +524,18 @@ __global__ void attn_decode_merge_kernel(T* __restrict__ ctx, long long ldc,
     }
 }
 
+int cm_attn_decode_mma_stage(float* part_o, float* part_ml, const void* q, long long ldq, const int* seq_pos,
+                             const int* seq_slot, const void* pool, long long pages, const int* ptab,
+                             int ptab_stride, int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
+                             float scale, cudaStream_t st);
+
 // Scratch: part_o holds B*QH*n_chunks*HD floats, part_ml B*QH*n_chunks*2 floats.
+// bfloat16 with a head size that is a multiple of 16 up to 128 runs its first stage on the
+// tensor cores (attention_mma.cu); everything else on the CUDA cores.  use_mma = 0 forces the
+// CUDA-core stage.
+static int g_decode_mma = 1;
+extern "C" void cm_attn_decode_set_mma(int on) { g_decode_mma = on; }
+
 extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, long long ldq,
                               const void* gate, long long ldg, const int* seq_pos, const int* seq_slot,
                               const void* pool, long long pages, const int* ptab, int ptab_stride,
@@ -463,33 +546,47 @@ extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, l
     if (QH % KVH) CM_REFUSE("attn_decode: %d query heads over %d key heads", QH, KVH);
     if (ring % PAGE_TOKENS) CM_REFUSE("attn_decode: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
     if (n_chunks <= 0) CM_REFUSE("attn_decode: %d chunks", n_chunks);
+    const int G = QH / KVH;
+    const int gb = G >= 8 ? 8 : (G >= 4 ? 4 : (G >= 2 ? 2 : 1));
     const int groups = AD_THREADS / (HD / 8);
-    const size_t smem = ((size_t)AD_GB * HD + (size_t)AD_GB * AD_CHUNK + (size_t)groups * AD_GB * HD) * sizeof(float);
+    const size_t smem = ((size_t)gb * HD + (size_t)gb * AD_CHUNK + (size_t)groups * gb * HD) * sizeof(float);
     dim3 grid(n_chunks, KVH, B);
     dim3 mgrid(QH, B);
     const int mthreads = HD <= 64 ? 64 : 128;
-    if (dt == DT_F32) {
-        cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cm_launch(attn_decode_kernel<float>, grid, AD_THREADS, smem, st, part_o, part_ml, (const float*)q, ldq, seq_pos,
-                                                                  seq_slot, (const float*)pool, pages, ptab,
-                                                                  ptab_stride, ring, window, QH, KVH, HD,
-                                                                  n_chunks, scale);
+#define AD_LAUNCH(TT, GB)                                                                                          \
+    do {                                                                                                           \
+        cudaFuncSetAttribute(attn_decode_kernel<TT, GB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+        cm_launch(attn_decode_kernel<TT, GB>, grid, AD_THREADS, smem, st, part_o, part_ml, (const TT*)q, ldq, seq_pos, \
+                  seq_slot, (const TT*)pool, pages, ptab, ptab_stride, ring, window, QH, KVH, HD, n_chunks, scale); \
+    } while (0)
+#define AD_DISPATCH(TT)                   \
+    do {                                  \
+        if (gb == 8) AD_LAUNCH(TT, 8);    \
+        else if (gb == 4) AD_LAUNCH(TT, 4); \
+        else if (gb == 2) AD_LAUNCH(TT, 2); \
+        else AD_LAUNCH(TT, 1);            \
+    } while (0)
+    if (dt == DT_BF16 && g_decode_mma && HD % 16 == 0 && HD <= 128 && ldq % 2 == 0 &&
+        ((uintptr_t)q & 3) == 0 && ((uintptr_t)pool & 15) == 0) {
+        const int rc = cm_attn_decode_mma_stage(part_o, part_ml, q, ldq, seq_pos, seq_slot, pool, pages, ptab,
+                                                ptab_stride, ring, window, B, QH, KVH, HD, n_chunks, scale, st);
+        if (rc != CM_OK) return rc;
+        cm_launch(attn_decode_merge_kernel<bf16>, mgrid, mthreads, 0, st, (bf16*)ctx, ldc, part_o, part_ml,
+                  (const bf16*)gate, ldg, seq_pos, ring, QH, HD, n_chunks);
+    } else if (dt == DT_F32) {
+        AD_DISPATCH(float);
         CM_CHECK_LAUNCH();
         cm_launch(attn_decode_merge_kernel<float>, mgrid, mthreads, 0, st, (float*)ctx, ldc, part_o, part_ml,
-                                                                    (const float*)gate, ldg, seq_pos, ring, QH,
-                                                                    HD, n_chunks);
+                  (const float*)gate, ldg, seq_pos, ring, QH, HD, n_chunks);
     } else if (dt == DT_BF16) {
-        cudaFuncSetAttribute(attn_decode_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cm_launch(attn_decode_kernel<bf16>, grid, AD_THREADS, smem, st, part_o, part_ml, (const bf16*)q, ldq, seq_pos,
-                                                                 seq_slot, (const bf16*)pool, pages, ptab,
-                                                                 ptab_stride, ring, window, QH, KVH, HD,
-                                                                 n_chunks, scale);
+        AD_DISPATCH(bf16);
         CM_CHECK_LAUNCH();
         cm_launch(attn_decode_merge_kernel<bf16>, mgrid, mthreads, 0, st, (bf16*)ctx, ldc, part_o, part_ml,
-                                                                   (const bf16*)gate, ldg, seq_pos, ring, QH,
-                                                                   HD, n_chunks);
+                  (const bf16*)gate, ldg, seq_pos, ring, QH, HD, n_chunks);
     } else
         return CM_ERR_DTYPE;
+#undef AD_DISPATCH
+#undef AD_LAUNCH
     CM_CHECK_LAUNCH();
     return CM_OK;
 }

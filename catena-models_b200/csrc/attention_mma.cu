@@ -247,3 +247,231 @@ extern "C" int cm_attn_prefill_mma(void* ctx, long long ldc, const void* q, cons
     }
 #undef FA_CASE
 }
+
+// =========================================================================================
+// Decode attention over the paged cache on the tensor cores (bfloat16, head sizes that are
+// multiples of 16 up to 128).  One new query token per sequence.
+//
+// Grid (chunk, kv head, sequence), chunk = 256 cache entries = 4 pages, one page per warp.  The
+// G = QH/KVH query heads that share the kv head are the rows of the 16-row mma operand (up to
+// 16 per pass), so every key and value that is read serves all of them.  A warp copies its page
+// of K and V into its own shared-memory region (cp.async, rows padded by 16 bytes), forms
+// S = Q K^T and O = P V with mma.sync exactly as the prefill kernel does for one key tile, and
+// leaves (max, sum, unnormalised O) of its page; the four pages of the block are merged in page
+// order and the chunk's partial result goes to the same scratch layout that the CUDA-core
+// kernel uses (cm_attn_decode's merge kernel finishes the job).  Maximum, sum and merging are
+// float; probabilities enter the second product as bfloat16, like in the prefill kernel.
+// =========================================================================================
+#define FD_CHUNK 256
+#define FD_PAGE 64
+
+template <int HD>
+__global__ void __launch_bounds__(128)
+attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
+                       long long ldq, const int* __restrict__ seq_pos, const int* __restrict__ seq_slot,
+                       const bf16* __restrict__ pool, long long pages, const int* __restrict__ ptab, int ptab_stride,
+                       int ring, int window, int QH, int KVH, int n_chunks, float scale_log2) {
+    constexpr int LDS = HD + 8;
+    constexpr int CH = HD / 8;
+    extern __shared__ __align__(16) uint8_t fd_smem[];
+    bf16* kv_s = reinterpret_cast<bf16*>(fd_smem);                       // [4 warps][K|V][64][LDS]
+    float* mrg = reinterpret_cast<float*>(fd_smem + (size_t)4 * 2 * FD_PAGE * LDS * sizeof(bf16));   // [4][16][HD+2]
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int G = QH / KVH;
+    const int pos = seq_pos[b];
+    const int n_entries = ring ? min(pos + 1, ring) : pos + 1;
+    const int e0 = c * FD_CHUNK;
+    if (e0 >= n_entries) return;
+    const int slot = seq_slot[b];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int page_idx = e0 / FD_PAGE + warp;
+    const bool live = page_idx * FD_PAGE < n_entries;
+    bf16* Ks = kv_s + (size_t)warp * 2 * FD_PAGE * LDS;
+    bf16* Vs = Ks + FD_PAGE * LDS;
+    if (live) {
+        const int page = ptab[(long long)slot * ptab_stride + page_idx];
+        const bf16* kp = pool + ((((long long)0 * pages + page) * KVH + hk) * FD_PAGE) * (long long)HD;
+        const bf16* vp = pool + ((((long long)1 * pages + page) * KVH + hk) * FD_PAGE) * (long long)HD;
+        const int rows_here = min(FD_PAGE, n_entries - page_idx * FD_PAGE);
+        for (int e = lane; e < FD_PAGE * CH; e += 32) {
+            const int r = e / CH, cc = e - r * CH;
+            const bool in = r < rows_here;                     // entries never written are zero-filled: a
+            cp_async16(Ks + r * LDS + cc * 8, kp + (long long)r * HD + cc * 8, in);   // stale NaN times a zero
+            cp_async16(Vs + r * LDS + cc * 8, vp + (long long)r * HD + cc * 8, in);   // probability would be NaN
+        }
+    }
+    cp_async_commit();
+
+    for (int g0 = 0; g0 < G; g0 += 16) {                   // 16 query heads per pass
+        const int ng = min(16, G - g0);
+        float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+        float o[HD / 8][4];
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
+        if (live) {
+            // Q fragments: rows g and g+8 are heads g0+g and g0+g+8 of this kv head (zero beyond ng)
+            uint32_t qf[HD / 16][4];
+            const bf16* q0 = q + (long long)b * ldq + (long long)(hk * G + g0 + g) * HD;
+            const bf16* q1 = q0 + 8 * HD;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                qf[kk][0] = g < ng ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 2 * t) : 0u;
+                qf[kk][1] = g + 8 < ng ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 2 * t) : 0u;
+                qf[kk][2] = g < ng ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
+                qf[kk][3] = g + 8 < ng ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + 2 * t) : 0u;
+            }
+            cp_async_wait<0>();
+            __syncwarp();
+            float s[8][4];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk)
+#pragma unroll
+                for (int jp = 0; jp < 4; ++jp) {
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, Ks + (jp * 16 + (lane & 7) + 8 * (lane >> 4)) * LDS + kk * 16 + 8 * ((lane >> 3) & 1));
+                    mma16816(s[2 * jp], qf[kk], kb[0], kb[1]);
+                    mma16816(s[2 * jp + 1], qf[kk], kb[2], kb[3]);
+                }
+            // visibility of the page's entries (columns of s)
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int e = page_idx * FD_PAGE + 8 * j + 2 * t + (i & 1);
+                    bool vis = e < n_entries;
+                    if (vis) {
+                        int kpos = e;
+                        if (ring) {
+                            int back = (pos - e) % ring;
+                            if (back < 0) back += ring;
+                            kpos = pos - back;
+                        }
+                        vis = kpos >= 0 && kpos <= pos && (window <= 0 || kpos + window > pos);
+                    }
+                    const float x = vis ? s[j][i] * scale_log2 : -INFINITY;
+                    s[j][i] = x;
+                    mx[i >> 1] = fmaxf(mx[i >> 1], x);
+                }
+            float m_use[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                m_row[h] = mx[h];
+                m_use[h] = mx[h] == -INFINITY ? 0.f : mx[h];
+            }
+            uint32_t pf[4][4];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
+                const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+                l_row[0] += p0 + p1;
+                l_row[1] += p2 + p3;
+                pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+                pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 1);
+                l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 2);
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+                for (int dp = 0; dp < HD / 16; ++dp) {
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, Vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+                    mma16816(o[2 * dp], pf[kk], vb[0], vb[1]);
+                    mma16816(o[2 * dp + 1], pf[kk], vb[2], vb[3]);
+                }
+        }
+        // ---- this warp's page result to shared memory: row r = head, [HD] outputs then max, sum
+        __syncthreads();                                       // mrg may still be read by the previous pass
+        float* mine = mrg + (size_t)warp * 16 * (HD + 2);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = g + 8 * h;
+#pragma unroll
+            for (int j = 0; j < HD / 8; ++j) {
+                mine[r * (HD + 2) + 8 * j + 2 * t] = o[j][2 * h];
+                mine[r * (HD + 2) + 8 * j + 2 * t + 1] = o[j][2 * h + 1];
+            }
+            if (t == 0) {
+                mine[r * (HD + 2) + HD] = m_row[h];            // log2-scaled maximum
+                mine[r * (HD + 2) + HD + 1] = l_row[h];
+            }
+        }
+        __syncthreads();
+        // ---- merge the four pages in page order; leave the chunk's partial result
+        for (int e = tid; e < ng * HD; e += 128) {
+            const int r = e / HD, d = e - r * HD;
+            float mxx = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mxx = fmaxf(mxx, mrg[((size_t)w * 16 + r) * (HD + 2) + HD]);
+            float den = 0.f, num = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float* row = mrg + ((size_t)w * 16 + r) * (HD + 2);
+                const float f = row[HD] == -INFINITY ? 0.f : exp2f(row[HD] - mxx);
+                den += row[HD + 1] * f;
+                num += row[d] * f;
+            }
+            const long long idx = ((long long)b * QH + hk * G + g0 + r) * n_chunks + c;
+            part_o[idx * HD + d] = num;
+            if (d == 0) {
+                // the merge kernel works with natural-log maxima: m_ln = m_log2 * ln 2
+                part_ml[idx * 2] = mxx == -INFINITY ? -INFINITY : mxx * 0.6931471805599453f;
+                part_ml[idx * 2 + 1] = den;
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+template <int HD>
+static int launch_fd(float* part_o, float* part_ml, const void* q, long long ldq, const int* seq_pos,
+                     const int* seq_slot, const void* pool, long long pages, const int* ptab, int ptab_stride,
+                     int ring, int window, int B, int QH, int KVH, int n_chunks, float scale, cudaStream_t st) {
+    const size_t smem = (size_t)4 * 2 * FD_PAGE * (HD + 8) * sizeof(bf16) + (size_t)4 * 16 * (HD + 2) * sizeof(float);
+    auto kernel = attn_decode_mma_kernel<HD>;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            CM_REFUSE("attn_decode_mma: %zu bytes of shared memory refused", smem);
+        }
+        configured = true;
+    }
+    cm_launch(kernel, dim3(n_chunks, KVH, B), 128, smem, st, part_o, part_ml, (const bf16*)q, ldq, seq_pos, seq_slot,
+              (const bf16*)pool, pages, ptab, ptab_stride, ring, window, QH, KVH, n_chunks,
+              scale * 1.4426950408889634f);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// First stage of decode attention on the tensor cores; the partial results have the layout and
+// meaning that cm_attn_decode's merge kernel expects.  Returns CM_ERR_SHAPE (and launches
+// nothing) for head sizes it does not take.
+int cm_attn_decode_mma_stage(float* part_o, float* part_ml, const void* q, long long ldq, const int* seq_pos,
+                             const int* seq_slot, const void* pool, long long pages, const int* ptab,
+                             int ptab_stride, int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
+                             float scale, cudaStream_t st) {
+    if (ldq % 2 || ((uintptr_t)q & 3) || ((uintptr_t)pool & 15)) CM_REFUSE("attn_decode_mma: misaligned operands");
+#define FD_CASE(D) \
+    case D: return launch_fd<D>(part_o, part_ml, q, ldq, seq_pos, seq_slot, pool, pages, ptab, ptab_stride, ring, \
+                                window, B, QH, KVH, n_chunks, scale, st);
+    switch (HD) {
+        FD_CASE(16) FD_CASE(32) FD_CASE(48) FD_CASE(64) FD_CASE(80) FD_CASE(96) FD_CASE(112) FD_CASE(128)
+        default: CM_REFUSE("attn_decode_mma: head size %d (multiples of 16 up to 128)", HD);
+    }
+#undef FD_CASE
+}

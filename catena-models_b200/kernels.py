@@ -216,6 +216,14 @@ def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, win
                                      HD, window, scale, _stream()), "attn_prefill_mma")
 
 
+def set_decode_attention_tensor_cores(on):
+    """bfloat16 decode attention normally runs its first stage on the tensor cores when the head
+    size allows it; off forces the CUDA-core stage (tests compare the two)."""
+    lib().cm_attn_decode_set_mma.argtypes = [_i]
+    lib().cm_attn_decode_set_mma.restype = None
+    lib().cm_attn_decode_set_mma(1 if on else 0)
+
+
 def attn_decode_scratch(B, QH, HD, n_chunks, device):
     return (torch.empty(B * QH * n_chunks * HD, dtype=torch.float32, device=device),
             torch.empty(B * QH * n_chunks * 2, dtype=torch.float32, device=device))

@@ -227,10 +227,18 @@ def _paged_cache(K, kv, KVH, HD, dtype, lens, ring, scramble_seed=0):
     return pool, total, ptab.to(DEV)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype,tensor_cores", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
 @pytest.mark.parametrize("QH,KVH,HD,window", [(4, 2, 16, 0), (4, 1, 24, 8), (5, 5, 32, 70), (32, 8, 64, 0),
-                                              (16, 1, 128, 300), (2, 1, 256, 0)])
-def test_attn_decode_paged(K, dtype, QH, KVH, HD, window):
+                                              (16, 1, 128, 300), (2, 1, 256, 0), (40, 2, 48, 0)])
+def test_attn_decode_paged(K, dtype, tensor_cores, QH, KVH, HD, window):
+    K.set_decode_attention_tensor_cores(tensor_cores)
+    try:
+        _attn_decode_paged(K, dtype, QH, KVH, HD, window)
+    finally:
+        K.set_decode_attention_tensor_cores(True)
+
+
+def _attn_decode_paged(K, dtype, QH, KVH, HD, window):
     ring = (window + 63) // 64 * 64 if window else 0
     lens = [1, 64, 65, 300, 700]                      # tokens held including the new one
     B = len(lens)
