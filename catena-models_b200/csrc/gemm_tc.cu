@@ -378,25 +378,24 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
 }
 
 // A [M,K] and B [N,K] (2N rows when swiglu) bfloat16, row pitches lda/ldb multiples of 8
-// elements, bases 16-byte aligned; C bfloat16 or float.  err: device int, raised by a block
-// whose pipeline wait ran out (0 otherwise); may be null.
-// Tile choice for experiments: 0 = 128 x 128 (6 stages), 1 = 128 x 256 (4 stages).
-static int g_tc_variant = 1;
-extern "C" void cm_gemm_tc_set_variant(int v) { g_tc_variant = v; }
-
+// elements, bases 16-byte aligned; C bfloat16 or float.  block_n: 256 (128 x 256 tiles, four
+// stages: the most arithmetic per byte moved) or 128 (128 x 128 tiles, six stages: twice as
+// many tiles, for products with few rows where the number of tiles decides how many SMs stream
+// weights).  err: device int, raised by a block whose pipeline wait ran out; may be null.
 extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M, int N, int K, long long lda,
-                          long long ldb, long long ldc, int swiglu, int* err, cudaStream_t st) {
+                          long long ldb, long long ldc, int swiglu, int block_n, int* err, cudaStream_t st) {
     if (M <= 0 || N <= 0) return CM_OK;
     if (K <= 0 || K % 8 || lda % 8 || ldb % 8)
         CM_REFUSE("gemm_tc: inner size %d and row pitches %lld, %lld must be multiples of 8", K, lda, ldb);
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15)
         CM_REFUSE("gemm_tc: operands must be 16-byte aligned");
+    if (block_n != 128 && block_n != 256) CM_REFUSE("gemm_tc: tile width %d (128 or 256)", block_n);
     if (swiglu) {
         if (dtc != DT_BF16) return CM_ERR_DTYPE;
-        if (g_tc_variant == 1) return launch_tc<256, 4, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
+        if (block_n == 256) return launch_tc<256, 4, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
         return launch_tc<128, 6, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     }
-    if (dtc == DT_BF16 && g_tc_variant == 1)
+    if (dtc == DT_BF16 && block_n == 256)
         return launch_tc<256, 4, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     if (dtc == DT_BF16) return launch_tc<128, 6, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     if (dtc == DT_F32) return launch_tc<128, 6, float, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);

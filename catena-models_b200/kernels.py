@@ -27,7 +27,7 @@ _SIGNATURES = {
     "cm_gather_rows": [_i, _vp, _vp, _vp, _i, _i, _vp],
     "cm_gemm_simt": [_i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
     "cm_gemm_skinny": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp],
-    "cm_gemm_tc": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp],
+    "cm_gemm_tc": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp],
     "cm_qk_prepare": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i,
                       _i, _f, _vp],
     "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
@@ -168,10 +168,11 @@ def gemm_skinny(y, x, w, swiglu=False):
                                 y.stride(0), int(swiglu), _stream()), "gemm_skinny")
 
 
-def gemm_tc(y, x, w, swiglu=False, err=None):
+def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256):
     """y = x @ w^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory), any
     number of bfloat16 rows.  swiglu: w is [gate; up] with 2F rows and y[M, F] = silu(g) * u.
-    err: device int32 that a block raises if one of its bounded pipeline waits runs out."""
+    err: device int32 that a block raises if one of its bounded pipeline waits runs out.
+    block_n: 256 (128 x 256 tiles) or 128 (twice as many 128 x 128 tiles, for few rows)."""
     _need_cuda(y, x, w)
     M, K = x.shape
     N = y.shape[1]
@@ -182,7 +183,7 @@ def gemm_tc(y, x, w, swiglu=False, err=None):
     if x.stride(1) != 1 or w.stride(1) != 1 or y.stride(1) != 1:
         raise KernelError("gemm_tc takes row-major operands")
     _check(lib().cm_gemm_tc(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
-                            y.stride(0), int(swiglu), _ptr(err), _stream()), "gemm_tc")
+                            y.stride(0), int(swiglu), block_n, _ptr(err), _stream()), "gemm_tc")
 
 
 # -------------------------------------------------------------------------- attention

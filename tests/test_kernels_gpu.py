@@ -426,13 +426,13 @@ def test_refusals_are_errors_not_wrong_results(K):
 
 @pytest.mark.parametrize("M,N,Kd", [(128, 128, 64), (100, 70, 72), (1, 8, 8), (257, 384, 520), (2048, 2048, 2048),
                                      (65, 3104, 2048), (300, 200, 1000)])
-@pytest.mark.parametrize("dty", [torch.bfloat16, torch.float32])
-def test_gemm_tc(K, M, N, Kd, dty):
+@pytest.mark.parametrize("dty,block_n", [(torch.bfloat16, 256), (torch.bfloat16, 128), (torch.float32, 128)])
+def test_gemm_tc(K, M, N, Kd, dty, block_n):
     """tcgen05/TMA GEMM: shapes that fill no tile in any dimension, K with a ragged last k-slice."""
     x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=1), rnd(N, Kd, dtype=torch.bfloat16, scale=0.1, seed=2)
     y = torch.full((M, N), float("nan"), dtype=dty, device=DEV)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
-    K.gemm_tc(y, x, w, err=err)
+    K.gemm_tc(y, x, w, err=err, block_n=block_n)
     ref = x.double() @ w.double().T
     assert int(err) == 0
     if dty == torch.float32:
@@ -441,12 +441,13 @@ def test_gemm_tc(K, M, N, Kd, dty):
         close(y, ref, torch.bfloat16)
 
 
+@pytest.mark.parametrize("block_n", [128, 256])
 @pytest.mark.parametrize("M,F,Kd", [(128, 64, 64), (200, 136, 520), (70, 1000, 264)])
-def test_gemm_tc_swiglu(K, M, F, Kd):
+def test_gemm_tc_swiglu(K, M, F, Kd, block_n):
     x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=1), rnd(2 * F, Kd, dtype=torch.bfloat16, scale=0.2, seed=2)
     a = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
-    K.gemm_tc(a, x, w, swiglu=True, err=err)
+    K.gemm_tc(a, x, w, swiglu=True, err=err, block_n=block_n)
     g = (x.double() @ w[:F].double().T).to(torch.bfloat16).double()
     u = (x.double() @ w[F:].double().T).to(torch.bfloat16).double()
     assert int(err) == 0
