@@ -112,6 +112,7 @@ class KVView:
     ptab: torch.Tensor          # [slots, pages per sequence] int32
     group: int
     owned: bool = True          # False: this layer reads a state that another layer writes
+    unit: int = -1              # the state unit of the plan this view belongs to
 
     @property
     def ring(self):
@@ -124,6 +125,7 @@ class FixedView:
     spec: FixedStateSpec
     tensor: torch.Tensor        # [slots, *shape]
     owned: bool = True
+    unit: int = -1
 
 
 class Cache:

@@ -56,6 +56,7 @@ class StepBatch:
         self.max_end = max((p + n for p, n in zip(positions, lengths)), default=0)
         self.n_want, self.n_updates = n_want, n_updates
         self.chunk_bucket = None                               # set by a captured decode graph
+        self.shared = {}                                       # what a layer leaves for later layers of this step
 
     def decode_chunks(self, kv_spec):
         """Chunks of cache entries the decode attention walks for this state spec."""

@@ -76,6 +76,7 @@ class DecoderModel:
     # ------------------------------------------------------------------ forward
     def forward(self, batch, cache):
         rt = self.rt
+        batch.shared.clear()
         if batch.layout.U:
             kernels.scatter_i32(cache.ptab_all, batch.upd_index, batch.upd_value, batch.upd_count, batch.layout.U)
         h = torch.empty((batch.T, self.hidden_size), dtype=rt.dtype, device=rt.device)
@@ -87,7 +88,7 @@ class DecoderModel:
             next_norm = self.blocks[plan[i + 1].block].input_norm if i + 1 < len(plan) else None
             state = cache.view(entry.state)
             if state is not None:
-                state.owned = entry.owns_state
+                state.owned, state.unit = entry.owns_state, entry.state
             h, n = block.forward(rt, batch, h, n, state, next_norm)
         rows = torch.empty((batch.n_want, self.hidden_size), dtype=rt.dtype, device=rt.device)
         if batch.n_want == 0:

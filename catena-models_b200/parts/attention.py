@@ -27,7 +27,7 @@ from .linear import Linear
 
 class GQAttention(Mixer):
     def __init__(self, prefix, hidden, heads, kv_heads, head_dim, window, position, qk_norm_eps,
-                 output_gate, names=None):
+                 output_gate, names=None, shares_kv=False):
         names = names or {}
         n = lambda key, default: prefix + names.get(key, default)
         self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, head_dim
@@ -36,8 +36,13 @@ class GQAttention(Mixer):
         self.qk_norm_eps = qk_norm_eps           # None: no head norm
         self.output_gate = bool(output_gate)
         self.q_size, self.kv_size = heads * head_dim, kv_heads * head_dim
-        mats = [n("q", "attn_q.weight"), n("k", "attn_k.weight"), n("v", "attn_v.weight")]
-        rows = [self.q_size, self.kv_size, self.kv_size]
+        # shares_kv: this layer has no key/value projections of its own; it attends over the keys
+        # and values of the layer that owns the state unit the plan gives it
+        self.shares_kv = bool(shares_kv)
+        mats, rows = [n("q", "attn_q.weight")], [self.q_size]
+        if not self.shares_kv:
+            mats += [n("k", "attn_k.weight"), n("v", "attn_v.weight")]
+            rows += [self.kv_size, self.kv_size]
         if self.output_gate:
             mats.append(n("gate", "attn_gate.weight"))
             rows.append(heads)
@@ -54,29 +59,53 @@ class GQAttention(Mixer):
     def tensor_specs(self):
         if self.qk_norm_eps is None:
             return []
-        return [TensorSpec(self.q_norm_name, (self.head_dim,), "norm"),
-                TensorSpec(self.k_norm_name, (self.head_dim,), "norm")]
+        specs = [TensorSpec(self.q_norm_name, (self.head_dim,), "norm")]
+        if not self.shares_kv:
+            specs.append(TensorSpec(self.k_norm_name, (self.head_dim,), "norm"))
+        return specs
 
     def bind(self, tensors, rt):
         if self.qk_norm_eps is not None:
             self.q_norm_w = tensors[self.q_norm_name].to(torch.float32).contiguous()
-            self.k_norm_w = tensors[self.k_norm_name].to(torch.float32).contiguous()
-            self._bound = [self.q_norm_w, self.k_norm_w]
+            self._bound = [self.q_norm_w]
+            if not self.shares_kv:
+                self.k_norm_w = tensors[self.k_norm_name].to(torch.float32).contiguous()
+                self._bound.append(self.k_norm_w)
 
     def state_spec(self):
         return KVStateSpec(self.kv_heads, self.head_dim, self.window)
 
     def forward(self, rt, batch, x, state):
         QS, KVS, QH, KVH, HD = self.q_size, self.kv_size, self.heads, self.kv_heads, self.head_dim
-        qkvg = self.qkvg.apply(rt, x)                                   # [T, QS + 2 KVS (+ QH)]
-        kernels.qk_prepare(qkvg, self.q_norm_w, self.k_norm_w, self.position.rate_table(), batch.tok_pos,
-                           batch.tok_seq, batch.seq_slot, batch.seq_end, state.pool, state.pages, state.ptab,
-                           state.ring, QH, KVH, HD, self.qk_norm_eps or 0.0)
-        q = qkvg[:, :QS]
-        gate = qkvg[:, QS + 2 * KVS:] if self.output_gate else None
+        if self.shares_kv != (not state.owned):
+            raise ValueError("a layer that shares keys and values must be given another layer's state unit "
+                             "by the plan (owns_state=False), and only such a layer")
+        proj = self.qkvg.apply(rt, x)                  # [T, QS + 2 KVS (+ QH)], or [T, QS (+ QH)] when sharing
+        if self.shares_kv:
+            # q only: head norm and rotation over the q heads, nothing written to the cache
+            kernels.qk_prepare(proj, self.q_norm_w, None, self.position.rate_table(), batch.tok_pos, batch.tok_seq,
+                               batch.seq_slot, batch.seq_end, None, 0, None, 0, QH, 0, HD, self.qk_norm_eps or 0.0)
+            gate = proj[:, QS:] if self.output_gate else None
+        else:
+            kernels.qk_prepare(proj, self.q_norm_w, self.k_norm_w, self.position.rate_table(), batch.tok_pos,
+                               batch.tok_seq, batch.seq_slot, batch.seq_end, state.pool, state.pages, state.ptab,
+                               state.ring, QH, KVH, HD, self.qk_norm_eps or 0.0)
+            gate = proj[:, QS + 2 * KVS:] if self.output_gate else None
+        q = proj[:, :QS]
         ctx = torch.empty((batch.T, QS), dtype=x.dtype, device=x.device)
         if batch.prefill:
-            k, v = qkvg[:, QS:QS + KVS], qkvg[:, QS + KVS:QS + 2 * KVS]
+            if self.shares_kv:
+                # the owner left this step's keys and values for its readers; bring them beside q so
+                # that the attention kernel sees one packed buffer
+                k_own, v_own = batch.shared[("kv", state.unit)]
+                packed = torch.empty((batch.T, QS + 2 * KVS), dtype=x.dtype, device=x.device)
+                packed[:, :QS].copy_(q)
+                packed[:, QS:QS + KVS].copy_(k_own)
+                packed[:, QS + KVS:].copy_(v_own)
+                q, k, v = packed[:, :QS], packed[:, QS:QS + KVS], packed[:, QS + KVS:]
+            else:
+                k, v = proj[:, QS:QS + KVS], proj[:, QS + KVS:QS + 2 * KVS]
+                batch.shared[("kv", state.unit)] = (k, v)
             rt.attention_prefill(ctx, q, k, v, gate, batch, QH, KVH, HD, self.window, self.scale)
         else:
             n_chunks = batch.decode_chunks(state.spec)

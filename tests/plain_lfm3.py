@@ -205,7 +205,7 @@ def forward(config, tensors, tokens, bf16=False):
     """Logits [T, V] of one whole sequence (src/lfm3.rs:333-524 in order)."""
     r = _round_bf16 if bf16 else _identity
     h = embedding(tensors["model.embed_tokens.weight"], tokens)
-    for l in range(config["num_hidden_layers"]):
+    for l in config.get("layer_order", range(config["num_hidden_layers"])):     # the order of layers is data
         h = block(h, layer_weights(tensors, l), config, layer_kind(config, l), r)
     n = rms_norm(h, tensors["model.norm.weight"], config["norm_eps"], r)
     return n @ lm_head_weight(config, tensors).T          # logits stay unrounded in this build

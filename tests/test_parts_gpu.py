@@ -300,3 +300,93 @@ def test_toy_mixer_with_its_own_state_registers_builds_and_steps():
         eng.release([slots[0]])
         for g, s in zip(got, seqs):
             torch.testing.assert_close(torch.cat(g).double().cpu(), plain(s), rtol=2e-5, atol=2e-5)
+
+
+def test_a_layer_reads_another_layers_cache():
+    """A toy architecture whose third layer has no key/value projections: the plan gives it the
+    state unit of the first layer (owns_state=False), so it attends over that layer's keys and
+    values, in the prompt step (the owner's keys of this step) and in decode steps (the cache)."""
+    from catena_models_b200 import register_architecture
+    from catena_models_b200.api import Model
+    from catena_models_b200.config.base import Reader
+    from catena_models_b200.engine.definition import ModelDefinition, PlanEntry
+    from catena_models_b200.engine.model import DecoderModel
+    from catena_models_b200.parts import build_part
+    from catena_models_b200.weights.random_init import random_tensors
+
+    H, QH, KVH, HD, F, V, EPS, THETA = 48, 3, 1, 16, 80, 60, 1e-5, 10000.0
+
+    class Cfg:
+        @classmethod
+        def from_dict(cls, data, where="config.json"):
+            r = Reader(data, where)
+            r.string("architecture")
+            r.finish()
+            return cls()
+
+    def attention(prefix, shares):
+        return build_part("mixer", "gqa_attention", prefix=prefix, hidden=H, heads=QH, kv_heads=KVH, head_dim=HD,
+                          window=0, position=build_part("position", "rotary", head_dim=HD, theta=THETA),
+                          qk_norm_eps=EPS, output_gate=False, shares_kv=shares)
+
+    def define(cfg):
+        blocks = []
+        for l, shares in enumerate((False, False, True)):
+            pre = f"l{l}."
+            blocks.append(build_part(
+                "block", "sandwich", mixer=attention(pre, shares),
+                feed_forward=build_part("feed_forward", "swiglu", prefix=pre, hidden=H, intermediate=F),
+                input_norm=build_part("norm", "rms", name=pre + "n1", width=H, eps=EPS),
+                ffn_norm=build_part("norm", "rms", name=pre + "n2", width=H, eps=EPS)))
+        plan = [PlanEntry(0, 0), PlanEntry(1, 1), PlanEntry(2, 0, owns_state=False)]
+        return ModelDefinition("toy_shared", V, H, "embed", blocks, plan,
+                               build_part("norm", "rms", name="nf", width=H, eps=EPS), None)
+
+    register_architecture("toy_shared", Cfg, define, replace=True)
+    config = dict(architecture="toy_shared")
+    raw = random_tensors(define(Cfg()).tensor_specs(), 9, std=0.2, norm_weights="random")
+    assert "l2.attn_k.weight" not in raw and "l2.attn_q.weight" in raw
+    w = {k: v.double() for k, v in raw.items()}
+    model = Model(DecoderModel.from_tensors(config, raw, torch.float32, DEV), max_tokens=512)
+    assert len(model.decoder.state_specs) == 2                    # two state units for three layers
+
+    def plain(tokens):
+        T = len(tokens)
+        pos = torch.arange(T)
+        ones = torch.ones(HD // 2, dtype=torch.float64)
+        h = w["embed"][tokens]
+        kv = {}
+        for l in range(3):
+            pre = f"l{l}."
+            n = P.rms_norm(h, w[pre + "n1"], EPS)
+            q = P.rms_norm((n @ w[pre + "attn_q.weight"].T).view(T, QH, HD), w[pre + "attn_q_norm.weight"], EPS)
+            q = P.rope(q, pos, THETA, ones, sliding=True)
+            if l < 2:
+                k = P.rms_norm((n @ w[pre + "attn_k.weight"].T).view(T, KVH, HD), w[pre + "attn_k_norm.weight"], EPS)
+                kv[l] = (P.rope(k, pos, THETA, ones, sliding=True), (n @ w[pre + "attn_v.weight"].T).view(T, KVH, HD))
+            k, v = kv[0] if l == 2 else kv[l]
+            ctx = torch.zeros(T, QH, HD, dtype=torch.float64)
+            for hq in range(QH):
+                s = (q[:, hq] @ k[:, 0].T) * HD ** -0.5
+                s = s.masked_fill(P.attention_mask(T, 0), float("-inf"))
+                ctx[:, hq] = torch.softmax(s, -1) @ v[:, 0]
+            h = h + ctx.reshape(T, QH * HD) @ w[pre + "attn_output.weight"].T
+            h = h + P.swiglu_ffn(P.rms_norm(h, w[pre + "n2"], EPS), {k2[len(pre):]: v2 for k2, v2 in w.items() if k2.startswith(pre)})
+        return P.rms_norm(h, w["nf"], EPS) @ w["embed"].T
+
+    eng = model.engine
+    seqs = [[1, 5, 9, 13, 17, 21, 25, 29, 33, 37, 41], [2, 4, 6]]
+    slots = eng.admit(2)
+    got = [[], []]
+    out = eng.step(slots, [seqs[0][:7], seqs[1][:2]], [list(range(7)), [0, 1]])
+    got[0].append(out[:7].clone())
+    got[1].append(out[7:].clone())
+    out = eng.step(slots, [[seqs[0][7]], [seqs[1][2]]])
+    got[0].append(out[0:1].clone())
+    got[1].append(out[1:2].clone())
+    eng.release([slots[1]])
+    for t in range(8, 11):
+        got[0].append(eng.step([slots[0]], [[seqs[0][t]]]).clone())
+    eng.release([slots[0]])
+    for g, s in zip(got, seqs):
+        torch.testing.assert_close(torch.cat(g).double().cpu(), plain(s), rtol=2e-5, atol=2e-5)

@@ -33,7 +33,11 @@ TINY_L = dict(
     max_position_embeddings=4096, post_norm=True, attn_output_gate=True)
 RANDOM_L = dict(std=0.05, norm_weights="random", rope_factors="uniform")
 
-ALL = {"A": (TINY_A, RANDOM_A), "B": (TINY_B, RANDOM_B), "C": (TINY_C, RANDOM_B), "L": (TINY_L, RANDOM_L)}
+# R runs its layers in an order of its own: layer 1 (sliding attention) three times, layer 2 last
+TINY_R = dict(TINY_A, layer_order=[0, 1, 1, 3, 2, 1], eos_token_id=[])
+
+ALL = {"A": (TINY_A, RANDOM_A), "B": (TINY_B, RANDOM_B), "C": (TINY_C, RANDOM_B), "L": (TINY_L, RANDOM_L),
+       "R": (TINY_R, RANDOM_B)}
 
 
 def make_folder(tmp, name, seed=0):
