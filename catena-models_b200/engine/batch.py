@@ -6,6 +6,7 @@ one int32 buffer, filled on the host in pinned memory and copied once:
 
     tokens[T] tok_seq[T] tok_pos[T] seq_slot[B] seq_start[B+1] seq_pos0[B] seq_end[B]
     want_rows[W] upd_count[1] upd_index[U] upd_value[U]
+    samp_seq[B] samp_step[B] samp_temp[B] (float bits) samp_seed[2]
 
 `want_rows` are rows of the packed batch whose logits are asked for; `upd_*` are page-table
 entries that the cache allocated for this step (applied on the device before any layer runs).
@@ -26,7 +27,7 @@ class BatchLayout:
         self.T, self.B, self.W, self.U = T, B, W, U
         fields = [("tokens", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B + 1),
                   ("seq_pos0", B), ("seq_end", B), ("want_rows", W), ("upd_count", 1), ("upd_index", U),
-                  ("upd_value", U)]
+                  ("upd_value", U), ("samp_seq", B), ("samp_step", B), ("samp_temp", B), ("samp_seed", 2)]
         self.offsets, off = {}, 0
         for name, n in fields:
             self.offsets[name] = (off, n)
@@ -49,6 +50,8 @@ class StepBatch:
         self.seq_pos0, self.seq_end = v["seq_pos0"], v["seq_end"]
         self.want_rows = v["want_rows"][:n_want]
         self.upd_count, self.upd_index, self.upd_value = v["upd_count"], v["upd_index"], v["upd_value"]
+        self.samp_seq, self.samp_step, self.samp_seed = v["samp_seq"], v["samp_step"], v["samp_seed"]
+        self.samp_temp = v["samp_temp"].view(torch.float32)
         self.prefill = prefill
         self.lengths, self.positions = list(lengths), list(positions)    # host copies, per sequence
         self.B, self.T = layout.B, layout.T
@@ -62,6 +65,37 @@ class StepBatch:
         """Chunks of cache entries the decode attention walks for this state spec."""
         entries = kv_spec.entries(self.chunk_bucket or self.max_end)
         return max(1, (entries + ATTN_DECODE_CHUNK - 1) // ATTN_DECODE_CHUNK)
+
+
+def fill_sampling(layout, host, sampling):
+    """The sampler's inputs of a step: sequence ids, step numbers, temperature, seed."""
+    v = layout.views(host)
+    n = len(sampling.sequence_ids)
+    v["samp_seq"][:n] = sampling.sequence_ids
+    v["samp_step"][:n] = sampling.steps
+    v["samp_temp"][:n] = np.float32(sampling.temperature).view(np.int32)
+    v["samp_seed"][0] = np.uint32(sampling.seed & 0xFFFFFFFF).view(np.int32)
+    v["samp_seed"][1] = np.uint32((sampling.seed >> 32) & 0xFFFFFFFF).view(np.int32)
+
+
+def fill_host_decode(layout, host, slots, tokens, positions, updates):
+    """A decode step (one token per sequence, every row wanted) written with whole-array stores."""
+    v = layout.views(host)
+    B = len(slots)
+    ar = np.arange(B + 1, dtype=np.int32)
+    pos = np.asarray(positions, dtype=np.int32)
+    v["tokens"][:B] = tokens
+    v["tok_seq"][:B] = ar[:B]
+    v["tok_pos"][:B] = pos
+    v["seq_slot"][:B] = slots
+    v["seq_start"][:B + 1] = ar
+    v["seq_pos0"][:B] = pos
+    v["seq_end"][:B] = pos + 1
+    v["want_rows"][:B] = ar[:B]
+    v["upd_count"][0] = len(updates)
+    for i, (idx, page) in enumerate(updates):
+        v["upd_index"][i] = idx
+        v["upd_value"][i] = page
 
 
 def fill_host(layout, host, slots, token_lists, positions, want, updates):

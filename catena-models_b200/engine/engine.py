@@ -13,6 +13,8 @@ copy before each replay.
 """
 from __future__ import annotations
 
+import dataclasses
+
 import numpy as np
 import torch
 
@@ -20,11 +22,21 @@ from ..cache.cache import Cache
 from ..cache.allocators import CacheError, CacheFull
 from .. import kernels as _kernels
 from ..kernels import ATTN_DECODE_CHUNK
-from .batch import BatchLayout, StepBatch, fill_host
+from .batch import BatchLayout, StepBatch, fill_host, fill_host_decode, fill_sampling
 
 
 class StepError(ValueError):
     """A step was refused before anything ran (bad token id, unknown slot, mixed batch...)."""
+
+
+@dataclasses.dataclass
+class Sampling:
+    """What the on-device sampler needs for one step: greedy when temperature is 0, else
+    temperature sampling with a uniform keyed by (seed, sequence id, step) per sequence."""
+    sequence_ids: list
+    steps: list
+    temperature: float = 0.0
+    seed: int = 0
 
 
 class _Staging:
@@ -58,6 +70,8 @@ class _DecodeGraph:
 
 
 class Engine:
+    fused_sampling = True          # step(..., sampling=...) chooses the next tokens on the device
+
     def __init__(self, model, max_tokens, max_seqs=None, use_graphs=True):
         self.model, self.rt = model, model.rt
         max_len = model.definition.max_positions or None
@@ -66,6 +80,7 @@ class Engine:
         self.use_graphs = use_graphs
         self._staging = _Staging()
         self._graphs = {}
+        self._sampled_host = None
         self.steps_run = 0
         self.kernel_launches = 0
 
@@ -132,30 +147,81 @@ class Engine:
             raise
         return updates
 
-    def step(self, slots, tokens, want=None):
+    def step(self, slots, tokens, want=None, sampling=None):
         """Run one step.  `tokens[i]` are the next tokens of the sequence in `slots[i]`;
         `want[i]` the places among them whose logits are returned (default: the last).
         Returns float32 logits [sum(len(want[i])), vocab] on the device, in the order of
-        `slots` and of `want`.  The tensor is valid until the next step of the same size."""
-        positions, prefill, want = self._check(slots, tokens, want)
-        updates = self._reserve(slots, positions, tokens)
+        `slots` and of `want`.  The tensor is valid until the next step of the same size.
+
+        With `sampling` (a `Sampling` record; `want` must be left at its default) the next token
+        of every sequence is chosen on the device in the same submission and the call returns
+        `(logits, tokens)` with `tokens` a list of Python ints: one host-to-device copy of the
+        step's inputs, one device-to-host copy of its result."""
         book = self.cache.book
-        B, T = len(slots), sum(len(t) for t in tokens)
-        if prefill or not self.use_graphs:
-            n_want = sum(len(w) for w in want)
-            layout = BatchLayout(T, B, n_want, len(updates))
-            host, idx = self._staging.take(layout.size)
-            fill_host(layout, host.numpy(), slots, tokens, positions, want, updates)
-            dev = host[:layout.size].to(self.rt.device, non_blocking=True)
-            self._staging.mark(idx)
-            batch = StepBatch(layout, dev, prefill, [len(t) for t in tokens], positions, n_want, len(updates))
-            logits = self.model.forward(batch, self.cache)
+        if sampling is not None and want is not None:
+            raise StepError("sampling takes the last place of every sequence; leave `want` out")
+        decode = self.use_graphs and want is None and self._is_plain_decode(slots, tokens)
+        if decode:
+            positions = [book.length[s] for s in slots]
+            flat = [t[0] for t in tokens]
+            V = self.model.vocab_size
+            if min(flat) < 0 or max(flat) >= V:
+                raise StepError(f"token id outside the vocabulary of {V}")
+            # a decode step needs a new page only when a sequence stands on a page border
+            updates = self._reserve(slots, positions, tokens) if any(p % 64 == 0 for p in positions) else []
+            logits, sampled = self._decode_graph_step(slots, flat, positions, updates, sampling)
+            for s, p in zip(slots, positions):
+                book.length[s] = p + 1
         else:
-            logits = self._decode_graph_step(slots, tokens, positions, want, updates)
-        for s, p, t in zip(slots, positions, tokens):
-            book.advance(s, p + len(t))
+            positions, prefill, want = self._check(slots, tokens, want)
+            updates = self._reserve(slots, positions, tokens)
+            B, T = len(slots), sum(len(t) for t in tokens)
+            if not prefill and self.use_graphs:
+                # decode with explicit wanted places: the graph computes every row, pick the wanted
+                logits, sampled = self._decode_graph_step(slots, [t[0] for t in tokens], positions, updates, sampling)
+                if any(w != [0] for w in want):
+                    logits = logits[[b for b, w in enumerate(want) for _ in w]]
+            else:
+                n_want = sum(len(w) for w in want)
+                layout = BatchLayout(T, B, n_want, len(updates))
+                host, idx = self._staging.take(layout.size)
+                fill_host(layout, host.numpy(), slots, tokens, positions, want, updates)
+                if sampling is not None:
+                    fill_sampling(layout, host.numpy(), sampling)
+                dev = host[:layout.size].to(self.rt.device, non_blocking=True)
+                self._staging.mark(idx)
+                batch = StepBatch(layout, dev, prefill, [len(t) for t in tokens], positions, n_want, len(updates))
+                logits = self.model.forward(batch, self.cache)
+                sampled = None
+                if sampling is not None:
+                    sampled = torch.empty(B, dtype=torch.int32, device=self.rt.device)
+                    _kernels.sample(sampled, logits, batch.samp_temp[:B], batch.samp_seq[:B], batch.samp_step[:B],
+                                    batch.samp_seed)
+            for s, p, t in zip(slots, positions, tokens):
+                book.advance(s, p + len(t))
         self.steps_run += 1
-        return logits
+        if sampling is None:
+            return logits
+        return logits, self._to_host(sampled)
+
+    def _is_plain_decode(self, slots, tokens):
+        """Every slot live and started, one token each, no slot twice: the lean path may take it."""
+        length = self.cache.book.length
+        if not slots or len(tokens) != len(slots) or len(set(slots)) != len(slots):
+            return False
+        for s, t in zip(slots, tokens):
+            if length.get(s, 0) == 0 or len(t) != 1:
+                return False
+        return True
+
+    def _to_host(self, sampled):
+        """Sampled tokens as Python ints (pinned buffer, one copy, one synchronisation)."""
+        n = sampled.shape[0]
+        if self._sampled_host is None or self._sampled_host.numel() < n:
+            self._sampled_host = torch.empty(max(64, 2 * n), dtype=torch.int32, pin_memory=True)
+        self._sampled_host[:n].copy_(sampled, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._sampled_host[:n].tolist()
 
     # ------------------------------------------------------------------ captured decode
     @staticmethod
@@ -165,34 +231,46 @@ class Engine:
             b *= 2
         return b
 
-    def _decode_graph_step(self, slots, tokens, positions, want, updates):
+    def _decode_graph_step(self, slots, flat_tokens, positions, updates, sampling):
         B = len(slots)
         bucket = self._bucket(max(positions) + 1)
         key = (B, bucket)
-        all_rows = [[0]] * B
         entry = self._graphs.get(key)
         if entry is None:
             layout = BatchLayout(B, B, B, B * max(1, self.n_kv_groups))
             device_buf = torch.zeros(layout.size, dtype=torch.int32, device=self.rt.device)
             entry = _DecodeGraph(layout, device_buf, None, None, None)
+            entry.sampled = torch.zeros(B, dtype=torch.int32, device=self.rt.device)
             self._graphs[key] = entry
         layout = entry.layout
         host, idx = self._staging.take(layout.size)
-        fill_host(layout, host.numpy(), slots, tokens, positions, all_rows, updates)
+        view = host.numpy()
+        fill_host_decode(layout, view, slots, flat_tokens, positions, updates)
+        if sampling is not None:
+            fill_sampling(layout, view, sampling)
         entry.device_buf.copy_(host[:layout.size], non_blocking=True)
         self._staging.mark(idx)
         if entry.graph is None:
             # First step of this size: run it eagerly (this is the step's result; it also loads
             # every kernel, which must not happen inside a capture), then record the same
             # launches into a graph for the steps that follow.  A capture executes nothing, so
-            # the cache and the fixed-size states advance exactly once.
+            # the cache and the fixed-size states advance exactly once.  The graph always ends
+            # with the sampling kernel; without a sampling request its output is ignored
+            # (temperature 0 and zeroed keys then make it an argmax).
             batch = StepBatch(layout, entry.device_buf, False, [1] * B, positions, B, len(updates))
             batch.chunk_bucket = bucket
-            logits = self.model.forward(batch, self.cache)
+
+            def run():
+                out = self.model.forward(batch, self.cache)
+                _kernels.sample(entry.sampled, out, batch.samp_temp[:B], batch.samp_seq[:B], batch.samp_step[:B],
+                                batch.samp_seed)
+                return out
+
+            logits = run()
             graph = torch.cuda.CUDAGraph()
             before = _kernels.launches
             with torch.cuda.graph(graph):
-                entry.logits = self.model.forward(batch, self.cache)
+                entry.logits = run()
             entry.launches = _kernels.launches - before       # kernels one replay runs
             _kernels.launches = before                         # the capture itself ran nothing
             entry.graph, entry.batch = graph, batch
@@ -200,7 +278,4 @@ class Engine:
             entry.graph.replay()
             _kernels.launches += entry.launches
             logits = entry.logits
-        if all(w == [0] for w in want):
-            return logits
-        rows = [b for b, w in enumerate(want) for _ in w]
-        return logits[rows]
+        return logits, entry.sampled

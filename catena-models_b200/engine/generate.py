@@ -62,11 +62,20 @@ def run_batch(engine, sampler, requests, ids, max_new_tokens, stop_token_ids, ig
         return
     slots = engine.admit(len(requests))
     live = list(range(len(requests)))
+    # An engine that samples on the device in the same submission as the step (`fused_sampling`)
+    # is asked to; any other pair of engine and sampler goes the two-call way.
+    fused = getattr(engine, "fused_sampling", False) and hasattr(sampler, "request")
+
+    def run_step(step_slots, step_tokens, step):
+        if fused:
+            return engine.step(step_slots, step_tokens, sampling=sampler.request([ids[i] for i in live], step))[1]
+        logits = engine.step(step_slots, step_tokens)
+        return sampler.sample(logits, [ids[i] for i in live], [step] * len(live))
+
     try:
-        logits = engine.step(slots, [r.prompt for r in requests])
         step = 0
+        tokens = run_step(slots, [r.prompt for r in requests], step)
         while True:
-            tokens = sampler.sample(logits, [ids[i] for i in live], [step] * len(live))
             still = []
             for i, tok in zip(live, tokens):
                 r = requests[i]
@@ -83,7 +92,7 @@ def run_batch(engine, sampler, requests, ids, max_new_tokens, stop_token_ids, ig
             if not live:
                 break
             step += 1
-            logits = engine.step([slots[i] for i in live], [[requests[i].tokens[-1]] for i in live])
+            tokens = run_step([slots[i] for i in live], [[requests[i].tokens[-1]] for i in live], step)
     finally:
         engine.release([s for s in slots if s is not None])
 

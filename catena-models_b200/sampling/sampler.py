@@ -24,6 +24,12 @@ class Sampler:
         self.temperature, self.seed = float(temperature), int(seed)
         self._cap = 0
 
+    def request(self, sequence_ids, step):
+        """The record an engine with on-device sampling takes in place of a separate call."""
+        from ..engine.engine import Sampling
+
+        return Sampling(list(sequence_ids), [step] * len(sequence_ids), self.temperature, self.seed)
+
     @staticmethod
     def staging_ints(n):
         """int32 words copied to the device per call for n rows (ids, steps, temperatures, seed)."""
