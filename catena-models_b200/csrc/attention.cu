@@ -46,7 +46,9 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
                                   int ptab_stride, int ring, int QH, int KVH, int HD, float eps) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float ubuf[];              // [warps][HD]
+    // a lane owns the rotation pairs (i, i + HD/2) for i = lane, lane + 32, ...: no exchange between
+    // lanes is needed beyond the sum of squares
+    constexpr int MAXP = 4;                       // pairs per lane: head sizes up to 256
     const int lane = threadIdx.x, warp = threadIdx.y;
     const int head = blockIdx.x * blockDim.y + warp;
     const int t = blockIdx.y;
@@ -54,24 +56,34 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
     const bool is_q = head < QH;
     const int kvh = head - QH;
     T* x = qkv + (long long)t * ld + (is_q ? (long long)head * HD : (long long)QH * HD + (long long)kvh * HD);
-    float* u = ubuf + warp * HD;
     const float* w = is_q ? wq : wk;
     const int pos = tok_pos[t];
     const int half = HD >> 1;
 
+    float lo[MAXP], hi[MAXP];
     float ss = 0.f;
-    for (int d = lane; d < HD; d += 32) {
-        const float v = to_f32(x[d]);
-        u[d] = v;
-        ss += v * v;
+#pragma unroll
+    for (int p = 0; p < MAXP; ++p) {
+        const int i = lane + 32 * p;
+        lo[p] = hi[p] = 0.f;
+        if (i < half) {
+            lo[p] = to_f32(x[i]);
+            hi[p] = to_f32(x[i + half]);
+            ss += lo[p] * lo[p] + hi[p] * hi[p];
+        }
     }
     if (w) {
         ss = warp_sum(ss);
         const float inv = 1.f / sqrtf(ss / (float)HD + eps);
-        for (int d = lane; d < HD; d += 32) u[d] = rounded<T>((u[d] * inv) * w[d]);
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p) {
+            const int i = lane + 32 * p;
+            if (i < half) {
+                lo[p] = rounded<T>((lo[p] * inv) * w[i]);
+                hi[p] = rounded<T>((hi[p] * inv) * w[i + half]);
+            }
+        }
     }
-    __syncwarp();
-
     T* kdst = nullptr;
     T* vdst = nullptr;
     if (!is_q && pool) {
@@ -86,18 +98,24 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
             vdst = kv_tile(pool, 1, pages, page, kvh, KVH, HD) + (long long)row * HD;
         }
     }
-    for (int d = lane; d < HD; d += 32) {
-        float o = u[d];
+#pragma unroll
+    for (int p = 0; p < MAXP; ++p) {
+        const int i = lane + 32 * p;
+        if (i >= half) continue;
+        float a = lo[p], bq = hi[p];
         if (rate) {
-            const int i = d < half ? d : d - half;
-            const float a = (float)pos * rate[i];
-            float s, c;
-            sincosf(a, &s, &c);
-            o = d < half ? u[d] * c - u[d + half] * s : u[d] * c + u[d - half] * s;
+            float sn, cs;
+            sincosf((float)pos * rate[i], &sn, &cs);
+            a = lo[p] * cs - hi[p] * sn;
+            bq = hi[p] * cs + lo[p] * sn;
         }
-        const T ot = from_f32<T>(o);
-        x[d] = ot;
-        if (kdst) kdst[d] = ot;
+        const T at = from_f32<T>(a), bt = from_f32<T>(bq);
+        x[i] = at;
+        x[i + half] = bt;
+        if (kdst) {
+            kdst[i] = at;
+            kdst[i + half] = bt;
+        }
     }
     if (vdst) {
         const T* v = x + (long long)KVH * HD;
@@ -113,9 +131,9 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
     if (T <= 0) return CM_OK;
     if (HD % 2 || HD <= 0) CM_REFUSE("qk_prepare: head size %d is not even", HD);
     if (ring % PAGE_TOKENS) CM_REFUSE("qk_prepare: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
+    if (HD > 256) CM_REFUSE("qk_prepare: head size %d above 256", HD);
     dim3 block(32, 4), grid((QH + KVH + 3) / 4, T);
-    const size_t smem = 4 * (size_t)HD * sizeof(float);
-    if (smem > 48 * 1024) CM_REFUSE("qk_prepare: head size %d too large", HD);
+    const size_t smem = 0;
     if (dt == DT_F32)
         cm_launch(qk_prepare_kernel<float>, grid, block, smem, st, (float*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
                                                             seq_slot, seq_end, (float*)pool, pages, ptab,

@@ -40,40 +40,6 @@ extern "C" int cm_embed_gather(int dt, void* out, const void* table, const int* 
 #define NV_THREADS 256
 #define NV_MAXC 4
 
-template <typename T>
-__device__ __forceinline__ void load8f(const T* p, float* out);
-template <>
-__device__ __forceinline__ void load8f<float>(const float* p, float* out) {
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
-}
-template <>
-__device__ __forceinline__ void load8f<bf16>(const bf16* p, float* out) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(p);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(h[i]);
-        out[2 * i] = f.x;
-        out[2 * i + 1] = f.y;
-    }
-}
-template <typename T>
-__device__ __forceinline__ void store8f(T* p, const float* v);
-template <>
-__device__ __forceinline__ void store8f<float>(float* p, const float* v) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
-}
-template <>
-__device__ __forceinline__ void store8f<bf16>(bf16* p, const float* v) {
-    uint4 raw;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    *reinterpret_cast<uint4*>(p) = raw;
-}
-
 // -------------------------------------------------------------------------- RMSNorm
 // y = T((x * inv) * w), inv = 1/sqrt(mean(x^2) + eps); w is float.
 template <typename T, int C>

@@ -60,6 +60,77 @@ __global__ void shortconv_kernel(T* __restrict__ y, const T* __restrict__ bcx, l
     }
 }
 
+// The same, eight channels per thread with 16-byte accesses (H a multiple of 8, aligned rows).
+template <typename T>
+__global__ void __launch_bounds__(128)
+shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld, const float* __restrict__ w,
+                     float* __restrict__ state, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                     const int* __restrict__ seq_slot, int H, int K, int from_zero) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    const int t = blockIdx.y;
+    if (c >= H) return;
+    const int b = tok_seq[t];
+    const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
+    const int i = t - s0;
+    float* st = state + (long long)seq_slot[b] * (K - 1) * H + c;
+    float z[8], cur[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) z[e] = cur[e] = 0.f;
+    for (int j = 0; j < K; ++j) {
+        const int r = i + j - (K - 1);
+        float sv[8];
+        if (r >= 0) {
+            const T* row = bcx + (long long)(s0 + r) * ld;
+            float bb[8], xx[8];
+            load8f<T>(row + c, bb);
+            load8f<T>(row + 2 * H + c, xx);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sv[e] = bb[e] * xx[e];
+        } else if (from_zero) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sv[e] = 0.f;
+        } else {
+            load8f<float>(st + (long long)(K - 1 + r) * H, sv);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            z[e] += w[(long long)(c + e) * K + j] * sv[e];
+            if (j == K - 1) cur[e] = sv[e];
+        }
+    }
+    float cc[8], out[8];
+    load8f<T>(bcx + (long long)t * ld + H + c, cc);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = z[e] * cc[e];
+    store8f<T>(y + (long long)t * H + c, out);
+
+    if (i == len - 1) {
+        for (int j = 0; j < K - 1; ++j) {
+            const int r = len + j - (K - 1);
+            float sv[8];
+            if (r == len - 1) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sv[e] = cur[e];
+            } else if (r >= 0) {
+                const T* row = bcx + (long long)(s0 + r) * ld;
+                float bb[8], xx[8];
+                load8f<T>(row + c, bb);
+                load8f<T>(row + 2 * H + c, xx);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sv[e] = bb[e] * xx[e];
+            } else if (from_zero) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sv[e] = 0.f;
+            } else {
+                load8f<float>(st + (long long)(len + j) * H, sv);       // len + j > j: not yet overwritten
+            }
+            store8f<float>(st + (long long)j * H, sv);
+        }
+    }
+}
+
 extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, const float* w, float* state,
                             const int* tok_seq, const int* seq_start, const int* seq_slot, int T, int H,
                             int K, int from_zero, int one_token_each, cudaStream_t st) {
@@ -67,6 +138,20 @@ extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, cons
     if (K < 2 || K > SC_MAXK) CM_REFUSE("shortconv: %d taps (2..%d)", K, SC_MAXK);
     if (!from_zero && !one_token_each)
         CM_REFUSE("shortconv: several tokens of a sequence on top of a stored state are not supported");
+    const bool vec = H % 8 == 0 && ld % 8 == 0 && (((uintptr_t)y | (uintptr_t)bcx | (uintptr_t)state) & 15) == 0;
+    if (vec) {
+        dim3 vgrid((H / 8 + 127) / 128, T);
+        if (dt == DT_F32)
+            cm_launch(shortconv_vec_kernel<float>, vgrid, 128, 0, st, (float*)y, (const float*)bcx, ld, w, state,
+                      tok_seq, seq_start, seq_slot, H, K, from_zero);
+        else if (dt == DT_BF16)
+            cm_launch(shortconv_vec_kernel<bf16>, vgrid, 128, 0, st, (bf16*)y, (const bf16*)bcx, ld, w, state, tok_seq,
+                      seq_start, seq_slot, H, K, from_zero);
+        else
+            return CM_ERR_DTYPE;
+        CM_CHECK_LAUNCH();
+        return CM_OK;
+    }
     dim3 grid((H + 127) / 128, T);
     if (dt == DT_F32)
         cm_launch(shortconv_kernel<float>, grid, 128, 0, st, (float*)y, (const float*)bcx, ld, w, state, tok_seq,
