@@ -1,0 +1,91 @@
+"""Layer sizes of the 1.7B-class model (hidden 2048, 32 heads over 8 kv heads of size 64, FFN 8192,
+vocabulary 65536, window 4096) with three layers, against the plain implementation: the sizes at
+which the tensor-core GEMM, the weight-streaming GEMM with its cluster split, the tensor-core
+attention kernels and the 4096-tile output head actually run in the benchmark."""
+import pytest
+import torch
+
+import plain_lfm3
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+BIG = dict(
+    architecture="lfm3", vocab_size=65536, hidden_size=2048, intermediate_size=8192, num_hidden_layers=3,
+    layer_types=["conv", "sliding_attention", "full_attention"], num_attention_heads=32, num_key_value_heads=8,
+    head_dim=64, conv_L_cache=3, sliding_window=4096, rope_theta=1000000.0, norm_eps=1e-5,
+    tie_word_embeddings=True, max_position_embeddings=4096)
+
+
+@pytest.fixture(scope="module")
+def big(tmp_path_factory):
+    from catena_models_b200.weights.random_init import write_random_model
+
+    folder = write_random_model(str(tmp_path_factory.mktemp("big") / "m"), BIG, seed=11, std=0.02,
+                                norm_weights="random", rope_factors="uniform")
+    return folder, plain_lfm3.load_folder(folder, dtype=torch.float32)
+
+
+def rel(got, ref):
+    return float((got.double().cpu() - ref.double()).abs().max() / ref.double().abs().max())
+
+
+def test_prompt_then_decode_in_batches_at_full_width(big):
+    from catena_models_b200.api import Model
+
+    folder, (cfg, tensors) = big
+    lens, extra = [300, 70, 1], 6
+    seqs = [tiny.random_prompt(n + extra, cfg["vocab_size"], seed=n) for n in lens]
+    exact = [plain_lfm3.forward(cfg, tensors, s) for s in seqs]
+    noise = [plain_lfm3.forward(cfg, tensors, s, bf16=True) for s in seqs]
+    for dtype in ("bfloat16", "float32"):
+        model = Model.load(folder, dtype=dtype, max_tokens=1024)
+        eng = model.engine
+        slots = eng.admit(3)
+        want = [[0, n // 2, n - 1] if n > 2 else [0] for n in lens]
+        out = eng.step(slots, [s[:n] for s, n in zip(seqs, lens)], want)
+        got = [[] for _ in lens]
+        pos = [list(w) for w in want]
+        off = 0
+        for i, w in enumerate(want):
+            got[i].append(out[off:off + len(w)].clone())
+            off += len(w)
+        for t in range(extra):
+            out = eng.step(slots, [[s[n + t]] for s, n in zip(seqs, lens)])
+            for i in range(3):
+                got[i].append(out[i:i + 1].clone())
+                pos[i].append(lens[i] + t)
+        eng.release(slots)
+        model.decoder.rt.check_errors()
+        for i in range(3):
+            g, ref = torch.cat(got[i]), exact[i][pos[i]]
+            if dtype == "float32":
+                assert rel(g, ref) < 5e-5                      # the plain model runs in float32 here
+            else:
+                assert rel(g, ref) < 2.0 * rel(noise[i][pos[i]], ref)
+                assert torch.equal(g.argmax(-1).cpu(), ref.argmax(-1)) or rel(g, ref) < 0.02
+        del model, eng
+        torch.cuda.empty_cache()
+
+
+def test_twenty_sequences_decode_on_the_tiled_kernel(big):
+    """17 to 64 rows take the 128-wide tiles of the tensor-core GEMM for the wide products and the
+    weight-streaming kernel for the narrow ones."""
+    from catena_models_b200.api import Model
+
+    folder, (cfg, tensors) = big
+    lens = list(range(1, 21))
+    seqs = [tiny.random_prompt(n + 3, cfg["vocab_size"], seed=100 + n) for n in lens]
+    model = Model.load(folder, dtype="bfloat16", max_tokens=2048)
+    eng = model.engine
+    slots = eng.admit(20)
+    got = [eng.step(slots, [s[:n] for s, n in zip(seqs, lens)]).clone()]
+    for t in range(3):
+        got.append(eng.step(slots, [[s[n + t]] for s, n in zip(seqs, lens)]).clone())
+    eng.release(slots)
+    model.decoder.rt.check_errors()
+    for i, (s, n) in enumerate(zip(seqs, lens)):
+        ref = plain_lfm3.forward(cfg, tensors, s)[n - 1:]
+        noise = plain_lfm3.forward(cfg, tensors, s, bf16=True)[n - 1:]
+        g = torch.stack([step[i] for step in got])
+        assert rel(g, ref) < 2.0 * rel(noise, ref), i
