@@ -50,8 +50,8 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
     // lanes is needed beyond the sum of squares
     constexpr int MAXP = 4;                       // pairs per lane: head sizes up to 256
     const int lane = threadIdx.x, warp = threadIdx.y;
-    const int head = blockIdx.x * blockDim.y + warp;
-    const int t = blockIdx.y;
+    const int head = blockIdx.y * blockDim.y + warp;
+    const int t = blockIdx.x;                     // tokens on x: a step may carry more than 65535 of them
     if (head >= QH + KVH) return;
     const bool is_q = head < QH;
     const int kvh = head - QH;
@@ -132,7 +132,7 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
     if (HD % 2 || HD <= 0) CM_REFUSE("qk_prepare: head size %d is not even", HD);
     if (ring % PAGE_TOKENS) CM_REFUSE("qk_prepare: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
     if (HD > 256) CM_REFUSE("qk_prepare: head size %d above 256", HD);
-    dim3 block(32, 4), grid((QH + KVH + 3) / 4, T);
+    dim3 block(32, 4), grid(T, (QH + KVH + 3) / 4);
     const size_t smem = 0;
     if (dt == DT_F32)
         cm_launch(qk_prepare_kernel<float>, grid, block, smem, st, (float*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,

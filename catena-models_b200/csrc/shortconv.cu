@@ -17,8 +17,8 @@ __global__ void shortconv_kernel(T* __restrict__ y, const T* __restrict__ bcx, l
                                  const int* __restrict__ seq_slot, int H, int K, int from_zero) {
     pdl_trigger();
     pdl_wait();
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    const int t = blockIdx.y;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x;                     // tokens on x: a step may carry more than 65535 of them
     if (c >= H) return;
     const int b = tok_seq[t];
     const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
@@ -68,8 +68,8 @@ shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld,
                      const int* __restrict__ seq_slot, int H, int K, int from_zero) {
     pdl_trigger();
     pdl_wait();
-    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-    const int t = blockIdx.y;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    const int t = blockIdx.x;
     if (c >= H) return;
     const int b = tok_seq[t];
     const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
@@ -140,7 +140,7 @@ extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, cons
         CM_REFUSE("shortconv: several tokens of a sequence on top of a stored state are not supported");
     const bool vec = H % 8 == 0 && ld % 8 == 0 && (((uintptr_t)y | (uintptr_t)bcx | (uintptr_t)state) & 15) == 0;
     if (vec) {
-        dim3 vgrid((H / 8 + 127) / 128, T);
+        dim3 vgrid(T, (H / 8 + 127) / 128);
         if (dt == DT_F32)
             cm_launch(shortconv_vec_kernel<float>, vgrid, 128, 0, st, (float*)y, (const float*)bcx, ld, w, state,
                       tok_seq, seq_start, seq_slot, H, K, from_zero);
@@ -152,7 +152,7 @@ extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, cons
         CM_CHECK_LAUNCH();
         return CM_OK;
     }
-    dim3 grid((H + 127) / 128, T);
+    dim3 grid(T, (H + 127) / 128);
     if (dt == DT_F32)
         cm_launch(shortconv_kernel<float>, grid, 128, 0, st, (float*)y, (const float*)bcx, ld, w, state, tok_seq,
                                                       seq_start, seq_slot, H, K, from_zero);

@@ -487,3 +487,32 @@ def test_attn_prefill_mma_long_and_window_edge(K, window):
     if window:
         expect &= torch.arange(T, device=DEV) < far + window
     assert torch.equal(hit, expect)
+
+
+def test_more_tokens_than_a_grid_dimension_holds(K):
+    """A prompt step may carry more than 65,535 tokens (64 prompts of 2,048): the per-token kernels
+    must not put the token index on a grid axis that ends there."""
+    T, H, taps = 70000, 8, 3
+    bcx = rnd(T, 3 * H, dtype=torch.bfloat16, seed=1)
+    w = rnd(H, taps, seed=2)
+    state = torch.zeros(1, taps - 1, H, device=DEV)
+    tok_seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    starts = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    K.shortconv(y, bcx, w, state, tok_seq, starts, torch.zeros(1, dtype=torch.int32, device=DEV), taps, True, False)
+    b, c, x = bcx[:, :H].float(), bcx[:, H:2 * H].float(), bcx[:, 2 * H:].float()
+    bx = torch.cat([torch.zeros(taps - 1, H, device=DEV), b * x])
+    z = sum(w[:, j][None, :] * bx[j:j + T] for j in range(taps))
+    close(y[-5:], (z * c)[-5:], torch.bfloat16)
+    QH, KVH, HD = 2, 1, 16
+    qkv = rnd(T, (QH + 2 * KVH) * HD, dtype=torch.bfloat16, seed=3)
+    orig = qkv.clone()
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    rate = torch.full((HD // 2,), 0.001, device=DEV)
+    K.qk_prepare(qkv, None, None, rate, pos, tok_seq, torch.zeros(1, dtype=torch.int32, device=DEV),
+                 torch.tensor([T], dtype=torch.int32, device=DEV), None, 0, None, 0, QH, KVH, HD, 0.0)
+    t = T - 1
+    ang = t * 0.001
+    lo, hi = orig[t, :HD // 2].float(), orig[t, HD // 2:HD].float()
+    ref = torch.cat([lo * math.cos(ang) - hi * math.sin(ang), hi * math.cos(ang) + lo * math.sin(ang)])
+    close(qkv[t, :HD], ref, torch.bfloat16)
