@@ -43,83 +43,87 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
                                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                   const int* __restrict__ seq_slot, const int* __restrict__ seq_end,
                                   T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
-                                  int ptab_stride, int ring, int QH, int KVH, int HD, float eps) {
+                                  int ptab_stride, int ring, int QH, int KVH, int HD, float eps, int T_tokens,
+                                  int heads_per_warp) {
     pdl_trigger();
     pdl_wait();
-    // a lane owns the rotation pairs (i, i + HD/2) for i = lane, lane + 32, ...: no exchange between
-    // lanes is needed beyond the sum of squares
+    // One warp per token and group of `heads_per_warp` heads (grid.y walks the groups: many heads
+    // per warp when tokens are plenty, one when they are few).  A lane owns the rotation pairs (i, i + HD/2)
+    // for i = lane, lane + 32, ...; sine and cosine depend on the position and the pair only, so
+    // they are formed once per token and serve every head.
     constexpr int MAXP = 4;                       // pairs per lane: head sizes up to 256
-    const int lane = threadIdx.x, warp = threadIdx.y;
-    const int head = blockIdx.y * blockDim.y + warp;
-    const int t = blockIdx.x;                     // tokens on x: a step may carry more than 65535 of them
-    if (head >= QH + KVH) return;
-    const bool is_q = head < QH;
-    const int kvh = head - QH;
-    T* x = qkv + (long long)t * ld + (is_q ? (long long)head * HD : (long long)QH * HD + (long long)kvh * HD);
-    const float* w = is_q ? wq : wk;
+    const int lane = threadIdx.x;
+    const int t = blockIdx.x * blockDim.y + threadIdx.y;
+    if (t >= T_tokens) return;
     const int pos = tok_pos[t];
     const int half = HD >> 1;
-
-    float lo[MAXP], hi[MAXP];
-    float ss = 0.f;
+    float sn[MAXP], cs[MAXP];
 #pragma unroll
     for (int p = 0; p < MAXP; ++p) {
         const int i = lane + 32 * p;
-        lo[p] = hi[p] = 0.f;
-        if (i < half) {
-            lo[p] = to_f32(x[i]);
-            hi[p] = to_f32(x[i + half]);
-            ss += lo[p] * lo[p] + hi[p] * hi[p];
+        sn[p] = 0.f;
+        cs[p] = 1.f;
+        if (rate && i < half) sincosf((float)pos * rate[i], &sn[p], &cs[p]);
+    }
+    // where this token's key and value go in the cache (if it is kept at all)
+    int page = -1, row = 0;
+    if (pool) {
+        const int b = tok_seq[t];
+        if (ring == 0 || pos + ring >= seq_end[b]) {
+            const int entry = ring ? pos % ring : pos;
+            page = ptab[(long long)seq_slot[b] * ptab_stride + entry / PAGE_TOKENS];
+            row = entry % PAGE_TOKENS;
         }
     }
-    if (w) {
-        ss = warp_sum(ss);
-        const float inv = 1.f / sqrtf(ss / (float)HD + eps);
+    const int head0 = blockIdx.y * heads_per_warp;
+    const int head1 = min(QH + KVH, head0 + heads_per_warp);
+    for (int head = head0; head < head1; ++head) {
+        const bool is_q = head < QH;
+        T* x = qkv + (long long)t * ld + (long long)head * HD;     // k heads follow the q heads
+        const float* w = is_q ? wq : wk;
+        float lo[MAXP], hi[MAXP];
+        float ss = 0.f;
 #pragma unroll
         for (int p = 0; p < MAXP; ++p) {
             const int i = lane + 32 * p;
+            lo[p] = hi[p] = 0.f;
             if (i < half) {
-                lo[p] = rounded<T>((lo[p] * inv) * w[i]);
-                hi[p] = rounded<T>((hi[p] * inv) * w[i + half]);
+                lo[p] = to_f32(x[i]);
+                hi[p] = to_f32(x[i + half]);
+                ss += lo[p] * lo[p] + hi[p] * hi[p];
+            }
+        }
+        float inv = 1.f;
+        if (w) {
+            ss = warp_sum(ss);
+            inv = 1.f / sqrtf(ss / (float)HD + eps);
+        }
+        T* kdst = (!is_q && page >= 0) ? kv_tile(pool, 0, pages, page, head - QH, KVH, HD) + (long long)row * HD : nullptr;
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p) {
+            const int i = lane + 32 * p;
+            if (i >= half) continue;
+            float a = lo[p], bq = hi[p];
+            if (w) {
+                a = rounded<T>((a * inv) * w[i]);
+                bq = rounded<T>((bq * inv) * w[i + half]);
+            }
+            const T at = from_f32<T>(a * cs[p] - bq * sn[p]), bt = from_f32<T>(bq * cs[p] + a * sn[p]);
+            x[i] = at;
+            x[i + half] = bt;
+            if (kdst) {
+                kdst[i] = at;
+                kdst[i + half] = bt;
             }
         }
     }
-    T* kdst = nullptr;
-    T* vdst = nullptr;
-    if (!is_q && pool) {
-        const int b = tok_seq[t];
-        const int end = seq_end[b];
-        const bool keep = ring == 0 || pos + ring >= end;
-        if (keep) {
-            const int entry = ring ? pos % ring : pos;
-            const int page = ptab[(long long)seq_slot[b] * ptab_stride + entry / PAGE_TOKENS];
-            const int row = entry % PAGE_TOKENS;
-            kdst = kv_tile(pool, 0, pages, page, kvh, KVH, HD) + (long long)row * HD;
-            vdst = kv_tile(pool, 1, pages, page, kvh, KVH, HD) + (long long)row * HD;
+    if (page >= 0) {
+        // the raw values of the key heads this warp handled
+        const T* v = qkv + (long long)t * ld + (long long)(QH + KVH) * HD;
+        for (int kvh = max(0, head0 - QH); kvh < head1 - QH; ++kvh) {
+            T* vdst = kv_tile(pool, 1, pages, page, kvh, KVH, HD) + (long long)row * HD;
+            for (int d = lane; d < HD; d += 32) vdst[d] = v[kvh * HD + d];
         }
-    }
-#pragma unroll
-    for (int p = 0; p < MAXP; ++p) {
-        const int i = lane + 32 * p;
-        if (i >= half) continue;
-        float a = lo[p], bq = hi[p];
-        if (rate) {
-            float sn, cs;
-            sincosf((float)pos * rate[i], &sn, &cs);
-            a = lo[p] * cs - hi[p] * sn;
-            bq = hi[p] * cs + lo[p] * sn;
-        }
-        const T at = from_f32<T>(a), bt = from_f32<T>(bq);
-        x[i] = at;
-        x[i + half] = bt;
-        if (kdst) {
-            kdst[i] = at;
-            kdst[i + half] = bt;
-        }
-    }
-    if (vdst) {
-        const T* v = x + (long long)KVH * HD;
-        for (int d = lane; d < HD; d += 32) vdst[d] = v[d];
     }
 }
 
@@ -132,16 +136,17 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
     if (HD % 2 || HD <= 0) CM_REFUSE("qk_prepare: head size %d is not even", HD);
     if (ring % PAGE_TOKENS) CM_REFUSE("qk_prepare: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
     if (HD > 256) CM_REFUSE("qk_prepare: head size %d above 256", HD);
-    dim3 block(32, 4), grid(T, (QH + KVH + 3) / 4);
+    const int hpw = T >= 512 ? 4 : 1;
+    dim3 block(32, 4), grid((T + 3) / 4, (QH + KVH + hpw - 1) / hpw);
     const size_t smem = 0;
     if (dt == DT_F32)
         cm_launch(qk_prepare_kernel<float>, grid, block, smem, st, (float*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
                                                             seq_slot, seq_end, (float*)pool, pages, ptab,
-                                                            ptab_stride, ring, QH, KVH, HD, eps);
+                                                            ptab_stride, ring, QH, KVH, HD, eps, T, hpw);
     else if (dt == DT_BF16)
         cm_launch(qk_prepare_kernel<bf16>, grid, block, smem, st, (bf16*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
                                                            seq_slot, seq_end, (bf16*)pool, pages, ptab,
-                                                           ptab_stride, ring, QH, KVH, HD, eps);
+                                                           ptab_stride, ring, QH, KVH, HD, eps, T, hpw);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();

@@ -64,7 +64,7 @@ __global__ void shortconv_kernel(T* __restrict__ y, const T* __restrict__ bcx, l
 template <typename T>
 __global__ void __launch_bounds__(128)
 shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld, const float* __restrict__ w,
-                     float* __restrict__ state, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                     const float* __restrict__ w_t, float* __restrict__ state, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
                      const int* __restrict__ seq_slot, int H, int K, int from_zero) {
     pdl_trigger();
     pdl_wait();
@@ -94,9 +94,16 @@ shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld,
         } else {
             load8f<float>(st + (long long)(K - 1 + r) * H, sv);
         }
+        float wj[8];
+        if (w_t) {
+            load8f<float>(w_t + (long long)j * H + c, wj);       // taps stored [K][H]: eight channels at once
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) wj[e] = w[(long long)(c + e) * K + j];
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            z[e] += w[(long long)(c + e) * K + j] * sv[e];
+            z[e] += wj[e] * sv[e];
             if (j == K - 1) cur[e] = sv[e];
         }
     }
@@ -131,7 +138,10 @@ shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld,
     }
 }
 
-extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, const float* w, float* state,
+// w: taps [H][K]; w_t: the same taps stored [K][H] (optional; lets the vector kernel read them
+// eight channels at a time).
+extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, const float* w, const float* w_t,
+                            float* state,
                             const int* tok_seq, const int* seq_start, const int* seq_slot, int T, int H,
                             int K, int from_zero, int one_token_each, cudaStream_t st) {
     if (T <= 0) return CM_OK;
@@ -142,10 +152,10 @@ extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, cons
     if (vec) {
         dim3 vgrid(T, (H / 8 + 127) / 128);
         if (dt == DT_F32)
-            cm_launch(shortconv_vec_kernel<float>, vgrid, 128, 0, st, (float*)y, (const float*)bcx, ld, w, state,
+            cm_launch(shortconv_vec_kernel<float>, vgrid, 128, 0, st, (float*)y, (const float*)bcx, ld, w, w_t, state,
                       tok_seq, seq_start, seq_slot, H, K, from_zero);
         else if (dt == DT_BF16)
-            cm_launch(shortconv_vec_kernel<bf16>, vgrid, 128, 0, st, (bf16*)y, (const bf16*)bcx, ld, w, state, tok_seq,
+            cm_launch(shortconv_vec_kernel<bf16>, vgrid, 128, 0, st, (bf16*)y, (const bf16*)bcx, ld, w, w_t, state, tok_seq,
                       seq_start, seq_slot, H, K, from_zero);
         else
             return CM_ERR_DTYPE;

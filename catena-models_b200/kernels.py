@@ -34,7 +34,7 @@ _SIGNATURES = {
     "cm_attn_prefill_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "cm_attn_decode": [_i, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _i,
                        _i, _f, _vp, _vp, _vp],
-    "cm_shortconv": [_i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "cm_shortconv": [_i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "cm_sample": [_vp, _vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "cm_scatter_i32": [_vp, _vp, _vp, _vp, _i, _vp],
     "cm_zero_rows_f32": [_vp, _vp, _i, _ll, _vp],
@@ -240,9 +240,10 @@ def attn_decode(ctx, q, gate, seq_pos, seq_slot, pool, pages, ptab, ring, window
 
 
 # -------------------------------------------------------------------------- short conv
-def shortconv(y, bcx, w, state, tok_seq, seq_start, seq_slot, K, from_zero, one_token_each):
+def shortconv(y, bcx, w, state, tok_seq, seq_start, seq_slot, K, from_zero, one_token_each, w_t=None):
+    """w: taps [H, K]; w_t: the same stored [K, H] (optional, for 16-byte reads of the taps)."""
     T, H = y.shape
-    _check(lib().cm_shortconv(dtype_code(y.dtype), _ptr(y), _ptr(bcx), bcx.stride(0), _ptr(w), _ptr(state),
+    _check(lib().cm_shortconv(dtype_code(y.dtype), _ptr(y), _ptr(bcx), bcx.stride(0), _ptr(w), _ptr(w_t), _ptr(state),
                               _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slot), T, H, K, int(from_zero),
                               int(one_token_each), _stream()), "shortconv")
 

@@ -23,7 +23,7 @@ class ShortConv(Mixer):
         self.in_proj = Linear(n("in_proj", "shortconv.in_proj.weight"), 3 * hidden, hidden)
         self.out_proj = Linear(n("out_proj", "shortconv.out_proj.weight"), hidden, hidden)
         self.conv_name = n("conv", "shortconv.conv.weight")
-        self.conv_w = None
+        self.conv_w = self.conv_w_t = None
 
     def children(self):
         return [self.in_proj, self.out_proj]
@@ -33,6 +33,7 @@ class ShortConv(Mixer):
 
     def bind(self, tensors, rt):
         self.conv_w = tensors[self.conv_name].to(torch.float32).contiguous()
+        self.conv_w_t = self.conv_w.t().contiguous()          # [taps, hidden]: the kernel reads 8 channels at once
         self._bound = [self.conv_w]
 
     def state_spec(self):
@@ -42,7 +43,7 @@ class ShortConv(Mixer):
         bcx = self.in_proj.apply(rt, x)                                   # [T, 3H]
         y = torch.empty((batch.T, self.hidden), dtype=x.dtype, device=x.device)
         kernels.shortconv(y, bcx, self.conv_w, state.tensor, batch.tok_seq, batch.seq_start, batch.seq_slot,
-                          self.taps, from_zero=batch.prefill, one_token_each=not batch.prefill)
+                          self.taps, from_zero=batch.prefill, one_token_each=not batch.prefill, w_t=self.conv_w_t)
         return self.out_proj.apply(rt, y)
 
 
