@@ -21,6 +21,7 @@
 // its loop, copies still in flight are awaited (bounded again), tensor memory is freed and the
 // block returns.
 #include "common.cuh"
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #define TC_BM 128
@@ -302,6 +303,224 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+__device__ __forceinline__ void store4(bf16* dst, const float* o) {
+    uint2 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+    h[0] = __floats2bfloat162_rn(o[0], o[1]);
+    h[1] = __floats2bfloat162_rn(o[2], o[3]);
+    *reinterpret_cast<uint2*>(dst) = raw;
+}
+__device__ __forceinline__ void store4(float* dst, const float* o) {
+    *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+}
+
+// Few rows (M <= 128), split over K: the form for decode steps of 17 to 128 sequences, where a
+// product has too few 128-column tiles to put every SM to streaming weights.  Grid (column
+// tile, split): the `splits` blocks of a column tile form a thread-block cluster, each takes a
+// contiguous share of the k-slices through the same TMA -> tcgen05 pipeline as above (one
+// accumulator, 128 columns of tensor memory) and leaves its partial sums as float rows in its own
+// shared memory (the drained stage ring).  After a cluster barrier, block r of the cluster adds
+// rows r, r + splits, ... over all blocks in rank order through distributed shared memory,
+// applies the epilogue and stores them; a second cluster barrier keeps every block's shared
+// memory alive until its peers have read it.  The weights' k-slices of the first stages are
+// requested before the wait on the previous kernel, the activations' after it.
+#define TCS_BN 128
+#define TCS_PITCH (TCS_BN + 4)          // floats per staged row: float4 stores of 32 lanes spread over all banks
+
+//
+// A_ROWS (64 or 128) rows of activations are brought per k-slice.  With 64, the upper half of the
+// 128-row operand that the tensor core reads is whatever follows in shared memory (the weights'
+// tile): those accumulator rows are never read, and a row of the product depends on its own row of
+// A only.  Shared memory stays under half an SM's in both forms (4 stages of 24 KB, 3 of 32 KB), so
+// that two blocks share an SM and the next kernel's blocks can request their weights while this
+// kernel's are still adding up.
+template <typename TC, int MODE, int A_ROWS, int TCS_STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 2)
+gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      TC* __restrict__ C, int M, int N, int K, long long ldc, int splits, int* err) {
+    constexpr uint32_t A_BYTES = A_ROWS * TC_BK * 2;
+    constexpr uint32_t B_BYTES = TCS_BN * TC_BK * 2;
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? TCS_BN / 2 : TCS_BN;
+    static_assert((size_t)TCS_STAGES * STAGE_BYTES >= (size_t)A_ROWS * TCS_PITCH * 4, "staged rows must fit the ring");
+    static_assert(TCS_STAGES * STAGE_BYTES <= 104 * 1024, "two blocks per SM");
+    static_assert(STAGE_BYTES >= TC_BM * TC_BK * 2, "the 128-row operand read stays inside its stage");
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bars[2 * TCS_STAGES + 1];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ int issued_kb;
+
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = blockIdx.y;                                 // clusters are (1, splits, 1) and gridDim.y == splits
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int per = (num_kb + splits - 1) / splits;
+    const int kb0 = rank * per;
+    const int my_kb = max(0, min(num_kb, kb0 + per) - kb0);
+    const int n0 = blockIdx.x * OUT_COLS;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    float* stage = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)));
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[TCS_STAGES]);
+    const uint32_t acc_full = smem_u32(&bars[2 * TCS_STAGES]);
+
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        for (int s = 0; s < TCS_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(acc_full, 1);
+        abort_flag = 0;
+        issued_kb = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"((uint32_t)TCS_BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    auto load_b = [&](int i) {
+        const int s = i % TCS_STAGES;
+        const uint32_t b_dst = tiles + s * STAGE_BYTES + A_BYTES;
+        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        if (MODE == TC_MODE_SWIGLU) {
+            tma_load_2d(b_dst, &map_b, full0 + 8 * s, (kb0 + i) * TC_BK, n0);
+            tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, (kb0 + i) * TC_BK, N + n0);
+        } else {
+            tma_load_2d(b_dst, &map_b, full0 + 8 * s, (kb0 + i) * TC_BK, n0);
+        }
+    };
+    auto load_a = [&](int i) {
+        const int s = i % TCS_STAGES;
+        tma_load_2d(tiles + s * STAGE_BYTES, &map_a, full0 + 8 * s, (kb0 + i) * TC_BK, 0);
+    };
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------- TMA loader
+        const int head = min(my_kb, TCS_STAGES);
+        for (int i = 0; i < head; ++i) load_b(i);               // weights do not depend on the previous kernel
+        pdl_wait();
+        for (int i = 0; i < head; ++i) load_a(i);
+        issued_kb = head;
+        for (int i = head; i < my_kb; ++i) {
+            const int s = i % TCS_STAGES;
+            if (!mbar_wait(empty0 + 8 * s, ((i / TCS_STAGES) & 1) ^ 1, &abort_flag, err, TC_ERR_TIMEOUT_LOAD)) break;
+            load_b(i);
+            load_a(i);
+            issued_kb = i + 1;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------- MMA issuer
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TCS_BN >> 3) << 17) |
+                                   ((uint32_t)(TC_BM >> 4) << 24);
+        bool ok = true;
+        for (int i = 0; i < my_kb; ++i) {
+            const int s = i % TCS_STAGES;
+            ok = mbar_wait(full0 + 8 * s, (i / TCS_STAGES) & 1, &abort_flag, err, TC_ERR_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t adesc = umma_desc(tiles + s * STAGE_BYTES);
+            const uint64_t bdesc = umma_desc(tiles + s * STAGE_BYTES + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k) umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
+            umma_commit(empty0 + 8 * s);
+        }
+        if (ok && my_kb > 0) umma_commit(acc_full);
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------- accumulator -> staged float rows
+        pdl_wait();
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        bool ok = true;
+        if (my_kb > 0) ok = mbar_wait(acc_full, 0, &abort_flag, err, TC_ERR_TIMEOUT_EPILOGUE);
+        tc_fence_after();
+        if (ok) {
+            // the ring is drained: every k-slice that was requested has been multiplied
+            const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < TCS_BN / 32; ++c) {
+                float v[32];
+                if (my_kb > 0) {
+                    tmem_load32(t_acc + (uint32_t)(c * 32), v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                }
+                if (row < M) {
+                    float4* dst = reinterpret_cast<float4*>(stage + (size_t)row * TCS_PITCH + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    if (warp < 2) pdl_wait();                                     // stores below must follow the previous kernel
+    __syncwarp();
+    if (splits > 1) cluster.sync(); else __syncthreads();
+
+    // ------------------------------------------------------------------ sum over the cluster, epilogue
+    {
+        const int col = n0 + (MODE == TC_MODE_SWIGLU ? (lane & 15) * 4 : lane * 4);
+        const bool vec_ok = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        for (int row = rank + splits * warp; row < M; row += splits * (TC_THREADS / 32)) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < splits; ++r) {
+                const float* src = splits > 1 ? cluster.map_shared_rank(stage, r) : stage;
+                const float4 x = *reinterpret_cast<const float4*>(src + (size_t)row * TCS_PITCH + lane * 4);
+                acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+            }
+            float o[4] = {acc.x, acc.y, acc.z, acc.w};
+            if (MODE == TC_MODE_SWIGLU) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float u = rounded<TC>(__shfl_down_sync(0xffffffffu, o[i], 16));
+                    const float g = rounded<TC>(o[i]);
+                    o[i] = __fdividef(g, 1.f + __expf(-g)) * u;
+                }
+                if (lane >= 16) continue;
+            }
+            TC* dst = C + (long long)row * ldc + col;
+            if (vec_ok && col + 3 < N) {
+                store4(dst, o);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (col + i < N) dst[i] = from_f32<TC>(o[i]);
+            }
+        }
+    }
+    if (splits > 1) cluster.sync();
+
+    // ------------------------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag && threadIdx.x == 0) {
+        const int issued = issued_kb;
+        for (int kb = max(0, issued - TCS_STAGES); kb < issued; ++kb) {
+            const int s = kb % TCS_STAGES;
+            for (int i = 0; i < TC_SPIN_LIMIT; ++i)
+                if (mbar_try_wait(full0 + 8 * s, (kb / TCS_STAGES) & 1)) break;
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TCS_BN)
+                     : "memory");
+    }
+}
+
 // --------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -377,6 +596,84 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
     return CM_OK;
 }
 
+// How many clusters of `splits` blocks of this kernel the device runs at once (0: not known).
+template <typename TC, int MODE, int A_ROWS, int STAGES>
+static int splitk_active_clusters(int splits, size_t smem) {
+    static int cached[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+    if (cached[splits] >= 0) return cached[splits];
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(8, splits);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = splits;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_splitk_kernel<TC, MODE, A_ROWS, STAGES>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    cached[splits] = n;
+    return n;
+}
+
+// Returns CM_OK after a launch, or 1 when the product is better left to the persistent kernel
+// (enough column tiles for every SM, or no room for clusters).
+template <typename TC, int MODE, int A_ROWS, int STAGES>
+static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, int force_splits, int* err, cudaStream_t st) {
+    constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? TCS_BN / 2 : TCS_BN;
+    const size_t smem = (size_t)STAGES * (A_ROWS * TC_BK * 2 + TCS_BN * TC_BK * 2) + 1024;
+    auto kernel = gemm_tc_splitk_kernel<TC, MODE, A_ROWS, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cm_set_error("gemm_tc: %zu bytes of shared memory refused", smem);
+            cudaGetLastError();
+            return CM_ERR_LAUNCH;
+        }
+        configured = true;
+    }
+    const int n_tiles = (N + OUT_COLS - 1) / OUT_COLS;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    int splits = 1;
+    if (force_splits > 0) {
+        splits = force_splits;
+    } else {
+        // As many blocks as 1.4 per SM (two share an SM; measured on B200 at 64 rows: 16 tiles are
+        // fastest split 8 ways, 48 tiles 4 ways, 128 tiles not at all); every block keeps at least
+        // two k-slices, and the device must have room for such a cluster.
+        static int sm_count = 0;
+        if (!sm_count) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+            if (sm_count <= 0) sm_count = 1;
+        }
+        for (int s = 8; s >= 2; --s) {
+            if (2 * s > num_kb || 5 * n_tiles * s > 7 * sm_count) continue;
+            if (splitk_active_clusters<TC, MODE, A_ROWS, STAGES>(s, smem) > 0) {
+                splits = s;
+                break;
+            }
+        }
+        if (splits == 1) return 1;
+    }
+    CUtensorMap map_a, map_b;
+    int rc = make_map(&map_a, A, M, K, lda, A_ROWS);
+    if (rc != CM_OK) return rc;
+    rc = make_map(&map_b, B, MODE == TC_MODE_SWIGLU ? 2LL * N : N, K, ldb, MODE == TC_MODE_SWIGLU ? TCS_BN / 2 : TCS_BN);
+    if (rc != CM_OK) return rc;
+    cm_launch_cluster(kernel, dim3(n_tiles, splits), TC_THREADS, smem, st, splits, map_a, map_b, (TC*)C, M, N, K, ldc,
+                      splits, err);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
 // A [M,K] and B [N,K] (2N rows when swiglu) bfloat16, row pitches lda/ldb multiples of 8
 // elements, bases 16-byte aligned; C bfloat16 or float.  block_n: 256 (128 x 256 tiles, four
 // stages: the most arithmetic per byte moved) or 128 (128 x 128 tiles, six stages: twice as
@@ -400,4 +697,39 @@ extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M,
     if (dtc == DT_BF16) return launch_tc<128, 6, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     if (dtc == DT_F32) return launch_tc<128, 6, float, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     return CM_ERR_DTYPE;
+}
+
+template <typename TC, int MODE>
+static int launch_splitk(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, int force_splits, int* err, cudaStream_t st) {
+    if (M <= 64) return launch_splitk_rows<TC, MODE, 64, 4>(C, A, B, M, N, K, lda, ldb, ldc, force_splits, err, st);
+    return launch_splitk_rows<TC, MODE, 128, 3>(C, A, B, M, N, K, lda, ldb, ldc, force_splits, err, st);
+}
+
+// The same product for at most 128 rows, with K split over a thread-block cluster when the
+// product has too few column tiles to occupy the device (see gemm_tc_splitk_kernel); otherwise
+// it is handed to cm_gemm_tc with 128-column tiles.  splits: 0 to choose, 1..8 to force.
+extern "C" int cm_gemm_tc_few_rows(int dtc, void* C, const void* A, const void* B, int M, int N, int K,
+                                   long long lda, long long ldb, long long ldc, int swiglu, int splits, int* err,
+                                   cudaStream_t st) {
+    if (M <= 0 || N <= 0) return CM_OK;
+    if (M > TC_BM) CM_REFUSE("gemm_tc_few_rows: %d rows (at most %d)", M, TC_BM);
+    if (splits < 0 || splits > 8) CM_REFUSE("gemm_tc_few_rows: %d splits (0 to 8)", splits);
+    if (K <= 0 || K % 8 || lda % 8 || ldb % 8)
+        CM_REFUSE("gemm_tc: inner size %d and row pitches %lld, %lld must be multiples of 8", K, lda, ldb);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15)
+        CM_REFUSE("gemm_tc: operands must be 16-byte aligned");
+    int rc;
+    if (swiglu) {
+        if (dtc != DT_BF16) return CM_ERR_DTYPE;
+        rc = launch_splitk<bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st);
+    } else if (dtc == DT_BF16) {
+        rc = launch_splitk<bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st);
+    } else if (dtc == DT_F32) {
+        rc = launch_splitk<float, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, splits, err, st);
+    } else {
+        return CM_ERR_DTYPE;
+    }
+    if (rc != 1) return rc;
+    return cm_gemm_tc(dtc, C, A, B, M, N, K, lda, ldb, ldc, swiglu, 128, err, st);
 }

@@ -57,46 +57,54 @@ class Runtime:
     def linear(self, x, w, out_dtype=None):
         """y = x @ w^T; y in the activation dtype unless `out_dtype` says float32."""
         y = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
-        if self._skinny(x, w):
+        kind = self._product_kernel(x, w)
+        if kind == "skinny":
             kernels.gemm_skinny(y, x, w)
-        elif self._tensor_core(x, w):
-            kernels.gemm_tc(y, x, w, err=self.error_flag, block_n=self._tile_width(x))
+        elif kind == "few_rows":
+            kernels.gemm_tc_few_rows(y, x, w, err=self.error_flag)
+        elif kind == "tiled":
+            kernels.gemm_tc(y, x, w, err=self.error_flag)
         else:
             kernels.gemm_simt(y, x, w)
         return y
 
-    def _tensor_core(self, x, w):
-        """Many bfloat16 rows: the TMA-fed tcgen05 kernel (prompt steps)."""
-        return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
-                and x.stride(0) % 8 == 0 and x.stride(1) == 1 and x.data_ptr() % 16 == 0 and w.stride(0) % 8 == 0)
-
     SKINNY_ROWS = 64          # most rows the weight-streaming kernel takes
-    SKINNY_SURE_ROWS = 16     # up to here it is always the better kernel
-    TILED_MIN_OUT = 4096      # above SKINNY_SURE_ROWS: outputs from which 128-wide tiles fill enough SMs
+    SKINNY_BEST_ROWS = 16     # up to here it is the fastest kernel
+    FEW_ROWS = 128            # most rows of the tensor-core kernel that splits K over a cluster
 
-    def _skinny(self, x, w):
-        """Few bfloat16 rows: the weight-streaming kernel (decode steps, wanted rows of the head).
-        Between 17 and 64 rows it re-reads the activations once per 16 weight rows, so wide
-        products go to the tiled tensor-core kernel instead (measured at 64 rows on B200:
-        16384 x 2048 with SwiGLU 39 us against 13 us)."""
+    def _product_kernel(self, x, w):
+        """Which kernel multiplies x by w^T.  Up to 16 bfloat16 rows: the weight-streaming mma.sync
+        kernel (decode steps of small batches, wanted rows of the head).  Up to 128 rows: the
+        tcgen05 kernel that splits K over a cluster when there are few column tiles (measured on
+        B200 at 64 rows, 2048 x 8192: 12.4 us against 26.0 us for the streaming kernel, which
+        re-reads the activations once per 16 weight rows).  More rows: the persistent tcgen05
+        kernel with 128 x 256 tiles.  Operands that TMA cannot take (pitch or base not 16-byte
+        aligned) fall to the streaming kernel while it takes the rows, else to the CUDA-core one,
+        which is also the float32 path."""
         rows = x.shape[0]
-        ok = (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and rows <= self.SKINNY_ROWS
-              and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
-        if ok and rows > self.SKINNY_SURE_ROWS and w.shape[0] >= self.TILED_MIN_OUT and self._tensor_core(x, w):
-            return False
-        return ok
-
-    def _tile_width(self, x):
-        return 256 if x.shape[0] > self.SKINNY_ROWS else 128
+        bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+        streams = (bf16 and rows <= self.SKINNY_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+                   and x.data_ptr() % 16 == 0)
+        tma = (bf16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
+               and x.data_ptr() % 16 == 0 and w.stride(0) % 8 == 0)
+        if streams and (rows <= self.SKINNY_BEST_ROWS or not tma):
+            return "skinny"
+        if tma:
+            return "few_rows" if rows <= self.FEW_ROWS else "tiled"
+        return "simt"
 
     def gate_up_swiglu(self, x, w_gate_up, F):
         """a = silu(x Wgate^T) * (x Wup^T) for the row-packed [Wgate; Wup]."""
         a = torch.empty((x.shape[0], F), dtype=x.dtype, device=x.device)
-        if self._skinny(x, w_gate_up):
+        kind = self._product_kernel(x, w_gate_up)
+        if kind == "skinny":
             kernels.gemm_skinny(a, x, w_gate_up, swiglu=True)
             return a
-        if self._tensor_core(x, w_gate_up):
-            kernels.gemm_tc(a, x, w_gate_up, swiglu=True, err=self.error_flag, block_n=self._tile_width(x))
+        if kind == "few_rows":
+            kernels.gemm_tc_few_rows(a, x, w_gate_up, swiglu=True, err=self.error_flag)
+            return a
+        if kind == "tiled":
+            kernels.gemm_tc(a, x, w_gate_up, swiglu=True, err=self.error_flag)
             return a
         gu = self.linear(x, w_gate_up)
         kernels.swiglu(a, gu)

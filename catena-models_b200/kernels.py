@@ -28,6 +28,7 @@ _SIGNATURES = {
     "cm_gemm_simt": [_i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
     "cm_gemm_skinny": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp],
     "cm_gemm_tc": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp],
+    "cm_gemm_tc_few_rows": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp],
     "cm_qk_prepare": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i,
                       _i, _f, _vp],
     "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
@@ -184,6 +185,24 @@ def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256):
         raise KernelError("gemm_tc takes row-major operands")
     _check(lib().cm_gemm_tc(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
                             y.stride(0), int(swiglu), block_n, _ptr(err), _stream()), "gemm_tc")
+
+
+def gemm_tc_few_rows(y, x, w, swiglu=False, err=None, splits=0):
+    """gemm_tc for at most 128 rows.  When the product has too few 128-column tiles for the
+    device, K is split over a thread-block cluster of up to 8 blocks that add their partial
+    sums through distributed shared memory.  splits: 0 chooses, 1..8 forces."""
+    _need_cuda(y, x, w)
+    M, K = x.shape
+    N = y.shape[1]
+    if w.shape[1] != K or w.shape[0] != (2 * N if swiglu else N) or y.shape[0] != M:
+        raise KernelError(f"gemm_tc_few_rows shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_few_rows takes bfloat16 operands")
+    if x.stride(1) != 1 or w.stride(1) != 1 or y.stride(1) != 1:
+        raise KernelError("gemm_tc_few_rows takes row-major operands")
+    _check(lib().cm_gemm_tc_few_rows(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0),
+                                     w.stride(0), y.stride(0), int(swiglu), splits, _ptr(err), _stream()),
+           "gemm_tc_few_rows")
 
 
 # -------------------------------------------------------------------------- attention

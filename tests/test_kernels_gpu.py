@@ -454,6 +454,46 @@ def test_gemm_tc_swiglu(K, M, F, Kd, block_n):
     close(a, g / (1 + torch.exp(-g)) * u, torch.bfloat16, rtol=2e-2)
 
 
+@pytest.mark.parametrize("splits", [0, 1, 2, 3, 5, 8])
+@pytest.mark.parametrize("M,N,Kd,dty", [(64, 2048, 2048, torch.bfloat16), (17, 200, 520, torch.bfloat16),
+                                        (128, 130, 1096, torch.bfloat16), (33, 384, 4096, torch.float32),
+                                        (100, 70, 72, torch.float32)])
+def test_gemm_tc_few_rows(K, M, N, Kd, dty, splits):
+    """K split over a cluster: every number of blocks (a share of k-slices may be empty or ragged),
+    rows and columns that fill no tile."""
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=1), rnd(N, Kd, dtype=torch.bfloat16, scale=0.1, seed=2)
+    ybuf = torch.full((M, N + 8), float("nan"), dtype=dty, device=DEV)
+    y = ybuf[:, :N]
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.gemm_tc_few_rows(y, x, w, err=err, splits=splits)
+    ref = x.double() @ w.double().T
+    assert int(err) == 0
+    assert bool(torch.isnan(ybuf[:, N:]).all())
+    if dty == torch.float32:
+        torch.testing.assert_close(y.double().cpu(), ref.cpu(), rtol=2e-5, atol=2e-5 * math.sqrt(Kd))
+    else:
+        close(y, ref, torch.bfloat16)
+
+
+@pytest.mark.parametrize("splits", [0, 1, 4, 7])
+@pytest.mark.parametrize("M,F,Kd", [(64, 64, 64), (40, 136, 520), (128, 1000, 2048)])
+def test_gemm_tc_few_rows_swiglu(K, M, F, Kd, splits):
+    x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=1), rnd(2 * F, Kd, dtype=torch.bfloat16, scale=0.2, seed=2)
+    a = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.gemm_tc_few_rows(a, x, w, swiglu=True, err=err, splits=splits)
+    g = (x.double() @ w[:F].double().T).to(torch.bfloat16).double()
+    u = (x.double() @ w[F:].double().T).to(torch.bfloat16).double()
+    assert int(err) == 0
+    close(a, g / (1 + torch.exp(-g)) * u, torch.bfloat16, rtol=2e-2)
+
+
+def test_gemm_tc_few_rows_refuses_more_rows(K):
+    x, w = rnd(129, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16)
+    with pytest.raises(Exception, match="rows"):
+        K.gemm_tc_few_rows(torch.empty(129, 64, dtype=torch.bfloat16, device=DEV), x, w)
+
+
 def test_gemm_tc_strided_operands(K):
     """A is a column block of a wider buffer (the attention context inside qkv-sized rows)."""
     buf = rnd(150, 96 + 40, dtype=torch.bfloat16, seed=3)
