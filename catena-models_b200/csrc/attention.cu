@@ -550,7 +550,7 @@ __global__ void attn_decode_merge_kernel(T* __restrict__ ctx, long long ldc,
 int cm_attn_decode_mma_stage(float* part_o, float* part_ml, const void* q, long long ldq, const int* seq_pos,
                              const int* seq_slot, const void* pool, long long pages, const int* ptab,
                              int ptab_stride, int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
-                             float scale, cudaStream_t st);
+                             float scale, int* n_parts_out, cudaStream_t st);
 
 // Scratch: part_o holds B*QH*n_chunks*HD floats, part_ml B*QH*n_chunks*2 floats.
 // bfloat16 with a head size that is a multiple of 16 up to 128 runs its first stage on the
@@ -591,11 +591,13 @@ extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, l
     } while (0)
     if (dt == DT_BF16 && g_decode_mma && HD % 16 == 0 && HD <= 128 && ldq % 2 == 0 &&
         ((uintptr_t)q & 3) == 0 && ((uintptr_t)pool & 15) == 0) {
+        int n_parts = n_chunks;                    // blocks per (sequence, kv head): at most n_chunks
         const int rc = cm_attn_decode_mma_stage(part_o, part_ml, q, ldq, seq_pos, seq_slot, pool, pages, ptab,
-                                                ptab_stride, ring, window, B, QH, KVH, HD, n_chunks, scale, st);
+                                                ptab_stride, ring, window, B, QH, KVH, HD, n_chunks, scale,
+                                                &n_parts, st);
         if (rc != CM_OK) return rc;
         cm_launch(attn_decode_merge_kernel<bf16>, mgrid, mthreads, 0, st, (bf16*)ctx, ldc, part_o, part_ml,
-                  (const bf16*)gate, ldg, seq_pos, ring, QH, HD, n_chunks);
+                  (const bf16*)gate, ldg, seq_pos, ring, QH, HD, n_parts);
     } else if (dt == DT_F32) {
         AD_DISPATCH(float);
         CM_CHECK_LAUNCH();

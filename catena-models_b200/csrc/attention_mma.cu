@@ -62,7 +62,6 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
     bf16* Qs = reinterpret_cast<bf16*>(fa_smem);              // [BQ][LDS]
     bf16* Ks = Qs + BQ * LDS;                              // [2][FA_BK][LDS]
     bf16* Vs = Ks + 2 * FA_BK * LDS;                          // [2][FA_BK][LDS]
-    pdl_trigger();
     pdl_wait();
     const int b = blockIdx.z, hq = blockIdx.y, hk = hq / (QH / KVH);
     const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
@@ -215,6 +214,7 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
         __syncthreads();                                       // the other buffer is refilled next round
     }
     cp_async_wait<0>();
+    pdl_trigger();                                             // keys and values are read: the next kernel may start up
 
     // ---- normalise, gate, store
 #pragma unroll
@@ -295,15 +295,19 @@ extern "C" int cm_attn_prefill_mma(void* ctx, long long ldc, const void* q, cons
 // Decode attention over the paged cache on the tensor cores (bfloat16, head sizes that are
 // multiples of 16 up to 128).  One new query token per sequence.
 //
-// Grid (chunk, kv head, sequence), chunk = 256 cache entries = 4 pages, one page per warp.  The
-// G = QH/KVH query heads that share the kv head are the rows of the 16-row mma operand (up to
-// 16 per pass), so every key and value that is read serves all of them.  A warp copies its page
-// of K and V into its own shared-memory region (cp.async, rows padded by 16 bytes), forms
-// S = Q K^T and O = P V with mma.sync exactly as the prefill kernel does for one key tile, and
-// leaves (max, sum, unnormalised O) of its page; the four pages of the block are merged in page
-// order and the chunk's partial result goes to the same scratch layout that the CUDA-core
-// kernel uses (cm_attn_decode's merge kernel finishes the job).  Maximum, sum and merging are
-// float; probabilities enter the second product as bfloat16, like in the prefill kernel.
+// Grid (part, kv head, sequence).  The cache entries of a sequence are cut into chunks of 256 =
+// 4 pages; block `part` of n_parts walks chunks part, part + n_parts, ... and its warp w takes
+// page w of each, so the entries that a sequence really holds are spread evenly over the blocks
+// whatever length the grid was sized for.  The G = QH/KVH query heads that share the kv head are
+// the rows of the 16-row mma operand (up to 16 per pass), so every key and value that is read
+// serves all of them.  A warp keeps one page of K and one of V in its own shared-memory region
+// (cp.async, rows padded by 16 bytes) and overlaps copies with arithmetic: while S = Q K^T and
+// the softmax of page i run, V of page i is still arriving; K of page i+1 is requested as soon
+// as S is formed, V of page i+1 as soon as O += P V is done.  Maximum, sum and O are carried
+// from page to page as in the prefill kernel (float; probabilities enter the second product as
+// bfloat16).  The four warps' results are merged in warp order and the block's partial result
+// goes to the scratch layout that the CUDA-core kernel uses, n_parts slots per (sequence, head);
+// cm_attn_decode's merge kernel finishes the job.
 // =========================================================================================
 #define FD_CHUNK 256
 #define FD_PAGE 64
@@ -313,51 +317,58 @@ __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
                        long long ldq, const int* __restrict__ seq_pos, const int* __restrict__ seq_slot,
                        const bf16* __restrict__ pool, long long pages, const int* __restrict__ ptab, int ptab_stride,
-                       int ring, int window, int QH, int KVH, int n_chunks, float scale_log2) {
+                       int ring, int window, int QH, int KVH, int n_parts, float scale_log2) {
     constexpr int LDS = HD + 8;
     constexpr int CH = HD / 8;
     extern __shared__ __align__(16) uint8_t fd_smem[];
     bf16* kv_s = reinterpret_cast<bf16*>(fd_smem);                       // [4 warps][K|V][64][LDS]
-    float* mrg = reinterpret_cast<float*>(fd_smem + (size_t)4 * 2 * FD_PAGE * LDS * sizeof(bf16));   // [4][16][HD+2]
-    pdl_trigger();
+    float* mrg = reinterpret_cast<float*>(fd_smem);                      // [4][16][HD+2], over kv_s once it is done with
+    static_assert((size_t)4 * 16 * (HD + 2) * sizeof(float) <= (size_t)4 * 2 * FD_PAGE * LDS * sizeof(bf16),
+                  "the merge rows must fit the page buffers");
     pdl_wait();
     const int c = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int G = QH / KVH;
     const int pos = seq_pos[b];
     const int n_entries = ring ? min(pos + 1, ring) : pos + 1;
-    const int e0 = c * FD_CHUNK;
-    if (e0 >= n_entries) return;
+    if (c * FD_CHUNK >= n_entries) return;
     const int slot = seq_slot[b];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int page_idx = e0 / FD_PAGE + warp;
-    const bool live = page_idx * FD_PAGE < n_entries;
+    const int page_step = 4 * n_parts;                         // this warp's pages: c*4 + warp, + page_step, ...
     bf16* Ks = kv_s + (size_t)warp * 2 * FD_PAGE * LDS;
     bf16* Vs = Ks + FD_PAGE * LDS;
-    if (live) {
-        const int page = ptab[(long long)slot * ptab_stride + page_idx];
-        const bf16* kp = pool + ((((long long)0 * pages + page) * KVH + hk) * FD_PAGE) * (long long)HD;
-        const bf16* vp = pool + ((((long long)1 * pages + page) * KVH + hk) * FD_PAGE) * (long long)HD;
+    const int* my_ptab = ptab + (long long)slot * ptab_stride;
+    // every full page is wholly visible unless the ring is wider than the window
+    const bool mask_all = window > 0 && ring != window;
+
+    // one of a page's two halves (which: 0 keys, 1 values) into this warp's buffer
+    auto request = [&](bf16* dst, int which, int page_idx) {
+        const int page = my_ptab[page_idx];
+        const bf16* src = pool + ((((long long)which * pages + page) * KVH + hk) * FD_PAGE) * (long long)HD;
         const int rows_here = min(FD_PAGE, n_entries - page_idx * FD_PAGE);
         for (int e = lane; e < FD_PAGE * CH; e += 32) {
             const int r = e / CH, cc = e - r * CH;
-            const bool in = r < rows_here;                     // entries never written are zero-filled: a
-            cp_async16(Ks + r * LDS + cc * 8, kp + (long long)r * HD + cc * 8, in);   // stale NaN times a zero
-            cp_async16(Vs + r * LDS + cc * 8, vp + (long long)r * HD + cc * 8, in);   // probability would be NaN
+            // entries never written are zero-filled: a stale NaN times a zero probability would be NaN
+            cp_async16(dst + r * LDS + cc * 8, src + (long long)r * HD + cc * 8, r < rows_here);
         }
-    }
-    cp_async_commit();
+    };
 
     for (int g0 = 0; g0 < G; g0 += 16) {                   // 16 query heads per pass
         const int ng = min(16, G - g0);
-        float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
         float o[HD / 8][4];
 #pragma unroll
         for (int j = 0; j < HD / 8; ++j)
 #pragma unroll
             for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
-        if (live) {
-            // Q fragments: rows g and g+8 are heads g0+g and g0+g+8 of this kv head (zero beyond ng)
-            uint32_t qf[HD / 16][4];
+        int page_idx = c * 4 + warp;
+        bool live = page_idx * FD_PAGE < n_entries;
+        if (live) request(Ks, 0, page_idx);
+        cp_async_commit();
+        if (live) request(Vs, 1, page_idx);
+        cp_async_commit();
+        // Q fragments: rows g and g+8 are heads g0+g and g0+g+8 of this kv head (zero beyond ng)
+        uint32_t qf[HD / 16][4];
+        {
             const bf16* q0 = q + (long long)b * ldq + (long long)(hk * G + g0 + g) * HD;
             const bf16* q1 = q0 + 8 * HD;
 #pragma unroll
@@ -367,7 +378,11 @@ attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, 
                 qf[kk][2] = g < ng ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + 2 * t) : 0u;
                 qf[kk][3] = g + 8 < ng ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + 2 * t) : 0u;
             }
-            cp_async_wait<0>();
+        }
+        while (live) {
+            const int next_idx = page_idx + page_step;
+            const bool next_live = next_idx * FD_PAGE < n_entries;
+            cp_async_wait<1>();                                // this page's keys are here; its values may not be
             __syncwarp();
             float s[8][4];
 #pragma unroll
@@ -383,50 +398,66 @@ attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, 
                     mma16816(s[2 * jp], qf[kk], kb[0], kb[1]);
                     mma16816(s[2 * jp + 1], qf[kk], kb[2], kb[3]);
                 }
-            // visibility of the page's entries (columns of s)
+            __syncwarp();                                      // every lane has read the keys
+            if (next_live) request(Ks, 0, next_idx);
+            cp_async_commit();
+            // visibility of the page's entries (columns of s); raw scores, the scale goes into the exponent
+            if (mask_all || (page_idx + 1) * FD_PAGE > n_entries) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int e = page_idx * FD_PAGE + 8 * j + 2 * t + (i & 1);
+                        bool vis = e < n_entries;
+                        if (vis) {
+                            int kpos = e;
+                            if (ring) {
+                                int back = (pos - e) % ring;
+                                if (back < 0) back += ring;
+                                kpos = pos - back;
+                            }
+                            vis = kpos >= 0 && kpos <= pos && (window <= 0 || kpos + window > pos);
+                        }
+                        s[j][i] = vis ? s[j][i] : -INFINITY;
+                    }
+            }
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int e = page_idx * FD_PAGE + 8 * j + 2 * t + (i & 1);
-                    bool vis = e < n_entries;
-                    if (vis) {
-                        int kpos = e;
-                        if (ring) {
-                            int back = (pos - e) % ring;
-                            if (back < 0) back += ring;
-                            kpos = pos - back;
-                        }
-                        vis = kpos >= 0 && kpos <= pos && (window <= 0 || kpos + window > pos);
-                    }
-                    const float x = vis ? s[j][i] * scale_log2 : -INFINITY;
-                    s[j][i] = x;
-                    mx[i >> 1] = fmaxf(mx[i >> 1], x);
-                }
-            float m_use[2];
+                for (int i = 0; i < 4; ++i) mx[i >> 1] = fmaxf(mx[i >> 1], s[j][i]);
+            float alpha[2], m_use[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
                 mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-                m_row[h] = mx[h];
-                m_use[h] = mx[h] == -INFINITY ? 0.f : mx[h];
+                const float m_new = fmaxf(m_run[h], mx[h] * scale_log2);
+                m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+                alpha[h] = fast_exp2(m_run[h] - m_use[h]);
+                m_run[h] = m_new;
             }
+            float rs[2] = {0.f, 0.f};
             uint32_t pf[4][4];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
-                const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
-                l_row[0] += p0 + p1;
-                l_row[1] += p2 + p3;
+                const float p0 = fast_exp2(fmaf(s[j][0], scale_log2, -m_use[0])), p1 = fast_exp2(fmaf(s[j][1], scale_log2, -m_use[0]));
+                const float p2 = fast_exp2(fmaf(s[j][2], scale_log2, -m_use[1])), p3 = fast_exp2(fmaf(s[j][3], scale_log2, -m_use[1]));
+                rs[0] += p0 + p1;
+                rs[1] += p2 + p3;
                 pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
                 pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
             }
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 1);
-                l_row[h] += __shfl_xor_sync(0xffffffffu, l_row[h], 2);
+            for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * alpha[h] + rs[h];
+#pragma unroll
+            for (int j = 0; j < HD / 8; ++j) {
+                o[j][0] *= alpha[0];
+                o[j][1] *= alpha[0];
+                o[j][2] *= alpha[1];
+                o[j][3] *= alpha[1];
             }
+            cp_async_wait<1>();                                // this page's values are here
+            __syncwarp();
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
 #pragma unroll
@@ -436,9 +467,21 @@ attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, 
                     mma16816(o[2 * dp], pf[kk], vb[0], vb[1]);
                     mma16816(o[2 * dp + 1], pf[kk], vb[2], vb[3]);
                 }
+            __syncwarp();                                      // every lane has read the values
+            if (next_live) request(Vs, 1, next_idx);
+            cp_async_commit();
+            page_idx = next_idx;
+            live = next_live;
         }
-        // ---- this warp's page result to shared memory: row r = head, [HD] outputs then max, sum
-        __syncthreads();                                       // mrg may still be read by the previous pass
+        cp_async_wait<0>();
+        if (g0 + 16 >= G) pdl_trigger();                       // the cache is read: the next kernel may start up
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+            l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+        }
+        // ---- this warp's result to shared memory: row r = head, [HD] outputs then max, sum
+        __syncthreads();                                       // every warp is done with its page buffers
         float* mine = mrg + (size_t)warp * 16 * (HD + 2);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -449,12 +492,12 @@ attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, 
                 mine[r * (HD + 2) + 8 * j + 2 * t + 1] = o[j][2 * h + 1];
             }
             if (t == 0) {
-                mine[r * (HD + 2) + HD] = m_row[h];            // log2-scaled maximum
-                mine[r * (HD + 2) + HD + 1] = l_row[h];
+                mine[r * (HD + 2) + HD] = m_run[h];            // log2-scaled maximum
+                mine[r * (HD + 2) + HD + 1] = l_run[h];
             }
         }
         __syncthreads();
-        // ---- merge the four pages in page order; leave the chunk's partial result
+        // ---- merge the four warps in warp order; leave the block's partial result
         for (int e = tid; e < ng * HD; e += 128) {
             const int r = e / HD, d = e - r * HD;
             float mxx = -INFINITY;
@@ -468,7 +511,7 @@ attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, 
                 den += row[HD + 1] * f;
                 num += row[d] * f;
             }
-            const long long idx = ((long long)b * QH + hk * G + g0 + r) * n_chunks + c;
+            const long long idx = ((long long)b * QH + hk * G + g0 + r) * n_parts + c;
             part_o[idx * HD + d] = num;
             if (d == 0) {
                 // the merge kernel works with natural-log maxima: m_ln = m_log2 * ln 2
@@ -476,15 +519,18 @@ attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, 
                 part_ml[idx * 2 + 1] = den;
             }
         }
+        __syncthreads();                                       // the next pass copies pages over the merge rows
     }
-    cp_async_wait<0>();
 }
 
+// n_chunks: chunks of 256 entries that cover the longest sequence.  *n_parts_out: how many blocks
+// per (sequence, kv head) were launched = slots per (sequence, head) in the scratch arrays.
 template <int HD>
 static int launch_fd(float* part_o, float* part_ml, const void* q, long long ldq, const int* seq_pos,
                      const int* seq_slot, const void* pool, long long pages, const int* ptab, int ptab_stride,
-                     int ring, int window, int B, int QH, int KVH, int n_chunks, float scale, cudaStream_t st) {
-    const size_t smem = (size_t)4 * 2 * FD_PAGE * (HD + 8) * sizeof(bf16) + (size_t)4 * 16 * (HD + 2) * sizeof(float);
+                     int ring, int window, int B, int QH, int KVH, int n_chunks, float scale, int* n_parts_out,
+                     cudaStream_t st) {
+    const size_t smem = (size_t)4 * 2 * FD_PAGE * (HD + 8) * sizeof(bf16);
     auto kernel = attn_decode_mma_kernel<HD>;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
@@ -494,8 +540,20 @@ static int launch_fd(float* part_o, float* part_ml, const void* q, long long ldq
         }
         configured = true;
     }
-    cm_launch(kernel, dim3(n_chunks, KVH, B), 128, smem, st, part_o, part_ml, (const bf16*)q, ldq, seq_pos, seq_slot,
-              (const bf16*)pool, pages, ptab, ptab_stride, ring, window, QH, KVH, n_chunks,
+    // about eight blocks per SM keep every SM copying; beyond that a block walks several chunks
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 1;
+    }
+    const long long blocks = (long long)n_chunks * KVH * B;
+    const int rounds = (int)((blocks + 8LL * sm_count - 1) / (8LL * sm_count));
+    const int n_parts = (n_chunks + rounds - 1) / rounds;
+    *n_parts_out = n_parts;
+    cm_launch(kernel, dim3(n_parts, KVH, B), 128, smem, st, part_o, part_ml, (const bf16*)q, ldq, seq_pos, seq_slot,
+              (const bf16*)pool, pages, ptab, ptab_stride, ring, window, QH, KVH, n_parts,
               scale * 1.4426950408889634f);
     CM_CHECK_LAUNCH();
     return CM_OK;
@@ -507,11 +565,11 @@ static int launch_fd(float* part_o, float* part_ml, const void* q, long long ldq
 int cm_attn_decode_mma_stage(float* part_o, float* part_ml, const void* q, long long ldq, const int* seq_pos,
                              const int* seq_slot, const void* pool, long long pages, const int* ptab,
                              int ptab_stride, int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
-                             float scale, cudaStream_t st) {
+                             float scale, int* n_parts_out, cudaStream_t st) {
     if (ldq % 2 || ((uintptr_t)q & 3) || ((uintptr_t)pool & 15)) CM_REFUSE("attn_decode_mma: misaligned operands");
 #define FD_CASE(D) \
     case D: return launch_fd<D>(part_o, part_ml, q, ldq, seq_pos, seq_slot, pool, pages, ptab, ptab_stride, ring, \
-                                window, B, QH, KVH, n_chunks, scale, st);
+                                window, B, QH, KVH, n_chunks, scale, n_parts_out, st);
     switch (HD) {
         FD_CASE(16) FD_CASE(32) FD_CASE(48) FD_CASE(64) FD_CASE(80) FD_CASE(96) FD_CASE(112) FD_CASE(128)
         default: CM_REFUSE("attn_decode_mma: head size %d (multiples of 16 up to 128)", HD);

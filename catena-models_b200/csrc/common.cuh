@@ -32,11 +32,20 @@ void cm_set_error(const char* fmt, ...);
 
 // ---- programmatic dependent launch --------------------------------------------------
 // Every kernel of this library is launched with the "programmatic stream serialization"
-// attribute (unless cm_set_pdl(0)): the next kernel of the stream may be scheduled while this
-// one still runs, and blocks in pdl_wait() until this one has finished and its writes are
-// visible.  A kernel may read constants (weights) before pdl_wait(), and nothing else; every
-// block calls pdl_wait() before it reads an activation, writes anything, or exits, so that
-// completion of a kernel implies completion of all kernels before it.
+// attribute (unless cm_set_pdl(0)): the next kernel of the stream may be scheduled once every
+// block of this one has called pdl_trigger() or left, and blocks in pdl_wait() until this one
+// has finished and its writes are visible.  A kernel may read constants (weights) before
+// pdl_wait(), and nothing else; every block calls pdl_wait() before it reads an activation,
+// writes anything, or exits, so that completion of a kernel implies completion of all kernels
+// before it.
+// Where to trigger: the short row-wise kernels (norms, convolution, rotation, gathers) trigger
+// at once, so that the matrix product after them is resident and has asked for its first
+// weights while they run.  The kernels that stream weights or the cache trigger only when their
+// last loads are under way: triggered at once, kernel after kernel became resident and waited,
+// and decode steps of 1 and 8 sequences took up to 1.5 times as long as without any overlap
+// (measured on B200).  The weight-streaming product of decode steps (gemm_skinny.cu) is launched
+// in plain stream order: started early it made those steps 6% slower, while the TMA-fed products
+// gain from setting up their barriers and tensor memory early (batch 64: 5% faster).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -58,10 +67,11 @@ static inline cudaError_t cm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
-// The same, for a grid whose blocks form clusters of (1, cluster_y, 1).
+// The same, for a grid whose blocks form clusters of (1, cluster_y, 1).  early = false launches
+// in plain stream order (the kernel starts when the one before it has finished).
 template <typename... KArgs, typename... Args>
 static inline cudaError_t cm_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                            cudaStream_t st, int cluster_y, Args... args) {
+                                            cudaStream_t st, int cluster_y, bool early, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -76,7 +86,7 @@ static inline cudaError_t cm_launch_cluster(void (*kernel)(KArgs...), dim3 grid,
         attr[n].val.clusterDim.z = 1;
         ++n;
     }
-    if (cm_pdl_enabled()) {
+    if (early && cm_pdl_enabled()) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;

@@ -70,7 +70,6 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
 
     // The weights of the first k-blocks are requested before this kernel waits for the one
     // before it: they are constants, and their latency hides behind the predecessor's tail.
-    pdl_trigger();
     uint4 wa[UNROLL], wb[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -113,6 +112,7 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
             wb[u] = nb[u];
         }
     }
+    pdl_trigger();                                 // the weights are read: the next kernel may ask for its own
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
@@ -174,7 +174,7 @@ static int launch_skinny(void* Y, const void* X, const void* W, int M, int N, in
     // Two k-blocks per step and 64 registers: four blocks per SM (measured on B200: 6144 x 2048
     // goes from 8.6 to 6.7 us against four k-blocks per step at two blocks per SM).
     constexpr int UNROLL = 2;
-    cm_launch_cluster(gemm_skinny_kernel<NT, TY, MODE, UNROLL>, dim3(tiles, ksplit), SK_WARPS * 32, 0, st, ksplit,
+    cm_launch_cluster(gemm_skinny_kernel<NT, TY, MODE, UNROLL>, dim3(tiles, ksplit), SK_WARPS * 32, 0, st, ksplit, false,
                       (TY*)Y, (const bf16*)X, (const bf16*)W, M, N, K, ldx, ldw, ldy);
     CM_CHECK_LAUNCH();
     return CM_OK;

@@ -172,7 +172,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
     const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = smem_u32(&bars[2 * STAGES + 2]);
 
-    pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full0 + 8 * s, 1);
@@ -221,6 +220,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 issued_kb = it + 1;
             }
         }
+        pdl_trigger();                            // every k-slice is requested: the next kernel may start up
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------- MMA issuer
         // instruction descriptor: float accumulator, bf16 A and B, both K-major, N/8 and M/16
@@ -365,7 +365,6 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[TCS_STAGES]);
     const uint32_t acc_full = smem_u32(&bars[2 * TCS_STAGES]);
 
-    pdl_trigger();
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
@@ -419,6 +418,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             load_a(i);
             issued_kb = i + 1;
         }
+        pdl_trigger();                            // every k-slice is requested: the next kernel may start up
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------- MMA issuer
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TCS_BN >> 3) << 17) |
@@ -668,7 +668,7 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
     if (rc != CM_OK) return rc;
     rc = make_map(&map_b, B, MODE == TC_MODE_SWIGLU ? 2LL * N : N, K, ldb, MODE == TC_MODE_SWIGLU ? TCS_BN / 2 : TCS_BN);
     if (rc != CM_OK) return rc;
-    cm_launch_cluster(kernel, dim3(n_tiles, splits), TC_THREADS, smem, st, splits, map_a, map_b, (TC*)C, M, N, K, ldc,
+    cm_launch_cluster(kernel, dim3(n_tiles, splits), TC_THREADS, smem, st, splits, true, map_a, map_b, (TC*)C, M, N, K, ldc,
                       splits, err);
     CM_CHECK_LAUNCH();
     return CM_OK;
