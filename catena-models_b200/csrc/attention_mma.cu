@@ -523,6 +523,11 @@ attn_decode_mma_kernel(float* __restrict__ part_o, float* __restrict__ part_ml, 
     }
 }
 
+// Blocks the decode grid aims at (0: eight per SM).  A smaller number makes every block walk
+// more chunks; tests use it to reach that path with small inputs.
+static int g_fd_target_blocks = 0;
+extern "C" void cm_attn_decode_set_target_blocks(int blocks) { g_fd_target_blocks = blocks > 0 ? blocks : 0; }
+
 // n_chunks: chunks of 256 entries that cover the longest sequence.  *n_parts_out: how many blocks
 // per (sequence, kv head) were launched = slots per (sequence, head) in the scratch arrays.
 template <int HD>
@@ -549,7 +554,8 @@ static int launch_fd(float* part_o, float* part_ml, const void* q, long long ldq
         if (sm_count <= 0) sm_count = 1;
     }
     const long long blocks = (long long)n_chunks * KVH * B;
-    const int rounds = (int)((blocks + 8LL * sm_count - 1) / (8LL * sm_count));
+    const long long target = g_fd_target_blocks ? g_fd_target_blocks : 8LL * sm_count;
+    const int rounds = (int)((blocks + target - 1) / target);
     const int n_parts = (n_chunks + rounds - 1) / rounds;
     *n_parts_out = n_parts;
     cm_launch(kernel, dim3(n_parts, KVH, B), 128, smem, st, part_o, part_ml, (const bf16*)q, ldq, seq_pos, seq_slot,

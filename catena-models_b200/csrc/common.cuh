@@ -38,14 +38,15 @@ void cm_set_error(const char* fmt, ...);
 // pdl_wait(), and nothing else; every block calls pdl_wait() before it reads an activation,
 // writes anything, or exits, so that completion of a kernel implies completion of all kernels
 // before it.
-// Where to trigger: the short row-wise kernels (norms, convolution, rotation, gathers) trigger
-// at once, so that the matrix product after them is resident and has asked for its first
-// weights while they run.  The kernels that stream weights or the cache trigger only when their
-// last loads are under way: triggered at once, kernel after kernel became resident and waited,
-// and decode steps of 1 and 8 sequences took up to 1.5 times as long as without any overlap
-// (measured on B200).  The weight-streaming product of decode steps (gemm_skinny.cu) is launched
-// in plain stream order: started early it made those steps 6% slower, while the TMA-fed products
-// gain from setting up their barriers and tensor memory early (batch 64: 5% faster).
+// Where to trigger, and what to launch early (all measured on B200, LFM3 1.7B-class decode):
+//  - the short row-wise kernels (norms, convolution, rotation, gathers, merges) trigger at once;
+//  - the TMA-fed products and the attention kernels trigger when their last loads are under way.
+//    Triggered at once, kernel after kernel became resident and sat waiting, and steps of 1 and
+//    8 sequences took up to 1.5 times as long as without any overlap;
+//  - the weight-streaming product of small decode batches (gemm_skinny.cu) is launched in plain
+//    stream order and triggers as soon as it runs: started early it made those steps 5% slower
+//    (with or without reading weights ahead of its wait), while the TMA-fed products gain from
+//    setting up their barriers and tensor memory early (batch 64: 7% faster).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

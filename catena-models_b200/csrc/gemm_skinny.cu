@@ -79,6 +79,7 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
         wb[u] = (kv && v1) ? ld_stream16(w1 + k) : zero;
     }
     pdl_wait();
+    pdl_trigger();                                 // what follows a product is a short kernel: let it start up now
 
     for (int blk = b0; blk < b1; blk += UNROLL) {
         uint4 xv[UNROLL][NT], na[UNROLL], nb[UNROLL];
@@ -112,7 +113,6 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
             wb[u] = nb[u];
         }
     }
-    pdl_trigger();                                 // the weights are read: the next kernel may ask for its own
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll

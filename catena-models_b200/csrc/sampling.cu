@@ -39,10 +39,30 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long
     const float* x = logits + (long long)row * ld;
     const float temp = temperature ? temperature[row] : 0.f;
 
-    // ---- maximum and its first index
+    // ---- maximum and its first index (a thread meets its indices in rising order, so a strict
+    // comparison keeps the lowest); four 16-byte loads in flight per thread where the row allows
     float best = -INFINITY;
     int arg = 0x7fffffff;
-    for (int i = tid; i < V; i += SM_THREADS) {
+    const bool vec = (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
+    const int n4 = vec ? V / 4 : 0;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    for (int i = tid; i < n4; i += 4 * SM_THREADS) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = i + u * SM_THREADS;
+            v[u] = j < n4 ? x4[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j4 = 4 * (i + u * SM_THREADS);
+            if (v[u].x > best) { best = v[u].x; arg = j4; }
+            if (v[u].y > best) { best = v[u].y; arg = j4 + 1; }
+            if (v[u].z > best) { best = v[u].z; arg = j4 + 2; }
+            if (v[u].w > best) { best = v[u].w; arg = j4 + 3; }
+        }
+    }
+    for (int i = 4 * n4 + tid; i < V; i += SM_THREADS) {
         const float v = x[i];
         if (v > best) {
             best = v;

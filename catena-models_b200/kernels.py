@@ -236,6 +236,12 @@ def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, win
                                      HD, window, scale, _stream()), "attn_prefill_mma")
 
 
+def set_decode_attention_target_blocks(blocks):
+    """Blocks the tensor-core decode attention aims at (0: eight per SM, the default).  With fewer,
+    each block walks several 256-entry chunks of a sequence."""
+    lib().cm_attn_decode_set_target_blocks(int(blocks))
+
+
 def set_decode_attention_tensor_cores(on):
     """bfloat16 decode attention normally runs its first stage on the tensor cores when the head
     size allows it; off forces the CUDA-core stage (tests compare the two)."""

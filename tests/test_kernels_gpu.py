@@ -238,9 +238,9 @@ def test_attn_decode_paged(K, dtype, tensor_cores, QH, KVH, HD, window):
         K.set_decode_attention_tensor_cores(True)
 
 
-def _attn_decode_paged(K, dtype, QH, KVH, HD, window):
+def _attn_decode_paged(K, dtype, QH, KVH, HD, window, lens=(1, 64, 65, 300, 700), n_chunks=4):
     ring = (window + 63) // 64 * 64 if window else 0
-    lens = [1, 64, 65, 300, 700]                      # tokens held including the new one
+    lens = list(lens)                                  # tokens held including the new one
     B = len(lens)
     g = torch.Generator().manual_seed(HD + window)
     kv = [torch.randn(n, 2, KVH, HD, generator=g) for n in lens]
@@ -249,7 +249,7 @@ def _attn_decode_paged(K, dtype, QH, KVH, HD, window):
     gate = rnd(B, QH, dtype=dtype, seed=8)
     pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
     slots = torch.arange(1, B + 1, dtype=torch.int32, device=DEV)
-    n_chunks = 4                                       # more chunks than the short sequences have
+    # n_chunks: more chunks than the short sequences have
     part_o, part_ml = K.attn_decode_scratch(B, QH, HD, n_chunks, DEV)
     ctx = torch.full((B, QH * HD), float("nan"), dtype=dtype, device=DEV)
     scale = HD ** -0.5
@@ -262,6 +262,19 @@ def _attn_decode_paged(K, dtype, QH, KVH, HD, window):
         gg[-1] = gate[b].float().cpu()
         ref = _ref_attention(qq, kk, vv, window, scale, gg)[-1]
         close(ctx[b].view(QH, HD), ref, dtype)
+
+
+@pytest.mark.parametrize("target_blocks", [1, 12, 40])
+@pytest.mark.parametrize("QH,KVH,HD,window", [(8, 2, 64, 0), (4, 1, 32, 1000), (6, 2, 128, 1024), (20, 1, 16, 0)])
+def test_attn_decode_blocks_that_walk_several_chunks(K, QH, KVH, HD, window, target_blocks):
+    """With a small target of blocks every block takes chunks c, c + n_parts, ... of its sequence
+    (1: one block per sequence and kv head walks them all), carrying maximum and sum from page to
+    page; sequences end inside a page, at a page's edge and at a chunk's edge."""
+    K.set_decode_attention_target_blocks(target_blocks)
+    try:
+        _attn_decode_paged(K, torch.bfloat16, QH, KVH, HD, window, lens=(1, 256, 257, 1024, 1500, 1983), n_chunks=8)
+    finally:
+        K.set_decode_attention_target_blocks(0)
 
 
 def test_attn_decode_finds_a_far_key_and_respects_the_window_edge(K):
