@@ -1,14 +1,19 @@
 // C[M,N] = A[M,K] * B[N,K]^T in bfloat16 on the 5th-generation tensor cores (prompt steps).
 //
-// One block per SM computes 128 x BLOCK_N tiles of C, one after another.  Roles (six warps):
+// One block per SM computes 128 x BLOCK_N tiles of C, one after another.  Roles (ten warps):
 //   warp 0  one thread: TMA loads of the A and B k-slices (128 x 64 and BLOCK_N x 64 bf16,
 //           128-byte swizzle) into a ring of STAGES shared-memory stages;
 //   warp 1  allocates the tensor-memory columns of the accumulator; one thread issues
 //           tcgen05.mma (128 x BLOCK_N x 16 per instruction, float accumulation in tensor
 //           memory) and commits each stage back to the loader and the finished tile to the
 //           epilogue through mbarriers;
-//   warps 2-5  epilogue: tcgen05.ld of the accumulator (a warp reaches the 32 lanes
-//           32*(warp%4)..), conversion, bounds-checked stores to C.
+//   warps 2-9  epilogue, two groups of four warps that take alternate 128-byte-wide pieces of
+//           the tile: tcgen05.ld of the accumulator (a warp reaches the 32 lanes 32*(warp%4)..),
+//           conversion, the piece into the group's 16 KB staging buffer (128-byte swizzle), and a
+//           TMA store of it to C, clipped at M and N.  (Stores straight from registers, 16 bytes per row per instruction, held
+//           the tensor cores back: 2048 x 6144 x 2048 took 53.6 us with them, 38.4 us with the
+//           epilogue's work removed.)  Outputs whose pitch or base is not 16-byte aligned
+//           keep the direct stores.
 // Rows or columns beyond M, N, K are zero-filled by TMA on load and masked on store, so any
 // M and N and any K that is a multiple of 8 (16-byte row pitch) is taken.
 //
@@ -27,6 +32,7 @@
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
+#define TCP_THREADS 320          // the persistent kernel: loader, issuer, two groups of four epilogue warps
 #define TC_MODE_PLAIN 0
 #define TC_MODE_SWIGLU 1
 #define TC_SPIN_LIMIT (1 << 24)
@@ -70,6 +76,32 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void st_shared16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// 32 consecutive outputs of row r into a staged tile of 128-byte rows with the 128-byte swizzle
+// (16-byte piece j of row r lies at piece j ^ (r % 8)); `first` = index of the first piece.
+__device__ __forceinline__ void stage_cols(uint32_t buf, int r, int first, const float* v, bf16*) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(h);
+        st_shared16(buf + r * 128 + (((first + i) ^ (r & 7)) << 4), w[0], w[1], w[2], w[3]);
+    }
+}
+__device__ __forceinline__ void stage_cols(uint32_t buf, int r, int first, const float* v, float*) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        st_shared16(buf + r * 128 + (((first + i) ^ (r & 7)) << 4), __float_as_uint(v[4 * i]),
+                    __float_as_uint(v[4 * i + 1]), __float_as_uint(v[4 * i + 2]), __float_as_uint(v[4 * i + 3]));
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -126,7 +158,9 @@ __device__ __forceinline__ void store_cols<bf16>(bf16* dst, const float* v, int 
             *reinterpret_cast<uint4*>(dst + 8 * i) = raw;
         }
     } else {
-        for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)                       // unrolled: v stays in registers
+            if (i < n_valid) dst[i] = __float2bfloat16_rn(v[i]);
     }
 }
 template <>
@@ -136,7 +170,9 @@ __device__ __forceinline__ void store_cols<float>(float* dst, const float* v, in
         for (int i = 0; i < 8; ++i)
             *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
     } else {
-        for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = v[i];
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < n_valid) dst[i] = v[i];
     }
 }
 
@@ -150,9 +186,10 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // columns), so the epilogue of one tile runs while the next tile's products are issued; the
 // shared-memory ring of k-slices keeps turning across tile borders.
 template <int BLOCK_N, int STAGES, typename TC, int MODE>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TCP_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               TC* __restrict__ C, int M, int N, int K, long long ldc, int* err) {
+               const __grid_constant__ CUtensorMap map_c, int tma_store, TC* __restrict__ C, int M, int N, int K,
+               long long ldc, int* err) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = BLOCK_N * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -179,7 +216,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full0 + 8 * a, 1);
-            mbar_init(acc_empty0 + 8 * a, 4);                   // one arrival per epilogue warp
+            mbar_init(acc_empty0 + 8 * a, 8);                   // one arrival per epilogue warp
         }
         abort_flag = 0;
         issued_kb = 0;
@@ -252,36 +289,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else if (warp >= 2) {
         // ------------------------------------------------------------- epilogue
+        // The four warps run the same number of rounds whatever happens (a warp whose wait ran
+        // out goes on without loading or storing), so that the barriers between them always meet.
         const int q = warp & 3;                           // tensor-memory lane quarter of this warp
         const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        const int group = (warp - 2) >> 2;                // two groups of four warps take alternate pieces
+        const bool elected = lane == 0 && q == 2;         // first warp of the group: issues and awaits its TMA stores
+        constexpr int CHUNK_COLS = 128 / (int)sizeof(TC); // output columns of a staged piece: 128 bytes a row
+        constexpr int SUB = CHUNK_COLS / 32;              // tensor-memory loads of 32 columns per piece
+        const uint32_t sbuf = tiles + STAGES * STAGE_BYTES + (uint32_t)group * 16384u;   // the group's staging buffer
+        const int r_tile = q * 32 + lane;
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             const int acc = local & 1;
             const int m0 = (tile / n_tiles) * TC_BM, n0 = (tile % n_tiles) * OUT_COLS;
-            const int row = m0 + q * 32 + lane;
-            if (!mbar_wait(acc_full0 + 8 * acc, (local >> 1) & 1, &abort_flag, err, TC_ERR_TIMEOUT_EPILOGUE)) break;
+            const int row = m0 + r_tile;
+            const bool ok = mbar_wait(acc_full0 + 8 * acc, (local >> 1) & 1, &abort_flag, err, TC_ERR_TIMEOUT_EPILOGUE);
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (uint32_t)(acc * BLOCK_N) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < OUT_COLS / 32; ++c) {
-                float v[32];
-                tmem_load32(t_acc + (uint32_t)(c * 32), v);
-                if (MODE == TC_MODE_SWIGLU) {
-                    float u[32];
-                    tmem_load32(t_acc + (uint32_t)(OUT_COLS + c * 32), u);
+            for (int c0 = group * CHUNK_COLS; c0 < OUT_COLS; c0 += 2 * CHUNK_COLS) {
+                if (tma_store) {
+                    // the group's last store must be done reading the buffer
+                    if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
+                }
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float g = rounded<TC>(v[i]), uu = rounded<TC>(u[i]);
-                        v[i] = __fdividef(g, 1.f + __expf(-g)) * uu;
+                for (int h = 0; h < SUB; ++h) {
+                    const int c = c0 + 32 * h;
+                    float v[32];
+                    if (ok) {
+                        tmem_load32(t_acc + (uint32_t)c, v);
+                        if (MODE == TC_MODE_SWIGLU) {
+                            float u[32];
+                            tmem_load32(t_acc + (uint32_t)(OUT_COLS + c), u);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const float g = rounded<TC>(v[i]), uu = rounded<TC>(u[i]);
+                                v[i] = __fdividef(g, 1.f + __expf(-g)) * uu;
+                            }
+                        }
+                        if (tma_store) {
+                            stage_cols(sbuf, r_tile, h * (32 * (int)sizeof(TC) / 16), v, (TC*)nullptr);
+                        } else {
+                            const int col = n0 + c;
+                            if (row < M && col < N) store_cols<TC>(C + (long long)row * ldc + col, v, N - col, vec_ok);
+                        }
                     }
                 }
-                const int col = n0 + c * 32;
-                if (row < M && col < N) store_cols<TC>(C + (long long)row * ldc + col, v, N - col, vec_ok);
+                if (tma_store) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
+                    if (elected) {
+                        if (ok && n0 + c0 < N) tma_store_2d(&map_c, sbuf, n0 + c0, m0);   // clipped at M and N
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);    // this warp has read its quarter
         }
+        if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     // ------------------------------------------------------------------ teardown
     tc_fence_before();
@@ -560,6 +629,29 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     return CM_OK;
 }
 
+// Tensor map of the output [M, N] (bfloat16 or float, row pitch ldc elements) for stores of
+// 128-row pieces whose rows are 128 bytes, 128-byte swizzle.
+template <typename TC>
+static int make_map_c(CUtensorMap* map, void* base, long long M, long long N, long long ldc) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        cm_set_error("gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+        return CM_ERR_DRIVER;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)ldc * sizeof(TC)};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / sizeof(TC)), TC_BM};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, sizeof(TC) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base,
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        cm_set_error("gemm_tc: tensor map for the output [%lld, %lld] pitch %lld refused (CUresult %d)", M, N, ldc, (int)r);
+        return CM_ERR_DRIVER;
+    }
+    return CM_OK;
+}
+
 template <int BLOCK_N, int STAGES, typename TC, int MODE>
 static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
                      long long ldc, int* err, cudaStream_t st) {
@@ -571,7 +663,15 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
     rc = make_map(&map_b, B, b_rows, K, ldb, b_box);
     if (rc != CM_OK) return rc;
     constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
-    const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BLOCK_N * TC_BK * 2) + 1024;
+    static_assert(OUT_COLS % (128 / (int)sizeof(TC)) == 0, "a tile is a whole number of staged pieces");
+    // TMA stores want a 16-byte aligned base and pitch; other outputs are stored from registers
+    CUtensorMap map_c = map_a;
+    const int tma_store = ((ldc * (long long)sizeof(TC)) % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
+    if (tma_store) {
+        rc = make_map_c<TC>(&map_c, C, M, N, ldc);
+        if (rc != CM_OK) return rc;
+    }
+    const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BLOCK_N * TC_BK * 2) + 2 * 16384 + 1024;
     auto kernel = gemm_tc_kernel<BLOCK_N, STAGES, TC, MODE>;
     static bool configured = false;
     if (!configured) {
@@ -591,7 +691,7 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
         if (sm_count <= 0) sm_count = 1;
     }
     dim3 grid(num_tiles < sm_count ? num_tiles : sm_count);
-    cm_launch(kernel, grid, TC_THREADS, smem, st, map_a, map_b, (TC*)C, M, N, K, ldc, err);
+    cm_launch(kernel, grid, TCP_THREADS, smem, st, map_a, map_b, map_c, tma_store, (TC*)C, M, N, K, ldc, err);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
