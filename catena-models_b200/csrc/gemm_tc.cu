@@ -180,6 +180,18 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// Order of the output tiles: groups of TC_GROUP_M row tiles, inside a group down the rows first.
+// The blocks that run at the same time then share few B tiles (and few A tiles) instead of
+// touching every column tile of one or two row tiles.
+#define TC_GROUP_M 8
+__device__ __forceinline__ void tile_origin(int tile, int m_tiles, int n_tiles, int* m_tile, int* n_tile) {
+    const int per_group = TC_GROUP_M * n_tiles;
+    const int group = tile / per_group, in_group = tile - group * per_group;
+    const int rows = min(TC_GROUP_M, m_tiles - group * TC_GROUP_M);
+    *m_tile = group * TC_GROUP_M + in_group % rows;
+    *n_tile = in_group / rows;
+}
+
 // Persistent form: gridDim.x blocks (one per SM) walk the output tiles t = blockIdx.x,
 // blockIdx.x + gridDim.x, ...; tile t covers rows (t / n_tiles) * 128 and output columns
 // (t % n_tiles) * OUT_COLS.  The accumulator is double-buffered in tensor memory (2 * BLOCK_N
@@ -204,7 +216,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
     const int n_tiles = (N + OUT_COLS - 1) / OUT_COLS;
-    const int num_tiles = n_tiles * ((M + TC_BM - 1) / TC_BM);
+    const int m_tiles = (M + TC_BM - 1) / TC_BM;
+    const int num_tiles = n_tiles * m_tiles;
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;                    // swizzle atoms need 1024-byte alignment
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
     const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = smem_u32(&bars[2 * STAGES + 2]);
@@ -239,7 +252,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int it = 0;                               // k-slices issued so far, over all tiles
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const int m0 = (tile / n_tiles) * TC_BM, n0 = (tile % n_tiles) * OUT_COLS;
+            int m_tile, n_tile;
+            tile_origin(tile, m_tiles, n_tiles, &m_tile, &n_tile);
+            const int m0 = m_tile * TC_BM, n0 = n_tile * OUT_COLS;
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
@@ -302,7 +317,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int local = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
             const int acc = local & 1;
-            const int m0 = (tile / n_tiles) * TC_BM, n0 = (tile % n_tiles) * OUT_COLS;
+            int m_tile, n_tile;
+            tile_origin(tile, m_tiles, n_tiles, &m_tile, &n_tile);
+            const int m0 = m_tile * TC_BM, n0 = n_tile * OUT_COLS;
             const int row = m0 + r_tile;
             const bool ok = mbar_wait(acc_full0 + 8 * acc, (local >> 1) & 1, &abort_flag, err, TC_ERR_TIMEOUT_EPILOGUE);
             tc_fence_after();
