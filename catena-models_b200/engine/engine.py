@@ -77,7 +77,7 @@ class Engine:
         max_len = model.definition.max_positions or None
         self.cache = Cache(model.state_specs, max_tokens, self.rt.dtype, self.rt.device, max_seqs, max_len)
         self.n_kv_groups = len(self.cache.kv_specs)
-        self.use_graphs = use_graphs
+        self.use_graphs = use_graphs and model.capturable
         self._staging = _Staging()
         self._graphs = {}
         self._sampled_host = None

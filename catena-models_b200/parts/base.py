@@ -22,6 +22,8 @@ Interfaces (x, h, n are [tokens, width] activations of the step's packed batch):
         n = input_norm(h) was made by whoever ran before; n_next = next_norm(h) is made
         here (fused with the last residual sum) when next_norm is given, else None.
 
+A part sets `capturable = False` if its forward() reads device data on the host (see Part).
+
 `rt` is the engine's Runtime (dtype, device, scratch), `batch` the StepBatch (token
 positions, sequence boundaries, slots, prefill or decode).
 """
@@ -54,6 +56,12 @@ def build_part(category, kind, **params):
 class Part:
     """Base of every part: no tensors, nothing to bind."""
 
+    # False for a part whose forward() lets the host look at device data (a routed feed-forward
+    # that gathers each expert's tokens, say): its launches differ from step to step, so decode
+    # steps of a model that holds such a part are run kernel by kernel instead of being replayed
+    # from a captured graph.
+    capturable = True
+
     def tensor_specs(self):
         return []
 
@@ -74,6 +82,9 @@ class Part:
         for child in self.children():
             child.bind_all(tensors, rt)
         self.bind(tensors, rt)
+
+    def all_capturable(self):
+        return self.capturable and all(c.all_capturable() for c in self.children())
 
     def weight_bytes(self):
         """Bytes of weights a step reads from this part (each tensor once)."""

@@ -390,3 +390,173 @@ def test_a_layer_reads_another_layers_cache():
     eng.release([slots[0]])
     for g, s in zip(got, seqs):
         torch.testing.assert_close(torch.cat(g).double().cpu(), plain(s), rtol=2e-5, atol=2e-5)
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding():
+    """Two more toy parts defined here and registered from outside the package: a feed-forward
+    that routes every token to its best-scoring expert (router logits in float32) and a position
+    encoding that turns only the first quarter of a head's pairs, at linearly spaced rates.  One
+    toy architecture uses them in one layer and the stock parts in the other; prompt steps,
+    decode steps and a batch of unequal lengths are compared with plain torch."""
+    from catena_models_b200 import register_architecture, register_part
+    from catena_models_b200.api import Model
+    from catena_models_b200.config.base import Reader
+    from catena_models_b200.engine.definition import ModelDefinition, PlanEntry
+    from catena_models_b200.engine.model import DecoderModel
+    from catena_models_b200.parts import build_part
+    from catena_models_b200.parts.base import FeedForward, Position
+    from catena_models_b200.parts.linear import Linear
+    from catena_models_b200.weights.loader import TensorSpec
+    from catena_models_b200.weights.random_init import random_tensors
+
+    H, QH, KVH, HD, F, E, V, EPS = 40, 2, 2, 16, 56, 3, 70, 1e-6
+
+    class QuarterTurn(Position):
+        """angle(p, i) = p * step * (i + 1) for i < head_dim / 4, no rotation of the other pairs."""
+
+        def __init__(self, head_dim, step):
+            self.head_dim, self.step = head_dim, step
+            self._table = None
+
+        def rates(self):
+            r = torch.zeros(self.head_dim // 2, dtype=torch.float32)
+            q = self.head_dim // 4
+            r[:q] = self.step * torch.arange(1, q + 1, dtype=torch.float32)
+            return r
+
+        def bind(self, tensors, rt):
+            self._table = self.rates().to(rt.device)
+
+        def rate_table(self):
+            return self._table
+
+    class Top1Experts(FeedForward):
+        """y_t = SwiGLU_{e(t)}(x_t) * p_t, e(t) = argmax of the float32 router logits, p_t its softmax weight."""
+
+        capturable = False            # the host gathers each expert's rows: no graph replay of decode steps
+
+        def __init__(self, prefix, hidden, intermediate, experts):
+            self.router_name = prefix + "router.weight"
+            self.hidden, self.n = hidden, experts
+            self.gate_up = [Linear([f"{prefix}e{e}.gate.weight", f"{prefix}e{e}.up.weight"], [intermediate, intermediate], hidden)
+                            for e in range(experts)]
+            self.down = [Linear(f"{prefix}e{e}.down.weight", hidden, intermediate) for e in range(experts)]
+            self.intermediate = intermediate
+
+        def children(self):
+            return self.gate_up + self.down
+
+        def tensor_specs(self):
+            return [TensorSpec(self.router_name, (self.n, self.hidden), "matrix")]
+
+        def bind(self, tensors, rt):
+            self.router = tensors[self.router_name].float()
+
+        def forward(self, rt, batch, x):
+            logits = x.float() @ self.router.T                      # float32 whatever the activations are
+            prob = torch.softmax(logits, dim=-1)
+            best = logits.argmax(dim=-1)
+            y = torch.zeros_like(x)
+            for e in range(self.n):
+                rows = (best == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                xe = x[rows].contiguous()
+                a = rt.gate_up_swiglu(xe, self.gate_up[e].weight, self.intermediate)
+                out = self.down[e].apply(rt, a).float() * prob[rows, e].unsqueeze(1)
+                y[rows] = out.to(x.dtype)
+            return y
+
+    class Cfg:
+        @classmethod
+        def from_dict(cls, data, where="config.json"):
+            r = Reader(data, where)
+            r.string("architecture")
+            r.finish()
+            return cls()
+
+    def define(cfg):
+        blocks = []
+        for l in range(2):
+            pre = f"l{l}."
+            position = (build_part("position", "toy_quarter_turn", head_dim=HD, step=0.05) if l == 0
+                        else build_part("position", "rotary", head_dim=HD, theta=10000.0))
+            ff = (build_part("feed_forward", "toy_top1", prefix=pre, hidden=H, intermediate=F, experts=E) if l == 0
+                  else build_part("feed_forward", "swiglu", prefix=pre, hidden=H, intermediate=F))
+            blocks.append(build_part(
+                "block", "sandwich",
+                mixer=build_part("mixer", "gqa_attention", prefix=pre, hidden=H, heads=QH, kv_heads=KVH, head_dim=HD,
+                                 window=0, position=position, qk_norm_eps=None, output_gate=False),
+                feed_forward=ff,
+                input_norm=build_part("norm", "rms", name=pre + "n1", width=H, eps=EPS),
+                ffn_norm=build_part("norm", "rms", name=pre + "n2", width=H, eps=EPS)))
+        return ModelDefinition("toy_routed", V, H, "embed", blocks, [PlanEntry(0, 0), PlanEntry(1, 1)],
+                               build_part("norm", "rms", name="nf", width=H, eps=EPS), None)
+
+    register_part("position", "toy_quarter_turn", QuarterTurn, replace=True)
+    register_part("feed_forward", "toy_top1", Top1Experts, replace=True)
+    register_architecture("toy_routed", Cfg, define, replace=True)
+    config = dict(architecture="toy_routed")
+    raw = random_tensors(define(Cfg()).tensor_specs(), 21, std=0.3, norm_weights="random")
+    assert "l0.router.weight" in raw and "l0.e2.down.weight" in raw
+    w = {k: v.double() for k, v in raw.items()}
+    model = Model(DecoderModel.from_tensors(config, raw, torch.float32, DEV), max_tokens=512)
+
+    def turn(u, positions, rates):
+        ang = positions.double()[:, None, None] * rates.double()[None, None, :]
+        a, b = u[..., :HD // 2], u[..., HD // 2:]
+        return torch.cat([a * torch.cos(ang) - b * torch.sin(ang), b * torch.cos(ang) + a * torch.sin(ang)], dim=-1)
+
+    def plain(tokens):
+        T = len(tokens)
+        pos = torch.arange(T)
+        h = w["embed"][tokens]
+        experts_used = set()
+        for l in range(2):
+            pre = f"l{l}."
+            rates = (QuarterTurn(HD, 0.05).rates() if l == 0
+                     else P.rope_frequencies(10000.0, HD, torch.float64))
+            n = P.rms_norm(h, w[pre + "n1"], EPS)
+            q = turn((n @ w[pre + "attn_q.weight"].T).view(T, QH, HD), pos, rates)
+            k = turn((n @ w[pre + "attn_k.weight"].T).view(T, KVH, HD), pos, rates)
+            v = (n @ w[pre + "attn_v.weight"].T).view(T, KVH, HD)
+            ctx = torch.zeros(T, QH, HD, dtype=torch.float64)
+            for hq in range(QH):
+                s = (q[:, hq] @ k[:, hq].T) * HD ** -0.5
+                s = s.masked_fill(P.attention_mask(T, 0), float("-inf"))
+                ctx[:, hq] = torch.softmax(s, -1) @ v[:, hq]
+            h = h + ctx.reshape(T, QH * HD) @ w[pre + "attn_output.weight"].T
+            n2 = P.rms_norm(h, w[pre + "n2"], EPS)
+            if l == 0:
+                logits = n2 @ w[pre + "router.weight"].T
+                prob, best = torch.softmax(logits, -1), logits.argmax(-1)
+                f = torch.zeros_like(n2)
+                for t in range(T):
+                    e = int(best[t])
+                    experts_used.add(e)
+                    g, u = n2[t] @ w[f"{pre}e{e}.gate.weight"].T, n2[t] @ w[f"{pre}e{e}.up.weight"].T
+                    f[t] = ((g * torch.sigmoid(g) * u) @ w[f"{pre}e{e}.down.weight"].T) * prob[t, e]
+                h = h + f
+            else:
+                h = h + P.swiglu_ffn(n2, {k2[len(pre):]: v2 for k2, v2 in w.items() if k2.startswith(pre)})
+        return P.rms_norm(h, w["nf"], EPS) @ w["embed"].T, experts_used
+
+    eng = model.engine
+    assert not eng.use_graphs
+    seqs = [[(7 * i + 3) % V for i in range(14)], [5, 11, 2]]
+    refs = [plain(s) for s in seqs]
+    assert len(refs[0][1]) >= 2                                   # the router really spreads tokens over experts
+    slots = eng.admit(2)
+    got = [[], []]
+    out = eng.step(slots, [seqs[0][:9], seqs[1][:2]], [list(range(9)), [0, 1]])
+    got[0].append(out[:9].clone())
+    got[1].append(out[9:].clone())
+    out = eng.step(slots, [[seqs[0][9]], [seqs[1][2]]])
+    got[0].append(out[0:1].clone())
+    got[1].append(out[1:2].clone())
+    eng.release([slots[1]])
+    for t in range(10, 14):
+        got[0].append(eng.step([slots[0]], [[seqs[0][t]]]).clone())
+    eng.release([slots[0]])
+    for g, (ref, _) in zip(got, refs):
+        torch.testing.assert_close(torch.cat(g).double().cpu(), ref, rtol=3e-5, atol=3e-5)
