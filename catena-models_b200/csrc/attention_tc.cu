@@ -1,0 +1,402 @@
+// Prefill attention on the 5th-generation tensor cores (bfloat16, head sizes 64 and 128): causal or
+// sliding-window attention of packed sequences over their own keys and values, grouped query
+// heads, optional per-head sigmoid gate.  Same result as attn_prefill_mma (attention_mma.cu).
+//
+// One block per (128-query tile, query head, sequence), long tiles first.  Ten warps:
+//   warp 0   one thread: TMA loads of the Q tile and of 128-key K and V tiles into shared-memory
+//            rings (128-byte rows, 128-byte swizzle; a head of 128 is two 64-column pieces);
+//   warp 1   allocates tensor memory; one thread issues S = Q K^T (128 x 128, K-major operands)
+//            into one of two S buffers, and O' = P V (128 x HD, V as the MN-major B operand:
+//            its rows are keys) into one of two O' buffers, committing to mbarriers;
+//   warps 2-5 and 6-9  two softmax groups of 128 threads, one query row per thread.  Group g takes
+//            the key tiles g, g+2, ...: reads its S buffer from tensor memory (maximum first,
+//            then exponentials), writes P as bfloat16 into its shared-memory buffer in the A
+//            operand's layout, and adds the finished O' of its previous tile into float
+//            registers, rescaled by the change of its running maximum.  Each group keeps its own
+//            (maximum, sum, O); the two are merged at the end through shared memory, normalised,
+//            gated and stored.
+// So the tensor core forms the scores of the next tile while a group is busy with exponentials, and
+// the instructions per score drop to the softmax itself.
+//
+// Maximum, sum, exponent arguments and the rescaling are float; probabilities enter the second
+// product as bfloat16.  Every wait on an mbarrier is bounded; a wait that runs out raises *err, all
+// roles leave their loops, copies in flight are awaited (bounded), tensor memory is freed.
+#include "tc_common.cuh"
+
+#define FT_TILE 128
+#define FT_THREADS 320
+#define FT_PIECE_BYTES (128 * 64 * 2)      // 128 rows of 128 bytes
+#define FT_ERR_LOAD 111
+#define FT_ERR_MMA 112
+#define FT_ERR_SOFTMAX 113
+
+__device__ __forceinline__ float ft_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Descriptor of an MN-major operand tile with 128-byte rows and 128-byte swizzle: 64 contiguous
+// elements along N, groups of 8 rows along K 1024 bytes apart, further 64-element blocks along N
+// `lbo_bytes` apart.
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(FT_THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ ctx, long long ldc,
+                       const bf16* __restrict__ gate, long long ldg, const int* __restrict__ seq_start, int QH,
+                       int KVH, int window, float scale_log2, int* err) {
+    constexpr int KB = HD / 64;                                   // 64-column pieces of a head
+    constexpr uint32_t Q_BYTES = KB * FT_PIECE_BYTES, KV_BYTES = KB * FT_PIECE_BYTES, P_BYTES = 2 * FT_PIECE_BYTES;
+    constexpr uint32_t TMEM_COLS = 512;                           // S0 S1 (128 each), O'0 O'1 (HD each)
+    constexpr int NBARS = 1 + 4 * STAGES + 12;
+    static_assert(256 + 2 * HD <= 512, "tensor memory holds two S and two O' buffers");
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bars[NBARS];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ int issued_k, issued_v;
+
+    pdl_wait();
+    const int b = blockIdx.z, hq = blockIdx.y, hk = hq / (QH / KVH);
+    const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
+    const int q0 = (gridDim.x - 1 - blockIdx.x) * FT_TILE;        // long rows first
+    if (q0 >= len) return;                                        // the whole block, before anything is set up
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kt_begin = window > 0 ? max(0, q0 - window + 1) / FT_TILE : 0;
+    const int kt_end = min(q0 + FT_TILE - 1, len - 1) / FT_TILE;  // inclusive
+    const int n = kt_end - kt_begin + 1;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + STAGES * KV_BYTES, p_s = v_s + STAGES * KV_BYTES;
+    const uint32_t bar0 = smem_u32(&bars[0]);
+    const uint32_t q_full = bar0;
+    const uint32_t k_full = bar0 + 8, k_empty = k_full + 8 * STAGES, v_full = k_empty + 8 * STAGES,
+                   v_empty = v_full + 8 * STAGES;
+    const uint32_t s_full = v_empty + 8 * STAGES, s_empty = s_full + 16, p_full = s_empty + 16, o_full = p_full + 16,
+                   o_empty = o_full + 16, all_done = o_empty + 16, merge_full = all_done + 8;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(k_full + 8 * s, 1);
+            mbar_init(k_empty + 8 * s, 1);
+            mbar_init(v_full + 8 * s, 1);
+            mbar_init(v_empty + 8 * s, 1);
+        }
+        for (int g = 0; g < 2; ++g) {
+            mbar_init(s_full + 8 * g, 1);
+            mbar_init(s_empty + 8 * g, 4);                        // one arrival per warp of the group
+            mbar_init(p_full + 8 * g, 4);
+            mbar_init(o_full + 8 * g, 1);
+            mbar_init(o_empty + 8 * g, 4);
+        }
+        mbar_init(all_done, 8);
+        mbar_init(merge_full, 4);
+        abort_flag = 0;
+        issued_k = 0;
+        issued_v = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------- TMA loader
+        mbar_expect_tx(q_full, Q_BYTES);
+        for (int kb = 0; kb < KB; ++kb) tma_load_2d(q_s + kb * FT_PIECE_BYTES, &map_q, q_full, hq * HD + kb * 64, s0 + q0);
+        bool ok = true;
+        auto load_k = [&](int j) {
+            const int s = j % STAGES;
+            ok = mbar_wait(k_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
+            if (!ok) return;
+            mbar_expect_tx(k_full + 8 * s, KV_BYTES);
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_2d(k_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_k, k_full + 8 * s, hk * HD + kb * 64,
+                            s0 + (kt_begin + j) * FT_TILE);
+            issued_k = j + 1;
+        };
+        auto load_v = [&](int j) {
+            const int s = j % STAGES;
+            ok = mbar_wait(v_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
+            if (!ok) return;
+            mbar_expect_tx(v_full + 8 * s, KV_BYTES);
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_2d(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_v, v_full + 8 * s, hk * HD + kb * 64,
+                            s0 + (kt_begin + j) * FT_TILE);
+            issued_v = j + 1;
+        };
+        for (int j = 0; j < n && ok; ++j) {
+            load_k(j);
+            if (ok && j >= 1) load_v(j - 1);
+        }
+        if (ok) load_v(n - 1);
+        pdl_trigger();                            // every tile is requested: the next kernel may start up
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------- MMA issuer
+        // float accumulator, bf16 operands; S: both K-major, N = 128; O': B (V) MN-major, N = HD
+        constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FT_TILE >> 3) << 17) |
+                                     ((uint32_t)(FT_TILE >> 4) << 24);
+        constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
+                                     ((uint32_t)(FT_TILE >> 4) << 24);
+        bool ok = mbar_wait(q_full, 0, &abort_flag, err, FT_ERR_MMA);
+        auto issue_s = [&](int j) {
+            const int g = j & 1, t = j >> 1, s = j % STAGES;
+            ok = mbar_wait(k_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+            if (ok) ok = mbar_wait(s_empty + 8 * g, (t & 1) ^ 1, &abort_flag, err, FT_ERR_MMA);
+            if (!ok) return;
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k) {
+                const uint64_t a = umma_desc(q_s + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
+                const uint64_t bd = umma_desc(k_s + s * KV_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
+                umma_bf16(tmem_base + (uint32_t)(g * FT_TILE), a, bd, idesc_s, k != 0);
+            }
+            umma_commit(k_empty + 8 * s);
+            umma_commit(s_full + 8 * g);
+        };
+        auto issue_o = [&](int j) {
+            const int g = j & 1, t = j >> 1, s = j % STAGES;
+            ok = mbar_wait(p_full + 8 * g, t & 1, &abort_flag, err, FT_ERR_MMA);
+            if (ok) ok = mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+            if (ok) ok = mbar_wait(o_empty + 8 * g, (t & 1) ^ 1, &abort_flag, err, FT_ERR_MMA);
+            if (!ok) return;
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < FT_TILE / 16; ++k) {                // 16 keys per instruction
+                const uint64_t a = umma_desc(p_s + g * P_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
+                const uint64_t bd = umma_desc_mn(v_s + s * KV_BYTES + k * 2048, FT_PIECE_BYTES);
+                umma_bf16(tmem_base + (uint32_t)(2 * FT_TILE + g * HD), a, bd, idesc_o, k != 0);
+            }
+            umma_commit(v_empty + 8 * s);
+            umma_commit(o_full + 8 * g);
+        };
+        if (ok) issue_s(0);
+        if (ok && n > 1) issue_s(1);
+        for (int j = 0; j < n && ok; ++j) {
+            issue_o(j);
+            if (ok && j + 2 < n) issue_s(j + 2);
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------- softmax groups
+        const int g = (warp - 2) >> 2, quarter = warp & 3;
+        const int r = quarter * 32 + lane;                        // the row of the tile this thread owns
+        const int row = q0 + r;                                   // its position in the sequence
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t t_s = lane_base + (uint32_t)(g * FT_TILE), t_o = lane_base + (uint32_t)(2 * FT_TILE + g * HD);
+        const uint32_t my_p = p_s + g * P_BYTES + r * 128;
+        float o_acc[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+        bool ok = true;
+        int t = 0;
+        auto add_previous = [&](int tt) {                         // O += O' of this group's tile tt, which is finished
+            ok = mbar_wait(o_full + 8 * g, tt & 1, &abort_flag, err, FT_ERR_SOFTMAX);
+            if (!ok) return;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                float v[32];
+                tmem_load32(t_o + (uint32_t)(c * 32), v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha_prev, v[i]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_empty + 8 * g);
+        };
+        for (int j = g; j < n && ok; j += 2, ++t) {
+            const int k0 = (kt_begin + j) * FT_TILE;
+            ok = mbar_wait(s_full + 8 * g, t & 1, &abort_flag, err, FT_ERR_SOFTMAX);
+            if (!ok) break;
+            tc_fence_after();
+            // every key of the tile is visible to this row: no comparisons needed
+            const bool all_visible = k0 + FT_TILE - 1 <= row && k0 + FT_TILE - 1 < len && (window <= 0 || k0 + window > row);
+            auto masked = [&](float* v, int c) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = k0 + c * 32 + i;
+                    const bool vis = key <= row && key < len && (window <= 0 || key + window > row);
+                    v[i] = vis ? v[i] : -INFINITY;
+                }
+            };
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                tmem_load32(t_s + (uint32_t)(c * 32), v);
+                if (!all_visible) masked(v, c);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+            }
+            const float m_new = fmaxf(m_run, mx * scale_log2);    // scale > 0 keeps the order of the scores
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = ft_exp2(m_run - m_use);
+            m_run = m_new;
+            float rs = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                tmem_load32(t_s + (uint32_t)(c * 32), v);
+                if (!all_visible) masked(v, c);
+                uint32_t w[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = ft_exp2(fmaf(v[2 * i], scale_log2, -m_use));
+                    const float p1 = ft_exp2(fmaf(v[2 * i + 1], scale_log2, -m_use));
+                    rs += p0 + p1;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    w[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                // 32 probabilities = four 16-byte pieces of this row; keys 64.. go to the second 64-key block
+                const uint32_t dst = my_p + (uint32_t)(c >> 1) * FT_PIECE_BYTES;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    st_shared16(dst + ((((c & 1) * 4 + i) ^ (r & 7)) << 4), w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            }
+            tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(s_empty + 8 * g);                     // the S buffer is read out
+                mbar_arrive(p_full + 8 * g);                      // P of this tile is in shared memory
+            }
+            l_run = l_run * alpha + rs;
+            if (t > 0) add_previous(t - 1);
+            alpha_prev = alpha;
+        }
+        if (ok && t > 0) add_previous(t - 1);
+        // ---- both groups done with the tensor core: every buffer in shared memory is free
+        __syncwarp();
+        if (lane == 0) mbar_arrive(all_done);
+        if (ok) ok = mbar_wait(all_done, 0, &abort_flag, err, FT_ERR_SOFTMAX);
+        float* mrg = reinterpret_cast<float*>(smem_raw + (k_s - smem_u32(smem_raw)));   // [HD + 2][128] over the K and V rings
+        static_assert((size_t)(HD + 2) * FT_TILE * sizeof(float) <= (size_t)2 * STAGES * KV_BYTES, "merge rows fit the rings");
+        if (g == 1) {
+            if (ok) {
+#pragma unroll
+                for (int i = 0; i < HD; ++i) mrg[i * FT_TILE + r] = o_acc[i];
+                mrg[HD * FT_TILE + r] = m_run;
+                mrg[(HD + 1) * FT_TILE + r] = l_run;
+            }
+            __syncwarp();
+            __threadfence_block();
+            if (lane == 0) mbar_arrive(merge_full);
+        } else {
+            if (ok) ok = mbar_wait(merge_full, 0, &abort_flag, err, FT_ERR_SOFTMAX);
+            if (ok && row < len) {
+                const float m1 = mrg[HD * FT_TILE + r], l1 = mrg[(HD + 1) * FT_TILE + r];
+                const float m = fmaxf(m_run, m1);
+                const float f0 = m_run == -INFINITY ? 0.f : ft_exp2(m_run - m);
+                const float f1 = m1 == -INFINITY ? 0.f : ft_exp2(m1 - m);
+                float f = 1.f / (l_run * f0 + l1 * f1);
+                const long long tok = s0 + row;
+                if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + hq]));
+                bf16* dst = ctx + tok * ldc + (long long)hq * HD;
+#pragma unroll
+                for (int c = 0; c < HD / 8; ++c) {
+                    uint4 raw;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int d = 8 * c + 2 * i;
+                        h[i] = __floats2bfloat162_rn((o_acc[d] * f0 + mrg[d * FT_TILE + r] * f1) * f,
+                                                     (o_acc[d + 1] * f0 + mrg[(d + 1) * FT_TILE + r] * f1) * f);
+                    }
+                    *reinterpret_cast<uint4*>(dst + 8 * c) = raw;
+                }
+            }
+        }
+    }
+    // ------------------------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag && threadIdx.x == 0) {
+        // copies that were issued but never consumed must land before shared memory is given up
+        for (int i = 0; i < TC_SPIN_LIMIT; ++i)
+            if (mbar_try_wait(q_full, 0)) break;
+        for (int j = max(0, issued_k - STAGES); j < issued_k; ++j)
+            for (int i = 0; i < TC_SPIN_LIMIT; ++i)
+                if (mbar_try_wait(k_full + 8 * (j % STAGES), (j / STAGES) & 1)) break;
+        for (int j = max(0, issued_v - STAGES); j < issued_v; ++j)
+            for (int i = 0; i < TC_SPIN_LIMIT; ++i)
+                if (mbar_try_wait(v_full + 8 * (j % STAGES), (j / STAGES) & 1)) break;
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int HD, int STAGES>
+static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
+                     const void* gate, long long ldg, const int* seq_start, int B, int max_len, long long T, int QH,
+                     int KVH, int window, float scale, int* err, cudaStream_t st) {
+    CUtensorMap map_q, map_k, map_v;
+    int rc = make_map(&map_q, q, T, (long long)QH * HD, ld, FT_TILE);
+    if (rc == CM_OK) rc = make_map(&map_k, k, T, (long long)KVH * HD, ld, FT_TILE);
+    if (rc == CM_OK) rc = make_map(&map_v, v, T, (long long)KVH * HD, ld, FT_TILE);
+    if (rc != CM_OK) return rc;
+    constexpr int KB = HD / 64;
+    const size_t smem = (size_t)KB * FT_PIECE_BYTES * (1 + 2 * STAGES) + 2 * 2 * FT_PIECE_BYTES + 1024;
+    auto kernel = attn_prefill_tc_kernel<HD, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            CM_REFUSE("attn_prefill_tc: %zu bytes of shared memory refused", smem);
+        }
+        configured = true;
+    }
+    dim3 grid((max_len + FT_TILE - 1) / FT_TILE, QH, B);
+    cm_launch(kernel, grid, FT_THREADS, smem, st, map_q, map_k, map_v, (bf16*)ctx, ldc, (const bf16*)gate, ldg, seq_start,
+              QH, KVH, window, scale * 1.4426950408889634f, err);
+    {
+        cudaError_t e_ = cudaGetLastError();
+        if (e_ != cudaSuccess) {
+            cudaFuncAttributes fa;
+            cudaFuncGetAttributes(&fa, kernel);
+            cm_set_error("attn_prefill_tc launch failed: %s (registers %d, static smem %zu, dynamic %zu, max threads %d)",
+                         cudaGetErrorString(e_), fa.numRegs, fa.sharedSizeBytes, smem, fa.maxThreadsPerBlock);
+            return CM_ERR_LAUNCH;
+        }
+    }
+    return CM_OK;
+}
+
+// bfloat16; head size 64 or 128; q, k, v are column blocks of one row-major buffer of T rows with
+// a row pitch that is a multiple of 8 elements, every base 16-byte aligned, and so is the output's
+// base and pitch.  err: device int that a block raises when one of its bounded waits runs out.
+extern "C" int cm_attn_prefill_tc(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
+                                  const void* gate, long long ldg, const int* seq_start, int B, int max_len,
+                                  long long T, int QH, int KVH, int HD, int window, float scale, int* err,
+                                  cudaStream_t st) {
+    if (B <= 0 || max_len <= 0) return CM_OK;
+    if (QH % KVH) CM_REFUSE("attn_prefill_tc: %d query heads over %d key heads", QH, KVH);
+    if (ld % 8 || ldc % 8 || (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)ctx) & 15))
+        CM_REFUSE("attn_prefill_tc: row pitches %lld, %lld must be multiples of 8 and the operands 16-byte aligned", ld, ldc);
+    if (HD == 64)
+        return launch_ft<64, 3>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale, err, st);
+    if (HD == 128)
+        return launch_ft<128, 2>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale, err, st);
+    CM_REFUSE("attn_prefill_tc: head size %d (64 or 128)", HD);
+}

@@ -111,8 +111,22 @@ class Runtime:
         return a
 
     # ------------------------------------------------------------------ attention
+    TCGEN05_ATTENTION_MIN_LEN = 1024     # shorter prompts (or windows) give a block too few key tiles to pipeline
+
     def attention_prefill(self, ctx, q, k, v, gate, batch, QH, KVH, HD, window, scale):
-        tensor_cores = (q.dtype == torch.bfloat16 and HD % 16 == 0 and HD <= 128 and q.stride(0) % 8 == 0
-                        and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
-        fn = kernels.attn_prefill_mma if tensor_cores else kernels.attn_prefill_simt
+        """Attention of a prompt step over the step's own keys and values.  bfloat16 with head size
+        64 or 128 and long sequences: the tcgen05 kernel (measured on B200, 32 heads of 64: 79 us
+        against 105 us at 2,048 tokens, 431 against 264 TFLOP/s at 16,384; with 512-token windows or
+        512-token prompts the mma.sync kernel is the faster one).  Other bfloat16 head sizes that
+        are multiples of 16 up to 128: mma.sync.  Everything else, and float32: CUDA cores."""
+        aligned = (q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
+                   and v.data_ptr() % 16 == 0)
+        bf16 = q.dtype == torch.bfloat16
+        span = min(batch.max_len, window) if window else batch.max_len
+        if (bf16 and aligned and HD in (64, 128) and span >= self.TCGEN05_ATTENTION_MIN_LEN
+                and ctx.stride(0) % 8 == 0 and ctx.data_ptr() % 16 == 0):
+            kernels.attn_prefill_tc(ctx, q, k, v, gate, batch.seq_start, batch.B, batch.max_len, QH, KVH, HD, window,
+                                    scale, err=self.error_flag)
+            return
+        fn = kernels.attn_prefill_mma if (bf16 and aligned and HD % 16 == 0 and HD <= 128) else kernels.attn_prefill_simt
         fn(ctx, q, k, v, gate, batch.seq_start, batch.B, batch.max_len, QH, KVH, HD, window, scale)

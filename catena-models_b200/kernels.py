@@ -33,6 +33,7 @@ _SIGNATURES = {
                       _i, _f, _vp],
     "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "cm_attn_prefill_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "cm_attn_prefill_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _ll, _i, _i, _i, _i, _f, _vp, _vp],
     "cm_attn_decode": [_i, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _i,
                        _i, _f, _vp, _vp, _vp],
     "cm_shortconv": [_i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
@@ -234,6 +235,17 @@ def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, win
     _check(lib().cm_attn_prefill_mma(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
                                      0 if gate is None else gate.stride(0), _ptr(seq_start), B, max_len, QH, KVH,
                                      HD, window, scale, _stream()), "attn_prefill_mma")
+
+
+def attn_prefill_tc(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, err=None):
+    """The same on the tcgen05 tensor cores (TMA-fed, scores and outputs in tensor memory): bfloat16,
+    head size 64 or 128.  q, k and v are column blocks of one row-major buffer.  err: device int32
+    that a block raises if one of its bounded pipeline waits runs out."""
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.dtype != torch.bfloat16 or q.shape[0] != k.shape[0]:
+        raise KernelError("attn_prefill_tc: bfloat16 q, k and v that share rows and a row stride")
+    _check(lib().cm_attn_prefill_tc(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
+                                    0 if gate is None else gate.stride(0), _ptr(seq_start), B, max_len, q.shape[0],
+                                    QH, KVH, HD, window, scale, _ptr(err), _stream()), "attn_prefill_tc")
 
 
 def set_decode_attention_target_blocks(blocks):

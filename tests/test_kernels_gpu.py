@@ -542,6 +542,64 @@ def test_attn_prefill_mma_long_and_window_edge(K, window):
     assert torch.equal(hit, expect)
 
 
+@pytest.mark.parametrize("QH,KVH,HD,window,gated", [(8, 2, 64, 0, True), (4, 4, 64, 300, False), (2, 1, 128, 0, True),
+                                                    (4, 2, 128, 130, True), (3, 1, 64, 128, False)])
+def test_attn_prefill_tc_varlen(K, QH, KVH, HD, window, gated):
+    """tcgen05 prefill attention: packed sequences that end inside a tile, at a tile's edge and
+    after several tiles, so that the last tile of one runs into the next one's rows."""
+    lens = [17, 128, 1, 129, 700, 256]
+    T = sum(lens)
+    width = (QH * HD + 2 * KVH * HD + (QH if gated else 0) + 7) // 8 * 8
+    buf = rnd(T, width, dtype=torch.bfloat16, seed=HD + window)
+    q, k = buf[:, :QH * HD], buf[:, QH * HD:QH * HD + KVH * HD]
+    v = buf[:, QH * HD + KVH * HD:QH * HD + 2 * KVH * HD]
+    gate = buf[:, QH * HD + 2 * KVH * HD:QH * HD + 2 * KVH * HD + QH] if gated else None
+    bounds = [0]
+    for n in lens:
+        bounds.append(bounds[-1] + n)
+    starts = torch.tensor(bounds, dtype=torch.int32, device=DEV)
+    ctx = torch.full((T, QH * HD), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = HD ** -0.5
+    K.attn_prefill_tc(ctx, q, k, v, gate, starts, len(lens), max(lens), QH, KVH, HD, window, scale, err=err)
+    assert int(err) == 0
+    for b, n in enumerate(lens):
+        sl = slice(bounds[b], bounds[b] + n)
+        ref = _ref_attention(q[sl].cpu().view(n, QH, HD), k[sl].cpu().view(n, KVH, HD), v[sl].cpu().view(n, KVH, HD),
+                             window, scale, None if gate is None else gate[sl].cpu())
+        close(ctx[sl].view(n, QH, HD), ref, torch.bfloat16)
+
+
+@pytest.mark.parametrize("window", [0, 100])
+def test_attn_prefill_tc_far_key_and_window_edge(K, window):
+    """One key is made to dominate and must be seen by exactly the queries whose window holds it."""
+    QH, KVH, HD, T = 2, 1, 64, 700
+    buf = rnd(T, QH * HD + 2 * KVH * HD, dtype=torch.bfloat16, scale=0.3, seed=11)
+    far = 250
+    buf[far, QH * HD:QH * HD + HD] = 0
+    buf[far, QH * HD] = 30.0                       # the key
+    buf[:, 0] = 30.0                               # every query of head 0 looks for it
+    q, k, v = buf[:, :QH * HD], buf[:, QH * HD:QH * HD + HD], buf[:, QH * HD + HD:]
+    starts = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    ctx = torch.empty(T, QH * HD, dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.attn_prefill_tc(ctx, q, k, v, None, starts, 1, T, QH, KVH, HD, window, HD ** -0.5, err=err)
+    assert int(err) == 0
+    ref = _ref_attention(q.cpu().view(T, QH, HD), k.cpu().view(T, KVH, HD), v.cpu().view(T, KVH, HD), window, HD ** -0.5)
+    close(ctx.view(T, QH, HD), ref, torch.bfloat16)
+    hit = (ctx.view(T, QH, HD)[:, 0].float() - v[far].float()).abs().max(dim=-1).values < 0.05
+    expect = torch.arange(T, device=DEV) >= far
+    if window:
+        expect &= torch.arange(T, device=DEV) < far + window
+    assert torch.equal(hit, expect)
+
+
+def test_attn_prefill_tc_refuses_other_head_sizes(K):
+    x = torch.empty(4, 96, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(K.KernelError, match="head size"):
+        K.attn_prefill_tc(x, x, x, x, None, torch.zeros(2, dtype=torch.int32, device=DEV), 1, 4, 1, 1, 96, 0, 1.0)
+
+
 def test_more_tokens_than_a_grid_dimension_holds(K):
     """A prompt step may carry more than 65,535 tokens (64 prompts of 2,048): the per-token kernels
     must not put the token index on a grid axis that ends there."""
