@@ -2,13 +2,14 @@
 // sliding-window attention of packed sequences over their own keys and values, grouped query
 // heads, optional per-head sigmoid gate.  Same result as attn_prefill_mma (attention_mma.cu).
 //
-// One block per (128-query tile, query head, sequence), long tiles first.  Ten warps:
+// One block per (128-query tile, query head, sequence), long tiles first.  Twelve warps (the first
+// group of four gives most of its registers to the other two, setmaxnreg 40 / 232):
 //   warp 0   one thread: TMA loads of the Q tile and of 128-key K and V tiles into shared-memory
 //            rings (128-byte rows, 128-byte swizzle; a head of 128 is two 64-column pieces);
 //   warp 1   allocates tensor memory; one thread issues S = Q K^T (128 x 128, K-major operands)
 //            into one of two S buffers, and O' = P V (128 x HD, V as the MN-major B operand:
 //            its rows are keys) into one of two O' buffers, committing to mbarriers;
-//   warps 2-5 and 6-9  two softmax groups of 128 threads, one query row per thread.  Group g takes
+//   warps 4-7 and 8-11  two softmax groups of 128 threads, one query row per thread.  Group g takes
 //            the key tiles g, g+2, ...: reads its S buffer from tensor memory (maximum first,
 //            then exponentials), writes P as bfloat16 into its shared-memory buffer in the A
 //            operand's layout, and adds the finished O' of its previous tile into float
@@ -24,7 +25,7 @@
 #include "tc_common.cuh"
 
 #define FT_TILE 128
-#define FT_THREADS 320
+#define FT_THREADS 384                     // three groups of four warps: loader and issuer, softmax 0, softmax 1
 #define FT_PIECE_BYTES (128 * 64 * 2)      // 128 rows of 128 bytes
 #define FT_ERR_LOAD 111
 #define FT_ERR_MMA 112
@@ -57,9 +58,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        int KVH, int window, float scale_log2, int* err) {
     constexpr int KB = HD / 64;                                   // 64-column pieces of a head
     constexpr uint32_t Q_BYTES = KB * FT_PIECE_BYTES, KV_BYTES = KB * FT_PIECE_BYTES, P_BYTES = 2 * FT_PIECE_BYTES;
-    constexpr uint32_t TMEM_COLS = 512;                           // S0 S1 (128 each), O'0 O'1 (HD each)
-    constexpr int NBARS = 1 + 4 * STAGES + 12;
-    static_assert(256 + 2 * HD <= 512, "tensor memory holds two S and two O' buffers");
+    // tensor memory: NS score buffers of 128 columns, one per softmax group (a third one, which lets
+    // the scores of a group's next tile be formed earlier, was measured and gained nothing), then one
+    // O' buffer of HD columns per group
+    constexpr int NS = 2;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr int NBARS = 1 + 4 * STAGES + 2 * NS + 8;
+    static_assert(NS * FT_TILE + 2 * HD <= 512, "tensor memory holds the S and O' buffers");
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[NBARS];
     __shared__ uint32_t tmem_slot;
@@ -82,7 +87,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t q_full = bar0;
     const uint32_t k_full = bar0 + 8, k_empty = k_full + 8 * STAGES, v_full = k_empty + 8 * STAGES,
                    v_empty = v_full + 8 * STAGES;
-    const uint32_t s_full = v_empty + 8 * STAGES, s_empty = s_full + 16, p_full = s_empty + 16, o_full = p_full + 16,
+    const uint32_t s_full = v_empty + 8 * STAGES, s_empty = s_full + 8 * NS, p_full = s_empty + 8 * NS, o_full = p_full + 16,
                    o_empty = o_full + 16, all_done = o_empty + 16, merge_full = all_done + 8;
 
     if (threadIdx.x == 0) {
@@ -93,9 +98,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(v_full + 8 * s, 1);
             mbar_init(v_empty + 8 * s, 1);
         }
+        for (int i = 0; i < NS; ++i) {
+            mbar_init(s_full + 8 * i, 1);
+            mbar_init(s_empty + 8 * i, 4);                        // one arrival per warp of the group that read it
+        }
         for (int g = 0; g < 2; ++g) {
-            mbar_init(s_full + 8 * g, 1);
-            mbar_init(s_empty + 8 * g, 4);                        // one arrival per warp of the group
             mbar_init(p_full + 8 * g, 4);
             mbar_init(o_full + 8 * g, 1);
             mbar_init(o_empty + 8 * g, 4);
@@ -117,7 +124,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
-
+    // 384 threads x 168 registers fill the register file; the first four warps keep 40 each and the
+    // eight softmax warps take 232 (4 x 32 x 40 + 8 x 32 x 232 = 64,512 of 65,536)
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------- TMA loader
         mbar_expect_tx(q_full, Q_BYTES);
@@ -158,19 +168,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                                      ((uint32_t)(FT_TILE >> 4) << 24);
         bool ok = mbar_wait(q_full, 0, &abort_flag, err, FT_ERR_MMA);
         auto issue_s = [&](int j) {
-            const int g = j & 1, t = j >> 1, s = j % STAGES;
+            const int s = j % STAGES;
             ok = mbar_wait(k_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
-            if (ok) ok = mbar_wait(s_empty + 8 * g, (t & 1) ^ 1, &abort_flag, err, FT_ERR_MMA);
+            if (ok) ok = mbar_wait(s_empty + 8 * (j % NS), ((j / NS) & 1) ^ 1, &abort_flag, err, FT_ERR_MMA);
             if (!ok) return;
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < HD / 16; ++k) {
                 const uint64_t a = umma_desc(q_s + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
                 const uint64_t bd = umma_desc(k_s + s * KV_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
-                umma_bf16(tmem_base + (uint32_t)(g * FT_TILE), a, bd, idesc_s, k != 0);
+                umma_bf16(tmem_base + (uint32_t)((j % NS) * FT_TILE), a, bd, idesc_s, k != 0);
             }
             umma_commit(k_empty + 8 * s);
-            umma_commit(s_full + 8 * g);
+            umma_commit(s_full + 8 * (j % NS));
         };
         auto issue_o = [&](int j) {
             const int g = j & 1, t = j >> 1, s = j % STAGES;
@@ -183,24 +193,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int k = 0; k < FT_TILE / 16; ++k) {                // 16 keys per instruction
                 const uint64_t a = umma_desc(p_s + g * P_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
                 const uint64_t bd = umma_desc_mn(v_s + s * KV_BYTES + k * 2048, FT_PIECE_BYTES);
-                umma_bf16(tmem_base + (uint32_t)(2 * FT_TILE + g * HD), a, bd, idesc_o, k != 0);
+                umma_bf16(tmem_base + (uint32_t)(NS * FT_TILE + g * HD), a, bd, idesc_o, k != 0);
             }
             umma_commit(v_empty + 8 * s);
             umma_commit(o_full + 8 * g);
         };
-        if (ok) issue_s(0);
-        if (ok && n > 1) issue_s(1);
+        for (int j = 0; j < NS && j < n && ok; ++j) issue_s(j);
         for (int j = 0; j < n && ok; ++j) {
             issue_o(j);
-            if (ok && j + 2 < n) issue_s(j + 2);
+            if (ok && j + NS < n) issue_s(j + NS);
         }
-    } else if (warp >= 2) {
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
         // ------------------------------------------------------------- softmax groups
-        const int g = (warp - 2) >> 2, quarter = warp & 3;
+        const int g = (warp - 4) >> 2, quarter = warp & 3;
         const int r = quarter * 32 + lane;                        // the row of the tile this thread owns
         const int row = q0 + r;                                   // its position in the sequence
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t t_s = lane_base + (uint32_t)(g * FT_TILE), t_o = lane_base + (uint32_t)(2 * FT_TILE + g * HD);
+        const uint32_t t_o = lane_base + (uint32_t)(NS * FT_TILE + g * HD);
         const uint32_t my_p = p_s + g * P_BYTES + r * 128;
         float o_acc[HD];
 #pragma unroll
@@ -213,11 +224,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!ok) return;
             tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
-                float v[32];
-                tmem_load32(t_o + (uint32_t)(c * 32), v);
+            for (int c = 0; c < HD / 64; ++c) {
+                float v[64];
+                tmem_load32_issue(t_o + (uint32_t)(c * 64), v);
+                tmem_load32_issue(t_o + (uint32_t)(c * 64 + 32), v + 32);
+                tmem_load_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha_prev, v[i]);
+                for (int i = 0; i < 64; ++i) o_acc[c * 64 + i] = fmaf(o_acc[c * 64 + i], alpha_prev, v[i]);
             }
             tc_fence_before();
             __syncwarp();
@@ -225,9 +238,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         };
         for (int j = g; j < n && ok; j += 2, ++t) {
             const int k0 = (kt_begin + j) * FT_TILE;
-            ok = mbar_wait(s_full + 8 * g, t & 1, &abort_flag, err, FT_ERR_SOFTMAX);
+            ok = mbar_wait(s_full + 8 * (j % NS), (j / NS) & 1, &abort_flag, err, FT_ERR_SOFTMAX);
             if (!ok) break;
             tc_fence_after();
+            const uint32_t t_s = lane_base + (uint32_t)((j % NS) * FT_TILE);
             // every key of the tile is visible to this row: no comparisons needed
             const bool all_visible = k0 + FT_TILE - 1 <= row && k0 + FT_TILE - 1 < len && (window <= 0 || k0 + window > row);
             auto masked = [&](float* v, int c) {
@@ -238,25 +252,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     v[i] = vis ? v[i] : -INFINITY;
                 }
             };
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                float v[32];
-                tmem_load32(t_s + (uint32_t)(c * 32), v);
-                if (!all_visible) masked(v, c);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
-            }
-            const float m_new = fmaxf(m_run, mx * scale_log2);    // scale > 0 keeps the order of the scores
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = ft_exp2(m_run - m_use);
-            m_run = m_new;
-            float rs = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                float v[32];
-                tmem_load32(t_s + (uint32_t)(c * 32), v);
-                if (!all_visible) masked(v, c);
+            auto exp_and_stage = [&](const float* v, int c, float m_use, float& rs) {
                 uint32_t w[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -271,15 +267,51 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
                     st_shared16(dst + ((((c & 1) * 4 + i) ^ (r & 7)) << 4), w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            };
+            // Two passes over the row (maximum, then exponentials), CW columns per wait on tensor
+            // memory: 64 with the 64 output registers of a head of 64, 32 with the 128 of a head of 128.
+            constexpr int CW = HD == 64 ? 64 : 32;
+            float rs = 0.f, mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 128 / CW; ++c) {
+                float v[CW];
+#pragma unroll
+                for (int h = 0; h < CW / 32; ++h) tmem_load32_issue(t_s + (uint32_t)(c * CW + 32 * h), v + 32 * h);
+                tmem_load_wait();
+                if (!all_visible) {
+#pragma unroll
+                    for (int h = 0; h < CW / 32; ++h) masked(v + 32 * h, c * (CW / 32) + h);
+                }
+#pragma unroll
+                for (int i = 0; i < CW; ++i) mx = fmaxf(mx, v[i]);
+            }
+            const float m_new = fmaxf(m_run, mx * scale_log2);    // scale > 0 keeps the order of the scores
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = ft_exp2(m_run - m_use);
+            m_run = m_new;
+#pragma unroll 1
+            for (int c = 0; c < 128 / CW; ++c) {
+                float v[CW];
+#pragma unroll
+                for (int h = 0; h < CW / 32; ++h) tmem_load32_issue(t_s + (uint32_t)(c * CW + 32 * h), v + 32 * h);
+                tmem_load_wait();
+                if (!all_visible) {
+#pragma unroll
+                    for (int h = 0; h < CW / 32; ++h) masked(v + 32 * h, c * (CW / 32) + h);
+                }
+#pragma unroll
+                for (int h = 0; h < CW / 32; ++h) exp_and_stage(v + 32 * h, c * (CW / 32) + h, m_use, rs);
             }
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(s_empty + 8 * g);                     // the S buffer is read out
+                mbar_arrive(s_empty + 8 * (j % NS));              // the S buffer is read out
                 mbar_arrive(p_full + 8 * g);                      // P of this tile is in shared memory
             }
             l_run = l_run * alpha + rs;
+            // O' of the group's previous tile.  (Its P buffer was free before this tile's scores could
+            // be formed: the tensor core runs S of tile j + 2 after P V of tile j.)
             if (t > 0) add_previous(t - 1);
             alpha_prev = alpha;
         }
