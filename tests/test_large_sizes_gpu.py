@@ -89,3 +89,36 @@ def test_twenty_sequences_decode_on_the_tiled_kernel(big):
         noise = plain_lfm3.forward(cfg, tensors, s, bf16=True)[n - 1:]
         g = torch.stack([step[i] for step in got])
         assert rel(g, ref) < 2.0 * rel(noise, ref), i
+
+
+def test_long_prompts_on_the_tcgen05_attention_kernel(big):
+    """Two prompts of more than 1,024 tokens in one step (bfloat16): the prompt attention then runs
+    on the tcgen05 kernel, whose 128-key tiles of the first sequence run into the second one's
+    rows; two decode steps follow over the cache that the prompt step filled."""
+    from catena_models_b200.api import Model
+
+    folder, (cfg, tensors) = big
+    lens, extra = [1100, 1030], 2
+    seqs = [tiny.random_prompt(n + extra, cfg["vocab_size"], seed=7 * n) for n in lens]
+    exact = [plain_lfm3.forward(cfg, tensors, s) for s in seqs]
+    noise = [plain_lfm3.forward(cfg, tensors, s, bf16=True) for s in seqs]
+    model = Model.load(folder, dtype="bfloat16", max_tokens=4096)
+    eng = model.engine
+    slots = eng.admit(2)
+    want = [[0, 127, 128, 640, 1023, 1024, n - 1] for n in lens]
+    out = eng.step(slots, [s[:n] for s, n in zip(seqs, lens)], want)
+    got, pos, off = [[], []], [list(w) for w in want], 0
+    for i, w in enumerate(want):
+        got[i].append(out[off:off + len(w)].clone())
+        off += len(w)
+    for t in range(extra):
+        out = eng.step(slots, [[s[n + t]] for s, n in zip(seqs, lens)])
+        for i in range(2):
+            got[i].append(out[i:i + 1].clone())
+            pos[i].append(lens[i] + t)
+    eng.release(slots)
+    model.decoder.rt.check_errors()
+    for i in range(2):
+        g, ref = torch.cat(got[i]), exact[i][pos[i]]
+        assert rel(g, ref) < 2.0 * rel(noise[i][pos[i]], ref)
+        assert torch.equal(g.argmax(-1).cpu(), ref.argmax(-1)) or rel(g, ref) < 0.02
