@@ -28,12 +28,38 @@ def _dtype(d):
         raise ValueError(f"dtype must be bfloat16 or float32, got {d!r}") from None
 
 
+class Checkpoint:
+    """The state of a session that was set aside (`Session.into_checkpoint`, src/model.rs:208-246,
+    431-446): it keeps the sequence's slot of the cache until it is closed.  `Model.resume_checkpoint`
+    starts any number of sessions from it, each on a copy of its own."""
+
+    def __init__(self, model, slot, capacity):
+        self.model, self.slot, self.capacity = model, slot, capacity
+
+    @property
+    def position(self):
+        return self.model.engine.length(self.slot)
+
+    def close(self):
+        if self.slot is not None:
+            self.model.engine.release([self.slot])
+            self.slot = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
 class Session:
     """One sequence on a slot of the model's cache (src/model.rs:420-502)."""
 
-    def __init__(self, model, capacity):
+    def __init__(self, model, capacity, _slot=None):
         self.model, self.capacity = model, capacity
-        (self.slot,) = model.engine.admit(1)
+        if _slot is None:
+            (_slot,) = model.engine.admit(1)
+        self.slot = _slot
         self._greedy = Sampler(model.device)
 
     @property
@@ -56,6 +82,32 @@ class Session:
 
     def decode_next_token(self, token):
         return self._greedy.sample(self._run([token]), [0], [0])[0]
+
+    def append_logits(self, tokens):
+        """Logits after `tokens` on top of what the session holds (src/model.rs: append_logits).  A
+        fresh session takes them as one prompt step; a started one takes them one by one."""
+        tokens = list(tokens)
+        if not tokens:
+            raise ValueError("append needs at least one token")
+        if self.position == 0:
+            return self.prefill_logits(tokens)
+        if self.position + len(tokens) > self.capacity:
+            raise ValueError(f"session capacity {self.capacity} exceeded")
+        for t in tokens[:-1]:
+            self._run([t])
+        return self.decode_logits(tokens[-1])
+
+    def append_next_token(self, tokens):
+        logits = self.append_logits(tokens)
+        return int(torch.argmax(logits))                      # the first of equal maxima, as the device sampler
+
+    def into_checkpoint(self):
+        """Sets the session's state aside; the session itself is over."""
+        if self.slot is None:
+            raise ValueError("the session is closed")
+        ckpt = Checkpoint(self.model, self.slot, self.capacity)
+        self.slot = None
+        return ckpt
 
     def close(self):
         if self.slot is not None:
@@ -99,6 +151,21 @@ class Model:
 
     def session(self, capacity):
         return Session(self, capacity)
+
+    def resume_checkpoint(self, checkpoint):
+        """A new session that starts from a copy of the checkpoint's state.  Refused for a checkpoint
+        of another model (src/model.rs:210-213)."""
+        if checkpoint.model is not self:
+            raise ValueError("the checkpoint belongs to another model")
+        if checkpoint.slot is None:
+            raise ValueError("the checkpoint is closed")
+        (slot,) = self.engine.admit(1)
+        try:
+            self.engine.cache.copy_slot(checkpoint.slot, slot)
+        except Exception:
+            self.engine.release([slot])
+            raise
+        return Session(self, checkpoint.capacity, _slot=slot)
 
     def logits(self, tokens):
         """Logits after the last of `tokens`, as float32 on the host (src/model.rs:187-190)."""

@@ -192,6 +192,32 @@ class Cache:
     def release(self, slot):
         self.book.release(slot)
 
+    def copy_slot(self, src, dst):
+        """Give the fresh slot `dst` a copy of everything slot `src` holds: its pages (new pages,
+        same contents), its fixed-size states and its length.  All or nothing."""
+        book = self.book
+        if src not in book.length or dst not in book.length:
+            raise CacheError("copy_slot: both slots must be live")
+        if book.length[dst] != 0 or any(book.pages[dst]):
+            raise CacheError(f"copy_slot: slot {dst} already holds tokens")
+        length = book.length[src]
+        updates = book.reserve(dst, length)                  # raises CacheFull and takes nothing if short
+        flat = self.flat_updates(dst, updates)
+        if flat:
+            index = torch.tensor([i for i, _ in flat], dtype=torch.int32, device=self.device)
+            value = torch.tensor([p for _, p in flat], dtype=torch.int32, device=self.device)
+            count = torch.tensor([len(flat)], dtype=torch.int32, device=self.device)
+            kernels.scatter_i32(self.ptab_all, index, value, count, len(flat))
+        for g in range(len(self.kv_specs)):
+            n = len(book.pages[dst][g])
+            if n:
+                s_ids = torch.tensor(book.pages[src][g][:n], dtype=torch.int32, device=self.device)
+                d_ids = torch.tensor(book.pages[dst][g], dtype=torch.int32, device=self.device)
+                kernels.copy_pages(self.kv_storage[g], s_ids, d_ids)
+        for store in self.fixed_storage:
+            store[:, dst].copy_(store[:, src])
+        book.advance(dst, length)
+
     def flat_updates(self, slot, updates):
         """(index into ptab_all, page) pairs for the entries `CacheBook.reserve` returned."""
         return [(self._ptab_offset[g] + slot * self.book.pages_per_seq[g] + j, page) for g, j, page in updates]

@@ -56,3 +56,28 @@ extern "C" int cm_zero_rows_f32(float* x, const int* rows, int n, long long widt
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
+
+// Copies whole pages inside a paged pool [outer, pages, page_bytes]: page src[i] to page dst[i] for
+// every outer index (layer and key/value plane).  Used to give a resumed sequence its own copy of a
+// checkpointed one (catena-models copies session buffers with its copy-buffer kernel,
+// src/model.rs:208-246).  page_bytes is a multiple of 16; src and dst pages do not overlap.
+__global__ void copy_pages_kernel(uint4* __restrict__ pool, const int* __restrict__ src, const int* __restrict__ dst,
+                                  long long pages, long long page_vec) {
+    pdl_trigger();
+    pdl_wait();
+    const long long plane = (long long)blockIdx.y * pages;
+    const uint4* from = pool + (plane + src[blockIdx.x]) * page_vec;
+    uint4* to = pool + (plane + dst[blockIdx.x]) * page_vec;
+    for (long long i = threadIdx.x; i < page_vec; i += blockDim.x) to[i] = from[i];
+}
+
+extern "C" int cm_copy_pages(void* pool, const int* src, const int* dst, int n, int outer, long long pages,
+                             long long page_bytes, cudaStream_t st) {
+    if (n <= 0 || outer <= 0) return CM_OK;
+    if (page_bytes % 16 || (reinterpret_cast<uintptr_t>(pool) & 15))
+        CM_REFUSE("copy_pages: pages of %lld bytes (multiples of 16, 16-byte aligned pool)", page_bytes);
+    if (outer > 65535) CM_REFUSE("copy_pages: %d planes", outer);
+    cm_launch(copy_pages_kernel, dim3(n, outer), 256, 0, st, (uint4*)pool, src, dst, pages, page_bytes / 16);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "cm_sample": [_vp, _vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "cm_scatter_i32": [_vp, _vp, _vp, _vp, _i, _vp],
     "cm_zero_rows_f32": [_vp, _vp, _i, _ll, _vp],
+    "cm_copy_pages": [_vp, _vp, _vp, _i, _i, _ll, _ll, _vp],
 }
 
 
@@ -296,6 +297,15 @@ def sample(out, logits, temperature, sequence, step, seed_words):
 def scatter_i32(table, index, value, count, max_count):
     _check(lib().cm_scatter_i32(_ptr(table), _ptr(index), _ptr(value), _ptr(count), max_count, _stream()),
            "scatter_i32")
+
+
+def copy_pages(pool, src, dst):
+    """pool: [layers, 2, pages, ...] paged storage of one group; page src[i] is copied to page dst[i]
+    in every layer and plane (int32 device tensors of equal length)."""
+    n = src.numel()
+    outer, pages = pool.shape[0] * pool.shape[1], pool.shape[2]
+    page_bytes = pool[0, 0, 0].numel() * pool.element_size()
+    _check(lib().cm_copy_pages(_ptr(pool), _ptr(src), _ptr(dst), n, outer, pages, page_bytes, _stream()), "copy_pages")
 
 
 def zero_rows_f32(x, rows, n, width):

@@ -124,6 +124,56 @@ def test_session_api(folders):
     assert not model.engine.cache.book.live
 
 
+def test_checkpoint_resume_and_append(folders):
+    """A session is set aside as a checkpoint after 70 tokens (more than a page, the sliding ring
+    of 8 wrapped many times, conv state in use); two sessions resumed from it go different ways and
+    each must give the logits of its whole sequence, as must the append calls; closing everything
+    gives every page and slot back."""
+    from catena_models_b200.api import Model
+
+    cfg, tensors = plain_lfm3.load_folder(folders["B"])
+    model = Model.load(folders["B"], dtype="float32", max_tokens=1024)
+    book = model.engine.cache.book
+    free_pages = [a.free_count for a in book.page_alloc]
+    base = tiny.random_prompt(70, cfg["vocab_size"], seed=5)
+    tails = [tiny.random_prompt(6, cfg["vocab_size"], seed=6), tiny.random_prompt(4, cfg["vocab_size"], seed=7)]
+
+    s = model.session(capacity=128)
+    s.prefill_logits(base[:60])
+    got = s.append_logits(base[60:])                           # ten tokens on top of a started sequence
+    exact = plain_lfm3.forward(cfg, tensors, base)
+    assert float((got.double() - exact[-1]).abs().max()) < 1e-4
+    ckpt = s.into_checkpoint()
+    assert s.slot is None and ckpt.position == 70
+    with pytest.raises(ValueError):
+        s.into_checkpoint()
+
+    sessions = [model.resume_checkpoint(ckpt), model.resume_checkpoint(ckpt)]
+    assert len({x.slot for x in sessions} | {ckpt.slot}) == 3 and all(x.position == 70 for x in sessions)
+    outs = [[], []]
+    for step in range(6):                                       # the two go on in turns, not in one batch
+        for i, (x, tail) in enumerate(zip(sessions, tails)):
+            if step < len(tail):
+                outs[i].append(x.decode_logits(tail[step]))
+    for i, tail in enumerate(tails):
+        ref = plain_lfm3.forward(cfg, tensors, base + tail)[70:]
+        assert float((torch.stack(outs[i]).double() - ref).abs().max()) < 1e-4
+    # the checkpoint is still what it was: a third session from it gives the first tail's logits again
+    third = model.resume_checkpoint(ckpt)
+    tok = third.append_next_token(tails[0][:2])
+    assert tok == int(plain_lfm3.argmax_first(plain_lfm3.forward(cfg, tensors, base + tails[0][:2])[-1]))
+
+    other = Model.load(folders["B"], dtype="float32", max_tokens=256)
+    with pytest.raises(ValueError, match="another model"):
+        other.resume_checkpoint(ckpt)
+    for x in sessions + [third]:
+        x.close()
+    ckpt.close()
+    with pytest.raises(ValueError, match="closed"):
+        model.resume_checkpoint(ckpt)
+    assert not book.live and [a.free_count for a in book.page_alloc] == free_pages
+
+
 def test_command_line(folders, tmp_path):
     cfg, tensors = plain_lfm3.load_folder(folders["A"])
     p1, p2 = tiny.random_prompt(6, cfg["vocab_size"], 1), tiny.random_prompt(13, cfg["vocab_size"], 2)
