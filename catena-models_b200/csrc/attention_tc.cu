@@ -58,12 +58,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        int KVH, int window, float scale_log2, int* err) {
     constexpr int KB = HD / 64;                                   // 64-column pieces of a head
     constexpr uint32_t Q_BYTES = KB * FT_PIECE_BYTES, KV_BYTES = KB * FT_PIECE_BYTES, P_BYTES = 2 * FT_PIECE_BYTES;
-    // tensor memory: NS score buffers of 128 columns, one per softmax group (a third one, which lets
-    // the scores of a group's next tile be formed earlier, was measured and gained nothing), then one
-    // O' buffer of HD columns per group
-    constexpr int NS = 2;
+    // tensor memory: NS score buffers of 128 columns in rotation (three when the head leaves room:
+    // the scores of a group's next tile are then formed while the group is still busy), then one O'
+    // buffer of HD columns per softmax group
+    constexpr int NS = HD == 64 ? 3 : 2;
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr int NBARS = 1 + 4 * STAGES + 2 * NS + 8;
+    constexpr int NBARS = 1 + 4 * STAGES + NS + 6;
     static_assert(NS * FT_TILE + 2 * HD <= 512, "tensor memory holds the S and O' buffers");
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[NBARS];
@@ -87,8 +87,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t q_full = bar0;
     const uint32_t k_full = bar0 + 8, k_empty = k_full + 8 * STAGES, v_full = k_empty + 8 * STAGES,
                    v_empty = v_full + 8 * STAGES;
-    const uint32_t s_full = v_empty + 8 * STAGES, s_empty = s_full + 8 * NS, p_full = s_empty + 8 * NS, o_full = p_full + 16,
-                   o_empty = o_full + 16, all_done = o_empty + 16, merge_full = all_done + 8;
+    const uint32_t s_full = v_empty + 8 * STAGES, p_full = s_full + 8 * NS, o_full = p_full + 16, all_done = o_full + 16,
+                   merge_full = all_done + 8;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -98,14 +98,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(v_full + 8 * s, 1);
             mbar_init(v_empty + 8 * s, 1);
         }
-        for (int i = 0; i < NS; ++i) {
-            mbar_init(s_full + 8 * i, 1);
-            mbar_init(s_empty + 8 * i, 4);                        // one arrival per warp of the group that read it
-        }
+        for (int i = 0; i < NS; ++i) mbar_init(s_full + 8 * i, 1);
         for (int g = 0; g < 2; ++g) {
-            mbar_init(p_full + 8 * g, 4);
+            mbar_init(p_full + 8 * g, 4);                         // one arrival per warp of the group
             mbar_init(o_full + 8 * g, 1);
-            mbar_init(o_empty + 8 * g, 4);
         }
         mbar_init(all_done, 8);
         mbar_init(merge_full, 4);
@@ -169,8 +165,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         bool ok = mbar_wait(q_full, 0, &abort_flag, err, FT_ERR_MMA);
         auto issue_s = [&](int j) {
             const int s = j % STAGES;
+            // The S buffer is free: tile j - NS, which used it, had its P announced (p_full) before
+            // P V of that tile was issued, and this call comes after that.
             ok = mbar_wait(k_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
-            if (ok) ok = mbar_wait(s_empty + 8 * (j % NS), ((j / NS) & 1) ^ 1, &abort_flag, err, FT_ERR_MMA);
             if (!ok) return;
             tc_fence_after();
 #pragma unroll
@@ -184,9 +181,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         };
         auto issue_o = [&](int j) {
             const int g = j & 1, t = j >> 1, s = j % STAGES;
-            ok = mbar_wait(p_full + 8 * g, t & 1, &abort_flag, err, FT_ERR_MMA);
-            if (ok) ok = mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
-            if (ok) ok = mbar_wait(o_empty + 8 * g, (t & 1) ^ 1, &abort_flag, err, FT_ERR_MMA);
+            // V first: it has long been loaded, and P is what this thread really waits for.
+            ok = mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+            if (ok) ok = mbar_wait(p_full + 8 * g, t & 1, &abort_flag, err, FT_ERR_MMA);
+            // The group's O' buffer is free as well: the group adds the O' of its previous tile before it
+            // touches the scores of this one, so before the p_full that was just awaited.
             if (!ok) return;
             tc_fence_after();
 #pragma unroll
@@ -233,11 +232,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int i = 0; i < 64; ++i) o_acc[c * 64 + i] = fmaf(o_acc[c * 64 + i], alpha_prev, v[i]);
             }
             tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_empty + 8 * g);
         };
         for (int j = g; j < n && ok; j += 2, ++t) {
             const int k0 = (kt_begin + j) * FT_TILE;
+            // First O' of the group's previous tile: the tensor core then never waits for this group
+            // to free the O' buffer, and its arrival also says that P V of that tile is done reading
+            // the P buffer, which this tile's exponentials overwrite.
+            if (t > 0) add_previous(t - 1);
+            if (!ok) break;
             ok = mbar_wait(s_full + 8 * (j % NS), (j / NS) & 1, &abort_flag, err, FT_ERR_SOFTMAX);
             if (!ok) break;
             tc_fence_after();
@@ -252,13 +254,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     v[i] = vis ? v[i] : -INFINITY;
                 }
             };
-            auto exp_and_stage = [&](const float* v, int c, float m_use, float& rs) {
+            // four partial sums and four partial maxima: chains of 128 dependent adds or maxima would
+            // leave the thread waiting on arithmetic latency
+            auto exp_and_stage = [&](const float* v, int c, float m_use, float* rs) {
                 uint32_t w[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float p0 = ft_exp2(fmaf(v[2 * i], scale_log2, -m_use));
                     const float p1 = ft_exp2(fmaf(v[2 * i + 1], scale_log2, -m_use));
-                    rs += p0 + p1;
+                    rs[i & 3] += p0 + p1;
                     __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     w[i] = *reinterpret_cast<uint32_t*>(&h);
                 }
@@ -271,7 +275,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // Two passes over the row (maximum, then exponentials), CW columns per wait on tensor
             // memory: 64 with the 64 output registers of a head of 64, 32 with the 128 of a head of 128.
             constexpr int CW = HD == 64 ? 64 : 32;
-            float rs = 0.f, mx = -INFINITY;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
             for (int c = 0; c < 128 / CW; ++c) {
                 float v[CW];
@@ -283,8 +288,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     for (int h = 0; h < CW / 32; ++h) masked(v + 32 * h, c * (CW / 32) + h);
                 }
 #pragma unroll
-                for (int i = 0; i < CW; ++i) mx = fmaxf(mx, v[i]);
+                for (int i = 0; i < CW; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
             }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = fmaxf(m_run, mx * scale_log2);    // scale > 0 keeps the order of the scores
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = ft_exp2(m_run - m_use);
@@ -300,19 +306,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     for (int h = 0; h < CW / 32; ++h) masked(v + 32 * h, c * (CW / 32) + h);
                 }
 #pragma unroll
-                for (int h = 0; h < CW / 32; ++h) exp_and_stage(v + 32 * h, c * (CW / 32) + h, m_use, rs);
+                for (int h = 0; h < CW / 32; ++h) exp_and_stage(v + 32 * h, c * (CW / 32) + h, m_use, rs4);
             }
+            const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(s_empty + 8 * (j % NS));              // the S buffer is read out
-                mbar_arrive(p_full + 8 * g);                      // P of this tile is in shared memory
-            }
+            if (lane == 0) mbar_arrive(p_full + 8 * g);         // P is in shared memory; S and the old O' are read out
             l_run = l_run * alpha + rs;
-            // O' of the group's previous tile.  (Its P buffer was free before this tile's scores could
-            // be formed: the tensor core runs S of tile j + 2 after P V of tile j.)
-            if (t > 0) add_previous(t - 1);
             alpha_prev = alpha;
         }
         if (ok && t > 0) add_previous(t - 1);

@@ -115,8 +115,8 @@ class Runtime:
 
     def attention_prefill(self, ctx, q, k, v, gate, batch, QH, KVH, HD, window, scale):
         """Attention of a prompt step over the step's own keys and values.  bfloat16 with head size
-        64 or 128 and long sequences: the tcgen05 kernel (measured on B200, 32 heads of 64: 79 us
-        against 105 us at 2,048 tokens, 424 against 264 TFLOP/s at 16,384, heads of 128: 739 against
+        64 or 128 and long sequences: the tcgen05 kernel (measured on B200, 32 heads of 64: 73 us
+        against 105 us at 2,048 tokens, 501 against 264 TFLOP/s at 16,384, heads of 128: 840 against
         286; with 512-token windows or 512-token prompts the mma.sync kernel is the faster one).  Other bfloat16 head sizes that
         are multiples of 16 up to 128: mma.sync.  Everything else, and float32: CUDA cores."""
         aligned = (q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
