@@ -447,11 +447,22 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int col = n0 + (MODE == TC_MODE_SWIGLU ? (lane & 15) * 4 : lane * 4);
         const bool vec_ok = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
         for (int row = rank + splits * warp; row < M; row += splits * (TC_THREADS / 32)) {
+            // all ranks' pieces are requested before any is added: one round trip through distributed
+            // shared memory instead of one per rank; the sum still runs in rank order
+            float4 part[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r < splits) {
+                    const float* src = splits > 1 ? cluster.map_shared_rank(stage, r) : stage;
+                    part[r] = *reinterpret_cast<const float4*>(src + (size_t)row * TCS_PITCH + lane * 4);
+                }
+            }
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int r = 0; r < splits; ++r) {
-                const float* src = splits > 1 ? cluster.map_shared_rank(stage, r) : stage;
-                const float4 x = *reinterpret_cast<const float4*>(src + (size_t)row * TCS_PITCH + lane * 4);
-                acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r < splits) {
+                    acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w;
+                }
             }
             float o[4] = {acc.x, acc.y, acc.z, acc.w};
             if (MODE == TC_MODE_SWIGLU) {
