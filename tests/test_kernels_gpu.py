@@ -600,6 +600,20 @@ def test_attn_prefill_tc_refuses_other_head_sizes(K):
         K.attn_prefill_tc(x, x, x, x, None, torch.zeros(2, dtype=torch.int32, device=DEV), 1, 4, 1, 1, 96, 0, 1.0)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_copy_pages(K, dtype):
+    """Pages of a paged pool copied to other pages in every layer and plane; the rest untouched."""
+    layers, pages, kvh, hd = 3, 11, 2, 24
+    pool = rnd(layers, 2, pages, kvh, 64, hd, dtype=dtype, seed=5)
+    before = pool.clone()
+    src = torch.tensor([7, 0, 3], dtype=torch.int32, device=DEV)
+    dst = torch.tensor([1, 10, 5], dtype=torch.int32, device=DEV)
+    K.copy_pages(pool, src, dst)
+    expect = before.clone()
+    expect[:, :, dst.long()] = before[:, :, src.long()]
+    assert torch.equal(pool, expect)
+
+
 def test_more_tokens_than_a_grid_dimension_holds(K):
     """A prompt step may carry more than 65,535 tokens (64 prompts of 2,048): the per-token kernels
     must not put the token index on a grid axis that ends there."""
