@@ -59,6 +59,7 @@ class StepBatch:
         self.max_end = max((p + n for p, n in zip(positions, lengths)), default=0)
         self.n_want, self.n_updates = n_want, n_updates
         self.chunk_bucket = None                               # set by a captured decode graph
+        self.wants_every_row = False                           # want_rows is 0, 1, ..., T-1 (set by the decode path)
         self.shared = {}                                       # what a layer leaves for later layers of this step
 
     def decode_chunks(self, kv_spec):

@@ -259,6 +259,7 @@ class Engine:
             # (temperature 0 and zeroed keys then make it an argmax).
             batch = StepBatch(layout, entry.device_buf, False, [1] * B, positions, B, len(updates))
             batch.chunk_bucket = bucket
+            batch.wants_every_row = True                       # fill_host_decode wants every row, in order
 
             def run():
                 out = self.model.forward(batch, self.cache)

@@ -84,16 +84,22 @@ class DecoderModel:
         kernels.embed_gather(h, self.embedding, batch.tokens, self.token_error)
         plan = self.plan
         n = self.blocks[plan[0].block].input_norm.apply(rt, h)
+        # when every row is wanted in order (a decode step), the last block's fused residual kernel
+        # applies the final norm too and no rows need gathering
+        whole = batch.wants_every_row and batch.n_want == batch.T
         for i, entry in enumerate(plan):
             block = self.blocks[entry.block]
-            next_norm = self.blocks[plan[i + 1].block].input_norm if i + 1 < len(plan) else None
+            next_norm = (self.blocks[plan[i + 1].block].input_norm if i + 1 < len(plan)
+                         else (self.final_norm if whole else None))
             state = cache.view(entry.state)
             if state is not None:
                 state.owned, state.unit = entry.owns_state, entry.state
             h, n = block.forward(rt, batch, h, n, state, next_norm)
-        rows = torch.empty((batch.n_want, self.hidden_size), dtype=rt.dtype, device=rt.device)
         if batch.n_want == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=rt.device)
+        if whole and n is not None:
+            return rt.linear(n, self.head_weight, out_dtype=torch.float32)
+        rows = torch.empty((batch.n_want, self.hidden_size), dtype=rt.dtype, device=rt.device)
         kernels.gather_rows(rows, h, batch.want_rows)
         normed = self.final_norm.apply(rt, rows)
         return rt.linear(normed, self.head_weight, out_dtype=torch.float32)
