@@ -21,7 +21,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the 1.7B-class model.  The layer pattern (two conv layers, then an
+# The 1.7B-class model of the headline benchmark.  The layer pattern (two conv layers, then an
 # attention layer, alternately full and sliding) is this bench's choice; the reference fixes
 # only that its 24-layer model has conv, full and sliding layers (tests/lfm3.rs:39-42).
 FULL_LAYERS = 24

@@ -22,7 +22,7 @@ def folders(tmp_path_factory):
 
 
 def test_greedy_float32_equals_plain_tokens(folders):
-    """BASELINE workload of the first tiny model: prompts of 5, 11 and 17 tokens, 8 greedy steps."""
+    """The first tiny model on its named workload: prompts of 5, 11 and 17 tokens, 8 greedy steps."""
     from catena_models_b200.api import Model
 
     cfg, tensors = plain_lfm3.load_folder(folders["A"])
