@@ -123,86 +123,86 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // 384 threads x 168 registers fill the register file; the first four warps keep 40 each and the
     // eight softmax warps take 232 (4 x 32 x 40 + 8 x 32 x 232 = 64,512 of 65,536)
     if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp == 0 && lane == 0) {
-        // ------------------------------------------------------------- TMA loader
-        mbar_expect_tx(q_full, Q_BYTES);
-        for (int kb = 0; kb < KB; ++kb) tma_load_2d(q_s + kb * FT_PIECE_BYTES, &map_q, q_full, hq * HD + kb * 64, s0 + q0);
-        bool ok = true;
-        auto load_k = [&](int j) {
-            const int s = j % STAGES;
-            ok = mbar_wait(k_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
-            if (!ok) return;
-            mbar_expect_tx(k_full + 8 * s, KV_BYTES);
-            for (int kb = 0; kb < KB; ++kb)
-                tma_load_2d(k_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_k, k_full + 8 * s, hk * HD + kb * 64,
-                            s0 + (kt_begin + j) * FT_TILE);
-            issued_k = j + 1;
-        };
-        auto load_v = [&](int j) {
-            const int s = j % STAGES;
-            ok = mbar_wait(v_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
-            if (!ok) return;
-            mbar_expect_tx(v_full + 8 * s, KV_BYTES);
-            for (int kb = 0; kb < KB; ++kb)
-                tma_load_2d(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_v, v_full + 8 * s, hk * HD + kb * 64,
-                            s0 + (kt_begin + j) * FT_TILE);
-            issued_v = j + 1;
-        };
-        for (int j = 0; j < n && ok; ++j) {
-            load_k(j);
-            if (ok && j >= 1) load_v(j - 1);
-        }
-        if (ok) load_v(n - 1);
-        pdl_trigger();                            // every tile is requested: the next kernel may start up
-    } else if (warp == 1 && lane == 0) {
-        // ------------------------------------------------------------- MMA issuer
-        // float accumulator, bf16 operands; S: both K-major, N = 128; O': B (V) MN-major, N = HD
-        constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FT_TILE >> 3) << 17) |
-                                     ((uint32_t)(FT_TILE >> 4) << 24);
-        constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
-                                     ((uint32_t)(FT_TILE >> 4) << 24);
-        bool ok = mbar_wait(q_full, 0, &abort_flag, err, FT_ERR_MMA);
-        auto issue_s = [&](int j) {
-            const int s = j % STAGES;
-            // The S buffer is free: tile j - NS, which used it, had its P announced (p_full) before
-            // P V of that tile was issued, and this call comes after that.
-            ok = mbar_wait(k_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
-            if (!ok) return;
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < HD / 16; ++k) {
-                const uint64_t a = umma_desc(q_s + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
-                const uint64_t bd = umma_desc(k_s + s * KV_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
-                umma_bf16(tmem_base + (uint32_t)((j % NS) * FT_TILE), a, bd, idesc_s, k != 0);
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == 0 && lane == 0) {
+            // ------------------------------------------------------------- TMA loader
+            mbar_expect_tx(q_full, Q_BYTES);
+            for (int kb = 0; kb < KB; ++kb) tma_load_2d(q_s + kb * FT_PIECE_BYTES, &map_q, q_full, hq * HD + kb * 64, s0 + q0);
+            bool ok = true;
+            auto load_k = [&](int j) {
+                const int s = j % STAGES;
+                ok = mbar_wait(k_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
+                if (!ok) return;
+                mbar_expect_tx(k_full + 8 * s, KV_BYTES);
+                for (int kb = 0; kb < KB; ++kb)
+                    tma_load_2d(k_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_k, k_full + 8 * s, hk * HD + kb * 64,
+                                s0 + (kt_begin + j) * FT_TILE);
+                issued_k = j + 1;
+            };
+            auto load_v = [&](int j) {
+                const int s = j % STAGES;
+                ok = mbar_wait(v_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
+                if (!ok) return;
+                mbar_expect_tx(v_full + 8 * s, KV_BYTES);
+                for (int kb = 0; kb < KB; ++kb)
+                    tma_load_2d(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_v, v_full + 8 * s, hk * HD + kb * 64,
+                                s0 + (kt_begin + j) * FT_TILE);
+                issued_v = j + 1;
+            };
+            for (int j = 0; j < n && ok; ++j) {
+                load_k(j);
+                if (ok && j >= 1) load_v(j - 1);
             }
-            umma_commit(k_empty + 8 * s);
-            umma_commit(s_full + 8 * (j % NS));
-        };
-        auto issue_o = [&](int j) {
-            const int g = j & 1, t = j >> 1, s = j % STAGES;
-            // V first: it has long been loaded, and P is what this thread really waits for.
-            ok = mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
-            if (ok) ok = mbar_wait(p_full + 8 * g, t & 1, &abort_flag, err, FT_ERR_MMA);
-            // The group's O' buffer is free as well: the group adds the O' of its previous tile before it
-            // touches the scores of this one, so before the p_full that was just awaited.
-            if (!ok) return;
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < FT_TILE / 16; ++k) {                // 16 keys per instruction
-                const uint64_t a = umma_desc(p_s + g * P_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
-                const uint64_t bd = umma_desc_mn(v_s + s * KV_BYTES + k * 2048, FT_PIECE_BYTES);
-                umma_bf16(tmem_base + (uint32_t)(NS * FT_TILE + g * HD), a, bd, idesc_o, k != 0);
+            if (ok) load_v(n - 1);
+            pdl_trigger();                            // every tile is requested: the next kernel may start up
+        } else if (warp == 1 && lane == 0) {
+            // ------------------------------------------------------------- MMA issuer
+            // float accumulator, bf16 operands; S: both K-major, N = 128; O': B (V) MN-major, N = HD
+            constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FT_TILE >> 3) << 17) |
+                                         ((uint32_t)(FT_TILE >> 4) << 24);
+            constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
+                                         ((uint32_t)(FT_TILE >> 4) << 24);
+            bool ok = mbar_wait(q_full, 0, &abort_flag, err, FT_ERR_MMA);
+            auto issue_s = [&](int j) {
+                const int s = j % STAGES;
+                // The S buffer is free: tile j - NS, which used it, had its P announced (p_full) before
+                // P V of that tile was issued, and this call comes after that.
+                ok = mbar_wait(k_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+                if (!ok) return;
+                tc_fence_after();
+    #pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint64_t a = umma_desc(q_s + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
+                    const uint64_t bd = umma_desc(k_s + s * KV_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
+                    umma_bf16(tmem_base + (uint32_t)((j % NS) * FT_TILE), a, bd, idesc_s, k != 0);
+                }
+                umma_commit(k_empty + 8 * s);
+                umma_commit(s_full + 8 * (j % NS));
+            };
+            auto issue_o = [&](int j) {
+                const int g = j & 1, t = j >> 1, s = j % STAGES;
+                // V first: it has long been loaded, and P is what this thread really waits for.
+                ok = mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+                if (ok) ok = mbar_wait(p_full + 8 * g, t & 1, &abort_flag, err, FT_ERR_MMA);
+                // The group's O' buffer is free as well: the group adds the O' of its previous tile before it
+                // touches the scores of this one, so before the p_full that was just awaited.
+                if (!ok) return;
+                tc_fence_after();
+    #pragma unroll
+                for (int k = 0; k < FT_TILE / 16; ++k) {                // 16 keys per instruction
+                    const uint64_t a = umma_desc(p_s + g * P_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
+                    const uint64_t bd = umma_desc_mn(v_s + s * KV_BYTES + k * 2048, FT_PIECE_BYTES);
+                    umma_bf16(tmem_base + (uint32_t)(NS * FT_TILE + g * HD), a, bd, idesc_o, k != 0);
+                }
+                umma_commit(v_empty + 8 * s);
+                umma_commit(o_full + 8 * g);
+            };
+            for (int j = 0; j < NS && j < n && ok; ++j) issue_s(j);
+            for (int j = 0; j < n && ok; ++j) {
+                issue_o(j);
+                if (ok && j + NS < n) issue_s(j + NS);
             }
-            umma_commit(v_empty + 8 * s);
-            umma_commit(o_full + 8 * g);
-        };
-        for (int j = 0; j < NS && j < n && ok; ++j) issue_s(j);
-        for (int j = 0; j < n && ok; ++j) {
-            issue_o(j);
-            if (ok && j + NS < n) issue_s(j + NS);
         }
-    }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
         // ------------------------------------------------------------- softmax groups
