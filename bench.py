@@ -150,8 +150,10 @@ def decode_run(model, batch, prompt_len, steps, warmup, vocab):
 
 
 def e2e_run(model, batch, prompt_len, steps, warmup, vocab):
-    """The same decode through Model.generate: per step the host sends that step's tokens from
-    pinned memory and reads the sampled tokens back."""
+    """The same decode through Model.generate: per step the host sends that step's inputs from
+    pinned memory (positions, slots, page-table updates, sampler keys; the token ids themselves are
+    taken on the device from the step before, which chose them) and reads the chosen tokens back.
+    The loop keeps the device one step ahead of its own bookkeeping."""
     import torch
 
     prompts, state = [], 0x9E3779B97F4A7C15

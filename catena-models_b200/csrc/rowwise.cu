@@ -4,14 +4,17 @@
 
 // ------------------------------------------------------------------ embedding gather
 // out[t,:] = table[tokens[t],:].  A token id outside [0,V) writes zeros and raises *err.
+// With `sampled` given, a negative entry -(1 + i) stands for sampled[i]: the token that the step
+// before this one chose on the device for its i-th sequence, which the host has not seen yet.
 template <typename T>
 __global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ table,
-                                    const int* __restrict__ tokens, int H, int V,
+                                    const int* __restrict__ tokens, const int* __restrict__ sampled, int H, int V,
                                     int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
-    const int tok = tokens[t];
+    int tok = tokens[t];
+    if (tok < 0 && sampled) tok = sampled[-tok - 1];
     const bool ok = tok >= 0 && tok < V;
     if (!ok && threadIdx.x == 0 && err) atomicExch(err, 1);
     const T* src = table + (long long)(ok ? tok : 0) * H;
@@ -19,14 +22,14 @@ __global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ t
     for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = ok ? src[c] : from_f32<T>(0.f);
 }
 
-extern "C" int cm_embed_gather(int dt, void* out, const void* table, const int* tokens, int T,
+extern "C" int cm_embed_gather(int dt, void* out, const void* table, const int* tokens, const int* sampled, int T,
                                int H, int V, int* err, cudaStream_t st) {
     if (T <= 0) return CM_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (dt == DT_F32)
-        cm_launch(embed_gather_kernel<float>, T, threads, 0, st, (float*)out, (const float*)table, tokens, H, V, err);
+        cm_launch(embed_gather_kernel<float>, T, threads, 0, st, (float*)out, (const float*)table, tokens, sampled, H, V, err);
     else if (dt == DT_BF16)
-        cm_launch(embed_gather_kernel<bf16>, T, threads, 0, st, (bf16*)out, (const bf16*)table, tokens, H, V, err);
+        cm_launch(embed_gather_kernel<bf16>, T, threads, 0, st, (bf16*)out, (const bf16*)table, tokens, sampled, H, V, err);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();

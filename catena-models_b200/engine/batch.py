@@ -60,6 +60,7 @@ class StepBatch:
         self.n_want, self.n_updates = n_want, n_updates
         self.chunk_bucket = None                               # set by a captured decode graph
         self.wants_every_row = False                           # want_rows is 0, 1, ..., T-1 (set by the decode path)
+        self.prev_sampled = None                               # device int32: tokens the step before chose (decode path)
         self.shared = {}                                       # what a layer leaves for later layers of this step
 
     def decode_chunks(self, kv_spec):

@@ -63,6 +63,18 @@ class _Staging:
         self.events[i] = ev
 
 
+class PendingTokens:
+    """The tokens a step chose on the device, on their way to the host (`Engine.step(...,
+    wait=False)`).  `tokens()` waits for the copy and returns them as Python ints."""
+
+    def __init__(self, host, n, event):
+        self._host, self._n, self._event = host, n, event
+
+    def tokens(self):
+        self._event.synchronize()
+        return self._host[:self._n].tolist()
+
+
 class _DecodeGraph:
     def __init__(self, layout, device_buf, graph, logits, batch):
         self.layout, self.device_buf, self.graph, self.logits, self.batch = layout, device_buf, graph, logits, batch
@@ -81,6 +93,11 @@ class Engine:
         self._staging = _Staging()
         self._graphs = {}
         self._sampled_host = None
+        # the tokens the last sampling step chose, by position in that step's batch: the next step may
+        # take its input tokens from here without the host having seen them (`token_from`)
+        self._sampled = torch.zeros(self.cache.book.max_seqs, dtype=torch.int32, device=self.rt.device)
+        self._readback = [None, None]                          # two pinned buffers used in turn
+        self._readback_i = 0
         self.steps_run = 0
         self.kernel_launches = 0
 
@@ -147,7 +164,13 @@ class Engine:
             raise
         return updates
 
-    def step(self, slots, tokens, want=None, sampling=None):
+    @property
+    def overlapped_decode(self):
+        """True when decode steps can take their tokens from the step before on the device and hand
+        their own back without waiting (`token_from`, `wait=False`)."""
+        return self.fused_sampling and self.use_graphs
+
+    def step(self, slots, tokens, want=None, sampling=None, token_from=None, wait=True):
         """Run one step.  `tokens[i]` are the next tokens of the sequence in `slots[i]`;
         `want[i]` the places among them whose logits are returned (default: the last).
         Returns float32 logits [sum(len(want[i])), vocab] on the device, in the order of
@@ -156,16 +179,33 @@ class Engine:
         With `sampling` (a `Sampling` record; `want` must be left at its default) the next token
         of every sequence is chosen on the device in the same submission and the call returns
         `(logits, tokens)` with `tokens` a list of Python ints: one host-to-device copy of the
-        step's inputs, one device-to-host copy of its result."""
+        step's inputs, one device-to-host copy of its result.
+
+        A decode step with `sampling` may run ahead of the host (`overlapped_decode`):
+        `token_from[i] = j` takes sequence i's input token from what the sampling step before this
+        one chose for the j-th sequence of its batch (`tokens[i]` is then ignored; None keeps
+        `tokens[i]`), and `wait=False` returns `(logits, PendingTokens)` at once, the copy of the
+        chosen tokens to the host being under way."""
         book = self.cache.book
         if sampling is not None and want is not None:
             raise StepError("sampling takes the last place of every sequence; leave `want` out")
         decode = self.use_graphs and want is None and self._is_plain_decode(slots, tokens)
+        if (token_from is not None or not wait) and not (decode and sampling is not None):
+            raise StepError("token_from and wait=False belong to captured decode steps with sampling")
         if decode:
             positions = [book.length[s] for s in slots]
             flat = [t[0] for t in tokens]
             V = self.model.vocab_size
-            if min(flat) < 0 or max(flat) >= V:
+            if token_from is not None:
+                if len(token_from) != len(slots):
+                    raise StepError("one token_from entry per slot")
+                known = [t for t, j in zip(flat, token_from) if j is None]
+                if any(j is not None and not 0 <= j < self._sampled.numel() for j in token_from):
+                    raise StepError("token_from points outside the last step's batch")
+                flat = [t if j is None else -(1 + j) for t, j in zip(flat, token_from)]
+            else:
+                known = flat
+            if known and (min(known) < 0 or max(known) >= V):
                 raise StepError(f"token id outside the vocabulary of {V}")
             # a decode step needs a new page only when a sequence stands on a page border
             updates = self._reserve(slots, positions, tokens) if any(p % 64 == 0 for p in positions) else []
@@ -202,6 +242,8 @@ class Engine:
         self.steps_run += 1
         if sampling is None:
             return logits
+        if not wait:
+            return logits, self._to_host_later(sampled)
         return logits, self._to_host(sampled)
 
     def _is_plain_decode(self, slots, tokens):
@@ -213,6 +255,19 @@ class Engine:
             if length.get(s, 0) == 0 or len(t) != 1:
                 return False
         return True
+
+    def _to_host_later(self, sampled):
+        """Starts the copy of the chosen tokens to pinned memory and returns a handle to await it."""
+        n = sampled.shape[0]
+        self._readback_i ^= 1
+        host = self._readback[self._readback_i]
+        if host is None or host.numel() < n:
+            host = torch.empty(max(64, 2 * n), dtype=torch.int32, pin_memory=True)
+            self._readback[self._readback_i] = host
+        host[:n].copy_(sampled, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens(host, n, event)
 
     def _to_host(self, sampled):
         """Sampled tokens as Python ints (pinned buffer, one copy, one synchronisation)."""
@@ -240,7 +295,7 @@ class Engine:
             layout = BatchLayout(B, B, B, B * max(1, self.n_kv_groups))
             device_buf = torch.zeros(layout.size, dtype=torch.int32, device=self.rt.device)
             entry = _DecodeGraph(layout, device_buf, None, None, None)
-            entry.sampled = torch.zeros(B, dtype=torch.int32, device=self.rt.device)
+            entry.sampled = self._sampled[:B]                  # every graph leaves its tokens in the same place
             self._graphs[key] = entry
         layout = entry.layout
         host, idx = self._staging.take(layout.size)
@@ -260,6 +315,7 @@ class Engine:
             batch = StepBatch(layout, entry.device_buf, False, [1] * B, positions, B, len(updates))
             batch.chunk_bucket = bucket
             batch.wants_every_row = True                       # fill_host_decode wants every row, in order
+            batch.prev_sampled = self._sampled                 # negative token entries point into it
 
             def run():
                 out = self.model.forward(batch, self.cache)

@@ -15,6 +15,8 @@ from __future__ import annotations
 
 import dataclasses
 
+from ..cache.allocators import CacheFull
+
 PAGE = 64
 
 
@@ -72,29 +74,77 @@ def run_batch(engine, sampler, requests, ids, max_new_tokens, stop_token_ids, ig
         logits = engine.step(step_slots, step_tokens)
         return sampler.sample(logits, [ids[i] for i in live], [step] * len(live))
 
+    def settle(members, tokens, step, dropped=()):
+        """Book the tokens of one step; returns the members that go on.  `dropped` members had ended
+        before this step was known to be unnecessary for them: their token is thrown away."""
+        still = []
+        for i, tok in zip(members, tokens):
+            if i in dropped:
+                continue
+            r = requests[i]
+            r.tokens.append(int(tok))
+            r.finish_reason = finish_reason(int(tok), len(r.tokens), max_new_tokens, stop_token_ids, ignore_eos)
+            if r.finish_reason is None:
+                still.append(i)
+            else:
+                engine.release([slots[i]])
+                slots[i] = None
+        if on_step:
+            on_step(step, len(members) - len(dropped))
+        return still
+
     try:
         step = 0
         tokens = run_step(slots, [r.prompt for r in requests], step)
+        if fused and getattr(engine, "overlapped_decode", False):
+            _decode_ahead(engine, sampler, requests, ids, slots, settle(live, tokens, step), max_new_tokens, settle)
+            return
         while True:
-            still = []
-            for i, tok in zip(live, tokens):
-                r = requests[i]
-                r.tokens.append(int(tok))
-                r.finish_reason = finish_reason(int(tok), len(r.tokens), max_new_tokens, stop_token_ids, ignore_eos)
-                if r.finish_reason is None:
-                    still.append(i)
-                else:
-                    engine.release([slots[i]])
-                    slots[i] = None
-            if on_step:
-                on_step(step, len(live))
-            live = still
+            live = settle(live, tokens, step)
             if not live:
                 break
             step += 1
             tokens = run_step([slots[i] for i in live], [[requests[i].tokens[-1]] for i in live], step)
     finally:
         engine.release([s for s in slots if s is not None])
+
+
+def _decode_ahead(engine, sampler, requests, ids, slots, live, max_new_tokens, settle):
+    """Decode with the device one step ahead of the host.  Step k+1 is submitted before the tokens
+    of step k have reached the host: it takes them from the device (`token_from`), for every member
+    of step k that cannot end by its budget.  A member that step k's token then ends (a stop token)
+    has one token too many computed; it is dropped when step k+1 is booked.  The host's work per
+    step (bookkeeping, the next submission) so runs while the device computes."""
+    if not live:
+        return
+    step = 1
+    members = list(live)
+    pending = engine.step([slots[i] for i in members], [[requests[i].tokens[-1]] for i in members],
+                          sampling=sampler.request([ids[i] for i in members], step), wait=False)[1]
+    dropped = set()
+    while True:
+        # who can still be running after this step's token: everyone short of the budget by more than one
+        ahead = [i for i in members if i not in dropped and len(requests[i].tokens) + 1 < max_new_tokens]
+        nxt = None
+        if ahead:
+            where = {i: k for k, i in enumerate(members)}
+            try:
+                nxt = engine.step([slots[i] for i in ahead], [[0]] * len(ahead),
+                                  sampling=sampler.request([ids[i] for i in ahead], step + 1),
+                                  token_from=[where[i] for i in ahead], wait=False)[1]
+            except CacheFull:
+                nxt = None                                     # no room to run ahead: wait for this step first
+        still = settle(members, pending.tokens(), step, dropped)
+        step += 1
+        if nxt is None:
+            if not still:
+                return
+            members, dropped = still, set()
+            pending = engine.step([slots[i] for i in members], [[requests[i].tokens[-1]] for i in members],
+                                  sampling=sampler.request([ids[i] for i in members], step), wait=False)[1]
+            continue
+        # the step that ran ahead holds `ahead`; those of them that have just ended are dropped from it
+        members, dropped, pending = ahead, {i for i in ahead if i not in still}, nxt
 
 
 def generate(engine, sampler, prompts, max_new_tokens, stop_token_ids=(), ignore_eos=False, max_batch=64,

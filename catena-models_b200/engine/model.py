@@ -81,7 +81,7 @@ class DecoderModel:
         if batch.layout.U:
             kernels.scatter_i32(cache.ptab_all, batch.upd_index, batch.upd_value, batch.upd_count, batch.layout.U)
         h = torch.empty((batch.T, self.hidden_size), dtype=rt.dtype, device=rt.device)
-        kernels.embed_gather(h, self.embedding, batch.tokens, self.token_error)
+        kernels.embed_gather(h, self.embedding, batch.tokens, self.token_error, sampled=batch.prev_sampled)
         plan = self.plan
         n = self.blocks[plan[0].block].input_norm.apply(rt, h)
         # when every row is wanted in order (a decode step), the last block's fused residual kernel

@@ -20,7 +20,7 @@ ATTN_DECODE_CHUNK = 256
 _vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 
 _SIGNATURES = {
-    "cm_embed_gather": [_i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],
+    "cm_embed_gather": [_i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],
     "cm_rmsnorm": [_i, _vp, _vp, _vp, _i, _i, _f, _ll, _ll, _vp],
     "cm_add_norm": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
     "cm_swiglu": [_i, _vp, _vp, _i, _i, _vp],
@@ -112,10 +112,12 @@ def _need_cuda(*tensors):
 
 
 # ---------------------------------------------------------------------------- row-wise
-def embed_gather(out, table, tokens, err=None):
+def embed_gather(out, table, tokens, err=None, sampled=None):
+    """out[t] = table[tokens[t]]; with `sampled` (int32 device tensor) an entry -(1 + i) of tokens
+    stands for sampled[i]."""
     _need_cuda(out, table, tokens)
     T, H = out.shape
-    _check(lib().cm_embed_gather(dtype_code(out.dtype), _ptr(out), _ptr(table), _ptr(tokens), T, H,
+    _check(lib().cm_embed_gather(dtype_code(out.dtype), _ptr(out), _ptr(table), _ptr(tokens), _ptr(sampled), T, H,
                                  table.shape[0], _ptr(err), _stream()), "embed_gather")
 
 

@@ -104,3 +104,74 @@ def test_slots_come_back_when_a_step_fails():
     with pytest.raises(RuntimeError):
         gen.generate(eng, Greedy(), [[1], [2]], 5, max_tokens=10**6)
     assert not eng.live and eng.free == [0, 1, 2, 3]
+
+
+class AheadEngine(FakeEngine):
+    """The same model behind the interface of an engine that samples on the device and lets decode
+    steps run one ahead of the host: `step(..., sampling, token_from, wait)`."""
+
+    fused_sampling = True
+    overlapped_decode = True
+
+    def __init__(self, vocab=50, slots=4, refuse_ahead_at=None):
+        super().__init__(vocab, slots)
+        self.last_sampled = []
+        self.refuse_ahead_at = refuse_ahead_at           # decode step number whose run-ahead submission finds no room
+        self.ahead_submissions = 0
+
+    class _Pending:
+        def __init__(self, tokens):
+            self._tokens = tokens
+
+        def tokens(self):
+            return list(self._tokens)
+
+    def step(self, slots, tokens, want=None, sampling=None, token_from=None, wait=True):
+        assert sampling is not None and list(sampling.sequence_ids) is not None
+        if token_from is not None:
+            self.ahead_submissions += 1
+            if self.refuse_ahead_at is not None and self.ahead_submissions == self.refuse_ahead_at:
+                raise gen.CacheFull("no room to run ahead")
+            tokens = [[self.last_sampled[j]] if j is not None else t for t, j in zip(tokens, token_from)]
+        for s in slots:
+            assert s in self.live                         # a released slot is never stepped again
+        logits = super().step(slots, tokens)
+        chosen = logits.argmax(dim=-1).tolist()
+        self.last_sampled = chosen
+        self.requests_seen = (list(sampling.sequence_ids), list(sampling.steps))
+        return (logits, chosen) if wait else (logits, self._Pending(chosen))
+
+
+class Requester:
+    """The sampler's side of fused sampling: it only says which draw each sequence is at."""
+
+    def request(self, ids, step):
+        class R:
+            sequence_ids, steps = list(ids), [step] * len(ids)
+        return R
+
+
+@pytest.mark.parametrize("refuse", [None, 2])
+def test_decode_ahead_gives_the_same_tokens_and_drops_what_ran_too_far(refuse):
+    eng = AheadEngine(refuse_ahead_at=refuse)
+    prompts = [[1, 2, 3], [8], [20, 21], [30]]
+    out = gen.generate(eng, Requester(), prompts, max_new_tokens=6, stop_token_ids=[10, 33], max_batch=4,
+                       max_tokens=10**6)
+    assert out[0].tokens == [4, 5, 6, 7, 8, 9] and out[0].finish_reason == "length"
+    assert out[1].tokens == [9, 10] and out[1].finish_reason == "stop"       # ended by the first decode step
+    assert out[2].tokens == [22, 23, 24, 25, 26, 27] and out[2].finish_reason == "length"
+    assert out[3].tokens == [31, 32, 33] and out[3].finish_reason == "stop"
+    assert not eng.live and eng.free == [0, 1, 2, 3]
+    sizes = [len(s) for k, s, _ in eng.steps if k == "decode"]
+    if refuse is None:
+        # the step after a stop token still carries the sequence that stopped: one row too many, once each
+        assert sizes == [4, 4, 3, 2, 2]
+    assert len(sizes) == 5                                                   # never a step more than needed
+
+
+def test_decode_ahead_when_everyone_stops_at_once():
+    eng = AheadEngine()
+    out = gen.generate(eng, Requester(), [[5], [5]], max_new_tokens=9, stop_token_ids=[7], max_batch=4, max_tokens=10**6)
+    assert [g.tokens for g in out] == [[6, 7], [6, 7]] and not eng.live
+    # prompt step, the decode step that produced the stop tokens, and the one that had run ahead of them
+    assert [k for k, _, _ in eng.steps] == ["prefill", "decode", "decode"]
