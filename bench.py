@@ -170,7 +170,10 @@ def e2e_run(model, batch, prompt_len, steps, warmup, vocab):
             torch.cuda.synchronize()
             marks["t1"] = time.perf_counter()
 
-    model.generate(prompts, max_new_tokens=warmup + steps + 1, temperature=0.0, ignore_eos=True,
+    # Two tokens more than the marks need: with the device a step ahead, the step after each marked
+    # one is in flight when its mark synchronises, so both marks see the same amount of extra work
+    # and the interval holds exactly `steps` steps.
+    model.generate(prompts, max_new_tokens=warmup + steps + 2, temperature=0.0, ignore_eos=True,
                    stop_token_ids=(), max_batch=batch, on_step=on_step)
     sec = marks["t1"] - marks["t0"]
     eng = model.engine
