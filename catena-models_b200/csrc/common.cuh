@@ -48,10 +48,10 @@ void cm_set_error(const char* fmt, ...);
 //    (with or without reading weights ahead of its wait, with or without a cluster), while the
 //    TMA-fed products gain from setting up their barriers and tensor memory early (batch 64: 7%
 //    faster).  A chain of spinning kernels of the same shapes gains 40% from starting early, so
-//    the loss is not the launch mechanism: blocks that start early settle wherever the kernel
-//    before frees room, up to four on one SM and one on the next, and a kernel bound by memory
-//    bandwidth then waits for its fullest SM.  The TMA-fed kernels fit one or two blocks to an SM
-//    and spread evenly whenever they start.
+//    the loss is not the launch mechanism.  The likely reason: blocks that start early settle
+//    wherever the kernel before frees room, up to four on one SM and one on the next, and a kernel
+//    bound by memory bandwidth then waits for its fullest SM; the TMA-fed kernels fit one or two
+//    blocks to an SM and spread evenly whenever they start.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
