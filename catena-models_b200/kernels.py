@@ -252,8 +252,8 @@ def attn_prefill_tc(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, wind
 
 
 def set_decode_attention_target_blocks(blocks):
-    """Blocks the tensor-core decode attention aims at (0: eight per SM, the default).  With fewer,
-    each block walks several 256-entry chunks of a sequence."""
+    """Blocks the tensor-core decode attention aims at (0: chosen from the amount of work, the
+    default).  With fewer, each block walks several 256-entry chunks of a sequence."""
     lib().cm_attn_decode_set_target_blocks(int(blocks))
 
 
