@@ -8,6 +8,7 @@ import plain_lfm3
 import tiny
 
 pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
 
 # Error measure: largest |engine - plain| over all logits of a comparison, relative to the
 # largest |logit|.
@@ -234,3 +235,61 @@ def test_step_errors(folders):
     eng.release([slot])
     assert not eng.cache.book.live
     assert eng.cache.book.page_alloc[0].free_count == eng.cache.book.group_pages[0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_planted_far_key_decides_the_logits(dtype):
+    """Random weights can hide a key that attention never sees: among hundreds it moves the logits
+    by little.  Here the weights are made so that the last token's queries point at the key of the
+    very first token (600 positions back, on the first page of the cache) and at nothing else, so
+    that token's value decides the output: in the prompt step and in decode steps over the cache."""
+    from catena_models_b200.api import Model
+    from catena_models_b200.config.registry import config_from_dict
+    from catena_models_b200.engine.model import DecoderModel
+    from catena_models_b200.weights.random_init import random_tensors
+
+    cfg = dict(architecture="lfm3", vocab_size=97, hidden_size=64, intermediate_size=96, num_hidden_layers=1,
+               layer_types=["full_attention"], num_attention_heads=2, num_key_value_heads=1, head_dim=32,
+               conv_L_cache=3, sliding_window=64, rope_theta=10000.0, norm_eps=1e-6, tie_word_embeddings=True,
+               max_position_embeddings=2048, post_norm=True, attn_output_gate=False)
+    arch, typed = config_from_dict(cfg)
+    t = random_tensors(arch.define(typed).tensor_specs(), 3, std=0.5)
+    A, B = 7, 9                                                  # the far token and the asking token
+    pre = "model.layers.0."
+    emb = t["model.embed_tokens.weight"].float()
+    unit = lambda v: v / v.pow(2).mean().add(1e-6).sqrt()        # the layer's input norm (weight 1)
+    n_a, n_b = unit(emb[A]), unit(emb[B])
+    k_a = t[pre + "attn_k.weight"].float() @ n_a                 # the key of token A, before head norm
+    wq = 0.002 * torch.randn(64, 64, generator=torch.Generator().manual_seed(1))
+    for h in range(2):                                           # both query heads: q(B) = k(A) + a little noise
+        wq[32 * h:32 * h + 32] += torch.outer(k_a, n_b) / n_b.dot(n_b)
+    t[pre + "attn_q.weight"] = wq.to(torch.bfloat16)
+    t[pre + "attn_q_norm.weight"] = torch.full((32,), 4.0)       # head norms scale the scores: a match scores about 90
+    t[pre + "attn_k_norm.weight"] = torch.full((32,), 4.0)
+    t["rope_freqs.weight"] = torch.full((16,), 1e9)              # factors so large that no position turns anything
+    g = torch.Generator().manual_seed(2)
+    filler = [int(x) for x in torch.randint(10, 97, (600,), generator=g)]
+    seq = [A] + filler + [B, B, B, B]
+    other = [11] + filler + [B, B, B, B]                         # the same without the planted token
+    tensors64 = {k: v.double() if v.is_floating_point() else v for k, v in t.items()}
+    exact = plain_lfm3.forward(cfg, tensors64, seq)
+    without = plain_lfm3.forward(cfg, tensors64, other)
+    rng = float(exact[601:].abs().max())
+    assert float((exact[601:] - without[601:]).abs().max()) > 0.2 * rng      # the planted key matters a lot
+
+    model = Model(DecoderModel.from_tensors(cfg, t, torch.float32 if dtype == "float32" else torch.bfloat16, DEV), max_tokens=1024)
+    eng = model.engine
+    (slot,) = eng.admit(1)
+    got = [eng.step([slot], [seq[:602]], [[600, 601]]).clone()]            # the last filler and the first B
+    for tok in seq[602:]:
+        got.append(eng.step([slot], [[tok]]).clone())
+    eng.release([slot])
+    got = torch.cat(got)
+    ref = exact[600:]
+    if dtype == "float32":
+        assert rel_err(got, ref) < 5e-5
+    else:
+        same = plain_lfm3.forward(cfg, tensors64, seq, bf16=True)[600:]
+        assert rel_err(got, ref) < BF16_FACTOR * rel_err(same, ref) + 1e-3
+    # and far from what the sequence without the planted token gives
+    assert rel_err(got[1:], without[601:]) > 0.1
