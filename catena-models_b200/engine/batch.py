@@ -16,7 +16,6 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from ..cache.spec import PAGE_TOKENS
 from ..kernels import ATTN_DECODE_CHUNK
 
 

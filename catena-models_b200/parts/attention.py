@@ -14,7 +14,6 @@ constructor parameters; the part knows neither its layer index nor its model.
 """
 from __future__ import annotations
 
-import math
 
 import torch
 

@@ -5,8 +5,6 @@ are packed into one matrix at bind time so that one product reads x once
 """
 from __future__ import annotations
 
-import torch
-
 from .base import FeedForward, register_part
 from .linear import Linear
 
