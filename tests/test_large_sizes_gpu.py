@@ -122,3 +122,47 @@ def test_long_prompts_on_the_tcgen05_attention_kernel(big):
         g, ref = torch.cat(got[i]), exact[i][pos[i]]
         assert rel(g, ref) < 2.0 * rel(noise[i][pos[i]], ref)
         assert torch.equal(g.argmax(-1).cpu(), ref.argmax(-1)) or rel(g, ref) < 0.02
+
+
+def test_heads_of_128_with_one_kv_head_on_long_prompts(tmp_path):
+    """32 query heads of size 128 over a single kv head (two passes of 16 heads in the decode kernel),
+    prompts beyond 1,024 tokens (tcgen05 attention with two 64-column pieces per head), a sliding layer
+    whose window ends inside a page, float32 and bfloat16."""
+    from catena_models_b200.api import Model
+    from catena_models_b200.weights.random_init import write_random_model
+
+    cfg = dict(architecture="lfm3", vocab_size=500, hidden_size=128, intermediate_size=320, num_hidden_layers=3,
+               layer_types=["full_attention", "conv", "sliding_attention"], num_attention_heads=32,
+               num_key_value_heads=1, head_dim=128, conv_L_cache=3, sliding_window=1000, rope_theta=500000.0,
+               rope_theta_sliding=10000.0, norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=4096)
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=5, std=0.08, norm_weights="random", rope_factors="uniform")
+    config, tensors = plain_lfm3.load_folder(folder, dtype=torch.float32)
+    lens, extra = [1100, 1290], 3
+    seqs = [tiny.random_prompt(n + extra, 500, seed=n) for n in lens]
+    exact = [plain_lfm3.forward(config, tensors, s) for s in seqs]
+    noise = [plain_lfm3.forward(config, tensors, s, bf16=True) for s in seqs]
+    for dtype in ("bfloat16", "float32"):
+        model = Model.load(folder, dtype=dtype, max_tokens=4096)
+        eng = model.engine
+        slots = eng.admit(2)
+        want = [[0, 999, 1000, 1023, 1024, n - 1] for n in lens]
+        out = eng.step(slots, [s[:n] for s, n in zip(seqs, lens)], want)
+        got, pos, off = [[], []], [list(w) for w in want], 0
+        for i, w in enumerate(want):
+            got[i].append(out[off:off + len(w)].clone())
+            off += len(w)
+        for t in range(extra):
+            out = eng.step(slots, [[s[n + t]] for s, n in zip(seqs, lens)])
+            for i in range(2):
+                got[i].append(out[i:i + 1].clone())
+                pos[i].append(lens[i] + t)
+        eng.release(slots)
+        model.decoder.rt.check_errors()
+        for i in range(2):
+            g, ref = torch.cat(got[i]), exact[i][pos[i]]
+            if dtype == "float32":
+                assert rel(g, ref) < 5e-5
+            else:
+                assert rel(g, ref) < 2.0 * rel(noise[i][pos[i]], ref)
+        del model, eng
+        torch.cuda.empty_cache()
