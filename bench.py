@@ -231,6 +231,8 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--prefill-tokens", type=int, default=2048,
+                    help="prompt length of `--only prefill` (the full run always measures 2,048)")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only (small captures under a profiler); prints that part's facts")
     args = ap.parse_args()
@@ -264,7 +266,7 @@ def main():
         print(json.dumps(decode_run(model, args.batch, args.prompt_len, args.steps, args.warmup, vocab)))
         return 0
     if args.only == "prefill":
-        print(json.dumps(prefill_run(model, 2048, vocab, cfg, pk["bf16_tflops"])))
+        print(json.dumps(prefill_run(model, args.prefill_tokens, vocab, cfg, pk["bf16_tflops"])))
         return 0
     clocks = ClockSampler()
     clocks.start()
