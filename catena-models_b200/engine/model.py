@@ -76,6 +76,10 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ forward
     def forward(self, batch, cache):
+        with kernels.pinned_stream():
+            return self._forward(batch, cache)
+
+    def _forward(self, batch, cache):
         rt = self.rt
         batch.shared.clear()
         if batch.layout.U:

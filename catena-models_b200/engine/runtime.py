@@ -23,6 +23,7 @@ class Runtime:
         kernels.lib()                       # build and load now: fail loudly before any model work
         self._scratch = {}
         self._retired = []
+        self._sm_count = None
         # raised by a kernel whose bounded pipeline wait ran out (0 otherwise); see check_errors
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
 
@@ -63,10 +64,20 @@ class Runtime:
         elif kind == "few_rows":
             kernels.gemm_tc_few_rows(y, x, w, err=self.error_flag)
         elif kind == "tiled":
-            kernels.gemm_tc(y, x, w, err=self.error_flag)
+            kernels.gemm_tc(y, x, w, err=self.error_flag, block_n=self._tile_width(x.shape[0], w.shape[0]))
         else:
             kernels.gemm_simt(y, x, w)
         return y
+
+    def _tile_width(self, rows, out_columns):
+        """128 x 256 tiles move the fewest bytes per product, but a product with few of them leaves
+        SMs idle (512 rows x 2,048 columns: 32 tiles for 148 SMs).  128 x 128 tiles are used when
+        all of them still run at once, one per SM; with more than that the wide tiles win again
+        (measured at 512 to 1,536 rows)."""
+        if self._sm_count is None:
+            self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        narrow_tiles = -(-rows // 128) * -(-out_columns // 128)
+        return 128 if narrow_tiles <= self._sm_count else 256
 
     SKINNY_ROWS = 64          # most rows the weight-streaming kernel takes
     SKINNY_BEST_ROWS = 16     # up to here it is the fastest kernel
@@ -104,7 +115,9 @@ class Runtime:
             kernels.gemm_tc_few_rows(a, x, w_gate_up, swiglu=True, err=self.error_flag)
             return a
         if kind == "tiled":
-            kernels.gemm_tc(a, x, w_gate_up, swiglu=True, err=self.error_flag)
+            # a 256-wide tile of the packed matrix gives 128 output columns
+            kernels.gemm_tc(a, x, w_gate_up, swiglu=True, err=self.error_flag,
+                            block_n=self._tile_width(x.shape[0], 2 * F))
             return a
         gu = self.linear(x, w_gate_up)
         kernels.swiglu(a, gu)
