@@ -9,7 +9,8 @@ exceeded, token id outside the vocabulary, src/model.rs:697-710).
 
 Decode steps of a given batch size replay a captured CUDA graph: positions, slots and new
 page-table entries live in a fixed device buffer that is refreshed by one host-to-device
-copy before each replay.
+copy before each replay.  Short prompt steps whose shape repeats are recorded and replayed
+the same way.
 """
 from __future__ import annotations
 
@@ -23,6 +24,10 @@ from ..cache.allocators import CacheError, CacheFull
 from .. import kernels as _kernels
 from ..kernels import ATTN_DECODE_CHUNK
 from .batch import BatchLayout, StepBatch, fill_host, fill_host_decode, fill_sampling
+
+
+PROMPT_GRAPH_MAX_TOKENS = 1024     # longer prompt steps are bound by the device, not by their launches
+PROMPT_GRAPHS_KEPT = 4
 
 
 class StepError(ValueError):
@@ -92,6 +97,8 @@ class Engine:
         self.use_graphs = use_graphs and model.capturable
         self._staging = _Staging()
         self._graphs = {}
+        self._prompt_graphs = {}                               # shape of a prompt step -> its recorded graph
+        self._prompt_seen = {}
         self._sampled_host = None
         # the tokens the last sampling step chose, by position in that step's batch: the next step may
         # take its input tokens from here without the host having seen them (`token_from`)
@@ -222,21 +229,7 @@ class Engine:
                 if any(w != [0] for w in want):
                     logits = logits[[b for b, w in enumerate(want) for _ in w]]
             else:
-                n_want = sum(len(w) for w in want)
-                layout = BatchLayout(T, B, n_want, len(updates))
-                host, idx = self._staging.take(layout.size)
-                fill_host(layout, host.numpy(), slots, tokens, positions, want, updates)
-                if sampling is not None:
-                    fill_sampling(layout, host.numpy(), sampling)
-                dev = host[:layout.size].to(self.rt.device, non_blocking=True)
-                self._staging.mark(idx)
-                batch = StepBatch(layout, dev, prefill, [len(t) for t in tokens], positions, n_want, len(updates))
-                logits = self.model.forward(batch, self.cache)
-                sampled = None
-                if sampling is not None:
-                    sampled = torch.empty(B, dtype=torch.int32, device=self.rt.device)
-                    _kernels.sample(sampled, logits, batch.samp_temp[:B], batch.samp_seq[:B], batch.samp_step[:B],
-                                    batch.samp_seed)
+                logits, sampled = self._prompt_step(slots, tokens, positions, prefill, want, updates, sampling)
             for s, p, t in zip(slots, positions, tokens):
                 book.advance(s, p + len(t))
         self.steps_run += 1
@@ -277,6 +270,69 @@ class Engine:
         self._sampled_host[:n].copy_(sampled, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self._sampled_host[:n].tolist()
+
+    # ------------------------------------------------------------------ prompt steps
+    def _prompt_step(self, slots, tokens, positions, prefill, want, updates, sampling):
+        """A step with explicit tokens per sequence, launched kernel by kernel.  A prompt step whose
+        shape (the lengths, the number of wanted places) comes a second time is recorded into a graph
+        as it runs and replayed from then on: about 200 launches from Python cost more than a short
+        prompt's kernels take.  The few most recent shapes are kept."""
+        B, T = len(slots), sum(len(t) for t in tokens)
+        n_want = sum(len(w) for w in want)
+        key = entry = None
+        if prefill and self.use_graphs and self.model.prompt_capturable and T <= PROMPT_GRAPH_MAX_TOKENS:
+            key = (tuple(len(t) for t in tokens), n_want, len(updates), sampling is not None)
+            entry = self._prompt_graphs.get(key)
+        layout = entry.layout if entry else BatchLayout(T, B, n_want, len(updates))
+        host, idx = self._staging.take(layout.size)
+        fill_host(layout, host.numpy(), slots, tokens, positions, want, updates)
+        if sampling is not None:
+            fill_sampling(layout, host.numpy(), sampling)
+        if entry:
+            entry.device_buf.copy_(host[:layout.size], non_blocking=True)
+            self._staging.mark(idx)
+            self._prompt_graphs[key] = self._prompt_graphs.pop(key)        # most recently used last
+            entry.graph.replay()
+            _kernels.launches += entry.launches
+            # the graph writes its logits to the same place every time: the caller gets its own copy
+            return entry.logits.clone(), entry.sampled
+        record = False
+        if key is not None:
+            seen = self._prompt_seen.get(key, 0) + 1
+            if len(self._prompt_seen) > 4096:
+                self._prompt_seen.clear()
+            self._prompt_seen[key] = seen
+            record = seen >= 2
+        if record:
+            dev = torch.zeros(layout.size, dtype=torch.int32, device=self.rt.device)
+            dev.copy_(host[:layout.size], non_blocking=True)
+        else:
+            dev = host[:layout.size].to(self.rt.device, non_blocking=True)
+        self._staging.mark(idx)
+        batch = StepBatch(layout, dev, prefill, [len(t) for t in tokens], positions, n_want, len(updates))
+        sampled = torch.empty(B, dtype=torch.int32, device=self.rt.device) if sampling is not None else None
+
+        def run():
+            out = self.model.forward(batch, self.cache)
+            if sampled is not None:
+                _kernels.sample(sampled, out, batch.samp_temp[:B], batch.samp_seq[:B], batch.samp_step[:B],
+                                batch.samp_seed)
+            return out
+
+        logits = run()
+        if record:
+            # as for decode: this run was the step's result; the capture executes nothing
+            entry = _DecodeGraph(layout, dev, torch.cuda.CUDAGraph(), None, batch)
+            entry.sampled = sampled
+            before = _kernels.launches
+            with torch.cuda.graph(entry.graph):
+                entry.logits = run()
+            entry.launches = _kernels.launches - before
+            _kernels.launches = before
+            while len(self._prompt_graphs) >= PROMPT_GRAPHS_KEPT:
+                self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
+            self._prompt_graphs[key] = entry
+        return logits, sampled
 
     # ------------------------------------------------------------------ captured decode
     @staticmethod

@@ -25,6 +25,7 @@ class DecoderModel:
         self.head_weight = self.embedding if self.head is None else self.head.weight
         self.state_specs = definition.state_specs()
         self.capturable = all(part.all_capturable() for part in definition.parts())   # decode graphs allowed
+        self.prompt_capturable = all(part.all_prompt_capturable() for part in definition.parts())
         self.token_error = torch.zeros(1, dtype=torch.int32, device=rt.device)
 
     # ------------------------------------------------------------------ construction

@@ -25,6 +25,8 @@ from .linear import Linear
 
 
 class GQAttention(Mixer):
+    prompt_capturable = True
+
     def __init__(self, prefix, hidden, heads, kv_heads, head_dim, window, position, qk_norm_eps,
                  output_gate, names=None, shares_kv=False):
         names = names or {}

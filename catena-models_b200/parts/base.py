@@ -22,7 +22,8 @@ Interfaces (x, h, n are [tokens, width] activations of the step's packed batch):
         n = input_norm(h) was made by whoever ran before; n_next = next_norm(h) is made
         here (fused with the last residual sum) when next_norm is given, else None.
 
-A part sets `capturable = False` if its forward() reads device data on the host (see Part).
+A part sets `capturable = False` if its forward() reads device data on the host, and
+`prompt_capturable = True` if its prompt steps may be recorded as well (see Part).
 
 `rt` is the engine's Runtime (dtype, device, scratch), `batch` the StepBatch (token
 positions, sequence boundaries, slots, prefill or decode).
@@ -61,6 +62,10 @@ class Part:
     # steps of a model that holds such a part are run kernel by kernel instead of being replayed
     # from a captured graph.
     capturable = True
+    # True for a part whose prompt steps too launch the same kernels whenever the batch has the same
+    # shape (lengths, wanted places): the engine may then record a repeated prompt shape into a graph.
+    # A part says so itself; one that does not know is not recorded.
+    prompt_capturable = False
 
     def tensor_specs(self):
         return []
@@ -85,6 +90,9 @@ class Part:
 
     def all_capturable(self):
         return self.capturable and all(c.all_capturable() for c in self.children())
+
+    def all_prompt_capturable(self):
+        return self.capturable and self.prompt_capturable and all(c.all_prompt_capturable() for c in self.children())
 
     def weight_bytes(self):
         """Bytes of weights a step reads from this part (each tensor once)."""

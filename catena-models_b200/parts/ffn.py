@@ -10,6 +10,8 @@ from .linear import Linear
 
 
 class SwiGLU(FeedForward):
+    prompt_capturable = True
+
     def __init__(self, prefix, hidden, intermediate, names=None):
         names = names or {}
         n = lambda key, default: prefix + names.get(key, default)

@@ -14,6 +14,8 @@ from .base import Part
 
 
 class Linear(Part):
+    prompt_capturable = True
+
     def __init__(self, names, rows, in_features, role="matrix"):
         self.names = [names] if isinstance(names, str) else list(names)
         self.rows = [rows] if isinstance(rows, int) else list(rows)

@@ -14,6 +14,7 @@ from .base import Norm, register_part
 
 
 class RMSNorm(Norm):
+    prompt_capturable = True
     fused_kind = "rms"          # what the fused residual kernel can absorb
 
     def __init__(self, name, width, eps):

@@ -16,6 +16,8 @@ from .base import Position, register_part
 
 
 class Rotary(Position):
+    prompt_capturable = True
+
     def __init__(self, head_dim, theta, factors_name=None):
         self.head_dim, self.theta, self.factors_name = head_dim, float(theta), factors_name
         self._rate = None
@@ -39,6 +41,7 @@ class Rotary(Position):
 
 class NoPosition(Position):
     """No position encoding: the head vectors are left unrotated."""
+    prompt_capturable = True
 
 
 register_part("position", "rotary", Rotary)

@@ -16,6 +16,8 @@ from .linear import Linear
 
 
 class ShortConv(Mixer):
+    prompt_capturable = True
+
     def __init__(self, prefix, hidden, taps, names=None):
         names = names or {}
         n = lambda key, default: prefix + names.get(key, default)

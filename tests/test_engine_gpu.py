@@ -293,3 +293,33 @@ def test_a_planted_far_key_decides_the_logits(dtype):
         assert rel_err(got, ref) < BF16_FACTOR * rel_err(same, ref) + 1e-3
     # and far from what the sequence without the planted token gives
     assert rel_err(got[1:], without[601:]) > 0.1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_prompt_steps_of_a_repeated_shape(folders, plain, name, dtype):
+    """A prompt step whose shape repeats is recorded at its second run and replayed after that.
+    Six batches of the same lengths, each with other tokens and on other slots (one slot stays
+    held in between so that the slots and pages move), must each match the plain implementation,
+    and a result handed out earlier must not change when the graph runs again."""
+    eng = engine_for(folders, name, dtype)
+    vocab = plain[name][0]["vocab_size"]
+    lens = (9, 70, 31)
+    held, earlier = [], []
+    for rep in range(6):
+        prompts = [tiny.random_prompt(n, vocab, seed=1000 * rep + n) for n in lens]
+        slots = eng.admit(len(lens))
+        got = eng.step(slots, prompts)
+        earlier.append((got, got.clone()))
+        nxt = [tiny.random_prompt(1, vocab, seed=77 + rep + n) for n in lens]
+        got2 = eng.step(slots, nxt).clone()                    # a decode step on what the prompt step left
+        for b, (p, t) in enumerate(zip(prompts, nxt)):
+            exact, same = plain_logits(plain, name, p + t, dtype)
+            rows = torch.stack([got[b], got2[b]])
+            check(rows, exact[-2:], dtype, None if same is None else same[-2:])
+        eng.release(slots[1:])
+        held.append(slots[0])
+    assert len(eng._prompt_graphs) >= 1
+    for handed, copy in earlier:
+        assert torch.equal(handed, copy)
+    eng.release(held)
