@@ -38,30 +38,13 @@ __device__ __forceinline__ uint4 ld_stream16(const bf16* p) {
     return v;
 }
 
-template <int NT, typename TY, int MODE, int UNROLL>
-__global__ void __launch_bounds__(SK_WARPS * 32, NT <= 2 ? 4 : 2)
-gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* __restrict__ W, int M, int N,
-                   int K, long long ldx, long long ldw, long long ldy) {
-    __shared__ float red[SK_WARPS][NT][32][4];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int r0 = blockIdx.x * 16;
-    // plain: all 8 warps split K; swiglu: warps 0-3 take the gate rows, 4-7 the up rows
-    const int splits = MODE == SK_MODE_SWIGLU ? SK_WARPS / 2 : SK_WARPS;
-    const int part = MODE == SK_MODE_SWIGLU ? (warp & 3) : warp;
-    const int row_base = (MODE == SK_MODE_SWIGLU && warp >= 4) ? N + r0 : r0;     // N = F in swiglu mode
-    const int row_limit = (MODE == SK_MODE_SWIGLU && warp >= 4) ? 2 * N : N;
-    const int nblk = (K + 31) >> 5;
-    const int ksplit = gridDim.y;
-    const int per_cta = (nblk + ksplit - 1) / ksplit;
-    const int c0 = blockIdx.y * per_cta, c1 = min(nblk, c0 + per_cta);
-    const int per = (per_cta + splits - 1) / splits;
-    const int b0 = min(c1, c0 + part * per), b1 = min(c1, b0 + per);
-    const bool v0 = row_base + g < row_limit, v1 = row_base + g + 8 < row_limit;
-    const bf16* w0 = W + (long long)(row_base + g) * ldw;
-    const bf16* w1 = W + (long long)(row_base + g + 8) * ldw;
-
-    float acc[NT][4];
+// One warp's share of the product: the k-blocks b0 .. b1 of the weight rows w0 (fragment rows g) and
+// w1 (rows g + 8) against all M activation rows.  Waits for the kernel before this one after the
+// first weights are requested, and lets the next one start up right after.
+template <int NT, int UNROLL>
+__device__ __forceinline__ void skinny_stream(float (&acc)[NT][4], const bf16* __restrict__ X, const bf16* w0,
+                                              const bf16* w1, bool v0, bool v1, int b0, int b1, int M, int K,
+                                              long long ldx, int g, int t) {
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
@@ -113,6 +96,33 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
             wb[u] = nb[u];
         }
     }
+}
+
+template <int NT, typename TY, int MODE, int UNROLL>
+__global__ void __launch_bounds__(SK_WARPS * 32, NT <= 2 ? 4 : 2)
+gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* __restrict__ W, int M, int N,
+                   int K, long long ldx, long long ldw, long long ldy) {
+    __shared__ float red[SK_WARPS][NT][32][4];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = blockIdx.x * 16;
+    // plain: all 8 warps split K; swiglu: warps 0-3 take the gate rows, 4-7 the up rows
+    const int splits = MODE == SK_MODE_SWIGLU ? SK_WARPS / 2 : SK_WARPS;
+    const int part = MODE == SK_MODE_SWIGLU ? (warp & 3) : warp;
+    const int row_base = (MODE == SK_MODE_SWIGLU && warp >= 4) ? N + r0 : r0;     // N = F in swiglu mode
+    const int row_limit = (MODE == SK_MODE_SWIGLU && warp >= 4) ? 2 * N : N;
+    const int nblk = (K + 31) >> 5;
+    const int ksplit = gridDim.y;
+    const int per_cta = (nblk + ksplit - 1) / ksplit;
+    const int c0 = blockIdx.y * per_cta, c1 = min(nblk, c0 + per_cta);
+    const int per = (per_cta + splits - 1) / splits;
+    const int b0 = min(c1, c0 + part * per), b1 = min(c1, b0 + per);
+    const bool v0 = row_base + g < row_limit, v1 = row_base + g + 8 < row_limit;
+    const bf16* w0 = W + (long long)(row_base + g) * ldw;
+    const bf16* w1 = W + (long long)(row_base + g + 8) * ldw;
+
+    float acc[NT][4];
+    skinny_stream<NT, UNROLL>(acc, X, w0, w1, v0, v1, b0, b1, M, K, ldx, g, t);
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
@@ -188,6 +198,121 @@ static int dispatch_skinny(void* Y, const void* X, const void* W, int M, int N, 
     if (M <= 32) return launch_skinny<4, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
     if (M <= 64) return launch_skinny<8, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
     CM_REFUSE("gemm_skinny: %d rows (at most 64)", M);
+}
+
+// in_proj and the gated short convolution of a decode step in one kernel (one token per sequence).
+// W is the in_proj matrix [B: H rows | C: H rows | X: H rows] x K.  A block owns 16 channels: warps
+// 0-3 form the B rows of these channels, 4-7 the C rows, 8-11 the X rows, each group splitting K four
+// ways; the sums are rounded to bfloat16 as the unfused product's output is, and then
+//     bx = B * X;  z = sum_j taps[c][j] * s[j]  with s = (state[0 .. KT-2], bx);  y = T(z * C);
+//     state <- s[1 .. KT-1]
+// runs once per (sequence, channel), in the same order as shortconv_kernel does it.
+#define SKC_WARPS 12
+
+template <int NT, int UNROLL>
+__global__ void __launch_bounds__(SKC_WARPS * 32, 1)
+gemm_skinny_conv_kernel(bf16* __restrict__ Y, const bf16* __restrict__ X, const bf16* __restrict__ W,
+                        const float* __restrict__ taps, float* __restrict__ state, const int* __restrict__ seq_slot,
+                        int M, int H, int K, int KT, long long ldx, long long ldw, long long ldy) {
+    __shared__ float red[SKC_WARPS][NT][32][4];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = blockIdx.x * 16;
+    const int set = warp >> 2, part = warp & 3;
+    const int nblk = (K + 31) >> 5;
+    const int per = (nblk + 3) / 4;
+    const int b0 = min(nblk, part * per), b1 = min(nblk, b0 + per);
+    const bool v0 = r0 + g < H, v1 = r0 + g + 8 < H;
+    const bf16* w0 = W + ((long long)set * H + r0 + g) * ldw;
+    const bf16* w1 = W + ((long long)set * H + r0 + g + 8) * ldw;
+
+    // The thread that will finish element e = threadIdx.x (NT * 128 of them, fewer than the block
+    // has threads) asks for its channel's taps and its sequence's state now, so that they have
+    // arrived when the sums are ready (up to 4 taps; more are read at the end).
+    const int e = threadIdx.x;
+    const int en = e >> 7, el = (e >> 2) & 31, ej = e & 3;
+    const int c = r0 + (el >> 2) + (ej >= 2 ? 8 : 0);
+    const int m = en * 8 + (el & 3) * 2 + (ej & 1);
+    const bool owner = e < NT * 128 && c < H && m < M;
+    const bool early = KT <= 4;
+    float* st = nullptr;
+    const float* wc = taps + (long long)c * KT;
+    float s_pre[3] = {0.f, 0.f, 0.f}, w_pre[4] = {0.f, 0.f, 0.f, 0.f};
+    if (owner) {
+        st = state + (long long)seq_slot[m] * (KT - 1) * H + c;
+        if (early) {
+#pragma unroll
+            for (int q = 0; q < 3; ++q)
+                if (q < KT - 1) s_pre[q] = st[(long long)q * H];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (q < KT) w_pre[q] = wc[q];
+        }
+    }
+
+    float acc[NT][4];
+    skinny_stream<NT, UNROLL>(acc, X, w0, w1, v0, v1, b0, b1, M, K, ldx, g, t);
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) red[warp][n][lane][j] = acc[n][j];
+    __syncthreads();
+    if (!owner) return;
+    float sum[3];
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) v += red[q * 4 + w][en][el][ej];
+        sum[q] = rounded<bf16>(v);
+    }
+    const float bx = sum[0] * sum[2];
+    float z = 0.f;
+    if (early) {
+#pragma unroll
+        for (int q = 0; q < 3; ++q)
+            if (q < KT - 1) {
+                z += w_pre[q] * s_pre[q];
+                if (q > 0) st[(long long)(q - 1) * H] = s_pre[q];        // shift: entry q becomes entry q - 1
+            }
+#pragma unroll
+        for (int q = 1; q < 4; ++q)
+            if (q == KT - 1) z += w_pre[q] * bx;
+    } else {
+        for (int q = 0; q < KT - 1; ++q) {
+            const float sv = st[(long long)q * H];
+            z += wc[q] * sv;
+            if (q > 0) st[(long long)(q - 1) * H] = sv;
+        }
+        z += wc[KT - 1] * bx;
+    }
+    st[(long long)(KT - 2) * H] = bx;
+    Y[(long long)m * ldy + c] = from_f32<bf16>(z * sum[1]);
+}
+
+// y[M, H] = the short convolution's output for M sequences that bring one token each; x [M, K],
+// w [3H, K] bfloat16, taps [H][KT] float, state [slots][KT-1][H] float, seq_slot [M].
+extern "C" int cm_gemm_skinny_shortconv(void* Y, const void* X, const void* W, const float* taps, float* state,
+                                        const int* seq_slot, int M, int H, int K, int KT, long long ldx,
+                                        long long ldw, long long ldy, cudaStream_t st) {
+    if (M <= 0 || H <= 0) return CM_OK;
+    if (M > 16) CM_REFUSE("gemm_skinny_shortconv: %d rows (at most 16)", M);
+    if (KT < 2 || KT > 16) CM_REFUSE("gemm_skinny_shortconv: %d taps (2..16)", KT);
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8)
+        CM_REFUSE("gemm_skinny_shortconv: inner size %d and row strides %lld, %lld must be multiples of 8", K, ldx, ldw);
+    if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W)) & 15)
+        CM_REFUSE("gemm_skinny_shortconv: operands must be 16-byte aligned");
+    const int tiles = (H + 15) / 16;
+    // one block per SM at most (H / 16 blocks): four k-blocks of weights in flight per thread
+    constexpr int UNROLL = 4;
+    if (M <= 8)
+        cm_launch_cluster(gemm_skinny_conv_kernel<1, UNROLL>, dim3(tiles), SKC_WARPS * 32, 0, st, 1, false, (bf16*)Y,
+                          (const bf16*)X, (const bf16*)W, taps, state, seq_slot, M, H, K, KT, ldx, ldw, ldy);
+    else
+        cm_launch_cluster(gemm_skinny_conv_kernel<2, UNROLL>, dim3(tiles), SKC_WARPS * 32, 0, st, 1, false, (bf16*)Y,
+                          (const bf16*)X, (const bf16*)W, taps, state, seq_slot, M, H, K, KT, ldx, ldw, ldy);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
 }
 
 // X and W bfloat16; Y bfloat16 (dty = DT_BF16) or float (DT_F32).  swiglu: W has 2N rows

@@ -104,6 +104,10 @@ class Runtime:
             return "few_rows" if rows <= self.FEW_ROWS else "tiled"
         return "simt"
 
+    def streams_weights(self, x, w):
+        """True if x @ w^T goes to the weight-streaming kernel (a part may then use that kernel's fused forms)."""
+        return self._product_kernel(x, w) == "skinny"
+
     def gate_up_swiglu(self, x, w_gate_up, F):
         """a = silu(x Wgate^T) * (x Wup^T) for the row-packed [Wgate; Wup]."""
         a = torch.empty((x.shape[0], F), dtype=x.dtype, device=x.device)

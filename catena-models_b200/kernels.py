@@ -36,6 +36,7 @@ _SIGNATURES = {
     "cm_attn_prefill_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _ll, _i, _i, _i, _i, _f, _vp, _vp],
     "cm_attn_decode": [_i, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _i,
                        _i, _f, _vp, _vp, _vp],
+    "cm_gemm_skinny_shortconv": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
     "cm_shortconv": [_i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "cm_sample": [_vp, _vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "cm_scatter_i32": [_vp, _vp, _vp, _vp, _i, _vp],
@@ -307,6 +308,25 @@ def shortconv(y, bcx, w, state, tok_seq, seq_start, seq_slot, K, from_zero, one_
     _check(lib().cm_shortconv(dtype_code(y.dtype), _ptr(y), _ptr(bcx), bcx.stride(0), _ptr(w), _ptr(w_t), _ptr(state),
                               _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slot), T, H, K, int(from_zero),
                               int(one_token_each), _stream()), "shortconv")
+
+
+def gemm_skinny_shortconv(y, x, w_in, taps, state, seq_slot):
+    """A decode step's in_proj and short convolution in one kernel: x [M <= 16, K] and w_in [3H, K]
+    bfloat16 (rows B | C | X), taps [H, KT] float, state [slots, KT - 1, H] float (shifted in
+    place), seq_slot [M]; y [M, H] bfloat16."""
+    _need_cuda(y, x, w_in)
+    M, K = x.shape
+    H, KT = taps.shape
+    if w_in.shape != (3 * H, K) or y.shape != (M, H) or state.shape[1:] != (KT - 1, H):
+        raise KernelError(f"gemm_skinny_shortconv shapes: x {tuple(x.shape)}, w {tuple(w_in.shape)}, "
+                          f"y {tuple(y.shape)}, taps {tuple(taps.shape)}, state {tuple(state.shape)}")
+    if not (x.dtype == w_in.dtype == y.dtype == torch.bfloat16 and taps.dtype == state.dtype == torch.float32):
+        raise KernelError("gemm_skinny_shortconv takes bfloat16 operands, float taps and state")
+    if not (taps.is_contiguous() and state.is_contiguous()):
+        raise KernelError("gemm_skinny_shortconv: taps and state must be contiguous")
+    _check(lib().cm_gemm_skinny_shortconv(_ptr(y), _ptr(x), _ptr(w_in), _ptr(taps), _ptr(state), _ptr(seq_slot), M, H,
+                                          K, KT, x.stride(0), w_in.stride(0), y.stride(0), _stream()),
+           "gemm_skinny_shortconv")
 
 
 # ---------------------------------------------------------------------------- sampling

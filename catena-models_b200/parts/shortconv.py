@@ -42,8 +42,12 @@ class ShortConv(Mixer):
         return FixedStateSpec((self.taps - 1, self.hidden), "float32")
 
     def forward(self, rt, batch, x, state):
-        bcx = self.in_proj.apply(rt, x)                                   # [T, 3H]
         y = torch.empty((batch.T, self.hidden), dtype=x.dtype, device=x.device)
+        if not batch.prefill and rt.streams_weights(x, self.in_proj.weight):
+            # a decode step of a small batch: the convolution runs where in_proj's sums are formed
+            kernels.gemm_skinny_shortconv(y, x, self.in_proj.weight, self.conv_w, state.tensor, batch.seq_slot)
+            return self.out_proj.apply(rt, y)
+        bcx = self.in_proj.apply(rt, x)                                   # [T, 3H]
         kernels.shortconv(y, bcx, self.conv_w, state.tensor, batch.tok_seq, batch.seq_start, batch.seq_slot,
                           self.taps, from_zero=batch.prefill, one_token_each=not batch.prefill, w_t=self.conv_w_t)
         return self.out_proj.apply(rt, y)

@@ -393,6 +393,68 @@ def test_shortconv_prompt_then_decode(K, dtype, H, taps):
         K.shortconv(y, bcx, w, state, dec_seq, dec_start, slots, taps, from_zero=False, one_token_each=False)
 
 
+@pytest.mark.parametrize("M,H,Kin,taps", [(1, 48, 40, 2), (5, 100, 72, 3), (8, 2048, 2048, 3), (13, 304, 1000, 4),
+                                          (16, 64, 4104, 3)])
+def test_gemm_skinny_shortconv_matches_the_two_kernels(K, M, H, Kin, taps):
+    """in_proj and the decode form of the short convolution in one kernel: several steps on the same
+    slots (the state shifts each time), against float64 formulas and against the product followed by
+    the convolution kernel; widths that are no multiple of 16, a row count between the kernel's two
+    tile heights, an inner size with a ragged last block.
+    The fused kernel splits K four ways where the plain product splits it eight ways, so a float sum
+    that lies near a bfloat16 rounding boundary may round the other way: B, C and X are each right
+    to one bfloat16 step (2^-8 of the value) plus the float summation's own error (1e-5 covers sums
+    of this size).  The test carries these per-element error bounds through the formulas (products,
+    taps, the state of earlier steps, the output's rounding) instead of using a flat tolerance: a
+    flat one would have to be loose enough for the largest element and would then hide a wrong tap
+    on a small one."""
+    g = torch.Generator().manual_seed(M * 1000 + H)
+    w_in = (torch.randn(3 * H, Kin, generator=g) * Kin ** -0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(H, taps, generator=g) * 0.5).to(DEV)
+    slots = torch.randperm(M + 3, generator=g)[:M].to(torch.int32).to(DEV)
+    start = torch.randn(M + 3, taps - 1, H, generator=g).to(DEV)
+    state_a, state_b = start.clone(), start.clone()
+    seq = torch.arange(M, dtype=torch.int32, device=DEV)
+    seq_start = torch.arange(M + 1, dtype=torch.int32, device=DEV)
+    hist = [start[slots.long()].double().cpu()[:, j] for j in range(taps - 1)]        # per slot: s[0 .. taps-2]
+    hist_err = [torch.zeros_like(h) for h in hist]                                    # the given state is exact
+    wd = w.double().cpu()
+    step_err = lambda v: 2.0 ** -8 * v.abs() + 1e-5
+    for step in range(4):
+        x = torch.randn(M, Kin, generator=g).to(torch.bfloat16).to(DEV)
+        y_a = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+        K.gemm_skinny_shortconv(y_a, x, w_in, w, state_a, slots)
+        bcx = torch.empty(M, 3 * H, dtype=torch.bfloat16, device=DEV)
+        K.gemm_skinny(bcx, x, w_in)
+        y_b = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+        K.shortconv(y_b, bcx, w, state_b, seq, seq_start, slots, taps, from_zero=False, one_token_each=True)
+        r = (x.double().cpu() @ w_in.double().cpu().T).to(torch.bfloat16).double()   # the product, rounded once
+        B_, C_, X_ = r[:, :H], r[:, H:2 * H], r[:, 2 * H:]
+        dB, dC, dX = step_err(B_), step_err(C_), step_err(X_)
+        hist.append(B_ * X_)
+        hist_err.append(B_.abs() * dX + X_.abs() * dB + dB * dX)
+        z = sum(wd[:, j][None, :] * hist[j] for j in range(taps))
+        dz = sum(wd[:, j].abs()[None, :] * hist_err[j] for j in range(taps)) + 1e-6 * sum(
+            wd[:, j].abs()[None, :] * hist[j].abs() for j in range(taps))
+        hist.pop(0)
+        hist_err.pop(0)
+        ref = z * C_
+        bound = C_.abs() * dz + z.abs() * dC + dz * dC + 2.0 ** -8 * ref.abs() + 1e-30
+        for name, y in (("fused", y_a), ("two kernels", y_b)):
+            excess = ((y.double().cpu() - ref).abs() / bound).max()
+            assert excess <= 1.0, f"{name}, step {step}: {float(excess):.2f} of the bound"
+        for st in (state_a, state_b):
+            new = st[slots.long()].double().cpu()
+            for j in range(taps - 1):
+                assert ((new[:, j] - hist[j]).abs() <= hist_err[j] + 1e-30).all(), f"state entry {j}, step {step}"
+        assert (y_a != y_b).float().mean() < 0.02, "the two paths differ in more than stray roundings"
+    untouched = [s for s in range(M + 3) if s not in slots.tolist()]
+    assert torch.equal(state_a[untouched], start[untouched])
+    with pytest.raises(K.KernelError):
+        K.gemm_skinny_shortconv(torch.empty(17, H, dtype=torch.bfloat16, device=DEV),
+                                torch.zeros(17, Kin, dtype=torch.bfloat16, device=DEV), w_in, w, state_a,
+                                torch.zeros(17, dtype=torch.int32, device=DEV))
+
+
 def test_sample_greedy_ties_and_temperature(K):
     import plain_lfm3 as P
 
