@@ -35,6 +35,9 @@ class ModelDefinition:
     max_positions: int = 0
     embedding_aliases: tuple = ()
     extra_tensors: tuple = ()        # tensors every checkpoint holds although no part may read them
+    # Other names the same tensors may carry in a file: (prefix, other prefix) pairs; a tensor whose
+    # name starts with `prefix` is also looked for under the name with `other prefix` in its place.
+    alias_prefixes: tuple = ()
 
     def parts(self):
         out = list(self.blocks) + [self.final_norm]
@@ -55,6 +58,10 @@ class ModelDefinition:
                 if seen[s.name].shape != s.shape:
                     raise ValueError(f"tensor '{s.name}' is wanted with shapes {seen[s.name].shape} and {s.shape}")
                 continue
+            more = tuple(other + s.name[len(prefix):] for prefix, other in self.alias_prefixes
+                         if s.name.startswith(prefix))
+            if more:
+                s = dataclasses.replace(s, aliases=tuple(s.aliases) + more)
             seen[s.name] = s
             out.append(s)
         return out

@@ -8,6 +8,9 @@ attn_{q,k,v,gate,output}.weight and attn_{q,k}_norm.weight on attention layers;
 ffn_{gate,up,down}.weight; model.norm.weight; rope_freqs.weight; lm_head.weight when the head
 is not tied.  Full-attention layers rotate with rope_theta and the per-frequency factors,
 sliding layers with rope_theta_sliding and no factors (src/catena/lfm3.hex:726-734).
+A file may carry the same tensors under the names the reference's GGUF checkpoints use
+(`blk.{l}.*`, `token_embd.weight`, `output_norm.weight`, `output.weight`: the second name of
+every entry of src/spec.rs:714-808).
 """
 from __future__ import annotations
 
@@ -52,7 +55,9 @@ def define(cfg: Lfm3Config) -> ModelDefinition:
         head=head, stop_token_ids=tuple(cfg.eos_token_id), max_positions=cfg.max_position_embeddings,
         # rope_freqs.weight is part of every LFM3 checkpoint (src/spec.rs:789-794), also of one
         # whose layers are all sliding or conv and never read it
-        extra_tensors=(TensorSpec("rope_freqs.weight", (cfg.head_dim // 2,), "rope_factors"),))
+        extra_tensors=(TensorSpec("rope_freqs.weight", (cfg.head_dim // 2,), "rope_factors"),),
+        alias_prefixes=(("model.layers.", "blk."), ("model.embed_tokens.weight", "token_embd.weight"),
+                        ("model.norm.weight", "output_norm.weight"), ("lm_head.weight", "output.weight")))
     return definition
 
 

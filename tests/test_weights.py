@@ -113,3 +113,33 @@ def test_round_trip_values(tmp_path):
     from safetensors.torch import load_file
     other = load_file(str(tmp_path / "t.safetensors"))              # the reference implementation reads it too
     assert all(torch.equal(other[k], v) for k, v in t.items())
+
+
+def test_the_reference_checkpoint_names_are_accepted(tmp_path):
+    """The same tensors under the names of the reference's GGUF checkpoints (blk.{l}.*,
+    token_embd.weight, output_norm.weight, output.weight; src/spec.rs:428-441, 714-808) load to the
+    same values; a tensor present under both names leaves one of them unexpected."""
+    folder = tiny.make_folder(tmp_path, "B", seed=2)
+    specs = specs_of(tiny.TINY_B)
+    first = loader.load_tensors(folder, specs, "cpu")
+    path = os.path.join(folder, "model.safetensors")
+    f = SafetensorsFile(path)
+    stored = {n: f.tensor(n) for n in f.names()}
+    f.close()
+
+    def other(name):
+        if name.startswith("model.layers."):
+            return "blk." + name[len("model.layers."):]
+        return {"model.embed_tokens.weight": "token_embd.weight", "model.norm.weight": "output_norm.weight",
+                "lm_head.weight": "output.weight"}.get(name, name)
+
+    renamed = {other(n): t for n, t in stored.items()}
+    assert "blk.0.shortconv.in_proj.weight" in renamed and "rope_freqs.weight" in renamed
+    write_safetensors(path, renamed)
+    again = loader.load_tensors(folder, specs, "cpu")
+    assert set(again) == set(first) and all(torch.equal(again[k], first[k]) for k in first)
+    renamed["model.norm.weight"] = renamed["output_norm.weight"]
+    write_safetensors(path, renamed)
+    with pytest.raises(WeightError) as err:
+        loader.load_tensors(folder, specs, "cpu")
+    assert err.value.unexpected == ["output_norm.weight"] and not err.value.missing
