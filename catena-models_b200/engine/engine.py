@@ -330,6 +330,7 @@ class Engine:
             entry.launches = _kernels.launches - before
             _kernels.launches = before
             while len(self._prompt_graphs) >= PROMPT_GRAPHS_KEPT:
+                torch.cuda.current_stream().synchronize()      # its last replay may still be running
                 self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
             self._prompt_graphs[key] = entry
         return logits, sampled

@@ -323,3 +323,24 @@ def test_prompt_steps_of_a_repeated_shape(folders, plain, name, dtype):
     for handed, copy in earlier:
         assert torch.equal(handed, copy)
     eng.release(held)
+
+
+def test_recorded_prompt_shapes_are_bounded_and_evicted_ones_run_again(folders, plain):
+    """More repeated prompt shapes than the engine keeps graphs for: the oldest recording is dropped,
+    and a dropped shape that comes back runs kernel by kernel again with the same result."""
+    from catena_models_b200.engine.engine import PROMPT_GRAPHS_KEPT
+
+    name, dtype = "A", "bfloat16"
+    eng = engine_for(folders, name, dtype)
+    vocab = plain[name][0]["vocab_size"]
+    shapes = [(n,) for n in range(40, 40 + PROMPT_GRAPHS_KEPT + 3)]
+    for rnd in range(2):
+        for lens in shapes:
+            for rep in range(3):
+                prompts = [tiny.random_prompt(n, vocab, seed=rnd * 100 + rep * 10 + n) for n in lens]
+                slots = eng.admit(len(lens))
+                got = eng.step(slots, prompts)
+                eng.release(slots)
+                exact, same = plain_logits(plain, name, prompts[0], dtype)
+                check(got, exact[-1:], dtype, same[-1:])
+            assert len(eng._prompt_graphs) <= PROMPT_GRAPHS_KEPT
