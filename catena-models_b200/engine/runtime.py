@@ -34,9 +34,6 @@ class Runtime:
             self.error_flag.zero_()
             raise RuntimeError(f"a kernel's pipeline wait ran out (code {code}); its output is not valid")
 
-    def _unused(self):
-        pass
-
     # ------------------------------------------------------------------ scratch
     def scratch(self, key, numel, dtype=torch.float32):
         """A grow-only device buffer shared by the kernels that run one after another."""
