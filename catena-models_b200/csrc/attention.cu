@@ -127,6 +127,102 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
     }
 }
 
+// The same with 16-byte accesses (head sizes that are multiples of 16, aligned rows).  A head's two
+// halves are cut into runs of eight channels; LPH = HD / 16 lanes own one run of each half, so a
+// warp works on 32 / LPH heads of one token at a time and walks the token's heads in such passes.
+// The sum of squares of a head is added over its lanes in lane order.
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_prepare_vec_kernel(T* __restrict__ qkv, long long ld, const float* __restrict__ wq,
+                      const float* __restrict__ wk, const float* __restrict__ rate,
+                      const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                      const int* __restrict__ seq_slot, const int* __restrict__ seq_end,
+                      T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
+                      int ptab_stride, int ring, int QH, int KVH, int HD, float eps, int T_tokens,
+                      int passes_per_warp) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x;
+    const int t = blockIdx.x * blockDim.y + threadIdx.y;
+    if (t >= T_tokens) return;
+    const int half = HD >> 1, LPH = half >> 3, HPP = 32 / LPH;
+    const int sub = lane % LPH, hsel = lane / LPH;          // lanes past HPP * LPH idle along
+    const int pos = tok_pos[t];
+    float sn[8], cs[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        sn[e] = 0.f;
+        cs[e] = 1.f;
+        if (rate) sincosf((float)pos * rate[sub * 8 + e], &sn[e], &cs[e]);
+    }
+    int page = -1, row = 0;
+    if (pool) {
+        const int b = tok_seq[t];
+        if (ring == 0 || pos + ring >= seq_end[b]) {
+            const int entry = ring ? pos % ring : pos;
+            page = ptab[(long long)seq_slot[b] * ptab_stride + entry / PAGE_TOKENS];
+            row = entry % PAGE_TOKENS;
+        }
+    }
+    const int n_heads = QH + KVH;
+    const int pass0 = blockIdx.y * passes_per_warp;
+    for (int pass = pass0; pass < pass0 + passes_per_warp; ++pass) {
+        const int head = pass * HPP + hsel;
+        const bool live = hsel < HPP && head < n_heads;
+        const bool is_q = head < QH;
+        T* x = qkv + (long long)t * ld + (long long)head * HD + sub * 8;
+        const float* w = is_q ? wq : wk;
+        float lo[8], hi[8];
+        float ss = 0.f;
+        if (live) {
+            load8f<T>(x, lo);
+            load8f<T>(x + half, hi);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+        }
+        float inv = 1.f;
+        if (wq || wk) {                                             // the shuffles are for the whole warp
+            float tot = 0.f;
+            for (int j = 0; j < LPH; ++j) tot += __shfl_sync(0xffffffffu, ss, (hsel * LPH + j) & 31);
+            if (w) inv = 1.f / sqrtf(tot / (float)HD + eps);
+        }
+        if (!live) continue;
+        if (w) {
+            float wl[8], wh[8];
+            load8f<float>(w + sub * 8, wl);
+            load8f<float>(w + half + sub * 8, wh);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                lo[e] = rounded<T>((lo[e] * inv) * wl[e]);
+                hi[e] = rounded<T>((hi[e] * inv) * wh[e]);
+            }
+        }
+        float ol[8], oh[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            ol[e] = lo[e] * cs[e] - hi[e] * sn[e];
+            oh[e] = hi[e] * cs[e] + lo[e] * sn[e];
+        }
+        store8f<T>(x, ol);
+        store8f<T>(x + half, oh);
+        if (!is_q && page >= 0) {
+            T* kdst = kv_tile(pool, 0, pages, page, head - QH, KVH, HD) + (long long)row * HD + sub * 8;
+            store8f<T>(kdst, ol);
+            store8f<T>(kdst + half, oh);
+        }
+    }
+    // the raw values: copied by the warp that has the token's last pass
+    if (page >= 0 && pass0 + passes_per_warp >= (n_heads + HPP - 1) / HPP) {
+        const T* v = qkv + (long long)t * ld + (long long)(QH + KVH) * HD;
+        for (int e = lane * 8; e < KVH * HD; e += 256) {
+            const int kvh = e / HD, d = e - kvh * HD;
+            float tmp[8];
+            load8f<T>(v + e, tmp);
+            store8f<T>(kv_tile(pool, 1, pages, page, kvh, KVH, HD) + (long long)row * HD + d, tmp);
+        }
+    }
+}
+
 extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, const float* wk,
                              const float* rate, const int* tok_pos, const int* tok_seq,
                              const int* seq_slot, const int* seq_end, void* pool, long long pages,
@@ -136,6 +232,27 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
     if (HD % 2 || HD <= 0) CM_REFUSE("qk_prepare: head size %d is not even", HD);
     if (ring % PAGE_TOKENS) CM_REFUSE("qk_prepare: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
     if (HD > 256) CM_REFUSE("qk_prepare: head size %d above 256", HD);
+    const size_t esz = dt == DT_F32 ? 4 : 2;
+    const bool vec = HD % 16 == 0 && (ld * esz) % 16 == 0 &&
+                     (((uintptr_t)qkv | (uintptr_t)pool | (uintptr_t)wq | (uintptr_t)wk) & 15) == 0;
+    // Measured on B200 (32 + 8 heads of 64): 2,048 tokens 23.4 -> 12.4 us, 8,192 tokens 81.8 -> 24.2 us;
+    // a decode step of 8 or 64 tokens is quicker with a channel per lane (3.2 against 3.9 us).
+    if (vec && T >= 128 && (dt == DT_F32 || dt == DT_BF16)) {
+        const int hpp = 32 / (HD / 16), passes = (QH + KVH + hpp - 1) / hpp;
+        // A warp walks several passes of its token (sine and cosine are formed once per warp) when
+        // the tokens alone give the SMs enough warps; with fewer tokens the passes are spread.
+        int ppw = passes;
+        while (ppw > 1 && (long long)T * ((passes + ppw - 1) / ppw) < 8192) ppw = (ppw + 1) / 2;
+        dim3 vblock(32, 4), vgrid((T + 3) / 4, (passes + ppw - 1) / ppw);
+        if (dt == DT_F32)
+            cm_launch(qk_prepare_vec_kernel<float>, vgrid, vblock, 0, st, (float*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
+                      seq_slot, seq_end, (float*)pool, pages, ptab, ptab_stride, ring, QH, KVH, HD, eps, T, ppw);
+        else
+            cm_launch(qk_prepare_vec_kernel<bf16>, vgrid, vblock, 0, st, (bf16*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
+                      seq_slot, seq_end, (bf16*)pool, pages, ptab, ptab_stride, ring, QH, KVH, HD, eps, T, ppw);
+        CM_CHECK_LAUNCH();
+        return CM_OK;
+    }
     const int hpw = T >= 512 ? 4 : 1;
     dim3 block(32, 4), grid((T + 3) / 4, (QH + KVH + hpw - 1) / hpw);
     const size_t smem = 0;

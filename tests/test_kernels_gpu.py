@@ -303,12 +303,14 @@ def test_attn_decode_finds_a_far_key_and_respects_the_window_edge(K):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("extra", [3, 8])        # 3: rows that 16-byte accesses cannot take; 8: rows they can
 @pytest.mark.parametrize("QH,KVH,HD,ring,normed,rotated", [(4, 2, 16, 0, True, True), (3, 1, 24, 64, True, False),
-                                                          (2, 2, 128, 0, False, True), (5, 5, 32, 128, True, True)])
-def test_qk_prepare(K, dtype, QH, KVH, HD, ring, normed, rotated):
+                                                          (2, 2, 128, 0, False, True), (5, 5, 32, 128, True, True),
+                                                          (7, 3, 48, 64, True, True), (9, 3, 64, 0, True, True)])
+def test_qk_prepare(K, dtype, QH, KVH, HD, ring, normed, rotated, extra):
     lens, pos0 = [5, 150, 1], [0, 0, 0]
     T = sum(lens)
-    width = QH * HD + 2 * KVH * HD + 3
+    width = QH * HD + 2 * KVH * HD + extra
     qkv = rnd(T, width, dtype=dtype, seed=ring + HD)
     orig = qkv.clone()
     wq, wk = 1 + 0.1 * rnd(HD, seed=1), 1 + 0.1 * rnd(HD, seed=2)
@@ -352,6 +354,37 @@ def test_qk_prepare(K, dtype, QH, KVH, HD, ring, normed, rotated):
         t = 5 + p
         close(pool[0, page, :, e % 64], k_ref[t], dtype)
         assert torch.equal(pool[1, page, :, e % 64].cpu(), v_ref[t])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,QH,KVH,HD", [(600, 6, 2, 64), (600, 3, 3, 48), (600, 2, 1, 128), (8200, 20, 4, 64)])
+def test_qk_prepare_long_prompt_both_access_widths(K, dtype, T, QH, KVH, HD):
+    """Prompts long enough for the kernel with 16-byte accesses (the longest also for the form in
+    which one warp walks several groups of heads of its token): rows that take such accesses
+    against the same values in rows that do not (one channel of padding), which run the
+    one-channel-per-lane kernel checked above; cache contents included."""
+    pages = (T + 63) // 64
+    g = torch.Generator().manual_seed(HD)
+    core = torch.randn(T, (QH + 2 * KVH) * HD, generator=g).to(dtype)
+    wq, wk = 1 + 0.1 * rnd(HD, seed=1), 1 + 0.1 * rnd(HD, seed=2)
+    rate = (torch.rand(HD // 2, generator=g) * 0.5).to(DEV)
+    tok_seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    tok_pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([1], dtype=torch.int32, device=DEV)
+    seq_end = torch.tensor([T], dtype=torch.int32, device=DEV)
+    ptab = torch.stack([torch.zeros(pages, dtype=torch.int32), torch.randperm(pages, generator=g).to(torch.int32)]).to(DEV)
+    out = []
+    for pad in (8, 1):
+        qkv = torch.zeros(T, core.shape[1] + pad, dtype=dtype, device=DEV)
+        qkv[:, :core.shape[1]] = core.to(DEV)
+        pool = torch.zeros(2, pages, KVH, 64, HD, dtype=dtype, device=DEV)
+        K.qk_prepare(qkv, wq, wk, rate, tok_pos, tok_seq, slots, seq_end, pool, pages, ptab, 0, QH, KVH, HD, 1e-6)
+        out.append((qkv[:, :core.shape[1]].clone(), pool))
+    (a, pool_a), (b, pool_b) = out
+    close(a, b, dtype)
+    close(pool_a[0], pool_b[0], dtype)
+    assert torch.equal(pool_a[1], pool_b[1])                    # the values are copied as they are
+    assert pool_a[1].abs().sum() > 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
