@@ -56,10 +56,11 @@ def test_rmsnorm(K, dtype, rows, H):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,H", [(7, 328), (301, 328), (258, 2048), (257, 2568), (256, 3200)])
+@pytest.mark.parametrize("rows,H", [(7, 328), (301, 328), (258, 2048), (1500, 2048), (1100, 2568), (1030, 4104)])
 @pytest.mark.parametrize("post,nxt", [(True, True), (False, True), (True, False), (False, False)])
 def test_add_norm(K, dtype, post, nxt, rows, H):
-    """A few rows and a few hundred; widths that take one, two and four chunks of a thread."""
+    """A few rows, a few hundred and more than a thousand; widths that take one, two and four chunks
+    of a thread."""
     m, h = rnd(rows, H, dtype=dtype, scale=2.0, seed=1), rnd(rows, H, dtype=dtype, seed=2)
     wp, wn = 1 + 0.1 * rnd(H, seed=3), 1 + 0.1 * rnd(H, seed=4)
     h_out, n_out = torch.empty_like(h), torch.empty_like(h)
