@@ -61,16 +61,22 @@ __global__ void shortconv_kernel(T* __restrict__ y, const T* __restrict__ bcx, l
 }
 
 // The same, eight channels per thread with 16-byte accesses (H a multiple of 8, aligned rows).
-template <typename T>
+// KT: the number of taps when it is one of the usual ones (the loops over taps are then unrolled and
+// every load of a thread is in flight at once; with a loop that waits tap by tap a thread has two
+// loads in flight and 2,048 tokens of 2,048 channels take 10.4 us), or 0 for any number.
+template <typename T, int KT>
 __global__ void __launch_bounds__(128)
 shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld, const float* __restrict__ w,
                      const float* __restrict__ w_t, float* __restrict__ state, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
-                     const int* __restrict__ seq_slot, int H, int K, int from_zero) {
+                     const int* __restrict__ seq_slot, int T_tokens, int H, int K_any, int from_zero) {
     pdl_trigger();
     pdl_wait();
+    // threadIdx.y walks consecutive tokens: the rows a token shares with its neighbours (K - 1 of
+    // its K) are then read by the same block and come from L1 after the first time
+    const int K = KT ? KT : K_any;
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
-    const int t = blockIdx.x;
-    if (c >= H) return;
+    const int t = blockIdx.x * blockDim.y + threadIdx.y;
+    if (c >= H || t >= T_tokens) return;
     const int b = tok_seq[t];
     const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
     const int i = t - s0;
@@ -78,6 +84,7 @@ shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld,
     float z[8], cur[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) z[e] = cur[e] = 0.f;
+#pragma unroll
     for (int j = 0; j < K; ++j) {
         const int r = i + j - (K - 1);
         float sv[8];
@@ -150,13 +157,26 @@ extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, cons
         CM_REFUSE("shortconv: several tokens of a sequence on top of a stored state are not supported");
     const bool vec = H % 8 == 0 && ld % 8 == 0 && (((uintptr_t)y | (uintptr_t)bcx | (uintptr_t)state) & 15) == 0;
     if (vec) {
-        dim3 vgrid(T, (H / 8 + 127) / 128);
+        // few tokens: a token per block (128 channel groups); many: 4 consecutive tokens per block
+        const int ty = T >= 256 ? 4 : 1, tx = 128 / ty;
+        dim3 vblock(tx, ty), vgrid((T + ty - 1) / ty, (H / 8 + tx - 1) / tx);
+#define SC_LAUNCH_VEC(TT, KT)                                                                                      \
+    cm_launch(shortconv_vec_kernel<TT, KT>, vgrid, vblock, 0, st, (TT*)y, (const TT*)bcx, ld, w, w_t, state, tok_seq, \
+              seq_start, seq_slot, T, H, K, from_zero)
+#define SC_LAUNCH_TAPS(TT)                \
+    do {                                  \
+        switch (K) {                      \
+            case 2: SC_LAUNCH_VEC(TT, 2); break; \
+            case 3: SC_LAUNCH_VEC(TT, 3); break; \
+            case 4: SC_LAUNCH_VEC(TT, 4); break; \
+            case 7: SC_LAUNCH_VEC(TT, 7); break; \
+            default: SC_LAUNCH_VEC(TT, 0); break; \
+        }                                 \
+    } while (0)
         if (dt == DT_F32)
-            cm_launch(shortconv_vec_kernel<float>, vgrid, 128, 0, st, (float*)y, (const float*)bcx, ld, w, w_t, state,
-                      tok_seq, seq_start, seq_slot, H, K, from_zero);
+            SC_LAUNCH_TAPS(float);
         else if (dt == DT_BF16)
-            cm_launch(shortconv_vec_kernel<bf16>, vgrid, 128, 0, st, (bf16*)y, (const bf16*)bcx, ld, w, w_t, state, tok_seq,
-                      seq_start, seq_slot, H, K, from_zero);
+            SC_LAUNCH_TAPS(bf16);
         else
             return CM_ERR_DTYPE;
         CM_CHECK_LAUNCH();

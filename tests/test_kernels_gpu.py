@@ -390,9 +390,10 @@ def test_qk_prepare_long_prompt_both_access_widths(K, dtype, T, QH, KVH, HD):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,taps", [(8, 2), (72, 3), (200, 4), (136, 7)])
-def test_shortconv_prompt_then_decode(K, dtype, H, taps):
-    lens = [1, 2, 9, 30]
+@pytest.mark.parametrize("H,taps", [(8, 2), (72, 3), (200, 4), (136, 7), (40, 5), (27, 3)])
+@pytest.mark.parametrize("longest", [30, 300])       # 300: enough tokens for blocks that cover four tokens each
+def test_shortconv_prompt_then_decode(K, dtype, H, taps, longest):
+    lens = [1, 2, 9, longest]
     extra = 5
     g = torch.Generator().manual_seed(H)
     w = (torch.randn(H, taps, generator=g) * 0.5).to(DEV)
@@ -410,7 +411,7 @@ def test_shortconv_prompt_then_decode(K, dtype, H, taps):
     bcx = torch.cat([s[:n] for s, n in zip(seqs, lens)]).to(DEV)
     T = bcx.shape[0]
     tok_seq = torch.tensor(sum([[b] * n for b, n in enumerate(lens)], []), dtype=torch.int32, device=DEV)
-    starts = torch.tensor([0, 1, 3, 12, 42], dtype=torch.int32, device=DEV)
+    starts = torch.tensor([0, 1, 3, 12, 12 + longest], dtype=torch.int32, device=DEV)
     y = torch.empty(T, H, dtype=dtype, device=DEV)
     K.shortconv(y, bcx, w, state, tok_seq, starts, slots, taps, from_zero=True, one_token_each=False)
     got = [[y[a:b]] for a, b in zip(starts.tolist()[:-1], starts.tolist()[1:])]
