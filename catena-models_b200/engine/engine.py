@@ -80,7 +80,9 @@ class PendingTokens:
         return self._host[:self._n].tolist()
 
 
-class _DecodeGraph:
+class _RecordedStep:
+    """A captured step: its metadata layout and device buffer, the graph, and where its outputs land."""
+
     def __init__(self, layout, device_buf, graph, logits, batch):
         self.layout, self.device_buf, self.graph, self.logits, self.batch = layout, device_buf, graph, logits, batch
         self.launches = 0
@@ -322,7 +324,7 @@ class Engine:
         logits = run()
         if record:
             # as for decode: this run was the step's result; the capture executes nothing
-            entry = _DecodeGraph(layout, dev, torch.cuda.CUDAGraph(), None, batch)
+            entry = _RecordedStep(layout, dev, torch.cuda.CUDAGraph(), None, batch)
             entry.sampled = sampled
             before = _kernels.launches
             with torch.cuda.graph(entry.graph):
@@ -351,7 +353,7 @@ class Engine:
         if entry is None:
             layout = BatchLayout(B, B, B, B * max(1, self.n_kv_groups))
             device_buf = torch.zeros(layout.size, dtype=torch.int32, device=self.rt.device)
-            entry = _DecodeGraph(layout, device_buf, None, None, None)
+            entry = _RecordedStep(layout, device_buf, None, None, None)
             entry.sampled = self._sampled[:B]                  # every graph leaves its tokens in the same place
             self._graphs[key] = entry
         layout = entry.layout
