@@ -21,6 +21,7 @@ namespace cg = cooperative_groups;
 #define SK_WARPS 8
 #define SK_MODE_PLAIN 0
 #define SK_MODE_SWIGLU 1
+#define SK_MODE_PARTS 2          // float partial sums per k-slice, no exchange between the blocks of a row tile
 
 __device__ __forceinline__ void mma_bf16_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -101,7 +102,7 @@ __device__ __forceinline__ void skinny_stream(float (&acc)[NT][4], const bf16* _
 template <int NT, typename TY, int MODE, int UNROLL>
 __global__ void __launch_bounds__(SK_WARPS * 32, NT <= 2 ? 4 : 2)
 gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* __restrict__ W, int M, int N,
-                   int K, long long ldx, long long ldw, long long ldy) {
+                   int K, long long ldx, long long ldw, long long ldy, long long part_stride) {
     __shared__ float red[SK_WARPS][NT][32][4];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -148,6 +149,17 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
             csum[0][e] = s;
         }
     }
+    if (MODE == SK_MODE_PARTS) {
+        // every k-slice leaves its sums where whoever consumes the product adds them in slice order
+        __syncthreads();
+        for (int e = threadIdx.x; e < NT * 128; e += SK_WARPS * 32) {
+            const int n = e >> 7, l = (e >> 2) & 31, j = e & 3;
+            const int row = r0 + (l >> 2) + (j >= 2 ? 8 : 0);
+            const int m = n * 8 + (l & 3) * 2 + (j & 1);
+            if (row < N && m < M) Y[(long long)blockIdx.y * part_stride + (long long)m * ldy + row] = from_f32<TY>(csum[0][e]);
+        }
+        return;
+    }
     cg::cluster_group cluster = cg::this_cluster();
     if (ksplit > 1) cluster.sync(); else __syncthreads();
     if (blockIdx.y == 0) {
@@ -185,7 +197,17 @@ static int launch_skinny(void* Y, const void* X, const void* W, int M, int N, in
     // goes from 8.6 to 6.7 us against four k-blocks per step at two blocks per SM).
     constexpr int UNROLL = 2;
     cm_launch_cluster(gemm_skinny_kernel<NT, TY, MODE, UNROLL>, dim3(tiles, ksplit), SK_WARPS * 32, 0, st, ksplit, false,
-                      (TY*)Y, (const bf16*)X, (const bf16*)W, M, N, K, ldx, ldw, ldy);
+                      (TY*)Y, (const bf16*)X, (const bf16*)W, M, N, K, ldx, ldw, ldy, 0LL);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+template <int NT>
+static int launch_skinny_parts(float* P, const void* X, const void* W, int M, int N, int K, long long ldx, long long ldw,
+                               long long ldp, long long part_stride, int ksplit, cudaStream_t st) {
+    const int tiles = (N + 15) / 16;
+    cm_launch_cluster(gemm_skinny_kernel<NT, float, SK_MODE_PARTS, 2>, dim3(tiles, ksplit), SK_WARPS * 32, 0, st, 1, false, P,
+                      (const bf16*)X, (const bf16*)W, M, N, K, ldx, ldw, ldp, part_stride);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -198,6 +220,22 @@ static int dispatch_skinny(void* Y, const void* X, const void* W, int M, int N, 
     if (M <= 32) return launch_skinny<4, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
     if (M <= 64) return launch_skinny<8, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
     CM_REFUSE("gemm_skinny: %d rows (at most 64)", M);
+}
+
+// P[s][m][n] = sum over the s-th of `ksplit` slices of K of X[m,k] W[n,k], float: the product with its
+// inner dimension cut over independent blocks.  The slices are part_stride elements apart; the
+// consumer (cm_add_norm with m_parts) adds them in slice order.  At most 16 rows.
+extern "C" int cm_gemm_skinny_parts(float* P, const void* X, const void* W, int M, int N, int K, long long ldx,
+                                    long long ldw, long long ldp, long long part_stride, int ksplit, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return CM_OK;
+    if (M > 16) CM_REFUSE("gemm_skinny_parts: %d rows (at most 16)", M);
+    if (ksplit < 1 || ksplit > 8) CM_REFUSE("gemm_skinny_parts: %d slices (1 to 8)", ksplit);
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8)
+        CM_REFUSE("gemm_skinny_parts: inner size %d and row strides %lld, %lld must be multiples of 8", K, ldx, ldw);
+    if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W)) & 15)
+        CM_REFUSE("gemm_skinny_parts: operands must be 16-byte aligned");
+    if (M <= 8) return launch_skinny_parts<1>(P, X, W, M, N, K, ldx, ldw, ldp, part_stride, ksplit, st);
+    return launch_skinny_parts<2>(P, X, W, M, N, K, ldx, ldw, ldp, part_stride, ksplit, st);
 }
 
 // in_proj and the gated short convolution of a decode step in one kernel (one token per sequence).

@@ -310,7 +310,8 @@ __device__ __forceinline__ void store4(float* dst, const float* o) {
 template <typename TC, int MODE, int A_ROWS, int TCS_STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 2)
 gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                      TC* __restrict__ C, int M, int N, int K, long long ldc, int splits, int* err) {
+                      TC* __restrict__ C, float* __restrict__ parts, long long part_stride, int M, int N, int K,
+                      long long ldc, int splits, int* err) {
     constexpr uint32_t A_BYTES = A_ROWS * TC_BK * 2;
     constexpr uint32_t B_BYTES = TCS_BN * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -429,7 +430,19 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.f;
                 }
-                if (row < M) {
+                if (row < M && parts) {
+                    // no exchange: this k-slice's sums go to where the consumer of the product adds the slices
+                    float* dst = parts + (long long)rank * part_stride + (long long)row * ldc + n0 + c * 32;
+                    if ((ldc & 3) == 0 && n0 + c * 32 + 31 < N) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n0 + c * 32 + i < N) dst[i] = v[i];
+                    }
+                } else if (row < M) {
                     float4* dst = reinterpret_cast<float4*>(stage + (size_t)row * TCS_PITCH + c * 32);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -440,10 +453,11 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
     if (warp < 2) pdl_wait();                                     // stores below must follow the previous kernel
     __syncwarp();
-    if (splits > 1) cluster.sync(); else __syncthreads();
+    const bool exchange = splits > 1 && !parts;
+    if (exchange) cluster.sync(); else __syncthreads();
 
     // ------------------------------------------------------------------ sum over the cluster, epilogue
-    {
+    if (!parts) {
         const int col = n0 + (MODE == TC_MODE_SWIGLU ? (lane & 15) * 4 : lane * 4);
         const bool vec_ok = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
         for (int row = rank + splits * warp; row < M; row += splits * (TC_THREADS / 32)) {
@@ -453,7 +467,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
                 if (r < splits) {
-                    const float* src = splits > 1 ? cluster.map_shared_rank(stage, r) : stage;
+                    const float* src = exchange ? cluster.map_shared_rank(stage, r) : stage;
                     part[r] = *reinterpret_cast<const float4*>(src + (size_t)row * TCS_PITCH + lane * 4);
                 }
             }
@@ -484,7 +498,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             }
         }
     }
-    if (splits > 1) cluster.sync();
+    if (exchange) cluster.sync();
 
     // ------------------------------------------------------------------ teardown
     tc_fence_before();
@@ -601,7 +615,8 @@ static int splitk_active_clusters(int splits, size_t smem) {
 // (enough column tiles for every SM, or no room for clusters).
 template <typename TC, int MODE, int A_ROWS, int STAGES>
 static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
-                         long long ldc, int force_splits, int* err, cudaStream_t st) {
+                         long long ldc, int force_splits, int* err, cudaStream_t st, float* parts = nullptr,
+                         long long part_stride = 0) {
     constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? TCS_BN / 2 : TCS_BN;
     const size_t smem = (size_t)STAGES * (A_ROWS * TC_BK * 2 + TCS_BN * TC_BK * 2) + 1024;
     auto kernel = gemm_tc_splitk_kernel<TC, MODE, A_ROWS, STAGES>;
@@ -644,8 +659,9 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
     if (rc != CM_OK) return rc;
     rc = make_map(&map_b, B, MODE == TC_MODE_SWIGLU ? 2LL * N : N, K, ldb, MODE == TC_MODE_SWIGLU ? TCS_BN / 2 : TCS_BN);
     if (rc != CM_OK) return rc;
-    cm_launch_cluster(kernel, dim3(n_tiles, splits), TC_THREADS, smem, st, splits, true, map_a, map_b, (TC*)C, M, N, K, ldc,
-                      splits, err);
+    // with `parts` the k-slices are independent blocks (no cluster): each leaves its sums in parts[slice]
+    cm_launch_cluster(kernel, dim3(n_tiles, splits), TC_THREADS, smem, st, parts ? 1 : splits, true, map_a, map_b, (TC*)C,
+                      parts, part_stride, M, N, K, ldc, splits, err);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -677,14 +693,33 @@ extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M,
 
 template <typename TC, int MODE>
 static int launch_splitk(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
-                         long long ldc, int force_splits, int* err, cudaStream_t st) {
-    if (M <= 64) return launch_splitk_rows<TC, MODE, 64, 4>(C, A, B, M, N, K, lda, ldb, ldc, force_splits, err, st);
-    return launch_splitk_rows<TC, MODE, 128, 3>(C, A, B, M, N, K, lda, ldb, ldc, force_splits, err, st);
+                         long long ldc, int force_splits, int* err, cudaStream_t st, float* parts = nullptr,
+                         long long part_stride = 0) {
+    if (M <= 64)
+        return launch_splitk_rows<TC, MODE, 64, 4>(C, A, B, M, N, K, lda, ldb, ldc, force_splits, err, st, parts, part_stride);
+    return launch_splitk_rows<TC, MODE, 128, 3>(C, A, B, M, N, K, lda, ldb, ldc, force_splits, err, st, parts, part_stride);
 }
 
 // The same product for at most 128 rows, with K split over a thread-block cluster when the
 // product has too few column tiles to occupy the device (see gemm_tc_splitk_kernel); otherwise
 // it is handed to cm_gemm_tc with 128-column tiles.  splits: 0 to choose, 1..8 to force.
+// P[s][m][n] = the product over the s-th of `splits` slices of K, float, the slices part_stride
+// elements apart and each [M, N] with row pitch N: the few-rows product without the exchange between
+// the blocks of a tile (cm_add_norm with m_parts adds the slices in order).  At most 128 rows.
+extern "C" int cm_gemm_tc_few_rows_parts(float* P, const void* A, const void* B, int M, int N, int K, long long lda,
+                                         long long ldb, long long part_stride, int splits, int* err, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return CM_OK;
+    if (M > TC_BM) CM_REFUSE("gemm_tc_few_rows_parts: %d rows (at most %d)", M, TC_BM);
+    if (splits < 1 || splits > 8 || 2 * splits > (K + TC_BK - 1) / TC_BK)
+        CM_REFUSE("gemm_tc_few_rows_parts: %d slices of an inner size of %d (1 to 8, two 64-wide steps each at least)",
+                  splits, K);
+    if (K <= 0 || K % 8 || lda % 8 || ldb % 8)
+        CM_REFUSE("gemm_tc: inner size %d and row pitches %lld, %lld must be multiples of 8", K, lda, ldb);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(P)) & 15)
+        CM_REFUSE("gemm_tc: operands must be 16-byte aligned");
+    return launch_splitk<float, TC_MODE_PLAIN>(nullptr, A, B, M, N, K, lda, ldb, N, splits, err, st, P, part_stride);
+}
+
 extern "C" int cm_gemm_tc_few_rows(int dtc, void* C, const void* A, const void* B, int M, int N, int K,
                                    long long lda, long long ldb, long long ldc, int swiglu, int splits, int* err,
                                    cudaStream_t st) {

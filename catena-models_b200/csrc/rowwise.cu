@@ -116,9 +116,13 @@ extern "C" int cm_rmsnorm(int dt, void* y, const void* x, const float* w, int ro
 // n_out  = w_next ? T((h_out * inv(h_out)) * w_next)      (pre-norm of whatever runs next,
 //                                                          taken over the stored h_out)
 // h_out may alias h_in.  The row stays in registers between the passes.
-template <typename T, int C>
+// PARTS: m comes as n_parts float partial sums [n_parts][rows][H] (a product that split its inner
+// dimension over blocks left them); they are added in index order and rounded to T, which is the
+// value the product would have stored itself.
+template <typename T, int C, bool PARTS>
 __global__ void __launch_bounds__(NV_THREADS)
 add_norm_kernel(T* __restrict__ h_out, T* __restrict__ n_out, const T* __restrict__ m,
+                const float* __restrict__ m_parts, int n_parts, long long part_stride,
                 const T* __restrict__ h_in, const float* __restrict__ w_post,
                 const float* __restrict__ w_next, int H, float eps_post, float eps_next) {
     __shared__ float scratch[32];
@@ -139,8 +143,24 @@ add_norm_kernel(T* __restrict__ h_out, T* __restrict__ n_out, const T* __restric
     for (int c = 0; c < C; ++c) {
         const int e = (c * NV_THREADS + threadIdx.x) * 8;
         if (e < H) {
-            load8f<T>(m + off + e, mv[c]);
-            load8f<T>(h_in + off + e, hv[c]);
+            if (PARTS) {
+                float part[8][8];
+#pragma unroll
+                for (int r = 0; r < 8; ++r)
+                    if (r < n_parts) load8f<float>(m_parts + (long long)r * part_stride + off + e, part[r]);
+                load8f<T>(h_in + off + e, hv[c]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int r = 0; r < 8; ++r)
+                        if (r < n_parts) acc += part[r][i];
+                    mv[c][i] = rounded<T>(acc);
+                }
+            } else {
+                load8f<T>(m + off + e, mv[c]);
+                load8f<T>(h_in + off + e, hv[c]);
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) ss += mv[c][i] * mv[c][i];
         }
@@ -180,35 +200,52 @@ add_norm_kernel(T* __restrict__ h_out, T* __restrict__ n_out, const T* __restric
     }
 }
 
-template <typename T>
-static int launch_add_norm(void* h_out, void* n_out, const void* m, const void* h_in, const float* w_post,
-                           const float* w_next, int rows, int H, float eps_post, float eps_next, cudaStream_t st) {
+template <typename T, bool PARTS>
+static int launch_add_norm(void* h_out, void* n_out, const void* m, const float* m_parts, int n_parts,
+                           long long part_stride, const void* h_in, const float* w_post, const float* w_next, int rows,
+                           int H, float eps_post, float eps_next, cudaStream_t st) {
     const int chunks = (H / 8 + NV_THREADS - 1) / NV_THREADS;
     if (chunks <= 1)
-        cm_launch(add_norm_kernel<T, 1>, rows, NV_THREADS, 0, st, (T*)h_out, (T*)n_out, (const T*)m, (const T*)h_in,
-                  w_post, w_next, H, eps_post, eps_next);
+        cm_launch(add_norm_kernel<T, 1, PARTS>, rows, NV_THREADS, 0, st, (T*)h_out, (T*)n_out, (const T*)m, m_parts,
+                  n_parts, part_stride, (const T*)h_in, w_post, w_next, H, eps_post, eps_next);
     else if (chunks <= 2)
-        cm_launch(add_norm_kernel<T, 2>, rows, NV_THREADS, 0, st, (T*)h_out, (T*)n_out, (const T*)m, (const T*)h_in,
-                  w_post, w_next, H, eps_post, eps_next);
+        cm_launch(add_norm_kernel<T, 2, PARTS>, rows, NV_THREADS, 0, st, (T*)h_out, (T*)n_out, (const T*)m, m_parts,
+                  n_parts, part_stride, (const T*)h_in, w_post, w_next, H, eps_post, eps_next);
     else
-        cm_launch(add_norm_kernel<T, NV_MAXC>, rows, NV_THREADS, 0, st, (T*)h_out, (T*)n_out, (const T*)m,
-                  (const T*)h_in, w_post, w_next, H, eps_post, eps_next);
+        cm_launch(add_norm_kernel<T, NV_MAXC, PARTS>, rows, NV_THREADS, 0, st, (T*)h_out, (T*)n_out, (const T*)m,
+                  m_parts, n_parts, part_stride, (const T*)h_in, w_post, w_next, H, eps_post, eps_next);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
 
-extern "C" int cm_add_norm(int dt, void* h_out, void* n_out, const void* m, const void* h_in,
-                           const float* w_post, const float* w_next, int rows, int H,
-                           float eps_post, float eps_next, cudaStream_t st) {
+// m: [rows, H] in the activation dtype, or (m_parts given) n_parts float partial sums of it,
+// part_stride elements apart, each [rows, H].
+extern "C" int cm_add_norm(int dt, void* h_out, void* n_out, const void* m, const float* m_parts, int n_parts,
+                           long long part_stride, const void* h_in, const float* w_post, const float* w_next,
+                           int rows, int H, float eps_post, float eps_next, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
     if (H % 8 || H > 8 * NV_THREADS * NV_MAXC)
         CM_REFUSE("add_norm: width %d must be a multiple of 8, at most %d", H, 8 * NV_THREADS * NV_MAXC);
-    if (((uintptr_t)h_out | (uintptr_t)n_out | (uintptr_t)m | (uintptr_t)h_in | (uintptr_t)w_post | (uintptr_t)w_next) & 15)
+    if (((uintptr_t)h_out | (uintptr_t)n_out | (uintptr_t)m | (uintptr_t)m_parts | (uintptr_t)h_in | (uintptr_t)w_post |
+         (uintptr_t)w_next) & 15)
         CM_REFUSE("add_norm: operands must be 16-byte aligned");
+    if (m_parts) {
+        if (n_parts < 1 || n_parts > 8 || part_stride % 4)
+            CM_REFUSE("add_norm: %d partial sums (1 to 8), %lld elements apart (a multiple of 4)", n_parts, part_stride);
+        if (dt == DT_F32)
+            return launch_add_norm<float, true>(h_out, n_out, m, m_parts, n_parts, part_stride, h_in, w_post, w_next,
+                                                rows, H, eps_post, eps_next, st);
+        if (dt == DT_BF16)
+            return launch_add_norm<bf16, true>(h_out, n_out, m, m_parts, n_parts, part_stride, h_in, w_post, w_next,
+                                               rows, H, eps_post, eps_next, st);
+        return CM_ERR_DTYPE;
+    }
     if (dt == DT_F32)
-        return launch_add_norm<float>(h_out, n_out, m, h_in, w_post, w_next, rows, H, eps_post, eps_next, st);
+        return launch_add_norm<float, false>(h_out, n_out, m, nullptr, 0, 0, h_in, w_post, w_next, rows, H, eps_post,
+                                             eps_next, st);
     if (dt == DT_BF16)
-        return launch_add_norm<bf16>(h_out, n_out, m, h_in, w_post, w_next, rows, H, eps_post, eps_next, st);
+        return launch_add_norm<bf16, false>(h_out, n_out, m, nullptr, 0, 0, h_in, w_post, w_next, rows, H, eps_post,
+                                            eps_next, st);
     return CM_ERR_DTYPE;
 }
 

@@ -61,6 +61,8 @@ class StepBatch:
         self.wants_every_row = False                           # want_rows is 0, 1, ..., T-1 (set by the decode path)
         self.prev_sampled = None                               # device int32: tokens the step before chose (decode path)
         self.shared = {}                                       # what a layer leaves for later layers of this step
+        self.partial_sums_ok = False                           # set by a block around its mixer / feed-forward: their
+                                                               # output may be kernels.PartialSums
 
     def decode_chunks(self, kv_spec):
         """Chunks of cache entries the decode attention walks for this state spec."""

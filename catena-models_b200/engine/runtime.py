@@ -52,10 +52,24 @@ class Runtime:
                 self.scratch("attn_decode_ml", B * QH * n_chunks * 2))
 
     # ------------------------------------------------------------------ matrix products
-    def linear(self, x, w, out_dtype=None):
-        """y = x @ w^T; y in the activation dtype unless `out_dtype` says float32."""
-        y = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+    def linear(self, x, w, out_dtype=None, partial_ok=False):
+        """y = x @ w^T; y in the activation dtype unless `out_dtype` says float32.  With `partial_ok`
+        the caller can take `kernels.PartialSums` instead (the product cut over K, to be added by the
+        fused residual kernel): used where it spares the product an exchange between its blocks."""
         kind = self._product_kernel(x, w)
+        if partial_ok and out_dtype is None and kind == "skinny":
+            slices = self._skinny_slices(w.shape[0], w.shape[1])
+            if slices > 1:
+                parts = torch.empty((slices, x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+                kernels.gemm_skinny_parts(parts, x, w)
+                return kernels.PartialSums(parts, x.dtype)
+        if partial_ok and out_dtype is None and kind == "few_rows":
+            slices = self._few_rows_slices(w.shape[0], w.shape[1])
+            if slices > 1:
+                parts = torch.empty((slices, x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+                kernels.gemm_tc_few_rows_parts(parts, x, w, err=self.error_flag)
+                return kernels.PartialSums(parts, x.dtype)
+        y = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
         if kind == "skinny":
             kernels.gemm_skinny(y, x, w)
         elif kind == "few_rows":
@@ -65,6 +79,29 @@ class Runtime:
         else:
             kernels.gemm_simt(y, x, w)
         return y
+
+    SKINNY_SLICES = 4
+
+    def _skinny_slices(self, out_columns, inner):
+        """Into how many slices of K the weight-streaming product is cut when its consumer adds the
+        slices: products with few row tiles (at most 160 tiles of 16 output columns), whose blocks
+        would otherwise leave SMs idle or exchange sums through a cluster."""
+        tiles = -(-out_columns // 16)
+        if tiles > 160 or inner < 64 * self.SKINNY_SLICES:
+            return 1
+        return self.SKINNY_SLICES
+
+    def _few_rows_slices(self, out_columns, inner):
+        """Slices of K for the few-rows product when its consumer adds them: as many blocks as 1.4
+        per SM (the rule the kernel uses for its clusters), each with two 64-wide steps at least."""
+        if self._sm_count is None:
+            self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        tiles = -(-out_columns // 128)
+        steps = -(-inner // 64)
+        for s in range(8, 1, -1):
+            if 2 * s <= steps and 5 * tiles * s <= 7 * self._sm_count:
+                return s
+        return 1
 
     def _tile_width(self, rows, out_columns):
         """128 x 256 tiles move the fewest bytes per product, but a product with few of them leaves

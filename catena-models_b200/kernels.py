@@ -22,7 +22,9 @@ _vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_fl
 _SIGNATURES = {
     "cm_embed_gather": [_i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],
     "cm_rmsnorm": [_i, _vp, _vp, _vp, _i, _i, _f, _ll, _ll, _vp],
-    "cm_add_norm": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
+    "cm_add_norm": [_i, _vp, _vp, _vp, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
+    "cm_gemm_tc_few_rows_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp],
+    "cm_gemm_skinny_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _ll, _i, _vp],
     "cm_swiglu": [_i, _vp, _vp, _i, _i, _vp],
     "cm_gather_rows": [_i, _vp, _vp, _vp, _i, _i, _vp],
     "cm_gemm_simt": [_i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
@@ -150,11 +152,35 @@ def rmsnorm(out, x, w, eps):
                             out.stride(0), _stream()), "rmsnorm")
 
 
+class PartialSums:
+    """A product x @ w^T left as float partial sums over slices of its inner dimension:
+    `parts` [slices, rows, width].  Whoever consumes it adds the slices in index order and rounds
+    the total to the activation dtype (`add_norm` does both while it reads them)."""
+
+    def __init__(self, parts, dtype):
+        self.parts, self.dtype = parts, dtype
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+
 def add_norm(h_out, n_out, m, h_in, w_post, w_next, eps_post, eps_next):
-    """h_out = h_in + (norm(m; w_post) or m); n_out = norm(h_out; w_next) when w_next is given."""
+    """h_out = h_in + (norm(m; w_post) or m); n_out = norm(h_out; w_next) when w_next is given.
+    m: a tensor, or the PartialSums a product left."""
+    if isinstance(m, PartialSums):
+        parts = m.parts
+        _need_cuda(h_out, parts, h_in)
+        n_parts, rows, H = parts.shape
+        if parts.dtype != torch.float32 or not parts.is_contiguous():
+            raise KernelError("add_norm: partial sums must be contiguous float32")
+        _check(lib().cm_add_norm(dtype_code(h_in.dtype), _ptr(h_out), _ptr(n_out), None, _ptr(parts), n_parts, rows * H,
+                                 _ptr(h_in), _ptr(w_post), _ptr(w_next), rows, H, eps_post, eps_next, _stream()),
+               "add_norm")
+        return
     _need_cuda(h_out, m, h_in)
     rows, H = m.shape
-    _check(lib().cm_add_norm(dtype_code(m.dtype), _ptr(h_out), _ptr(n_out), _ptr(m), _ptr(h_in), _ptr(w_post),
+    _check(lib().cm_add_norm(dtype_code(m.dtype), _ptr(h_out), _ptr(n_out), _ptr(m), None, 0, 0, _ptr(h_in), _ptr(w_post),
                              _ptr(w_next), rows, H, eps_post, eps_next, _stream()), "add_norm")
 
 
@@ -193,6 +219,34 @@ def gemm_skinny(y, x, w, swiglu=False):
         raise KernelError("gemm_skinny takes bfloat16 operands")
     _check(lib().cm_gemm_skinny(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
                                 y.stride(0), int(swiglu), _stream()), "gemm_skinny")
+
+
+def gemm_skinny_parts(parts, x, w):
+    """parts[s] = x[:, slice s of K] @ w[:, slice s of K]^T in float, for at most 16 bfloat16 rows:
+    the weight-streaming product with K cut over parts.shape[0] independent groups of blocks."""
+    _need_cuda(parts, x, w)
+    M, K = x.shape
+    S, _, N = parts.shape
+    if w.shape != (N, K) or parts.shape[1] != M or parts.dtype != torch.float32 or not parts.is_contiguous():
+        raise KernelError(f"gemm_skinny_parts shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, parts {tuple(parts.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny_parts takes bfloat16 operands")
+    _check(lib().cm_gemm_skinny_parts(_ptr(parts), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), N, M * N, S,
+                                      _stream()), "gemm_skinny_parts")
+
+
+def gemm_tc_few_rows_parts(parts, x, w, err=None):
+    """The same from the tcgen05 few-rows product (at most 128 bfloat16 rows): parts[s] holds the
+    float sums over the s-th slice of K; no exchange between the blocks of a column tile."""
+    _need_cuda(parts, x, w)
+    M, K = x.shape
+    S, _, N = parts.shape
+    if w.shape != (N, K) or parts.shape[1] != M or parts.dtype != torch.float32 or not parts.is_contiguous():
+        raise KernelError(f"gemm_tc_few_rows_parts shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, parts {tuple(parts.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError("gemm_tc_few_rows_parts takes row-major bfloat16 operands")
+    _check(lib().cm_gemm_tc_few_rows_parts(_ptr(parts), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), M * N, S,
+                                           _ptr(err), _stream()), "gemm_tc_few_rows_parts")
 
 
 def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256):

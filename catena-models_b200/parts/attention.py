@@ -113,7 +113,7 @@ class GQAttention(Mixer):
             part_o, part_ml = rt.scratch_attn_decode(batch.B, QH, HD, n_chunks)
             kernels.attn_decode(ctx, q, gate, batch.seq_pos0, batch.seq_slot, state.pool, state.pages, state.ptab,
                                 state.ring, self.window, QH, KVH, HD, n_chunks, self.scale, part_o, part_ml)
-        return self.out.apply(rt, ctx)
+        return self.out.apply(rt, ctx, partial_ok=batch.partial_sums_ok)
 
 
 register_part("mixer", "gqa_attention", GQAttention)

@@ -28,13 +28,16 @@ class SandwichBlock(Block):
         return self.mixer.state_spec()
 
     @staticmethod
-    def _residual(rt, h, m, post, nxt):
+    def _fusable(norm):
+        return getattr(norm, "fused_kind", None) == "rms"
+
+    @classmethod
+    def _residual(cls, rt, h, m, post, nxt):
         """h + post(m) in place of h, and next(h) when `nxt` is given.  Norms that the fused
         kernel cannot absorb (anything but an RMSNorm) run through their own `apply`."""
-        fusable = lambda norm: getattr(norm, "fused_kind", None) == "rms"
-        if post is not None and not fusable(post):
+        if post is not None and not cls._fusable(post):
             m, post = post.apply(rt, m), None
-        fuse_next = nxt is not None and fusable(nxt)
+        fuse_next = nxt is not None and cls._fusable(nxt)
         n_out = torch.empty_like(h) if fuse_next else None
         kernels.add_norm(h, n_out, m, h,
                          post.weight if post is not None else None,
@@ -46,9 +49,14 @@ class SandwichBlock(Block):
         return h, n_out
 
     def forward(self, rt, batch, h, n, state, next_norm):
+        # the fused residual kernel can add the partial sums of a product cut over K; a post-norm
+        # of another kind needs the finished product
+        batch.partial_sums_ok = self.post_mixer_norm is None or self._fusable(self.post_mixer_norm)
         m = self.mixer.forward(rt, batch, n, state)
         h, n2 = self._residual(rt, h, m, self.post_mixer_norm, self.ffn_norm)
+        batch.partial_sums_ok = self.post_ffn_norm is None or self._fusable(self.post_ffn_norm)
         f = self.feed_forward.forward(rt, batch, n2)
+        batch.partial_sums_ok = False
         return self._residual(rt, h, f, self.post_ffn_norm, next_norm)
 
 

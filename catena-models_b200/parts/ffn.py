@@ -25,7 +25,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, rt, batch, x):
         a = rt.gate_up_swiglu(x, self.gate_up.weight, self.intermediate)
-        return self.down.apply(rt, a)
+        return self.down.apply(rt, a, partial_ok=batch.partial_sums_ok)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -42,5 +42,7 @@ class Linear(Part):
         self.weight = weight
         self._bound = []
 
-    def apply(self, rt, x, out_dtype=None):
-        return rt.linear(x, self.weight, out_dtype)
+    def apply(self, rt, x, out_dtype=None, partial_ok=False):
+        """x @ weight^T.  `partial_ok`: the result goes straight into a residual sum that can add
+        partial sums (StepBatch.partial_sums_ok says so), so the runtime may leave it as such."""
+        return rt.linear(x, self.weight, out_dtype, partial_ok)

@@ -46,11 +46,11 @@ class ShortConv(Mixer):
         if not batch.prefill and rt.streams_weights(x, self.in_proj.weight):
             # a decode step of a small batch: the convolution runs where in_proj's sums are formed
             kernels.gemm_skinny_shortconv(y, x, self.in_proj.weight, self.conv_w, state.tensor, batch.seq_slot)
-            return self.out_proj.apply(rt, y)
+            return self.out_proj.apply(rt, y, partial_ok=batch.partial_sums_ok)
         bcx = self.in_proj.apply(rt, x)                                   # [T, 3H]
         kernels.shortconv(y, bcx, self.conv_w, state.tensor, batch.tok_seq, batch.seq_start, batch.seq_slot,
                           self.taps, from_zero=batch.prefill, one_token_each=not batch.prefill, w_t=self.conv_w_t)
-        return self.out_proj.apply(rt, y)
+        return self.out_proj.apply(rt, y, partial_ok=batch.partial_sums_ok)
 
 
 register_part("mixer", "short_conv", ShortConv)

@@ -82,6 +82,76 @@ def test_add_norm(K, dtype, post, nxt, rows, H):
     assert torch.equal(h2, h_out)
 
 
+@pytest.mark.parametrize("M,N,Kin,slices", [(1, 48, 256, 4), (8, 2048, 2048, 4), (13, 200, 1000, 3), (16, 72, 8192, 8),
+                                            (5, 40, 64, 2)])
+def test_gemm_skinny_parts_and_add_norm_over_them(K, M, N, Kin, slices):
+    """The weight-streaming product cut over K into float partial sums, and the fused residual
+    kernel that adds them: each slice against the float64 product over its own k range (the kernel's
+    rule: k-blocks of 32 dealt out evenly), the total against the whole product, and add_norm over
+    the slices against add_norm over the rounded total (the same bits: it adds the slices in order
+    and rounds once, as the product's own store would)."""
+    x = rnd(M, Kin, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, Kin, dtype=torch.bfloat16, scale=Kin ** -0.5, seed=2)
+    parts = torch.full((slices, M, N), float("nan"), device=DEV)
+    K.gemm_skinny_parts(parts, x, w)
+    nblk = (Kin + 31) // 32
+    per = (nblk + slices - 1) // slices
+    xd, wd = x.double().cpu(), w.double().cpu()
+    for s_ in range(slices):
+        k0, k1 = min(Kin, s_ * per * 32), min(Kin, (s_ + 1) * per * 32)
+        torch.testing.assert_close(parts[s_].double().cpu(), xd[:, k0:k1] @ wd[:, k0:k1].T, rtol=1e-4, atol=1e-4)
+    total = parts[0].clone()
+    for s_ in range(1, slices):
+        total += parts[s_]
+    m = total.to(torch.bfloat16)
+    h = rnd(M, N, dtype=torch.bfloat16, seed=3)
+    if N % 8 == 0:
+        wp, wn = 1 + 0.1 * rnd(N, seed=4), 1 + 0.1 * rnd(N, seed=5)
+        h_a, n_a, h_b, n_b = (torch.empty_like(h) for _ in range(4))
+        K.add_norm(h_a, n_a, K.PartialSums(parts, torch.bfloat16), h, wp, wn, 1e-5, 1e-6)
+        K.add_norm(h_b, n_b, m, h, wp, wn, 1e-5, 1e-6)
+        assert torch.equal(h_a, h_b) and torch.equal(n_a, n_b)
+        h_c = torch.empty_like(h)
+        K.add_norm(h_c, None, K.PartialSums(parts, torch.bfloat16), h, None, None, 0.0, 0.0)
+        assert torch.equal(h_c, (h.float() + m.float()).to(torch.bfloat16))
+    with pytest.raises(K.KernelError):
+        K.gemm_skinny_parts(torch.empty(2, 17, N, device=DEV), torch.zeros(17, Kin, dtype=torch.bfloat16, device=DEV), w)
+
+
+@pytest.mark.parametrize("M,N,Kin,slices", [(17, 2048, 2048, 8), (64, 200, 1000, 3), (128, 136, 8192, 8), (100, 2052, 512, 2),
+                                            (33, 72, 192, 1)])
+def test_gemm_tc_few_rows_parts(K, M, N, Kin, slices):
+    """The tcgen05 few-rows product cut over K into float partial sums without the exchange
+    between the blocks of a tile: each slice against the float64 product over its own k range
+    (64-wide steps dealt out evenly), widths that end inside a tile or are no multiple of 4, and
+    add_norm over the slices against add_norm over the rounded total."""
+    x = rnd(M, Kin, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, Kin, dtype=torch.bfloat16, scale=Kin ** -0.5, seed=2)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    parts = torch.full((slices, M, N), float("nan"), device=DEV)
+    K.gemm_tc_few_rows_parts(parts, x, w, err=err)
+    assert int(err) == 0
+    steps = (Kin + 63) // 64
+    per = (steps + slices - 1) // slices
+    xd, wd = x.double().cpu(), w.double().cpu()
+    for s_ in range(slices):
+        k0, k1 = min(Kin, s_ * per * 64), min(Kin, (s_ + 1) * per * 64)
+        torch.testing.assert_close(parts[s_].double().cpu(), xd[:, k0:k1] @ wd[:, k0:k1].T, rtol=1e-4, atol=1e-4)
+    if N % 8 == 0:
+        total = parts[0].clone()
+        for s_ in range(1, slices):
+            total += parts[s_]
+        m = total.to(torch.bfloat16)
+        h = rnd(M, N, dtype=torch.bfloat16, seed=3)
+        wp, wn = 1 + 0.1 * rnd(N, seed=4), 1 + 0.1 * rnd(N, seed=5)
+        h_a, n_a, h_b, n_b = (torch.empty_like(h) for _ in range(4))
+        K.add_norm(h_a, n_a, K.PartialSums(parts, torch.bfloat16), h, wp, wn, 1e-5, 1e-6)
+        K.add_norm(h_b, n_b, m, h, wp, wn, 1e-5, 1e-6)
+        assert torch.equal(h_a, h_b) and torch.equal(n_a, n_b)
+    with pytest.raises(K.KernelError):
+        K.gemm_tc_few_rows_parts(torch.empty(4, M, N, device=DEV), x[:, :64].contiguous(), w[:, :64].contiguous(), err=err)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu_and_gather(K, dtype):
     gu = rnd(5, 2 * 72, dtype=dtype, scale=2.0)
