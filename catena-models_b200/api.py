@@ -71,11 +71,16 @@ class Session:
             raise ValueError(f"session capacity {self.capacity} exceeded")
         return self.model.engine.step([self.slot], [list(tokens)])
 
+    def _to_host(self, logits):
+        out = logits[0].float().cpu()
+        self.model.engine.check_errors()                       # the copy has synchronised: the flags are final
+        return out
+
     def prefill_logits(self, tokens):
-        return self._run(tokens)[0].float().cpu()
+        return self._to_host(self._run(tokens))
 
     def decode_logits(self, token):
-        return self._run([token])[0].float().cpu()
+        return self._to_host(self._run([token]))
 
     def prefill_next_token(self, tokens):
         return self._greedy.sample(self._run(tokens), [0], [0])[0]
@@ -84,12 +89,13 @@ class Session:
         return self._greedy.sample(self._run([token]), [0], [0])[0]
 
     def append_logits(self, tokens):
-        """Logits after `tokens` on top of what the session holds (src/model.rs: append_logits).  A
-        fresh session takes them as one prompt step; a started one takes them one by one."""
+        """Logits after `tokens` on top of what the session holds, in one step wherever the session
+        stands (`Session::forward` takes any number of tokens at any position, src/model.rs:692-731).
+        A model with a part that has no append form takes them one by one."""
         tokens = list(tokens)
         if not tokens:
             raise ValueError("append needs at least one token")
-        if self.position == 0:
+        if self.position == 0 or self.model.decoder.supports_append:
             return self.prefill_logits(tokens)
         if self.position + len(tokens) > self.capacity:
             raise ValueError(f"session capacity {self.capacity} exceeded")

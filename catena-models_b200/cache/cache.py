@@ -11,9 +11,10 @@ pages it holds in which group); it needs no device and is what the CPU tests exe
 * a group of layers with equal `FixedStateSpec`: `storage[layer, slot, *shape]`.
 
 Sizing follows one number, `max_tokens`: the most tokens that live sequences hold at any
-time, each sequence rounded up to whole pages of 64.  Slots and pages are given back by
-`release` and used again by the next batch; nothing is cleared on release, because every
-kernel reads only entries below the sequence's own length.
+time, each sequence rounded up to whole pages.  Slots and pages are given back by `release`
+and used again by the next batch; nothing is cleared on release, because every kernel reads
+only entries below the sequence's own length.  Fixed-size states are cleared when a slot is
+admitted (`zero_slots`).
 """
 from __future__ import annotations
 
@@ -184,10 +185,14 @@ class Cache:
     # ------------------------------------------------------------------ bookkeeping
     def admit(self):
         """A fresh slot; its fixed-size states are cleared on the device."""
-        slot = self.book.admit()
+        return self.admit_many(1)[0]
+
+    def admit_many(self, count):
+        """`count` fresh slots; their fixed-size states are cleared by one launch per group."""
+        slots = [self.book.admit() for _ in range(count)]
         for store in self.fixed_storage:
-            store[:, slot].zero_()
-        return slot
+            kernels.zero_slots(store, slots)
+        return slots
 
     def release(self, slot):
         self.book.release(slot)

@@ -139,12 +139,13 @@ def main(argv=None):
         ap.error("--bench and --prompt exclude each other")
 
     from .api import Model
+    from .csrc.limits import PAGE_TOKENS
 
     if args.bench:
-        need = args.batch * (max(args.pp, args.tg_context + args.tg + 2) + 64)
+        need = args.batch * (max(args.pp, args.tg_context + args.tg + 2) + PAGE_TOKENS)
     else:
-        need = sum((len(p) + args.max_new_tokens + 63) // 64 * 64 for p in args.prompt)
-    max_tokens = args.max_tokens or max(need, 64)
+        need = sum(-(-(len(p) + args.max_new_tokens) // PAGE_TOKENS) * PAGE_TOKENS for p in args.prompt)
+    max_tokens = args.max_tokens or max(need, PAGE_TOKENS)
     t0 = time.perf_counter()
     if args.model:
         model = Model.load(args.model, dtype=args.dtype, max_tokens=max_tokens)

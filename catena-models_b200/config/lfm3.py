@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import dataclasses
 
+from ..csrc import limits
 from .base import ConfigError, Reader
 
 LAYER_TYPES = ("conv", "full_attention", "sliding_attention")
@@ -84,12 +85,15 @@ class Lfm3Config:
             problems.append(f"layer_types has {len(self.layer_types)} entries for {self.num_hidden_layers} layers")
         if self.num_attention_heads % self.num_key_value_heads:
             problems.append("num_attention_heads must be divisible by num_key_value_heads")
-        if self.head_dim % 8 or self.head_dim > 256:
-            problems.append(f"head_dim {self.head_dim}: the kernels take multiples of 8 up to 256")
+        if self.head_dim % 8 or self.head_dim > limits.MAX_HEAD_DIM:
+            problems.append(f"head_dim {self.head_dim}: the kernels take multiples of 8 up to {limits.MAX_HEAD_DIM}")
         if self.hidden_size % 8 or self.intermediate_size % 8:
             problems.append("hidden_size and intermediate_size must be multiples of 8 (16-byte rows)")
-        if self.conv_L_cache > 16:
-            problems.append(f"conv_L_cache {self.conv_L_cache}: the kernels take up to 16 taps")
+        if self.hidden_size > limits.NORM_MAX_WIDTH:
+            problems.append(f"hidden_size {self.hidden_size}: the norm kernels keep a row of at most "
+                            f"{limits.NORM_MAX_WIDTH} in registers")
+        if self.conv_L_cache > limits.MAX_CONV_TAPS:
+            problems.append(f"conv_L_cache {self.conv_L_cache}: the kernels take up to {limits.MAX_CONV_TAPS} taps")
         if any(i < 0 or i >= self.num_hidden_layers for i in self.layer_order):
             problems.append("layer_order names a layer that does not exist")
         if any(t < 0 or t >= self.vocab_size for t in self.eos_token_id):

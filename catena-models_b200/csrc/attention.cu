@@ -231,7 +231,7 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
     if (T <= 0) return CM_OK;
     if (HD % 2 || HD <= 0) CM_REFUSE("qk_prepare: head size %d is not even", HD);
     if (ring % PAGE_TOKENS) CM_REFUSE("qk_prepare: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
-    if (HD > 256) CM_REFUSE("qk_prepare: head size %d above 256", HD);
+    if (HD > CM_MAX_HEAD_DIM) CM_REFUSE("qk_prepare: head size %d above %d", HD, CM_MAX_HEAD_DIM);
     const size_t esz = dt == DT_F32 ? 4 : 2;
     const bool vec = HD % 16 == 0 && (ld * esz) % 16 == 0 &&
                      (((uintptr_t)qkv | (uintptr_t)pool | (uintptr_t)wq | (uintptr_t)wk) & 15) == 0;
@@ -275,18 +275,27 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
 // One block = 32 queries of one head of one sequence; keys come in tiles of 32 from the
 // step's own rows (all sequences of a prefill step start at position 0).
 // Warp w owns queries 8w..8w+7; a lane is a key for the scores and a set of channels for PV.
+// PAST: the sequences may stand at a position p0 > 0 (several tokens on top of a started
+// sequence).  Keys and values below p0 are then read from the paged cache (entry = position, or
+// position % ring), those from p0 on from the step's own rows; the step's rows are written to
+// the cache only after this kernel has run, so a ring still holds every position that the
+// windows of the step's queries reach.  Rows outside what the block's queries can see are not
+// read at all (they may be stale or never written) and enter the sums as zeros.
 // =========================================================================================
 #define AP_BQ 32
 #define AP_BK 32
 #define AP_MAXJ 8        // head_dim <= 32 * AP_MAXJ
+static_assert(32 * AP_MAXJ == CM_MAX_HEAD_DIM, "cm_limits.h: CM_MAX_HEAD_DIM");
 
-template <typename T>
+template <typename T, bool PAST>
 __global__ void __launch_bounds__(128)
 attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict__ q,
                          const T* __restrict__ k, const T* __restrict__ v, long long ld,
                          const T* __restrict__ gate, long long ldg,
                          const int* __restrict__ seq_start, int QH, int KVH, int HD, int window,
-                         float scale) {
+                         float scale, const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot,
+                         const T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
+                         int ptab_stride, int ring) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -296,15 +305,18 @@ attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict
     float* Vs = Ks + AP_BK * ldq;           // [AP_BK][HD]
     float* Ps = Vs + AP_BK * HD;            // [AP_BQ][AP_BK+1]
     const int b = blockIdx.z, hq = blockIdx.y, hk = hq / (QH / KVH);
-    const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
-    const int q0 = blockIdx.x * AP_BQ;
+    const int s0 = seq_start[b], n_new = seq_start[b + 1] - s0;
+    const int p0 = PAST ? seq_pos0[b] : 0;         // position of the step's first token of this sequence
+    const int len = p0 + n_new;                    // positions are absolute from here on
+    const int q0 = p0 + blockIdx.x * AP_BQ;
     if (q0 >= len) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nq = min(AP_BQ, len - q0);
+    const int* prow = PAST ? ptab + (long long)seq_slot[b] * ptab_stride : nullptr;
 
     for (int e = threadIdx.x; e < AP_BQ * HD; e += blockDim.x) {
         const int r = e / HD, d = e - r * HD;
-        Qs[r * ldq + d] = r < nq ? to_f32(q[(long long)(s0 + q0 + r) * ld + (long long)hq * HD + d]) : 0.f;
+        Qs[r * ldq + d] = r < nq ? to_f32(q[(long long)(s0 + q0 - p0 + r) * ld + (long long)hq * HD + d]) : 0.f;
     }
     float m[8], l[8], acc[8][AP_MAXJ];
 #pragma unroll
@@ -315,16 +327,31 @@ attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict
         for (int j = 0; j < AP_MAXJ; ++j) acc[i][j] = 0.f;
     }
     const int q_last = q0 + nq - 1;
-    int k_begin = 0;
-    if (window > 0) k_begin = max(0, q0 - window + 1) / AP_BK * AP_BK;
+    const int k_first = window > 0 ? max(0, q0 - window + 1) : 0;    // the first key any query of the block sees
+    const int k_begin = k_first / AP_BK * AP_BK;
     const int nj = (HD + 31) / 32;
 
     for (int k0 = k_begin; k0 <= q_last; k0 += AP_BK) {
         __syncthreads();
         for (int e = threadIdx.x; e < AP_BK * HD; e += blockDim.x) {
             const int r = e / HD, d = e - r * HD;
-            const bool in = k0 + r < len;
-            const long long row = (long long)(s0 + k0 + r) * ld + (long long)hk * HD + d;
+            const int kp = k0 + r;
+            if (PAST && kp < p0) {
+                const bool in = kp >= k_first;
+                float kv0 = 0.f, kv1 = 0.f;
+                if (in) {
+                    const int entry = ring ? kp % ring : kp;
+                    const long long off = (long long)(entry % PAGE_TOKENS) * HD + d;
+                    const int page = prow[entry / PAGE_TOKENS];
+                    kv0 = to_f32(kv_tile(pool, 0, pages, page, hk, KVH, HD)[off]);
+                    kv1 = to_f32(kv_tile(pool, 1, pages, page, hk, KVH, HD)[off]);
+                }
+                Ks[r * ldq + d] = kv0;
+                Vs[r * HD + d] = kv1;
+                continue;
+            }
+            const bool in = kp < len;
+            const long long row = (long long)(s0 + kp - p0) * ld + (long long)hk * HD + d;
             Ks[r * ldq + d] = in ? to_f32(k[row]) : 0.f;
             Vs[r * HD + d] = in ? to_f32(v[row]) : 0.f;
         }
@@ -370,7 +397,7 @@ attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict
     for (int i = 0; i < 8; ++i) {
         const int qi = warp * 8 + i;
         if (qi >= nq) continue;
-        const long long t = s0 + q0 + qi;
+        const long long t = s0 + q0 - p0 + qi;
         float g = 1.f;
         if (gate) g = sigmoid_f32(to_f32(gate[t * ldg + hq]));
         const float inv = 1.f / l[i];
@@ -382,6 +409,21 @@ attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict
     }
 }
 
+template <typename T, bool PAST>
+static int launch_attn_simt(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
+                            const void* gate, long long ldg, const int* seq_start, int B, int max_len, int QH, int KVH,
+                            int HD, int window, float scale, const int* seq_pos0, const int* seq_slot, const void* pool,
+                            long long pages, const int* ptab, int ptab_stride, int ring, cudaStream_t st) {
+    const size_t smem = ((size_t)(AP_BQ + AP_BK) * (HD + 1) + (size_t)AP_BK * HD + AP_BQ * (AP_BK + 1)) * sizeof(float);
+    dim3 grid((max_len + AP_BQ - 1) / AP_BQ, QH, B);
+    cudaFuncSetAttribute(attn_prefill_simt_kernel<T, PAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cm_launch(attn_prefill_simt_kernel<T, PAST>, grid, 128, smem, st, (T*)ctx, ldc, (const T*)q, (const T*)k, (const T*)v,
+              ld, (const T*)gate, ldg, seq_start, QH, KVH, HD, window, scale, seq_pos0, seq_slot, (const T*)pool, pages,
+              ptab, ptab_stride, ring);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
 extern "C" int cm_attn_prefill_simt(int dt, void* ctx, long long ldc, const void* q, const void* k,
                                     const void* v, long long ld, const void* gate, long long ldg,
                                     const int* seq_start, int B, int max_len, int QH, int KVH, int HD,
@@ -389,19 +431,73 @@ extern "C" int cm_attn_prefill_simt(int dt, void* ctx, long long ldc, const void
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (HD > 32 * AP_MAXJ) CM_REFUSE("attn_prefill: head size %d above %d", HD, 32 * AP_MAXJ);
     if (QH % KVH) CM_REFUSE("attn_prefill: %d query heads over %d key heads", QH, KVH);
-    const size_t smem = ((size_t)(AP_BQ + AP_BK) * (HD + 1) + (size_t)AP_BK * HD + AP_BQ * (AP_BK + 1)) * sizeof(float);
-    dim3 grid((max_len + AP_BQ - 1) / AP_BQ, QH, B);
-    if (dt == DT_F32) {
-        cudaFuncSetAttribute(attn_prefill_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cm_launch(attn_prefill_simt_kernel<float>, grid, 128, smem, st, (float*)ctx, ldc, (const float*)q, (const float*)k,
-                                                                 (const float*)v, ld, (const float*)gate, ldg,
-                                                                 seq_start, QH, KVH, HD, window, scale);
-    } else if (dt == DT_BF16) {
-        cudaFuncSetAttribute(attn_prefill_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cm_launch(attn_prefill_simt_kernel<bf16>, grid, 128, smem, st, (bf16*)ctx, ldc, (const bf16*)q, (const bf16*)k,
-                                                                (const bf16*)v, ld, (const bf16*)gate, ldg,
-                                                                seq_start, QH, KVH, HD, window, scale);
-    } else
+    if (dt == DT_F32)
+        return launch_attn_simt<float, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
+                                              scale, nullptr, nullptr, nullptr, 0, nullptr, 0, 0, st);
+    if (dt == DT_BF16)
+        return launch_attn_simt<bf16, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
+                                             scale, nullptr, nullptr, nullptr, 0, nullptr, 0, 0, st);
+    return CM_ERR_DTYPE;
+}
+
+// The same for sequences that stand at seq_pos0[b] >= 0: keys and values below that position come
+// from the paged cache of this layer (pool [2][pages][KVH][PAGE_TOKENS][HD], page table row of
+// seq_slot[b]), the rest from the step's rows.  max_len: the most new tokens of a sequence.
+extern "C" int cm_attn_append_simt(int dt, void* ctx, long long ldc, const void* q, const void* k,
+                                   const void* v, long long ld, const void* gate, long long ldg,
+                                   const int* seq_start, const int* seq_pos0, const int* seq_slot, const void* pool,
+                                   long long pages, const int* ptab, long long ptab_stride, int ring, int B,
+                                   int max_len, int QH, int KVH, int HD, int window, float scale, cudaStream_t st) {
+    if (B <= 0 || max_len <= 0) return CM_OK;
+    if (HD > 32 * AP_MAXJ) CM_REFUSE("attn_append: head size %d above %d", HD, 32 * AP_MAXJ);
+    if (QH % KVH) CM_REFUSE("attn_append: %d query heads over %d key heads", QH, KVH);
+    if (ring % PAGE_TOKENS) CM_REFUSE("attn_append: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
+    if (!seq_pos0 || !seq_slot || !pool || !ptab) CM_REFUSE("attn_append: positions, slots, cache and page table are needed");
+    if (dt == DT_F32)
+        return launch_attn_simt<float, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
+                                             scale, seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, st);
+    if (dt == DT_BF16)
+        return launch_attn_simt<bf16, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
+                                            scale, seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, st);
+    return CM_ERR_DTYPE;
+}
+
+// Keys (already normed and rotated) and values of the step's tokens into the paged cache: what
+// cm_qk_prepare does with a pool, as a step of its own for steps whose attention must still read
+// the entries that these rows replace.  kv: the k | v columns of the packed rows (k at column 0,
+// v at column KVH * HD), row pitch ld.  A ring keeps only the last `ring` positions of a sequence.
+template <typename T>
+__global__ void kv_store_kernel(const T* __restrict__ kv, long long ld, const int* __restrict__ tok_pos,
+                                const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                                const int* __restrict__ seq_end, T* __restrict__ pool, long long pages,
+                                const int* __restrict__ ptab, int ptab_stride, int ring, int KVH, int HD) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, b = tok_seq[t], pos = tok_pos[t];
+    if (ring && pos + ring < seq_end[b]) return;
+    const int entry = ring ? pos % ring : pos;
+    const int page = ptab[(long long)seq_slot[b] * ptab_stride + entry / PAGE_TOKENS];
+    const int row = entry % PAGE_TOKENS;
+    const int width = KVH * HD;
+    for (int e = threadIdx.x; e < 2 * width; e += blockDim.x) {
+        const int plane = e / width, c = e - plane * width, kvh = c / HD, d = c - kvh * HD;
+        kv_tile(pool, plane, pages, page, kvh, KVH, HD)[(long long)row * HD + d] = kv[(long long)t * ld + e];
+    }
+}
+
+extern "C" int cm_kv_store(int dt, const void* kv, long long ld, const int* tok_pos, const int* tok_seq,
+                           const int* seq_slot, const int* seq_end, void* pool, long long pages, const int* ptab,
+                           long long ptab_stride, int ring, int T, int KVH, int HD, cudaStream_t st) {
+    if (T <= 0) return CM_OK;
+    if (ring % PAGE_TOKENS) CM_REFUSE("kv_store: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
+    const int threads = 2 * KVH * HD >= 256 ? 256 : 128;
+    if (dt == DT_F32)
+        cm_launch(kv_store_kernel<float>, T, threads, 0, st, (const float*)kv, ld, tok_pos, tok_seq, seq_slot, seq_end,
+                  (float*)pool, pages, ptab, (int)ptab_stride, ring, KVH, HD);
+    else if (dt == DT_BF16)
+        cm_launch(kv_store_kernel<bf16>, T, threads, 0, st, (const bf16*)kv, ld, tok_pos, tok_seq, seq_slot, seq_end,
+                  (bf16*)pool, pages, ptab, (int)ptab_stride, ring, KVH, HD);
+    else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
     return CM_OK;
@@ -418,7 +514,7 @@ extern "C" int cm_attn_prefill_simt(int dt, void* ctx, long long ldc, const void
 //   growing group: entry e holds position e;          entries 0..pos
 //   ring group:    entry e holds the latest position <= pos that is congruent to e (mod ring)
 // =========================================================================================
-#define AD_CHUNK 256
+#define AD_CHUNK CM_ATTN_DECODE_CHUNK
 #define AD_THREADS 128
 
 // AD_GB: query heads of a kv head that one pass handles (1, 2, 4 or 8; more heads take more passes)
@@ -682,7 +778,8 @@ extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, l
                               int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
                               float scale, float* part_o, float* part_ml, cudaStream_t st) {
     if (B <= 0) return CM_OK;
-    if (HD % 8 || HD < 8 || HD > 256) CM_REFUSE("attn_decode: head size %d (multiples of 8 up to 256)", HD);
+    if (HD % 8 || HD < 8 || HD > CM_MAX_HEAD_DIM)
+        CM_REFUSE("attn_decode: head size %d (multiples of 8 up to %d)", HD, CM_MAX_HEAD_DIM);
     if (QH % KVH) CM_REFUSE("attn_decode: %d query heads over %d key heads", QH, KVH);
     if (ring % PAGE_TOKENS) CM_REFUSE("attn_decode: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
     if (n_chunks <= 0) CM_REFUSE("attn_decode: %d chunks", n_chunks);

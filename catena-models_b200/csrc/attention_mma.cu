@@ -8,6 +8,12 @@
 // mma.sync.m16n8k16 with float accumulation; the score accumulators are re-used as the
 // probability operand of the second product.  Maximum, sum, rescaling and the final division
 // are float; exp is taken as exp2 of log2(e)-prescaled scores.
+//
+// PAST: sequences may stand at a position p0 > 0 (several tokens on top of a started sequence).
+// Key tiles are then cut at multiples of 64 absolute positions, which are the cache's pages: a
+// row below p0 comes from the sequence's page of the cache (entry = position, or position % ring),
+// a row from p0 on from the step's own rows, which reach the cache only after this kernel.  Rows
+// that no query of the block can see are not read (zero-filled).
 #include "common.cuh"
 #include <math.h>
 
@@ -50,12 +56,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int HD, int BQ>
+template <int HD, int BQ, bool PAST>
 __global__ void __launch_bounds__(BQ * 2, HD <= 64 ? 512 / (BQ * 2) : 256 / (BQ * 2))
 attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __restrict__ q,
                         const bf16* __restrict__ k, const bf16* __restrict__ v, long long ld,
                         const bf16* __restrict__ gate, long long ldg, const int* __restrict__ seq_start, int QH,
-                        int KVH, int window, float scale_log2) {
+                        int KVH, int window, float scale_log2, const int* __restrict__ seq_pos0,
+                        const int* __restrict__ seq_slot, const bf16* __restrict__ pool, long long pages,
+                        const int* __restrict__ ptab, int ptab_stride, int ring) {
     constexpr int LDS = HD + 8;                   // padded row, elements
     constexpr int CH = HD / 8;                    // 16-byte chunks per row
     extern __shared__ __align__(16) uint8_t fa_smem[];
@@ -64,14 +72,18 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
     bf16* Vs = Ks + 2 * FA_BK * LDS;                          // [2][FA_BK][LDS]
     pdl_wait();
     const int b = blockIdx.z, hq = blockIdx.y, hk = hq / (QH / KVH);
-    const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
+    const int s0 = seq_start[b], n_new = seq_start[b + 1] - s0;
+    const int p0 = PAST ? seq_pos0[b] : 0;                 // position of the sequence's first row of this step
+    const int len = p0 + n_new;                            // positions are absolute from here on
     constexpr int THREADS = BQ * 2;
-    const int q0 = (gridDim.x - 1 - blockIdx.x) * BQ;      // long rows first
+    const int q0 = p0 + (gridDim.x - 1 - blockIdx.x) * BQ; // long rows first
     if (q0 >= len) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
 
-    const int kt_begin = window > 0 ? max(0, q0 - window + 1) / FA_BK : 0;
+    const int k_first = window > 0 ? max(0, q0 - window + 1) : 0;   // the first key a query of this block sees
+    const int kt_begin = k_first / FA_BK;
     const int kt_end = min(q0 + BQ - 1, len - 1) / FA_BK;  // inclusive
+    const int* prow = PAST ? ptab + (long long)seq_slot[b] * ptab_stride : nullptr;
 
     // a thread's share of a 64-row tile: chunks e = tid, tid + 128, ...; row and column of each
     // are the same for every tile, so they are worked out once
@@ -83,20 +95,47 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
         l_row[u] = e < FA_BK * CH ? e / CH : -1;
         l_off[u] = (e % CH) * 8;
     }
+    // rows row0 .. row0 + 63 (absolute positions) of the step's own q, k or v
     auto load_tile = [&](bf16* dst, const bf16* src, int row0) {
 #pragma unroll
         for (int u = 0; u < PER; ++u) {
             if (l_row[u] < 0) continue;
-            const bool in = row0 + l_row[u] < len;
-            const long long row = (long long)(s0 + (in ? row0 + l_row[u] : 0));
+            const int pos = row0 + l_row[u];
+            const bool in = pos < len && pos >= p0;
+            const long long row = (long long)(s0 + (in ? pos - p0 : 0));
             cp_async16(dst + l_row[u] * LDS + l_off[u], src + row * ld + l_off[u], in);
+        }
+    };
+    // the same for keys (plane 0) or values (plane 1), rows below p0 from the cache
+    auto load_kv = [&](bf16* dst, const bf16* src, int plane, int row0) {
+        if (!PAST || row0 >= p0) {
+            load_tile(dst, src, row0);
+            return;
+        }
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            if (l_row[u] < 0) continue;
+            const int pos = row0 + l_row[u];
+            const bf16* from = src;
+            bool in = pos < len;
+            if (pos >= p0) {
+                from = src + (long long)(s0 + (in ? pos - p0 : 0)) * ld + l_off[u];
+            } else {
+                in = pos >= k_first;
+                if (in) {
+                    const int entry = ring ? pos % ring : pos;
+                    from = kv_tile(pool, plane, pages, prow[entry / PAGE_TOKENS], hk, KVH, HD) +
+                           (long long)(entry % PAGE_TOKENS) * HD + l_off[u];
+                }
+            }
+            cp_async16(dst + l_row[u] * LDS + l_off[u], from, in);
         }
     };
     load_tile(Qs, q + (long long)hq * HD, q0);
     if (BQ > FA_BK) load_tile(Qs + FA_BK * LDS, q + (long long)hq * HD, q0 + FA_BK);
     cp_async_commit();
-    load_tile(Ks, k + (long long)hk * HD, kt_begin * FA_BK);
-    load_tile(Vs, v + (long long)hk * HD, kt_begin * FA_BK);
+    load_kv(Ks, k + (long long)hk * HD, 0, kt_begin * FA_BK);
+    load_kv(Vs, v + (long long)hk * HD, 1, kt_begin * FA_BK);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -118,8 +157,8 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
     for (int kt = kt_begin; kt <= kt_end; ++kt) {
         const int buf = (kt - kt_begin) & 1;
         if (kt + 1 <= kt_end) {
-            load_tile(Ks + (buf ^ 1) * FA_BK * LDS, k + (long long)hk * HD, (kt + 1) * FA_BK);
-            load_tile(Vs + (buf ^ 1) * FA_BK * LDS, v + (long long)hk * HD, (kt + 1) * FA_BK);
+            load_kv(Ks + (buf ^ 1) * FA_BK * LDS, k + (long long)hk * HD, 0, (kt + 1) * FA_BK);
+            load_kv(Vs + (buf ^ 1) * FA_BK * LDS, v + (long long)hk * HD, 1, (kt + 1) * FA_BK);
         }
         cp_async_commit();
         cp_async_wait<1>();
@@ -226,7 +265,7 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
     for (int h = 0; h < 2; ++h) {
         const int row = row_lo + 8 * h;
         if (row >= len) continue;
-        const long long tok = s0 + row;
+        const long long tok = s0 + row - p0;
         float f = 1.f / l_run[h];
         if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + hq]));
         bf16* dst = ctx + tok * ldc + (long long)hq * HD;
@@ -236,12 +275,22 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
     }
 }
 
-template <int HD, int BQ>
+struct FaPast {                      // where the keys and values below a sequence's first row of this step lie
+    const int* seq_pos0;
+    const int* seq_slot;
+    const void* pool;
+    long long pages;
+    const int* ptab;
+    int ptab_stride;
+    int ring;
+};
+
+template <int HD, int BQ, bool PAST>
 static int launch_fa_bq(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
-                     const void* gate, long long ldg, const int* seq_start, int B, int max_len, int QH, int KVH,
-                     int window, float scale, cudaStream_t st) {
+                        const void* gate, long long ldg, const int* seq_start, int B, int max_len, int QH, int KVH,
+                        int window, float scale, const FaPast& past, cudaStream_t st) {
     const size_t smem = (size_t)(BQ + 4 * FA_BK) * (HD + 8) * sizeof(bf16);
-    auto kernel = attn_prefill_mma_kernel<HD, BQ>;
+    auto kernel = attn_prefill_mma_kernel<HD, BQ, PAST>;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -252,7 +301,8 @@ static int launch_fa_bq(void* ctx, long long ldc, const void* q, const void* k, 
     }
     dim3 grid((max_len + BQ - 1) / BQ, QH, B);
     cm_launch(kernel, grid, BQ * 2, smem, st, (bf16*)ctx, ldc, (const bf16*)q, (const bf16*)k, (const bf16*)v, ld,
-              (const bf16*)gate, ldg, seq_start, QH, KVH, window, scale * 1.4426950408889634f);
+              (const bf16*)gate, ldg, seq_start, QH, KVH, window, scale * 1.4426950408889634f, past.seq_pos0,
+              past.seq_slot, (const bf16*)past.pool, past.pages, past.ptab, past.ptab_stride, past.ring);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -263,14 +313,32 @@ static int launch_fa_bq(void* ctx, long long ldc, const void* q, const void* k, 
 static int g_fa_bq = 0;                       // 0: by length; 64 or 128: forced (experiments)
 extern "C" void cm_attn_prefill_set_tile(int bq) { g_fa_bq = bq; }
 
-template <int HD>
+template <int HD, bool PAST>
 static int launch_fa(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
                      const void* gate, long long ldg, const int* seq_start, int B, int max_len, int QH, int KVH,
-                     int window, float scale, cudaStream_t st) {
+                     int window, float scale, const FaPast& past, cudaStream_t st) {
     const int bq = g_fa_bq ? g_fa_bq : (max_len >= 4096 ? 128 : 64);
     if (bq == 128)
-        return launch_fa_bq<HD, 128>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, window, scale, st);
-    return launch_fa_bq<HD, 64>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, window, scale, st);
+        return launch_fa_bq<HD, 128, PAST>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, window, scale,
+                                           past, st);
+    return launch_fa_bq<HD, 64, PAST>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, window, scale, past,
+                                      st);
+}
+
+template <bool PAST>
+static int dispatch_fa(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
+                       const void* gate, long long ldg, const int* seq_start, int B, int max_len, int QH, int KVH, int HD,
+                       int window, float scale, const FaPast& past, cudaStream_t st) {
+    if (QH % KVH) CM_REFUSE("attn_prefill_mma: %d query heads over %d key heads", QH, KVH);
+    if (ld % 8 || ldc % 2 || ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)past.pool) & 15 || (uintptr_t)ctx & 3)
+        CM_REFUSE("attn_prefill_mma: row pitch %lld must be a multiple of 8 and the operands 16-byte aligned", ld);
+#define FA_CASE(D) \
+    case D: return launch_fa<D, PAST>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, window, scale, past, st);
+    switch (HD) {
+        FA_CASE(16) FA_CASE(32) FA_CASE(48) FA_CASE(64) FA_CASE(80) FA_CASE(96) FA_CASE(112) FA_CASE(128)
+        default: CM_REFUSE("attn_prefill_mma: head size %d (multiples of 16 up to 128)", HD);
+    }
+#undef FA_CASE
 }
 
 // bfloat16 only; head size a multiple of 16 up to 128; q, k, v column blocks of one row-major
@@ -279,16 +347,23 @@ extern "C" int cm_attn_prefill_mma(void* ctx, long long ldc, const void* q, cons
                                    long long ld, const void* gate, long long ldg, const int* seq_start, int B,
                                    int max_len, int QH, int KVH, int HD, int window, float scale, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
-    if (QH % KVH) CM_REFUSE("attn_prefill_mma: %d query heads over %d key heads", QH, KVH);
-    if (ld % 8 || ldc % 2 || ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15 || (uintptr_t)ctx & 3)
-        CM_REFUSE("attn_prefill_mma: row pitch %lld must be a multiple of 8 and the operands 16-byte aligned", ld);
-#define FA_CASE(D) \
-    case D: return launch_fa<D>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, window, scale, st);
-    switch (HD) {
-        FA_CASE(16) FA_CASE(32) FA_CASE(48) FA_CASE(64) FA_CASE(80) FA_CASE(96) FA_CASE(112) FA_CASE(128)
-        default: CM_REFUSE("attn_prefill_mma: head size %d (multiples of 16 up to 128)", HD);
-    }
-#undef FA_CASE
+    const FaPast none = {nullptr, nullptr, nullptr, 0, nullptr, 0, 0};
+    return dispatch_fa<false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window, scale, none, st);
+}
+
+// The same for sequences that stand at seq_pos0[b] >= 0, with the keys and values below that
+// position read from this layer's paged cache (see the top of the file).
+extern "C" int cm_attn_append_mma(void* ctx, long long ldc, const void* q, const void* k, const void* v,
+                                  long long ld, const void* gate, long long ldg, const int* seq_start,
+                                  const int* seq_pos0, const int* seq_slot, const void* pool, long long pages,
+                                  const int* ptab, long long ptab_stride, int ring, int B, int max_len, int QH, int KVH,
+                                  int HD, int window, float scale, cudaStream_t st) {
+    if (B <= 0 || max_len <= 0) return CM_OK;
+    if (ring % PAGE_TOKENS) CM_REFUSE("attn_append_mma: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
+    if (!seq_pos0 || !seq_slot || !pool || !ptab)
+        CM_REFUSE("attn_append_mma: positions, slots, cache and page table are needed");
+    const FaPast past = {seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring};
+    return dispatch_fa<true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window, scale, past, st);
 }
 
 // =========================================================================================
@@ -309,7 +384,7 @@ extern "C" int cm_attn_prefill_mma(void* ctx, long long ldc, const void* q, cons
 // goes to the scratch layout that the CUDA-core kernel uses, n_parts slots per (sequence, head);
 // cm_attn_decode's merge kernel finishes the job.
 // =========================================================================================
-#define FD_CHUNK 256
+#define FD_CHUNK CM_ATTN_DECODE_CHUNK
 #define FD_PAGE 64
 
 template <int HD>

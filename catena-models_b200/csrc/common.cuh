@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "cm_limits.h"
+
 #define DT_F32 0
 #define DT_BF16 1
 
@@ -191,7 +193,7 @@ __device__ __forceinline__ void store8f<bf16>(bf16* p, const float* v) {
 
 // Page-table geometry shared by the cache kernels: a page holds PAGE_TOKENS consecutive
 // cache entries of one sequence for every layer of a group.
-#define PAGE_TOKENS 64
+#define PAGE_TOKENS CM_PAGE_TOKENS
 
 // Storage of one layer group: [layer][k|v][page][kv_head][PAGE_TOKENS][head_dim].
 template <typename T>

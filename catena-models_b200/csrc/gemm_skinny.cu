@@ -218,8 +218,9 @@ static int dispatch_skinny(void* Y, const void* X, const void* W, int M, int N, 
     if (M <= 8) return launch_skinny<1, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
     if (M <= 16) return launch_skinny<2, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
     if (M <= 32) return launch_skinny<4, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
-    if (M <= 64) return launch_skinny<8, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
-    CM_REFUSE("gemm_skinny: %d rows (at most 64)", M);
+    static_assert(CM_SKINNY_MAX_ROWS == 64, "cm_limits.h: CM_SKINNY_MAX_ROWS");
+    if (M <= CM_SKINNY_MAX_ROWS) return launch_skinny<8, TY, MODE>(Y, X, W, M, N, K, ldx, ldw, ldy, st);
+    CM_REFUSE("gemm_skinny: %d rows (at most %d)", M, CM_SKINNY_MAX_ROWS);
 }
 
 // P[s][m][n] = sum over the s-th of `ksplit` slices of K of X[m,k] W[n,k], float: the product with its
@@ -335,7 +336,7 @@ extern "C" int cm_gemm_skinny_shortconv(void* Y, const void* X, const void* W, c
                                         long long ldw, long long ldy, cudaStream_t st) {
     if (M <= 0 || H <= 0) return CM_OK;
     if (M > 16) CM_REFUSE("gemm_skinny_shortconv: %d rows (at most 16)", M);
-    if (KT < 2 || KT > 16) CM_REFUSE("gemm_skinny_shortconv: %d taps (2..16)", KT);
+    if (KT < 2 || KT > CM_MAX_CONV_TAPS) CM_REFUSE("gemm_skinny_shortconv: %d taps (2..%d)", KT, CM_MAX_CONV_TAPS);
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8)
         CM_REFUSE("gemm_skinny_shortconv: inner size %d and row strides %lld, %lld must be multiples of 8", K, ldx, ldw);
     if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W)) & 15)

@@ -29,6 +29,7 @@
 #include <cooperative_groups.h>
 
 #define TC_BM 128
+static_assert(TC_BM == CM_FEW_ROWS_MAX_ROWS, "cm_limits.h: CM_FEW_ROWS_MAX_ROWS");
 #define TC_THREADS 192
 #define TCP_THREADS 320          // the persistent kernel: loader, issuer, two groups of four epilogue warps
 #define TC_MODE_PLAIN 0

@@ -6,8 +6,10 @@
 // out[t,:] = table[tokens[t],:].  A token id outside [0,V) writes zeros and raises *err.
 // With `sampled` given, a negative entry -(1 + i) stands for sampled[i]: the token that the step
 // before this one chose on the device for its i-th sequence, which the host has not seen yet.
-template <typename T>
-__global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ table,
+// The table may be stored in another type than the activations (a checkpoint that keeps it in
+// 32-bit under a bfloat16 engine): the row is converted as it is read.
+template <typename T, typename TT>
+__global__ void embed_gather_kernel(T* __restrict__ out, const TT* __restrict__ table,
                                     const int* __restrict__ tokens, const int* __restrict__ sampled, int H, int V,
                                     int* __restrict__ err) {
     pdl_trigger();
@@ -17,19 +19,23 @@ __global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ t
     if (tok < 0 && sampled) tok = sampled[-tok - 1];
     const bool ok = tok >= 0 && tok < V;
     if (!ok && threadIdx.x == 0 && err) atomicExch(err, 1);
-    const T* src = table + (long long)(ok ? tok : 0) * H;
+    const TT* src = table + (long long)(ok ? tok : 0) * H;
     T* dst = out + (long long)t * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = ok ? src[c] : from_f32<T>(0.f);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = from_f32<T>(ok ? to_f32(src[c]) : 0.f);
 }
 
-extern "C" int cm_embed_gather(int dt, void* out, const void* table, const int* tokens, const int* sampled, int T,
-                               int H, int V, int* err, cudaStream_t st) {
+extern "C" int cm_embed_gather(int dt, int dt_table, void* out, const void* table, const int* tokens,
+                               const int* sampled, int T, int H, int V, int* err, cudaStream_t st) {
     if (T <= 0) return CM_OK;
     const int threads = H >= 1024 ? 256 : 128;
-    if (dt == DT_F32)
-        cm_launch(embed_gather_kernel<float>, T, threads, 0, st, (float*)out, (const float*)table, tokens, sampled, H, V, err);
-    else if (dt == DT_BF16)
-        cm_launch(embed_gather_kernel<bf16>, T, threads, 0, st, (bf16*)out, (const bf16*)table, tokens, sampled, H, V, err);
+    if (dt == DT_F32 && dt_table == DT_F32)
+        cm_launch(embed_gather_kernel<float, float>, T, threads, 0, st, (float*)out, (const float*)table, tokens, sampled, H, V, err);
+    else if (dt == DT_BF16 && dt_table == DT_BF16)
+        cm_launch(embed_gather_kernel<bf16, bf16>, T, threads, 0, st, (bf16*)out, (const bf16*)table, tokens, sampled, H, V, err);
+    else if (dt == DT_BF16 && dt_table == DT_F32)
+        cm_launch(embed_gather_kernel<bf16, float>, T, threads, 0, st, (bf16*)out, (const float*)table, tokens, sampled, H, V, err);
+    else if (dt == DT_F32 && dt_table == DT_BF16)
+        cm_launch(embed_gather_kernel<float, bf16>, T, threads, 0, st, (float*)out, (const bf16*)table, tokens, sampled, H, V, err);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
@@ -42,6 +48,7 @@ extern "C" int cm_embed_gather(int dt, void* out, const void* table, const int* 
 // issued before the first reduction.  H must be a multiple of 8 and at most 8 * 256 * NV_MAXC.
 #define NV_THREADS 256
 #define NV_MAXC 4
+static_assert(8 * NV_THREADS * NV_MAXC == CM_NORM_MAX_WIDTH, "cm_limits.h: CM_NORM_MAX_WIDTH");
 
 // -------------------------------------------------------------------------- RMSNorm
 // y = T((x * inv) * w), inv = 1/sqrt(mean(x^2) + eps); w is float.

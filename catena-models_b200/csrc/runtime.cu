@@ -2,6 +2,7 @@
 #include "common.cuh"
 #include <stdarg.h>
 #include <stdio.h>
+#include <string.h>
 
 static thread_local char g_last_error[512] = "";
 
@@ -14,7 +15,21 @@ void cm_set_error(const char* fmt, ...) {
 
 extern "C" const char* cm_last_error() { return g_last_error; }
 
-extern "C" int cm_abi_version() { return 2; }
+extern "C" int cm_abi_version() { return 3; }
+
+// The compiled value of a limit of cm_limits.h by its name without the CM_ prefix; -1 if unknown.
+extern "C" long long cm_limit(const char* name) {
+    struct Entry { const char* name; long long value; };
+    static const Entry table[] = {
+        {"PAGE_TOKENS", CM_PAGE_TOKENS},       {"ATTN_DECODE_CHUNK", CM_ATTN_DECODE_CHUNK},
+        {"NORM_MAX_WIDTH", CM_NORM_MAX_WIDTH}, {"MAX_HEAD_DIM", CM_MAX_HEAD_DIM},
+        {"MAX_CONV_TAPS", CM_MAX_CONV_TAPS},   {"SKINNY_MAX_ROWS", CM_SKINNY_MAX_ROWS},
+        {"FEW_ROWS_MAX_ROWS", CM_FEW_ROWS_MAX_ROWS},
+    };
+    for (const Entry& e : table)
+        if (strcmp(e.name, name) == 0) return e.value;
+    return -1;
+}
 
 static int g_pdl = 1;
 int cm_pdl_enabled() { return g_pdl; }
@@ -42,18 +57,35 @@ extern "C" int cm_scatter_i32(int* table, const int* index, const int* value, co
     return CM_OK;
 }
 
-// x[rows[i], :] = 0 for float rows of `width` elements (fixed-size state of admitted slots).
-__global__ void zero_rows_kernel(float* __restrict__ x, const int* __restrict__ rows, long long width) {
+// Clears the fixed-size state of newly admitted slots: x is [layers][slots][row_words] 32-bit
+// words, and row slot_ids[i] of every layer is set to zero.  The slot ids travel as a kernel
+// argument (up to ZS_MAX per launch), so admitting sequences costs no copy to the device.
+#define ZS_MAX 64
+struct ZeroSlots {
+    int id[ZS_MAX];
+};
+
+__global__ void zero_slots_kernel(uint32_t* __restrict__ x, long long slots, long long row_words, ZeroSlots ids) {
     pdl_trigger();
     pdl_wait();
-    float* dst = x + (long long)rows[blockIdx.x] * width;
-    for (long long c = threadIdx.x; c < width; c += blockDim.x) dst[c] = 0.f;
+    uint32_t* dst = x + ((long long)blockIdx.y * slots + ids.id[blockIdx.x]) * row_words;
+    for (long long c = threadIdx.x; c < row_words; c += blockDim.x) dst[c] = 0u;
 }
 
-extern "C" int cm_zero_rows_f32(float* x, const int* rows, int n, long long width, cudaStream_t st) {
-    if (n <= 0 || width <= 0) return CM_OK;
-    cm_launch(zero_rows_kernel, n, 256, 0, st, x, rows, width);
-    CM_CHECK_LAUNCH();
+extern "C" int cm_zero_slots(void* x, int layers, long long slots, long long row_bytes, const int* slot_ids, int n,
+                             cudaStream_t st) {
+    if (n <= 0 || layers <= 0 || row_bytes <= 0) return CM_OK;
+    if (row_bytes % 4 || (reinterpret_cast<uintptr_t>(x) & 3)) CM_REFUSE("zero_slots: rows of %lld bytes (multiples of 4)", row_bytes);
+    if (layers > 65535) CM_REFUSE("zero_slots: %d layers", layers);
+    for (int i = 0; i < n; ++i)
+        if (slot_ids[i] < 0 || slot_ids[i] >= slots) CM_REFUSE("zero_slots: slot %d of %lld", slot_ids[i], slots);
+    for (int first = 0; first < n; first += ZS_MAX) {
+        ZeroSlots ids;
+        const int count = n - first < ZS_MAX ? n - first : ZS_MAX;
+        for (int i = 0; i < count; ++i) ids.id[i] = slot_ids[first + i];
+        cm_launch(zero_slots_kernel, dim3(count, layers), 256, 0, st, (uint32_t*)x, slots, row_bytes / 4, ids);
+        CM_CHECK_LAUNCH();
+    }
     return CM_OK;
 }
 

@@ -6,15 +6,20 @@
 // One thread per (token, channel).  A prompt step starts every sequence from an empty state
 // (from_zero = 1: the stored state is not read, so a slot that is used again needs no
 // clearing); a decode step has one token per sequence and shifts the state in place.
+// A step that brings several tokens on top of a stored state (seq_pos0[b] > 0) runs in two
+// launches, because the first tokens of a sequence read the state that its last token replaces:
+// phase 1 writes the outputs only, phase 2 the state only.  With seq_pos0 given, a sequence whose
+// first position is 0 starts from an empty state whatever from_zero says.
 #include "common.cuh"
 
-#define SC_MAXK 16
+#define SC_MAXK CM_MAX_CONV_TAPS
 
 template <typename T>
 __global__ void shortconv_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld,
                                  const float* __restrict__ w, float* __restrict__ state,
                                  const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
-                                 const int* __restrict__ seq_slot, int H, int K, int from_zero) {
+                                 const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0, int H, int K,
+                                 int from_zero, int phase) {
     pdl_trigger();
     pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -23,6 +28,8 @@ __global__ void shortconv_kernel(T* __restrict__ y, const T* __restrict__ bcx, l
     const int b = tok_seq[t];
     const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
     const int i = t - s0;
+    if (phase == 2 && i != len - 1) return;
+    if (seq_pos0 && seq_pos0[b] == 0) from_zero = 1;
     float* st = state + (long long)seq_slot[b] * (K - 1) * H + c;     // [K-1] entries, stride H
     const float* wc = w + (long long)c * K;
 
@@ -40,10 +47,12 @@ __global__ void shortconv_kernel(T* __restrict__ y, const T* __restrict__ bcx, l
         }
         z += wc[j] * sv;
     }
-    const float cc = to_f32(bcx[(long long)t * ld + H + c]);
-    y[(long long)t * H + c] = from_f32<T>(z * cc);
+    if (phase != 2) {
+        const float cc = to_f32(bcx[(long long)t * ld + H + c]);
+        y[(long long)t * H + c] = from_f32<T>(z * cc);
+    }
 
-    if (i == len - 1) {
+    if (i == len - 1 && phase != 1) {
         // new state entry j = s[len + j]; s index below K-1 is an old state entry
         for (int j = 0; j < K - 1; ++j) {
             const int r = len + j - (K - 1);
@@ -68,7 +77,8 @@ template <typename T, int KT>
 __global__ void __launch_bounds__(128)
 shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld, const float* __restrict__ w,
                      const float* __restrict__ w_t, float* __restrict__ state, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
-                     const int* __restrict__ seq_slot, int T_tokens, int H, int K_any, int from_zero) {
+                     const int* __restrict__ seq_slot, const int* __restrict__ seq_pos0, int T_tokens, int H, int K_any,
+                     int from_zero, int phase) {
     pdl_trigger();
     pdl_wait();
     // threadIdx.y walks consecutive tokens: the rows a token shares with its neighbours (K - 1 of
@@ -80,6 +90,8 @@ shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld,
     const int b = tok_seq[t];
     const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
     const int i = t - s0;
+    if (phase == 2 && i != len - 1) return;
+    if (seq_pos0 && seq_pos0[b] == 0) from_zero = 1;
     float* st = state + (long long)seq_slot[b] * (K - 1) * H + c;
     float z[8], cur[8];
 #pragma unroll
@@ -114,13 +126,15 @@ shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld,
             if (j == K - 1) cur[e] = sv[e];
         }
     }
-    float cc[8], out[8];
-    load8f<T>(bcx + (long long)t * ld + H + c, cc);
+    if (phase != 2) {
+        float cc[8], out[8];
+        load8f<T>(bcx + (long long)t * ld + H + c, cc);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) out[e] = z[e] * cc[e];
-    store8f<T>(y + (long long)t * H + c, out);
+        for (int e = 0; e < 8; ++e) out[e] = z[e] * cc[e];
+        store8f<T>(y + (long long)t * H + c, out);
+    }
 
-    if (i == len - 1) {
+    if (i == len - 1 && phase != 1) {
         for (int j = 0; j < K - 1; ++j) {
             const int r = len + j - (K - 1);
             float sv[8];
@@ -149,12 +163,14 @@ shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld,
 // eight channels at a time).
 extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, const float* w, const float* w_t,
                             float* state,
-                            const int* tok_seq, const int* seq_start, const int* seq_slot, int T, int H,
-                            int K, int from_zero, int one_token_each, cudaStream_t st) {
+                            const int* tok_seq, const int* seq_start, const int* seq_slot, const int* seq_pos0,
+                            int T, int H, int K, int from_zero, int one_token_each, cudaStream_t st) {
     if (T <= 0) return CM_OK;
     if (K < 2 || K > SC_MAXK) CM_REFUSE("shortconv: %d taps (2..%d)", K, SC_MAXK);
-    if (!from_zero && !one_token_each)
-        CM_REFUSE("shortconv: several tokens of a sequence on top of a stored state are not supported");
+    // several tokens on top of a stored state: outputs first, then the state (see the top of the file)
+    const int first_phase = (!from_zero && !one_token_each) ? 1 : 0;
+    const int last_phase = first_phase ? 2 : 0;
+    for (int phase = first_phase; phase <= last_phase; ++phase) {
     const bool vec = H % 8 == 0 && ld % 8 == 0 && (((uintptr_t)y | (uintptr_t)bcx | (uintptr_t)state) & 15) == 0;
     if (vec) {
         // few tokens: a token per block (128 channel groups); many: 4 consecutive tokens per block
@@ -162,7 +178,7 @@ extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, cons
         dim3 vblock(tx, ty), vgrid((T + ty - 1) / ty, (H / 8 + tx - 1) / tx);
 #define SC_LAUNCH_VEC(TT, KT)                                                                                      \
     cm_launch(shortconv_vec_kernel<TT, KT>, vgrid, vblock, 0, st, (TT*)y, (const TT*)bcx, ld, w, w_t, state, tok_seq, \
-              seq_start, seq_slot, T, H, K, from_zero)
+              seq_start, seq_slot, seq_pos0, T, H, K, from_zero, phase)
 #define SC_LAUNCH_TAPS(TT)                \
     do {                                  \
         switch (K) {                      \
@@ -180,17 +196,18 @@ extern "C" int cm_shortconv(int dt, void* y, const void* bcx, long long ld, cons
         else
             return CM_ERR_DTYPE;
         CM_CHECK_LAUNCH();
-        return CM_OK;
+        continue;
     }
     dim3 grid(T, (H + 127) / 128);
     if (dt == DT_F32)
         cm_launch(shortconv_kernel<float>, grid, 128, 0, st, (float*)y, (const float*)bcx, ld, w, state, tok_seq,
-                                                      seq_start, seq_slot, H, K, from_zero);
+                                                      seq_start, seq_slot, seq_pos0, H, K, from_zero, phase);
     else if (dt == DT_BF16)
         cm_launch(shortconv_kernel<bf16>, grid, 128, 0, st, (bf16*)y, (const bf16*)bcx, ld, w, state, tok_seq,
-                                                     seq_start, seq_slot, H, K, from_zero);
+                                                     seq_start, seq_slot, seq_pos0, H, K, from_zero, phase);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
+    }
     return CM_OK;
 }

@@ -1,8 +1,9 @@
 """One step's batch as the kernels see it: packed tokens and their sequence geometry.
 
-A step is either a prompt step (every sequence starts at position 0 and brings its whole
-prompt) or a decode step (every sequence brings one token).  All integer metadata travels in
-one int32 buffer, filled on the host in pinned memory and copied once:
+A step is a prompt step (`kind` "prefill": every sequence starts at position 0 and brings its
+whole prompt), a decode step ("decode": every sequence brings one token) or an append step
+("append": anything else, for instance several tokens on top of started sequences).  All integer
+metadata travels in one int32 buffer, filled on the host in pinned memory and copied once:
 
     tokens[T] tok_seq[T] tok_pos[T] seq_slot[B] seq_start[B+1] seq_pos0[B] seq_end[B]
     want_rows[W] upd_count[1] upd_index[U] upd_value[U]
@@ -15,8 +16,6 @@ from __future__ import annotations
 
 import numpy as np
 import torch
-
-from ..kernels import ATTN_DECODE_CHUNK
 
 
 class BatchLayout:
@@ -40,7 +39,11 @@ class BatchLayout:
 class StepBatch:
     """Device-side views plus the host-side facts a part may need to size a launch."""
 
-    def __init__(self, layout, device_buf, prefill, lengths, positions, n_want, n_updates):
+    KINDS = ("prefill", "decode", "append")
+
+    def __init__(self, layout, device_buf, kind, lengths, positions, n_want, n_updates):
+        if kind not in self.KINDS:
+            raise ValueError(f"step kind {kind!r}; one of {self.KINDS}")
         self.layout = layout
         self.buf = device_buf
         v = layout.views(device_buf)
@@ -51,24 +54,19 @@ class StepBatch:
         self.upd_count, self.upd_index, self.upd_value = v["upd_count"], v["upd_index"], v["upd_value"]
         self.samp_seq, self.samp_step, self.samp_seed = v["samp_seq"], v["samp_step"], v["samp_seed"]
         self.samp_temp = v["samp_temp"].view(torch.float32)
-        self.prefill = prefill
+        self.kind = kind
+        self.prefill = kind == "prefill"                       # every sequence starts at position 0
+        self.append = kind == "append"                         # sequences stand anywhere and bring any number of tokens
         self.lengths, self.positions = list(lengths), list(positions)    # host copies, per sequence
         self.B, self.T = layout.B, layout.T
         self.max_len = max(lengths) if lengths else 0          # longest run of new tokens
         self.max_end = max((p + n for p, n in zip(positions, lengths)), default=0)
         self.n_want, self.n_updates = n_want, n_updates
-        self.chunk_bucket = None                               # set by a captured decode graph
         self.wants_every_row = False                           # want_rows is 0, 1, ..., T-1 (set by the decode path)
         self.prev_sampled = None                               # device int32: tokens the step before chose (decode path)
         self.shared = {}                                       # what a layer leaves for later layers of this step
         self.partial_sums_ok = False                           # set by a block around its mixer / feed-forward: their
                                                                # output may be kernels.PartialSums
-
-    def decode_chunks(self, kv_spec):
-        """Chunks of cache entries the decode attention walks for this state spec."""
-        entries = kv_spec.entries(self.chunk_bucket or self.max_end)
-        return max(1, (entries + ATTN_DECODE_CHUNK - 1) // ATTN_DECODE_CHUNK)
-
 
 def fill_sampling(layout, host, sampling):
     """The sampler's inputs of a step: sequence ids, step numbers, temperature, seed."""
@@ -79,6 +77,14 @@ def fill_sampling(layout, host, sampling):
     v["samp_temp"][:n] = np.float32(sampling.temperature).view(np.int32)
     v["samp_seed"][0] = np.uint32(sampling.seed & 0xFFFFFFFF).view(np.int32)
     v["samp_seed"][1] = np.uint32((sampling.seed >> 32) & 0xFFFFFFFF).view(np.int32)
+
+
+def clear_sampling(layout, host):
+    """A step that samples nothing still runs the sampling kernel when it is replayed from a
+    recording: give it temperature 0 and zeroed keys, whatever an earlier step left in the buffer."""
+    v = layout.views(host)
+    for name in ("samp_seq", "samp_step", "samp_temp", "samp_seed"):
+        v[name][:] = 0
 
 
 def fill_host_decode(layout, host, slots, tokens, positions, updates):

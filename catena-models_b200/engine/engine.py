@@ -7,10 +7,17 @@ returns float32 logits at the wanted places.  catena-models has the one-sequence
 this (`Session::forward`, src/model.rs:692-731, with its errors: empty input, capacity
 exceeded, token id outside the vocabulary, src/model.rs:697-710).
 
+A step in which a sequence brings several tokens on top of what it already holds (or in which
+started and new sequences meet) is an append step: it runs the same parts through their
+general forms, which read what is older than the step from the cache (the reference's
+`Session::forward` takes any number of tokens at any position, src/model.rs:692-731).
+
 Decode steps of a given batch size replay a captured CUDA graph: positions, slots and new
 page-table entries live in a fixed device buffer that is refreshed by one host-to-device
-copy before each replay.  Short prompt steps whose shape repeats are recorded and replayed
-the same way.
+copy before each replay.  Which recording serves a step is decided by the batch size and by
+what the model's state specs say about the sequences' length (`length_class`); the engine
+knows nothing of attention chunks.  Short prompt steps whose shape repeats are recorded and
+replayed the same way.
 """
 from __future__ import annotations
 
@@ -22,12 +29,13 @@ import torch
 from ..cache.cache import Cache
 from ..cache.allocators import CacheError, CacheFull
 from .. import kernels as _kernels
-from ..kernels import ATTN_DECODE_CHUNK
-from .batch import BatchLayout, StepBatch, fill_host, fill_host_decode, fill_sampling
+from ..csrc.limits import PAGE_TOKENS
+from .batch import BatchLayout, StepBatch, clear_sampling, fill_host, fill_host_decode, fill_sampling
 
 
 PROMPT_GRAPH_MAX_TOKENS = 1024     # longer prompt steps are bound by the device, not by their launches
 PROMPT_GRAPHS_KEPT = 4
+DECODE_GRAPHS_KEPT = 24            # recorded decode steps (batch size, length class) kept; the least recently used goes
 
 
 class StepError(ValueError):
@@ -72,11 +80,12 @@ class PendingTokens:
     """The tokens a step chose on the device, on their way to the host (`Engine.step(...,
     wait=False)`).  `tokens()` waits for the copy and returns them as Python ints."""
 
-    def __init__(self, host, n, event):
-        self._host, self._n, self._event = host, n, event
+    def __init__(self, host, n, event, check):
+        self._host, self._n, self._event, self._check = host, n, event, check
 
     def tokens(self):
         self._event.synchronize()
+        self._check(self._host[self._n:self._n + 2].tolist())   # the device's two fault flags travel behind the tokens
         return self._host[:self._n].tolist()
 
 
@@ -105,8 +114,14 @@ class Engine:
         # the tokens the last sampling step chose, by position in that step's batch: the next step may
         # take its input tokens from here without the host having seen them (`token_from`)
         self._sampled = torch.zeros(self.cache.book.max_seqs, dtype=torch.int32, device=self.rt.device)
+        self._sampled_count = 0                                # sequences of the last recorded decode step that sampled
         self._readback = [None, None]                          # two pinned buffers used in turn
         self._readback_i = 0
+        # the distinct state specs of the model: what they say about a length picks the recording
+        self._class_specs = []
+        for spec in self.cache.state_specs:
+            if spec is not None and spec not in self._class_specs:
+                self._class_specs.append(spec)
         self.steps_run = 0
         self.kernel_launches = 0
 
@@ -115,7 +130,7 @@ class Engine:
         """Slots for `count` new sequences (all or none)."""
         if count > self.cache.book.slots.free_count:
             raise CacheFull(f"{count} slot(s) wanted, {self.cache.book.slots.free_count} free")
-        return [self.cache.admit() for _ in range(count)]
+        return self.cache.admit_many(count)
 
     def release(self, slots):
         for s in slots:
@@ -123,6 +138,13 @@ class Engine:
 
     def length(self, slot):
         return self.cache.book.length[slot]
+
+    def check_errors(self):
+        """Reads the device's fault flags (synchronises) and raises `DeviceFault` if a kernel gave up
+        on a bounded wait or a token id outside the vocabulary reached the embedding.  Steps that
+        sample read the flags with their tokens; a caller that takes logits calls this before it
+        trusts them."""
+        self.rt.check_errors()
 
     # ------------------------------------------------------------------ the step
     def _check(self, slots, tokens, want):
@@ -139,9 +161,15 @@ class Engine:
         positions = [book.length[s] for s in slots]
         if any(len(t) == 0 for t in tokens):
             raise StepError("a sequence brought no tokens")
-        prefill = all(p == 0 for p in positions)
-        if not prefill and not all(len(t) == 1 for t in tokens):
-            raise StepError("sequences either all start at their first token or all go on by one token")
+        if all(p == 0 for p in positions):
+            kind = "prefill"
+        elif all(len(t) == 1 for t in tokens):
+            kind = "decode"
+        else:
+            kind = "append"
+            if not self.model.supports_append:
+                raise StepError("this model has a part without an append form: its sequences either all "
+                                "start at their first token or all go on by one token")
         V = self.model.vocab_size
         for t in tokens:
             arr = np.asarray(t)
@@ -154,7 +182,7 @@ class Engine:
         for w, t in zip(want, tokens):
             if any(i < 0 or i >= len(t) for i in w):
                 raise StepError("a wanted place lies outside the sequence's tokens of this step")
-        return positions, prefill, want
+        return positions, kind, want
 
     def _reserve(self, slots, positions, tokens):
         """Pages for the new tokens of every sequence; undone as a whole if one does not fit."""
@@ -209,29 +237,33 @@ class Engine:
                 if len(token_from) != len(slots):
                     raise StepError("one token_from entry per slot")
                 known = [t for t, j in zip(flat, token_from) if j is None]
-                if any(j is not None and not 0 <= j < self._sampled.numel() for j in token_from):
-                    raise StepError("token_from points outside the last step's batch")
+                if any(j is not None and not 0 <= j < self._sampled_count for j in token_from):
+                    raise StepError("token_from points outside what the step before sampled (a recorded decode "
+                                    "step with sampling must come right before)")
                 flat = [t if j is None else -(1 + j) for t, j in zip(flat, token_from)]
             else:
                 known = flat
             if known and (min(known) < 0 or max(known) >= V):
                 raise StepError(f"token id outside the vocabulary of {V}")
+            if max(positions) >= book.max_len:
+                raise CacheFull(f"sequence of {max(positions) + 1} tokens exceeds the longest allowed ({book.max_len})")
             # a decode step needs a new page only when a sequence stands on a page border
-            updates = self._reserve(slots, positions, tokens) if any(p % 64 == 0 for p in positions) else []
+            updates = self._reserve(slots, positions, tokens) if any(p % PAGE_TOKENS == 0 for p in positions) else []
             logits, sampled = self._decode_graph_step(slots, flat, positions, updates, sampling)
             for s, p in zip(slots, positions):
                 book.length[s] = p + 1
         else:
-            positions, prefill, want = self._check(slots, tokens, want)
+            positions, kind, want = self._check(slots, tokens, want)
             updates = self._reserve(slots, positions, tokens)
             B, T = len(slots), sum(len(t) for t in tokens)
-            if not prefill and self.use_graphs:
+            if kind == "decode" and self.use_graphs:
                 # decode with explicit wanted places: the graph computes every row, pick the wanted
                 logits, sampled = self._decode_graph_step(slots, [t[0] for t in tokens], positions, updates, sampling)
                 if any(w != [0] for w in want):
                     logits = logits[[b for b, w in enumerate(want) for _ in w]]
             else:
-                logits, sampled = self._prompt_step(slots, tokens, positions, prefill, want, updates, sampling)
+                self._sampled_count = 0                        # what this step samples does not land in `_sampled`
+                logits, sampled = self._prompt_step(slots, tokens, positions, kind, want, updates, sampling)
             for s, p, t in zip(slots, positions, tokens):
                 book.advance(s, p + len(t))
         self.steps_run += 1
@@ -256,25 +288,28 @@ class Engine:
         n = sampled.shape[0]
         self._readback_i ^= 1
         host = self._readback[self._readback_i]
-        if host is None or host.numel() < n:
-            host = torch.empty(max(64, 2 * n), dtype=torch.int32, pin_memory=True)
+        if host is None or host.numel() < n + 2:
+            host = torch.empty(max(64, 2 * n + 2), dtype=torch.int32, pin_memory=True)
             self._readback[self._readback_i] = host
         host[:n].copy_(sampled, non_blocking=True)
+        host[n:n + 2].copy_(self.rt.status, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
-        return PendingTokens(host, n, event)
+        return PendingTokens(host, n, event, self.rt.raise_for_status)
 
     def _to_host(self, sampled):
         """Sampled tokens as Python ints (pinned buffer, one copy, one synchronisation)."""
         n = sampled.shape[0]
-        if self._sampled_host is None or self._sampled_host.numel() < n:
-            self._sampled_host = torch.empty(max(64, 2 * n), dtype=torch.int32, pin_memory=True)
+        if self._sampled_host is None or self._sampled_host.numel() < n + 2:
+            self._sampled_host = torch.empty(max(64, 2 * n + 2), dtype=torch.int32, pin_memory=True)
         self._sampled_host[:n].copy_(sampled, non_blocking=True)
+        self._sampled_host[n:n + 2].copy_(self.rt.status, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        self.rt.raise_for_status(self._sampled_host[n:n + 2].tolist())
         return self._sampled_host[:n].tolist()
 
     # ------------------------------------------------------------------ prompt steps
-    def _prompt_step(self, slots, tokens, positions, prefill, want, updates, sampling):
+    def _prompt_step(self, slots, tokens, positions, kind, want, updates, sampling):
         """A step with explicit tokens per sequence, launched kernel by kernel.  A prompt step whose
         shape (the lengths, the number of wanted places) comes a second time is recorded into a graph
         as it runs and replayed from then on: about 200 launches from Python cost more than a short
@@ -282,7 +317,7 @@ class Engine:
         B, T = len(slots), sum(len(t) for t in tokens)
         n_want = sum(len(w) for w in want)
         key = entry = None
-        if prefill and self.use_graphs and self.model.prompt_capturable and T <= PROMPT_GRAPH_MAX_TOKENS:
+        if kind == "prefill" and self.use_graphs and self.model.prompt_capturable and T <= PROMPT_GRAPH_MAX_TOKENS:
             key = (tuple(len(t) for t in tokens), n_want, len(updates), sampling is not None)
             entry = self._prompt_graphs.get(key)
         layout = entry.layout if entry else BatchLayout(T, B, n_want, len(updates))
@@ -311,7 +346,7 @@ class Engine:
         else:
             dev = host[:layout.size].to(self.rt.device, non_blocking=True)
         self._staging.mark(idx)
-        batch = StepBatch(layout, dev, prefill, [len(t) for t in tokens], positions, n_want, len(updates))
+        batch = StepBatch(layout, dev, kind, [len(t) for t in tokens], positions, n_want, len(updates))
         sampled = torch.empty(B, dtype=torch.int32, device=self.rt.device) if sampling is not None else None
 
         def run():
@@ -338,19 +373,21 @@ class Engine:
         return logits, sampled
 
     # ------------------------------------------------------------------ captured decode
-    @staticmethod
-    def _bucket(n):
-        b = ATTN_DECODE_CHUNK
-        while b < n:
-            b *= 2
-        return b
+    def _length_classes(self, longest):
+        """What the model's state specs say about a step whose longest sequence holds `longest`
+        tokens: steps with equal answers launch the same kernels with the same arguments."""
+        return tuple(spec.length_class(longest) for spec in self._class_specs)
 
     def _decode_graph_step(self, slots, flat_tokens, positions, updates, sampling):
         B = len(slots)
-        bucket = self._bucket(max(positions) + 1)
-        key = (B, bucket)
+        key = (B, self._length_classes(max(positions) + 1))
         entry = self._graphs.get(key)
-        if entry is None:
+        if entry is not None:
+            self._graphs[key] = self._graphs.pop(key)          # most recently used last
+        else:
+            while len(self._graphs) >= DECODE_GRAPHS_KEPT:
+                torch.cuda.current_stream().synchronize()      # its last replay may still be running
+                self._graphs.pop(next(iter(self._graphs)))
             layout = BatchLayout(B, B, B, B * max(1, self.n_kv_groups))
             device_buf = torch.zeros(layout.size, dtype=torch.int32, device=self.rt.device)
             entry = _RecordedStep(layout, device_buf, None, None, None)
@@ -362,6 +399,9 @@ class Engine:
         fill_host_decode(layout, view, slots, flat_tokens, positions, updates)
         if sampling is not None:
             fill_sampling(layout, view, sampling)
+        else:
+            clear_sampling(layout, view)
+        self._sampled_count = B if sampling is not None else 0
         entry.device_buf.copy_(host[:layout.size], non_blocking=True)
         self._staging.mark(idx)
         if entry.graph is None:
@@ -369,10 +409,9 @@ class Engine:
             # every kernel, which must not happen inside a capture), then record the same
             # launches into a graph for the steps that follow.  A capture executes nothing, so
             # the cache and the fixed-size states advance exactly once.  The graph always ends
-            # with the sampling kernel; without a sampling request its output is ignored
-            # (temperature 0 and zeroed keys then make it an argmax).
-            batch = StepBatch(layout, entry.device_buf, False, [1] * B, positions, B, len(updates))
-            batch.chunk_bucket = bucket
+            # with the sampling kernel; without a sampling request its inputs are zeroed (an argmax)
+            # and its output is ignored.
+            batch = StepBatch(layout, entry.device_buf, "decode", [1] * B, positions, B, len(updates))
             batch.wants_every_row = True                       # fill_host_decode wants every row, in order
             batch.prev_sampled = self._sampled                 # negative token entries point into it
 

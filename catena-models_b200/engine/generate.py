@@ -16,8 +16,7 @@ from __future__ import annotations
 import dataclasses
 
 from ..cache.allocators import CacheFull
-
-PAGE = 64
+from ..csrc.limits import PAGE_TOKENS as PAGE
 
 
 @dataclasses.dataclass

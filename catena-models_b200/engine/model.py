@@ -26,7 +26,8 @@ class DecoderModel:
         self.state_specs = definition.state_specs()
         self.capturable = all(part.all_capturable() for part in definition.parts())   # decode graphs allowed
         self.prompt_capturable = all(part.all_prompt_capturable() for part in definition.parts())
-        self.token_error = torch.zeros(1, dtype=torch.int32, device=rt.device)
+        self.supports_append = all(part.all_support_append() for part in definition.parts())
+        self.token_error = rt.token_error
 
     # ------------------------------------------------------------------ construction
     @classmethod

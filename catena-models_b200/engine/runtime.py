@@ -12,6 +12,10 @@ import torch
 from .. import kernels
 
 
+class DeviceFault(RuntimeError):
+    """A kernel reported on the device that its output is not valid."""
+
+
 class Runtime:
     def __init__(self, dtype, device):
         if dtype not in (torch.float32, torch.bfloat16):
@@ -24,15 +28,31 @@ class Runtime:
         self._scratch = {}
         self._retired = []
         self._sm_count = None
-        # raised by a kernel whose bounded pipeline wait ran out (0 otherwise); see check_errors
-        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # Two flags that kernels raise on the device (0 otherwise), side by side so that one copy
+        # brings both to the host: [0] a kernel's bounded pipeline wait ran out and its output is not
+        # valid; [1] the embedding met a token id outside the vocabulary (one taken on the device from
+        # the step before, which the host could not check).  See check_errors / raise_for_status.
+        self.status = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.error_flag = self.status[0:1]
+        self.token_error = self.status[1:2]
 
     def check_errors(self):
-        """Read the device error flag (synchronises); raises if a kernel gave up on a wait."""
-        code = int(self.error_flag.item())
-        if code:
-            self.error_flag.zero_()
-            raise RuntimeError(f"a kernel's pipeline wait ran out (code {code}); its output is not valid")
+        """Read the device flags (synchronises); raises `DeviceFault` if one is set."""
+        self.raise_for_status(self.status.tolist())
+
+    def raise_for_status(self, status):
+        """`status`: the two flags as the host read them.  Clears the device flags and raises if one
+        is set, so that no output of a step that went wrong is handed on as if it were valid."""
+        wait, token = int(status[0]), int(status[1])
+        if not (wait or token):
+            return
+        self.status.zero_()
+        what = []
+        if wait:
+            what.append(f"a kernel's pipeline wait ran out (code {wait})")
+        if token:
+            what.append("a token id outside the vocabulary reached the embedding")
+        raise DeviceFault("; ".join(what) + ": the step's output is not valid")
 
     # ------------------------------------------------------------------ scratch
     def scratch(self, key, numel, dtype=torch.float32):

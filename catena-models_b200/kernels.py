@@ -12,15 +12,15 @@ import os
 import torch
 
 from .csrc import build as _build
+from .csrc import limits as _limits
+from .csrc.limits import ATTN_DECODE_CHUNK, PAGE_TOKENS  # noqa: F401  (re-exported)
 
 DT_F32, DT_BF16 = 0, 1
-PAGE_TOKENS = 64
-ATTN_DECODE_CHUNK = 256
 
 _vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 
 _SIGNATURES = {
-    "cm_embed_gather": [_i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],
+    "cm_embed_gather": [_i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],
     "cm_rmsnorm": [_i, _vp, _vp, _vp, _i, _i, _f, _ll, _ll, _vp],
     "cm_add_norm": [_i, _vp, _vp, _vp, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
     "cm_gemm_tc_few_rows_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp],
@@ -39,10 +39,15 @@ _SIGNATURES = {
     "cm_attn_decode": [_i, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _i,
                        _i, _f, _vp, _vp, _vp],
     "cm_gemm_skinny_shortconv": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
-    "cm_shortconv": [_i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "cm_shortconv": [_i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "cm_attn_append_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i,
+                            _i, _i, _i, _f, _vp],
+    "cm_attn_append_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _i,
+                           _i, _i, _f, _vp],
+    "cm_kv_store": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp],
     "cm_sample": [_vp, _vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "cm_scatter_i32": [_vp, _vp, _vp, _vp, _i, _vp],
-    "cm_zero_rows_f32": [_vp, _vp, _i, _ll, _vp],
+    "cm_zero_slots": [_vp, _i, _ll, _ll, ctypes.POINTER(ctypes.c_int), _i, _vp],
     "cm_copy_pages": [_vp, _vp, _vp, _i, _i, _ll, _ll, _vp],
 }
 
@@ -60,6 +65,7 @@ def lib():
     if _lib is None:
         handle = _build.load()
         handle.cm_last_error.restype = ctypes.c_char_p
+        _limits.check_library(handle)
         for name, args in _SIGNATURES.items():
             fn = getattr(handle, name)
             fn.argtypes = args
@@ -141,8 +147,8 @@ def embed_gather(out, table, tokens, err=None, sampled=None):
     stands for sampled[i]."""
     _need_cuda(out, table, tokens)
     T, H = out.shape
-    _check(lib().cm_embed_gather(dtype_code(out.dtype), _ptr(out), _ptr(table), _ptr(tokens), _ptr(sampled), T, H,
-                                 table.shape[0], _ptr(err), _stream()), "embed_gather")
+    _check(lib().cm_embed_gather(dtype_code(out.dtype), dtype_code(table.dtype), _ptr(out), _ptr(table), _ptr(tokens),
+                                 _ptr(sampled), T, H, table.shape[0], _ptr(err), _stream()), "embed_gather")
 
 
 def rmsnorm(out, x, w, eps):
@@ -316,6 +322,34 @@ def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, win
                                      HD, window, scale, _stream()), "attn_prefill_mma")
 
 
+def attn_append(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, ptab, ring, B, max_len, QH, KVH, HD,
+                window, scale, tensor_cores=True):
+    """Attention of a step whose sequences may stand at seq_pos0[b] > 0: keys and values below that
+    position come from the paged cache `pool`, the rest from the step's own rows (q, k, v as for the
+    prefill kernels), which the caller writes to the cache afterwards (`kv_store`).  bfloat16 with a
+    head size that is a multiple of 16 up to 128 runs on the tensor cores unless `tensor_cores` is off."""
+    if not (q.stride(0) == k.stride(0) == v.stride(0)):
+        raise KernelError("attn_append: q, k and v must share a row stride")
+    mma = (tensor_cores and q.dtype == torch.bfloat16 and HD % 16 == 0 and HD <= 128 and q.stride(0) % 8 == 0
+           and (q.data_ptr() | k.data_ptr() | v.data_ptr() | pool.data_ptr()) % 16 == 0)
+    common = (_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0), _ptr(seq_start),
+              _ptr(seq_pos0), _ptr(seq_slot), _ptr(pool), pages, _ptr(ptab), ptab.stride(0), ring, B, max_len, QH, KVH,
+              HD, window, scale, _stream())
+    if mma:
+        _check(lib().cm_attn_append_mma(_ptr(ctx), ctx.stride(0), *common), "attn_append_mma")
+    else:
+        _check(lib().cm_attn_append_simt(dtype_code(q.dtype), _ptr(ctx), ctx.stride(0), *common), "attn_append_simt")
+
+
+def kv_store(kv, tok_pos, tok_seq, seq_slot, seq_end, pool, pages, ptab, ring, KVH, HD):
+    """kv: the k | v columns [T, 2 * KVH * HD] of the step's packed rows (k normed and rotated);
+    writes them to the cache entries of their positions (a ring keeps the last `ring` of a sequence)."""
+    T = kv.shape[0]
+    _check(lib().cm_kv_store(dtype_code(kv.dtype), _ptr(kv), kv.stride(0), _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot),
+                             _ptr(seq_end), _ptr(pool), pages, _ptr(ptab), ptab.stride(0), ring, T, KVH, HD, _stream()),
+           "kv_store")
+
+
 def attn_prefill_tc(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, err=None):
     """The same on the tcgen05 tensor cores (TMA-fed, scores and outputs in tensor memory): bfloat16,
     head size 64 or 128.  q, k and v are column blocks of one row-major buffer.  err: device int32
@@ -356,12 +390,16 @@ def attn_decode(ctx, q, gate, seq_pos, seq_slot, pool, pages, ptab, ring, window
 
 
 # -------------------------------------------------------------------------- short conv
-def shortconv(y, bcx, w, state, tok_seq, seq_start, seq_slot, K, from_zero, one_token_each, w_t=None):
-    """w: taps [H, K]; w_t: the same stored [K, H] (optional, for 16-byte reads of the taps)."""
+def shortconv(y, bcx, w, state, tok_seq, seq_start, seq_slot, K, from_zero, one_token_each, w_t=None, seq_pos0=None):
+    """w: taps [H, K]; w_t: the same stored [K, H] (optional, for 16-byte reads of the taps).
+    from_zero: every sequence starts from an empty state; one_token_each: a decode step.  Neither:
+    several tokens on top of the stored state (two launches: outputs, then the state); seq_pos0
+    (first position per sequence) then lets a sequence that stands at 0 start from an empty state."""
     T, H = y.shape
+    two = not from_zero and not one_token_each
     _check(lib().cm_shortconv(dtype_code(y.dtype), _ptr(y), _ptr(bcx), bcx.stride(0), _ptr(w), _ptr(w_t), _ptr(state),
-                              _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slot), T, H, K, int(from_zero),
-                              int(one_token_each), _stream()), "shortconv")
+                              _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slot), _ptr(seq_pos0), T, H, K, int(from_zero),
+                              int(one_token_each), _stream()), "shortconv", 2 if two else 1)
 
 
 def gemm_skinny_shortconv(y, x, w_in, taps, state, seq_slot):
@@ -405,5 +443,13 @@ def copy_pages(pool, src, dst):
     _check(lib().cm_copy_pages(_ptr(pool), _ptr(src), _ptr(dst), n, outer, pages, page_bytes, _stream()), "copy_pages")
 
 
-def zero_rows_f32(x, rows, n, width):
-    _check(lib().cm_zero_rows_f32(_ptr(x), _ptr(rows), n, width, _stream()), "zero_rows_f32")
+def zero_slots(store, slots):
+    """store: [layers, slots, ...] fixed-size states (32-bit words or pairs of 16-bit); clears the rows
+    of the given slots (Python ints) in every layer."""
+    if not slots:
+        return
+    layers, total = store.shape[0], store.shape[1]
+    row_bytes = store[0, 0].numel() * store.element_size()
+    ids = (ctypes.c_int * len(slots))(*slots)
+    n_launches = -(-len(slots) // 64)
+    _check(lib().cm_zero_slots(_ptr(store), layers, total, row_bytes, ids, len(slots), _stream()), "zero_slots", n_launches)

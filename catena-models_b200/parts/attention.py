@@ -9,7 +9,10 @@ the value sum in float; context times sigmoid(gate) per head (src/catena/lfm3.he
 output projection.
 
 A prompt step attends over the step's own keys and values (every sequence of such a step
-starts at position 0); a decode step attends over the cache.  All sizes and switches are
+starts at position 0); a decode step attends over the cache; an append step (several tokens on
+top of started sequences) reads the keys below each sequence's first new position from the cache
+and the rest from the step, and writes the step's keys and values to the cache afterwards, so
+that a ring still holds what the step's windows reach back to.  All sizes and switches are
 constructor parameters; the part knows neither its layer index nor its model.
 """
 from __future__ import annotations
@@ -19,6 +22,7 @@ import torch
 
 from .. import kernels
 from ..cache.spec import KVStateSpec
+from ..csrc.limits import ATTN_DECODE_CHUNK
 from ..weights.loader import TensorSpec
 from .base import Mixer, register_part
 from .linear import Linear
@@ -26,6 +30,7 @@ from .linear import Linear
 
 class GQAttention(Mixer):
     prompt_capturable = True
+    supports_append = True
 
     def __init__(self, prefix, hidden, heads, kv_heads, head_dim, window, position, qk_norm_eps,
                  output_gate, names=None, shares_kv=False):
@@ -88,13 +93,18 @@ class GQAttention(Mixer):
                                batch.seq_slot, batch.seq_end, None, 0, None, 0, QH, 0, HD, self.qk_norm_eps or 0.0)
             gate = proj[:, QS:] if self.output_gate else None
         else:
+            # an append step keeps the cache as it is until its attention has run
+            pool = None if batch.append else state.pool
             kernels.qk_prepare(proj, self.q_norm_w, self.k_norm_w, self.position.rate_table(), batch.tok_pos,
-                               batch.tok_seq, batch.seq_slot, batch.seq_end, state.pool, state.pages, state.ptab,
+                               batch.tok_seq, batch.seq_slot, batch.seq_end, pool, state.pages, state.ptab,
                                state.ring, QH, KVH, HD, self.qk_norm_eps or 0.0)
             gate = proj[:, QS + 2 * KVS:] if self.output_gate else None
         q = proj[:, :QS]
         ctx = torch.empty((batch.T, QS), dtype=x.dtype, device=x.device)
-        if batch.prefill:
+        if batch.prefill or batch.append:
+            if self.shares_kv and batch.append and state.ring:
+                raise NotImplementedError("an append step of a layer that shares the keys and values of a sliding "
+                                          "layer: the owner's ring no longer holds what this layer's windows need")
             if self.shares_kv:
                 # the owner left this step's keys and values for its readers; bring them beside q so
                 # that the attention kernel sees one packed buffer
@@ -107,9 +117,20 @@ class GQAttention(Mixer):
             else:
                 k, v = proj[:, QS:QS + KVS], proj[:, QS + KVS:QS + 2 * KVS]
                 batch.shared[("kv", state.unit)] = (k, v)
-            rt.attention_prefill(ctx, q, k, v, gate, batch, QH, KVH, HD, self.window, self.scale)
+            if batch.append:
+                kernels.attn_append(ctx, q, k, v, gate, batch.seq_start, batch.seq_pos0, batch.seq_slot, state.pool,
+                                    state.pages, state.ptab, state.ring, batch.B, batch.max_len, QH, KVH, HD,
+                                    self.window, self.scale)
+                if not self.shares_kv:
+                    kernels.kv_store(proj[:, QS:QS + 2 * KVS], batch.tok_pos, batch.tok_seq, batch.seq_slot,
+                                     batch.seq_end, state.pool, state.pages, state.ptab, state.ring, KVH, HD)
+            else:
+                rt.attention_prefill(ctx, q, k, v, gate, batch, QH, KVH, HD, self.window, self.scale)
         else:
-            n_chunks = batch.decode_chunks(state.spec)
+            # launched for the longest sequence that this step's length class allows, so that a
+            # recording of the step serves every step of the class
+            entries = state.spec.entries(state.spec.length_class(batch.max_end))
+            n_chunks = max(1, -(-entries // ATTN_DECODE_CHUNK))
             part_o, part_ml = rt.scratch_attn_decode(batch.B, QH, HD, n_chunks)
             kernels.attn_decode(ctx, q, gate, batch.seq_pos0, batch.seq_slot, state.pool, state.pages, state.ptab,
                                 state.ring, self.window, QH, KVH, HD, n_chunks, self.scale, part_o, part_ml)

@@ -22,8 +22,9 @@ Interfaces (x, h, n are [tokens, width] activations of the step's packed batch):
         n = input_norm(h) was made by whoever ran before; n_next = next_norm(h) is made
         here (fused with the last residual sum) when next_norm is given, else None.
 
-A part sets `capturable = False` if its forward() reads device data on the host, and
-`prompt_capturable = True` if its prompt steps may be recorded as well (see Part).
+A part sets `capturable = False` if its forward() reads device data on the host,
+`prompt_capturable = True` if its prompt steps may be recorded as well, and
+`supports_append = True` if it handles steps of kind "append" (see Part).
 
 `rt` is the engine's Runtime (dtype, device, scratch), `batch` the StepBatch (token
 positions, sequence boundaries, slots, prefill or decode).
@@ -66,6 +67,12 @@ class Part:
     # shape (lengths, wanted places): the engine may then record a repeated prompt shape into a graph.
     # A part says so itself; one that does not know is not recorded.
     prompt_capturable = False
+    # True for a part that can take a step of kind "append" (StepBatch.kind): sequences that stand at
+    # any position and bring any number of tokens.  A part that works row by row (norm, feed-forward,
+    # projection) can; a mixer with state has to say so itself, after it has made sure that its
+    # forward() reads what is older than the step from its state.  A model with a part that cannot
+    # is stepped with whole prompts and single tokens only.
+    supports_append = False
 
     def tensor_specs(self):
         return []
@@ -90,6 +97,9 @@ class Part:
 
     def all_capturable(self):
         return self.capturable and all(c.all_capturable() for c in self.children())
+
+    def all_support_append(self):
+        return self.supports_append and all(c.all_support_append() for c in self.children())
 
     def all_prompt_capturable(self):
         return self.capturable and self.prompt_capturable and all(c.all_prompt_capturable() for c in self.children())

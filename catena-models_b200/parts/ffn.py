@@ -11,6 +11,7 @@ from .linear import Linear
 
 class SwiGLU(FeedForward):
     prompt_capturable = True
+    supports_append = True
 
     def __init__(self, prefix, hidden, intermediate, names=None):
         names = names or {}

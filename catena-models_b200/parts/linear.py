@@ -15,6 +15,7 @@ from .base import Part
 
 class Linear(Part):
     prompt_capturable = True
+    supports_append = True
 
     def __init__(self, names, rows, in_features, role="matrix"):
         self.names = [names] if isinstance(names, str) else list(names)

@@ -15,6 +15,7 @@ from .base import Norm, register_part
 
 class RMSNorm(Norm):
     prompt_capturable = True
+    supports_append = True
     fused_kind = "rms"          # what the fused residual kernel can absorb
 
     def __init__(self, name, width, eps):

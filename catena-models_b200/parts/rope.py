@@ -17,6 +17,7 @@ from .base import Position, register_part
 
 class Rotary(Position):
     prompt_capturable = True
+    supports_append = True
 
     def __init__(self, head_dim, theta, factors_name=None):
         self.head_dim, self.theta, self.factors_name = head_dim, float(theta), factors_name
@@ -42,6 +43,7 @@ class Rotary(Position):
 class NoPosition(Position):
     """No position encoding: the head vectors are left unrotated."""
     prompt_capturable = True
+    supports_append = True
 
 
 register_part("position", "rotary", Rotary)

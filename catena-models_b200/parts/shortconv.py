@@ -17,6 +17,7 @@ from .linear import Linear
 
 class ShortConv(Mixer):
     prompt_capturable = True
+    supports_append = True
 
     def __init__(self, prefix, hidden, taps, names=None):
         names = names or {}
@@ -43,13 +44,16 @@ class ShortConv(Mixer):
 
     def forward(self, rt, batch, x, state):
         y = torch.empty((batch.T, self.hidden), dtype=x.dtype, device=x.device)
-        if not batch.prefill and rt.streams_weights(x, self.in_proj.weight):
+        if batch.kind == "decode" and rt.streams_weights(x, self.in_proj.weight):
             # a decode step of a small batch: the convolution runs where in_proj's sums are formed
             kernels.gemm_skinny_shortconv(y, x, self.in_proj.weight, self.conv_w, state.tensor, batch.seq_slot)
             return self.out_proj.apply(rt, y, partial_ok=batch.partial_sums_ok)
         bcx = self.in_proj.apply(rt, x)                                   # [T, 3H]
+        # an append step: outputs from the stored state, then the state, in two launches; a sequence
+        # of such a step that stands at position 0 starts from an empty state
         kernels.shortconv(y, bcx, self.conv_w, state.tensor, batch.tok_seq, batch.seq_start, batch.seq_slot,
-                          self.taps, from_zero=batch.prefill, one_token_each=not batch.prefill, w_t=self.conv_w_t)
+                          self.taps, from_zero=batch.prefill, one_token_each=batch.kind == "decode",
+                          w_t=self.conv_w_t, seq_pos0=batch.seq_pos0 if batch.append else None)
         return self.out_proj.apply(rt, y, partial_ok=batch.partial_sums_ok)
 
 

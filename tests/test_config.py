@@ -37,6 +37,9 @@ def test_round_trip_through_json():
     (dict(layer_types=["conv"]), "layer_types has 1"),
     (dict(num_key_value_heads=3), "divisible"),
     (dict(head_dim=20), "head_dim"),
+    (dict(head_dim=264, hidden_size=1056), "head_dim 264"),
+    (dict(hidden_size=8200), "hidden_size 8200"),
+    (dict(conv_L_cache=17), "conv_L_cache 17"),
     (dict(conv_L_cache=1), "conv_L_cache"),
     (dict(sliding_window=0), "sliding_window"),
     (dict(rope_theta=-1.0), "rope_theta"),
@@ -106,3 +109,19 @@ def test_layer_order_is_data():
     d = arch.define(cfg)
     assert [e.block for e in d.plan] == [0, 1, 1, 3, 2]
     assert len(d.state_specs()) == 5                                   # a layer that runs twice has two states
+
+
+def test_limits_are_the_kernels_own():
+    """The sizes the configuration check refuses are read from the header the CUDA sources include;
+    the numbers stand nowhere else."""
+    import re
+
+    from catena_models_b200.csrc import limits
+
+    text = open(limits._HEADER).read()
+    for name in limits.NAMES:
+        assert re.search(rf"#define\s+CM_{name}\s+{getattr(limits, name)}\b", text)
+    d = dict(tiny.TINY_A, hidden_size=limits.NORM_MAX_WIDTH, num_attention_heads=512, num_key_value_heads=512)
+    Lfm3Config.from_dict(d)                                   # the limit itself passes
+    with pytest.raises(ConfigError):
+        Lfm3Config.from_dict(dict(d, hidden_size=limits.NORM_MAX_WIDTH + 8))

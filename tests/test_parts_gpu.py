@@ -29,7 +29,9 @@ def _batch(rt, cache, slots, token_lists, positions):
     layout = BatchLayout(T, len(slots), 0, len(updates))
     host = torch.zeros(layout.size, dtype=torch.int32)
     fill_host(layout, host.numpy(), slots, token_lists, positions, [[] for _ in slots], updates)
-    batch = StepBatch(layout, host.to(DEV), all(p == 0 for p in positions), [len(t) for t in token_lists], positions, 0, len(updates))
+    kind = ("prefill" if all(p == 0 for p in positions) else
+            "decode" if all(len(t) == 1 for t in token_lists) else "append")
+    batch = StepBatch(layout, host.to(DEV), kind, [len(t) for t in token_lists], positions, 0, len(updates))
     from catena_models_b200 import kernels
     if updates:
         kernels.scatter_i32(cache.ptab_all, batch.upd_index, batch.upd_value, batch.upd_count, layout.U)

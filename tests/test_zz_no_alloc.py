@@ -6,7 +6,10 @@ memory budget, or a plain C caller with no tensor library to ask for scratch buf
 them `cm_attn_decode_noalloc` keeps the kernel's per-chunk partial results in an array inside
 the library image.  This test calls it twice in a row (the array is shared between calls and
 keeps the previous call's contents) and compares each result with the ordinary entry point,
-which gets fresh scratch buffers from the caller.
+which gets fresh scratch buffers from the caller, and with attention computed in float64 from
+the same keys and values.  That nothing is allocated is checked on the device itself: the free
+memory that the driver reports does not shrink over the call (torch's own counters would not
+see an allocation made inside the library).
 
 The file is named so that pytest collects it last: a run that stops at the first failure has
 then already run every other test.
@@ -44,21 +47,38 @@ def _case(kernels, dtype, QH, KVH, HD, window, lens, seed):
     pool = torch.zeros(2, pages, KVH, 64, HD, dtype=dtype, device=DEV)
     ptab = torch.zeros(len(lens), max(per_seq), dtype=torch.int32)
     nxt = 0
+    kvs = []
     for b, n in enumerate(lens):
         for j in range(per_seq[b]):
             ptab[b, j] = perm[nxt]
             nxt += 1
-        kv = torch.randn(n, 2, KVH, HD, generator=g)
+        kv = torch.randn(n, 2, KVH, HD, generator=g).to(dtype)
+        kvs.append(kv)
         for p in range(max(0, n - ring) if ring else 0, n):
             e = p % ring if ring else p
-            pool[:, int(ptab[b, e // 64]), :, e % 64] = kv[p].to(dtype).to(DEV)
+            pool[:, int(ptab[b, e // 64]), :, e % 64] = kv[p].to(DEV)
     B = len(lens)
     q = torch.randn(B, QH * HD, generator=g).to(dtype).to(DEV)
     gate = torch.randn(B, QH, generator=g).to(dtype).to(DEV)
     pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
     slots = torch.arange(B, dtype=torch.int32, device=DEV)
     return dict(q=q, gate=gate, pos=pos, slots=slots, pool=pool, pages=pages, ptab=ptab.to(DEV), ring=ring,
-                window=window, QH=QH, KVH=KVH, HD=HD)
+                window=window, QH=QH, KVH=KVH, HD=HD, kv=kvs, lens=list(lens))
+
+
+def _exact(c):
+    """float64 attention of every sequence's newest token over all its keys and values."""
+    from test_kernels_gpu import _ref_attention
+
+    QH, HD = c["QH"], c["HD"]
+    rows = []
+    for b, n in enumerate(c["lens"]):
+        qq = torch.zeros(n, QH, HD)
+        qq[-1] = c["q"][b].float().cpu().view(QH, HD)
+        gg = torch.zeros(n, QH)
+        gg[-1] = c["gate"][b].float().cpu()
+        rows.append(_ref_attention(qq, c["kv"][b][:, 0], c["kv"][b][:, 1], c["window"], HD ** -0.5, gg)[-1].reshape(-1))
+    return torch.stack(rows)
 
 
 def _run_both(kernels, fn, c, n_chunks):
@@ -69,13 +89,17 @@ def _run_both(kernels, fn, c, n_chunks):
     kernels.attn_decode(ref, c["q"], c["gate"], c["pos"], c["slots"], c["pool"], c["pages"], c["ptab"], c["ring"],
                         c["window"], QH, KVH, HD, n_chunks, scale, part_o, part_ml)
     got = torch.full_like(c["q"], float("nan"))
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before, _ = torch.cuda.mem_get_info()
     rc = fn(kernels.dtype_code(c["q"].dtype), got.data_ptr(), got.stride(0), c["q"].data_ptr(), c["q"].stride(0),
             c["gate"].data_ptr(), c["gate"].stride(0), c["pos"].data_ptr(), c["slots"].data_ptr(),
             c["pool"].data_ptr(), c["pages"], c["ptab"].data_ptr(), c["ptab"].stride(0), c["ring"], c["window"],
             B, QH, KVH, HD, n_chunks, scale, torch.cuda.current_stream().cuda_stream)
-    assert torch.cuda.memory_allocated() == before          # no tensor was made on the way
     torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert torch.cuda.memory_allocated() == before          # no tensor was made on the way
+    assert free_after >= free_before                        # and nothing was taken from the device behind torch's back
     return rc, got, ref
 
 
@@ -90,6 +114,7 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point():
         assert rc == 0, handle.cm_last_error().decode()
         tol = dict(rtol=1e-5, atol=1e-5) if got.dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-2)
         torch.testing.assert_close(got.float().cpu(), ref.float().cpu(), **tol)
+        torch.testing.assert_close(got.float().cpu(), _exact(case).float(), **tol)
 
 
 def test_a_call_beyond_the_built_in_array_is_refused():
