@@ -347,6 +347,8 @@ class Engine:
             dev = host[:layout.size].to(self.rt.device, non_blocking=True)
         self._staging.mark(idx)
         batch = StepBatch(layout, dev, kind, [len(t) for t in tokens], positions, n_want, len(updates))
+        # a decode step that wants its every row: the same launches as its recorded form
+        batch.wants_every_row = kind == "decode" and all(w == [0] for w in want)
         sampled = torch.empty(B, dtype=torch.int32, device=self.rt.device) if sampling is not None else None
 
         def run():

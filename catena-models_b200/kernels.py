@@ -59,9 +59,68 @@ class KernelError(RuntimeError):
 _lib = None
 
 
+class Timeline:
+    """Times every launch of the library between `with kernels.Timeline() as t:` and its end, with a
+    pair of CUDA events around each entry-point call, and keeps what the binding knows about the
+    call: its name, the operands' shape and the bytes and floating-point operations that the
+    operation needs by its definition (each operand once).  `rows()` adds the calls up by name
+    and shape.  catena-models prints its own phase timers on request (CATENA_COMPILE_TIMINGS,
+    src/catena.rs:82-87; per-phase rates, src/main.rs:364-371); this is that habit for kernels.
+    Off unless entered: an ordinary run records no events."""
+
+    def __init__(self):
+        self.calls = []            # [name, shape, bytes, flops, start event, end event, launches]
+        self._start = None
+
+    def __enter__(self):
+        global _timeline
+        self._before, _timeline = _timeline, self
+        return self
+
+    def __exit__(self, *exc):
+        global _timeline
+        _timeline = self._before
+
+    def begin(self):
+        self._start = torch.cuda.Event(enable_timing=True)
+        self._start.record()
+
+    def end(self, name, n, cost):
+        if self._start is None:
+            return
+        stop = torch.cuda.Event(enable_timing=True)
+        stop.record()
+        shape, nbytes, flops = cost() if cost is not None else ("", 0, 0)
+        self.calls.append([name, shape, nbytes, flops, self._start, stop, n])
+        self._start = None
+
+    def rows(self):
+        """[{name, shape, calls, launches, us, bytes, flops}] by name and shape, in order of first use
+        (synchronises)."""
+        torch.cuda.synchronize()
+        out = {}
+        for name, shape, nbytes, flops, a, b, n in self.calls:
+            row = out.setdefault((name, shape), dict(name=name, shape=shape, calls=0, launches=0, us=0.0, bytes=0, flops=0))
+            row["calls"] += 1
+            row["launches"] += n
+            row["us"] += a.elapsed_time(b) * 1e3
+            row["bytes"] += nbytes
+            row["flops"] += flops
+        return list(out.values())
+
+
+_timeline = None
+
+
+def _nbytes(*tensors):
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
+
 def lib():
     """The loaded CUDA library, with argument types set."""
     global _lib
+    if _timeline is not None and _lib is not None:
+        _timeline.begin()          # every binding asks for the library right before its launch
     if _lib is None:
         handle = _build.load()
         handle.cm_last_error.restype = ctypes.c_char_p
@@ -128,11 +187,15 @@ class pinned_stream:
 launches = 0          # kernels launched (or recorded into a graph) by this process, counted per call
 
 
-def _check(code, name, n=1):
+def _check(code, name, n=1, cost=None):
+    """`cost`: a callable that gives (shape text, bytes, floating-point operations) of the call; it is
+    evaluated only while a Timeline records."""
     global launches
     launches += n
+    if _timeline is not None:
+        _timeline.end(name, n, cost)
     if code != 0:
-        raise KernelError(f"{name} returned {code}: {lib().cm_last_error().decode(errors='replace')}")
+        raise KernelError(f"{name} returned {code}: {_lib.cm_last_error().decode(errors='replace')}")
 
 
 def _need_cuda(*tensors):
@@ -148,14 +211,16 @@ def embed_gather(out, table, tokens, err=None, sampled=None):
     _need_cuda(out, table, tokens)
     T, H = out.shape
     _check(lib().cm_embed_gather(dtype_code(out.dtype), dtype_code(table.dtype), _ptr(out), _ptr(table), _ptr(tokens),
-                                 _ptr(sampled), T, H, table.shape[0], _ptr(err), _stream()), "embed_gather")
+                                 _ptr(sampled), T, H, table.shape[0], _ptr(err), _stream()), "embed_gather",
+           cost=lambda: (f"{T}x{H}", T * H * table.element_size() + _nbytes(out, tokens), 0))
 
 
 def rmsnorm(out, x, w, eps):
     _need_cuda(out, x, w)
     rows, H = x.shape
     _check(lib().cm_rmsnorm(dtype_code(x.dtype), _ptr(out), _ptr(x), _ptr(w), rows, H, eps, x.stride(0),
-                            out.stride(0), _stream()), "rmsnorm")
+                            out.stride(0), _stream()), "rmsnorm",
+           cost=lambda: (f"{rows}x{H}", _nbytes(x, out, w), 4 * rows * H))
 
 
 class PartialSums:
@@ -182,12 +247,14 @@ def add_norm(h_out, n_out, m, h_in, w_post, w_next, eps_post, eps_next):
             raise KernelError("add_norm: partial sums must be contiguous float32")
         _check(lib().cm_add_norm(dtype_code(h_in.dtype), _ptr(h_out), _ptr(n_out), None, _ptr(parts), n_parts, rows * H,
                                  _ptr(h_in), _ptr(w_post), _ptr(w_next), rows, H, eps_post, eps_next, _stream()),
-               "add_norm")
+               "add_norm", cost=lambda: (f"{rows}x{H} over {n_parts} partial sums",
+                                         _nbytes(parts, h_in, h_out, n_out, w_post, w_next), (n_parts + 8) * rows * H))
         return
     _need_cuda(h_out, m, h_in)
     rows, H = m.shape
     _check(lib().cm_add_norm(dtype_code(m.dtype), _ptr(h_out), _ptr(n_out), _ptr(m), None, 0, 0, _ptr(h_in), _ptr(w_post),
-                             _ptr(w_next), rows, H, eps_post, eps_next, _stream()), "add_norm")
+                             _ptr(w_next), rows, H, eps_post, eps_next, _stream()), "add_norm",
+           cost=lambda: (f"{rows}x{H}", _nbytes(m, h_in, h_out, n_out, w_post, w_next), 8 * rows * H))
 
 
 def swiglu(out, gate_up):
@@ -210,7 +277,8 @@ def gemm_simt(y, x, w):
     if w.shape[1] != K or tuple(y.shape) != (M, N):
         raise KernelError(f"gemm shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
     _check(lib().cm_gemm_simt(dtype_code(x.dtype), dtype_code(w.dtype), dtype_code(y.dtype), _ptr(y), _ptr(x),
-                              _ptr(w), M, N, K, x.stride(0), w.stride(0), y.stride(0), _stream()), "gemm_simt")
+                              _ptr(w), M, N, K, x.stride(0), w.stride(0), y.stride(0), _stream()), "gemm_simt",
+           cost=lambda: (f"{M}x{N}x{K}", _nbytes(x, w, y), 2 * M * N * K))
 
 
 def gemm_skinny(y, x, w, swiglu=False):
@@ -224,7 +292,8 @@ def gemm_skinny(y, x, w, swiglu=False):
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_skinny takes bfloat16 operands")
     _check(lib().cm_gemm_skinny(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
-                                y.stride(0), int(swiglu), _stream()), "gemm_skinny")
+                                y.stride(0), int(swiglu), _stream()), "gemm_skinny" + ("_swiglu" if swiglu else ""),
+           cost=lambda: (f"{M}x{w.shape[0]}x{K}", _nbytes(x, w, y), 2 * M * w.shape[0] * K))
 
 
 def gemm_skinny_parts(parts, x, w):
@@ -238,7 +307,8 @@ def gemm_skinny_parts(parts, x, w):
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_skinny_parts takes bfloat16 operands")
     _check(lib().cm_gemm_skinny_parts(_ptr(parts), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), N, M * N, S,
-                                      _stream()), "gemm_skinny_parts")
+                                      _stream()), "gemm_skinny_parts",
+           cost=lambda: (f"{M}x{N}x{K} in {S} slices", _nbytes(x, w, parts), 2 * M * N * K))
 
 
 def gemm_tc_few_rows_parts(parts, x, w, err=None):
@@ -252,7 +322,8 @@ def gemm_tc_few_rows_parts(parts, x, w, err=None):
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or w.stride(1) != 1:
         raise KernelError("gemm_tc_few_rows_parts takes row-major bfloat16 operands")
     _check(lib().cm_gemm_tc_few_rows_parts(_ptr(parts), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), M * N, S,
-                                           _ptr(err), _stream()), "gemm_tc_few_rows_parts")
+                                           _ptr(err), _stream()), "gemm_tc_few_rows_parts",
+           cost=lambda: (f"{M}x{N}x{K} in {S} slices", _nbytes(x, w, parts), 2 * M * N * K))
 
 
 def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256):
@@ -270,7 +341,8 @@ def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256):
     if x.stride(1) != 1 or w.stride(1) != 1 or y.stride(1) != 1:
         raise KernelError("gemm_tc takes row-major operands")
     _check(lib().cm_gemm_tc(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
-                            y.stride(0), int(swiglu), block_n, _ptr(err), _stream()), "gemm_tc")
+                            y.stride(0), int(swiglu), block_n, _ptr(err), _stream()), "gemm_tc" + ("_swiglu" if swiglu else ""),
+           cost=lambda: (f"{M}x{w.shape[0]}x{K}", _nbytes(x, w, y), 2 * M * w.shape[0] * K))
 
 
 def gemm_tc_few_rows(y, x, w, swiglu=False, err=None, splits=0):
@@ -288,7 +360,8 @@ def gemm_tc_few_rows(y, x, w, swiglu=False, err=None, splits=0):
         raise KernelError("gemm_tc_few_rows takes row-major operands")
     _check(lib().cm_gemm_tc_few_rows(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0),
                                      w.stride(0), y.stride(0), int(swiglu), splits, _ptr(err), _stream()),
-           "gemm_tc_few_rows")
+           "gemm_tc_few_rows" + ("_swiglu" if swiglu else ""),
+           cost=lambda: (f"{M}x{w.shape[0]}x{K}", _nbytes(x, w, y), 2 * M * w.shape[0] * K))
 
 
 # -------------------------------------------------------------------------- attention
@@ -300,7 +373,9 @@ def qk_prepare(qkv, wq, wk, rate, tok_pos, tok_seq, seq_slot, seq_end, pool, pag
     _check(lib().cm_qk_prepare(dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(wq), _ptr(wk), _ptr(rate),
                                _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(seq_end), _ptr(pool), pages,
                                _ptr(ptab), 0 if ptab is None else ptab.stride(0), ring, T, QH, KVH, HD, eps,
-                               _stream()), "qk_prepare")
+                               _stream()), "qk_prepare",
+           cost=lambda: (f"{T} tokens, {QH}+{KVH} heads of {HD}",
+                         T * HD * qkv.element_size() * (2 * QH + (2 * KVH if pool is None else 4 * KVH)), 0))
 
 
 def attn_prefill_simt(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale):
@@ -310,7 +385,8 @@ def attn_prefill_simt(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, wi
     _check(lib().cm_attn_prefill_simt(dtype_code(q.dtype), _ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v),
                                       q.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0),
                                       _ptr(seq_start), B, max_len, QH, KVH, HD, window, scale, _stream()),
-           "attn_prefill_simt")
+           "attn_prefill_simt",
+           cost=lambda: (f"{B} sequences up to {max_len}, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
 def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale):
@@ -319,7 +395,8 @@ def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, win
         raise KernelError("attn_prefill_mma: bfloat16 q, k and v that share a row stride")
     _check(lib().cm_attn_prefill_mma(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
                                      0 if gate is None else gate.stride(0), _ptr(seq_start), B, max_len, QH, KVH,
-                                     HD, window, scale, _stream()), "attn_prefill_mma")
+                                     HD, window, scale, _stream()), "attn_prefill_mma",
+           cost=lambda: (f"{B} sequences up to {max_len}, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
 def attn_append(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, ptab, ring, B, max_len, QH, KVH, HD,
@@ -358,7 +435,8 @@ def attn_prefill_tc(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, wind
         raise KernelError("attn_prefill_tc: bfloat16 q, k and v that share rows and a row stride")
     _check(lib().cm_attn_prefill_tc(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
                                     0 if gate is None else gate.stride(0), _ptr(seq_start), B, max_len, q.shape[0],
-                                    QH, KVH, HD, window, scale, _ptr(err), _stream()), "attn_prefill_tc")
+                                    QH, KVH, HD, window, scale, _ptr(err), _stream()), "attn_prefill_tc",
+           cost=lambda: (f"{B} sequences up to {max_len}, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
 def set_decode_attention_target_blocks(blocks):
@@ -386,7 +464,8 @@ def attn_decode(ctx, q, gate, seq_pos, seq_slot, pool, pages, ptab, ring, window
     _check(lib().cm_attn_decode(dtype_code(q.dtype), _ptr(ctx), ctx.stride(0), _ptr(q), q.stride(0), _ptr(gate),
                                 0 if gate is None else gate.stride(0), _ptr(seq_pos), _ptr(seq_slot), _ptr(pool),
                                 pages, _ptr(ptab), ptab.stride(0), ring, window, B, QH, KVH, HD, n_chunks, scale,
-                                _ptr(part_o), _ptr(part_ml), _stream()), "attn_decode", 2)
+                                _ptr(part_o), _ptr(part_ml), _stream()), "attn_decode", 2,
+           cost=lambda: (f"{B} sequences, {QH}/{KVH} heads of {HD}, window {window}, {n_chunks} chunks", 0, 0))
 
 
 # -------------------------------------------------------------------------- short conv
@@ -399,7 +478,8 @@ def shortconv(y, bcx, w, state, tok_seq, seq_start, seq_slot, K, from_zero, one_
     two = not from_zero and not one_token_each
     _check(lib().cm_shortconv(dtype_code(y.dtype), _ptr(y), _ptr(bcx), bcx.stride(0), _ptr(w), _ptr(w_t), _ptr(state),
                               _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slot), _ptr(seq_pos0), T, H, K, int(from_zero),
-                              int(one_token_each), _stream()), "shortconv", 2 if two else 1)
+                              int(one_token_each), _stream()), "shortconv", 2 if two else 1,
+           cost=lambda: (f"{T}x{H}, {K} taps", _nbytes(bcx, y), 2 * (K + 1) * T * H))
 
 
 def gemm_skinny_shortconv(y, x, w_in, taps, state, seq_slot):
@@ -418,14 +498,16 @@ def gemm_skinny_shortconv(y, x, w_in, taps, state, seq_slot):
         raise KernelError("gemm_skinny_shortconv: taps and state must be contiguous")
     _check(lib().cm_gemm_skinny_shortconv(_ptr(y), _ptr(x), _ptr(w_in), _ptr(taps), _ptr(state), _ptr(seq_slot), M, H,
                                           K, KT, x.stride(0), w_in.stride(0), y.stride(0), _stream()),
-           "gemm_skinny_shortconv")
+           "gemm_skinny_shortconv",
+           cost=lambda: (f"{M}x{3 * H}x{K}", _nbytes(x, w_in, y, taps) + 2 * M * (KT - 1) * H * 4, 2 * M * 3 * H * K))
 
 
 # ---------------------------------------------------------------------------- sampling
 def sample(out, logits, temperature, sequence, step, seed_words):
     n, V = logits.shape
     _check(lib().cm_sample(_ptr(out), _ptr(logits), logits.stride(0), n, V, _ptr(temperature), _ptr(sequence),
-                           _ptr(step), _ptr(seed_words), _stream()), "sample")
+                           _ptr(step), _ptr(seed_words), _stream()), "sample",
+           cost=lambda: (f"{n}x{V}", n * V * 4, 0))
 
 
 # ------------------------------------------------------------------------------- cache

@@ -1,6 +1,8 @@
 """bin/trace_run as a user drives it: a subprocess fed JSON lines on standard input.  The same
-requests whole, with the last 32 tokens one by one, and in unequal batches one after another
-(so slots and pages are used again), in 32-bit and in bfloat16, against the plain model."""
+requests whole, with the last 32 tokens one by one, in unequal batches one after another
+(so slots and pages are used again), and with their prompts cut into two steps (the second on
+top of what the first left, while another request starts beside it), in 32-bit and in bfloat16,
+against the plain model."""
 import json
 import os
 import subprocess
@@ -88,9 +90,18 @@ def test_replay_three_ways(tmp_path, name, dtype):
             quiet = False
             add(entries, end=[f"{k}:b" for k in ending])
             live = [k for k in live if k not in ending]
+    # 4) prompts in two chunks: every request brings its second chunk on top of its first, in one batch
+    #    with unequal cuts, while a request that has not started yet joins with its whole prompt
+    way = "chunks"
+    cuts = {"a": 13, "b": 64, "c": 1, "d": 100}
+    add([{"id": f"{k}:c", "tokens": reqs[k][:c], "want": [c - 1], "_pos": [c - 1]} for k, c in cuts.items()])
+    entries = [{"id": f"{k}:c", "tokens": reqs[k][c:], "want": list(range(len(reqs[k]) - c)),
+                "_pos": list(range(c, len(reqs[k])))} for k, c in cuts.items()]
+    entries.append({"id": "e:c", "tokens": reqs["e"], "want": list(range(len(reqs["e"]))), "_pos": list(range(len(reqs["e"])))})
+    add(entries, end=[f"{k}:c" for k in reqs])
     out = tmp_path / "out"
-    # peak: batch 3.2 holds 130 + 35 + 40 tokens -> 192 + 64 + 64
-    replay(folder, dtype, steps, out, max_tokens=320)
+    # peak: the chunked batch holds 40 + 97 + 33 + 130 + 35 tokens -> 64 + 128 + 64 + 192 + 64 = 512
+    replay(folder, dtype, steps, out, max_tokens=512)
     exact = {k: plain_lfm3.forward(cfg, tensors, t) for k, t in reqs.items()}
     same = {k: plain_lfm3.forward(cfg, tensors, t, bf16=True) for k, t in reqs.items()} if dtype == "bfloat16" else None
     assert sorted(int(f[:-4]) for f in os.listdir(out)) == sorted(expect)
@@ -105,7 +116,7 @@ def test_replay_three_ways(tmp_path, name, dtype):
         for key, positions in wanted:
             rows.setdefault((key, way_of[step]), []).append((got[off:off + len(positions)], positions))
             off += len(positions)
-    assert len(rows) == 15                                   # five requests, three ways
+    assert len(rows) == 20                                   # five requests, four ways
     for (k, way), parts in rows.items():
         got = torch.cat([g for g, _ in parts])
         pos = [p for _, ps in parts for p in ps]
