@@ -27,6 +27,7 @@ class DecoderModel:
         self.capturable = all(part.all_capturable() for part in definition.parts())   # decode graphs allowed
         self.prompt_capturable = all(part.all_prompt_capturable() for part in definition.parts())
         self.supports_append = all(part.all_support_append() for part in definition.parts())
+        self.fusable_decode = all(part.all_fused_decode_ok() for part in definition.parts())
         self.token_error = rt.token_error
 
     # ------------------------------------------------------------------ construction
@@ -79,7 +80,11 @@ class DecoderModel:
     # ------------------------------------------------------------------ forward
     def forward(self, batch, cache):
         with kernels.pinned_stream():
-            return self._forward(batch, cache)
+            fuse = self.rt.fused_decode_for(batch) if self.fusable_decode else None
+            if fuse is None:
+                return self._forward(batch, cache)
+            with fuse:                     # the step's small products and residual sums run in few persistent launches
+                return self._forward(batch, cache)
 
     def _forward(self, batch, cache):
         rt = self.rt

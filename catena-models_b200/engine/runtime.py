@@ -7,6 +7,8 @@ weight-streaming kernels.  Kernel choice never depends on which model or layer i
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import kernels
@@ -35,6 +37,12 @@ class Runtime:
         self.status = torch.zeros(2, dtype=torch.int32, device=self.device)
         self.error_flag = self.status[0:1]
         self.token_error = self.status[1:2]
+        # On request (CATENA_B200_FUSED_DECODE=1, or this attribute set before the first decode step) decode
+        # steps of up to 16 bfloat16 sequences run their products, residual sums and convolutions in a few
+        # persistent kernels (kernels.FusedDecode) instead of one launch per call.  Off by default: measured
+        # slower than the recorded chain of single kernels (csrc/decode_fused.cu gives the figures).
+        self.fused_decode = os.environ.get("CATENA_B200_FUSED_DECODE", "0") == "1"
+        self.fused_bar = torch.zeros(4, dtype=torch.int32, device=self.device)     # the fused kernel's barrier word
 
     def check_errors(self):
         """Read the device flags (synchronises); raises `DeviceFault` if one is set."""
@@ -47,12 +55,21 @@ class Runtime:
         if not (wait or token):
             return
         self.status.zero_()
+        self.fused_bar.zero_()             # a fused kernel that gave up has left its barrier word half-way
         what = []
         if wait:
             what.append(f"a kernel's pipeline wait ran out (code {wait})")
         if token:
             what.append("a token id outside the vocabulary reached the embedding")
         raise DeviceFault("; ".join(what) + ": the step's output is not valid")
+
+    def fused_decode_for(self, batch):
+        """The collector for this step's fusable calls, or None: decode steps of the bfloat16 engine with
+        at most 16 sequences."""
+        if (self.fused_decode and self.dtype == torch.bfloat16 and batch.kind == "decode"
+                and batch.T <= kernels.FD_MAX_ROWS):
+            return kernels.FusedDecode(self.fused_bar, self.error_flag)
+        return None
 
     # ------------------------------------------------------------------ scratch
     def scratch(self, key, numel, dtype=torch.float32):

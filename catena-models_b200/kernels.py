@@ -116,9 +116,90 @@ def _nbytes(*tensors):
     return sum(t.numel() * t.element_size() for t in tensors if t is not None)
 
 
+# ------------------------------------------------------------------ fused decode segments
+FD_GEMV, FD_ADD_NORM, FD_CONV = 0, 1, 2
+FD_PLAIN, FD_SWIGLU, FD_PARTS, FD_F32 = 0, 1, 2, 3
+FD_MAX_ROWS = 16
+
+
+class _FdOp(ctypes.Structure):
+    """csrc/decode_fused.h: FdOp."""
+    _fields_ = ([(n, ctypes.c_int) for n in ("kind", "mode", "M", "N", "K", "ksplit", "n_parts", "taps")]
+                + [(n, ctypes.c_longlong) for n in ("ldx", "ldw", "ldy", "part_stride")]
+                + [(n, ctypes.c_void_p) for n in ("x", "w", "y", "aux0", "aux1", "aux2", "aux3", "idx")]
+                + [("eps0", ctypes.c_float), ("eps1", ctypes.c_float), ("pad0", ctypes.c_int), ("pad1", ctypes.c_int)])
+
+
+class FusedDecode:
+    """While entered, the calls of a decode step that the fused kernel knows (`gemm_skinny` and its
+    forms, `add_norm`, the short convolution's decode form; bfloat16, at most 16 rows) are not
+    launched but collected, in program order, and run as ONE cooperative launch (`cm_fused_decode`)
+    as soon as a call comes that the kernel does not know, when the kernel's table is full, or at
+    the end.  Memory that the collected calls use stays referenced until they have been launched.
+    `bar`: the kernel's barrier word (uint32 zero on the device); `err`: the device flag that a
+    block raises when its wait at the barrier runs out."""
+
+    def __init__(self, bar, err):
+        self.bar, self.err = bar, err
+        self.ops, self.keep = [], []
+        self.max_ops = lib().cm_fused_decode_max_ops()
+        self.max_width = lib().cm_fused_decode_max_width()
+        self._flushing = False
+
+    def __enter__(self):
+        global _fuser
+        self._before, _fuser = _fuser, self
+        return self
+
+    def __exit__(self, exc_type, *exc):
+        global _fuser
+        try:
+            if exc_type is None:
+                self.flush()
+        finally:
+            _fuser = self._before
+            self.ops, self.keep = [], []
+
+    def add(self, keep, **fields):
+        op = _FdOp()
+        for k, v in fields.items():
+            setattr(op, k, v)
+        self.ops.append(op)
+        self.keep.extend(keep)
+        if len(self.ops) >= self.max_ops:
+            self.flush()
+
+    def flush(self):
+        if not self.ops or self._flushing:
+            return
+        self._flushing = True
+        try:
+            n = len(self.ops)
+            seg = (ctypes.c_int * 4)(n, 0, 0, 0)
+            blob = bytes(seg) + b"".join(bytes(op) for op in self.ops)
+            blob += b"\0" * (16 + self.max_ops * ctypes.sizeof(_FdOp) - len(blob))
+            ops, self.ops, self.keep = self.ops, [], []
+            _check(lib().cm_fused_decode(blob, _ptr(self.bar), _ptr(self.err), _stream()), "fused_decode",
+                   cost=lambda: (f"{n} operations", 0, 0))
+        finally:
+            self._flushing = False
+
+
+_fuser = None
+
+
+def _fusable_rows(x, w):
+    """x @ w^T can join a fused segment: bfloat16, at most 16 rows, 16-byte aligned rows."""
+    return (_fuser is not None and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= FD_MAX_ROWS
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.stride(1) == 1
+            and w.stride(1) == 1 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 def lib():
     """The loaded CUDA library, with argument types set."""
     global _lib
+    if _fuser is not None and _fuser.ops and not _fuser._flushing:
+        _fuser.flush()             # a call that is launched on its own: what was collected runs before it
     if _timeline is not None and _lib is not None:
         _timeline.begin()          # every binding asks for the library right before its launch
     if _lib is None:
@@ -131,6 +212,8 @@ def lib():
             fn.restype = _i
         handle.cm_set_pdl.argtypes = [_i]
         handle.cm_set_pdl.restype = None
+        handle.cm_fused_decode.argtypes = [ctypes.c_char_p, _vp, _vp, _vp]
+        handle.cm_fused_decode.restype = _i
         if os.environ.get("CATENA_B200_PDL", "1") == "0":
             handle.cm_set_pdl(0)
         _lib = handle
@@ -239,6 +322,21 @@ class PartialSums:
 def add_norm(h_out, n_out, m, h_in, w_post, w_next, eps_post, eps_next):
     """h_out = h_in + (norm(m; w_post) or m); n_out = norm(h_out; w_next) when w_next is given.
     m: a tensor, or the PartialSums a product left."""
+    if (_fuser is not None and h_in.dtype == torch.bfloat16 and h_in.shape[0] <= FD_MAX_ROWS and h_in.shape[1] % 8 == 0
+            and h_in.shape[1] <= _fuser.max_width and h_in.is_contiguous() and h_out.is_contiguous()
+            and (n_out is None or n_out.is_contiguous())):
+        rows, H = h_in.shape
+        if isinstance(m, PartialSums):
+            src, n_parts, stride = m.parts, m.parts.shape[0], rows * H
+            ok = src.dtype == torch.float32 and src.is_contiguous() and n_parts <= 8
+        else:
+            src, n_parts, stride = m, 0, 0
+            ok = m.dtype == torch.bfloat16 and m.is_contiguous()
+        if ok:
+            _fuser.add((h_out, n_out, src, h_in, w_post, w_next), kind=FD_ADD_NORM, M=rows, N=H, n_parts=n_parts,
+                       part_stride=stride, x=_ptr(h_in), y=_ptr(h_out), aux0=_ptr(src), aux1=_ptr(w_post),
+                       aux2=_ptr(w_next), aux3=_ptr(n_out), eps0=eps_post, eps1=eps_next)
+            return
     if isinstance(m, PartialSums):
         parts = m.parts
         _need_cuda(h_out, parts, h_in)
@@ -291,6 +389,11 @@ def gemm_skinny(y, x, w, swiglu=False):
         raise KernelError(f"gemm_skinny shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_skinny takes bfloat16 operands")
+    if _fusable_rows(x, w) and y.stride(1) == 1 and (y.dtype == torch.bfloat16 or (y.dtype == torch.float32 and not swiglu)):
+        mode = FD_SWIGLU if swiglu else (FD_PLAIN if y.dtype == torch.bfloat16 else FD_F32)
+        _fuser.add((y, x, w), kind=FD_GEMV, mode=mode, M=M, N=N, K=K, ksplit=1, ldx=x.stride(0), ldw=w.stride(0),
+                   ldy=y.stride(0), x=_ptr(x), w=_ptr(w), y=_ptr(y))
+        return
     _check(lib().cm_gemm_skinny(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0),
                                 y.stride(0), int(swiglu), _stream()), "gemm_skinny" + ("_swiglu" if swiglu else ""),
            cost=lambda: (f"{M}x{w.shape[0]}x{K}", _nbytes(x, w, y), 2 * M * w.shape[0] * K))
@@ -306,6 +409,10 @@ def gemm_skinny_parts(parts, x, w):
         raise KernelError(f"gemm_skinny_parts shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, parts {tuple(parts.shape)}")
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_skinny_parts takes bfloat16 operands")
+    if _fusable_rows(x, w) and S <= 8:
+        _fuser.add((parts, x, w), kind=FD_GEMV, mode=FD_PARTS, M=M, N=N, K=K, ksplit=S, ldx=x.stride(0), ldw=w.stride(0),
+                   ldy=N, part_stride=M * N, x=_ptr(x), w=_ptr(w), y=_ptr(parts))
+        return
     _check(lib().cm_gemm_skinny_parts(_ptr(parts), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), N, M * N, S,
                                       _stream()), "gemm_skinny_parts",
            cost=lambda: (f"{M}x{N}x{K} in {S} slices", _nbytes(x, w, parts), 2 * M * N * K))
@@ -496,6 +603,14 @@ def gemm_skinny_shortconv(y, x, w_in, taps, state, seq_slot):
         raise KernelError("gemm_skinny_shortconv takes bfloat16 operands, float taps and state")
     if not (taps.is_contiguous() and state.is_contiguous()):
         raise KernelError("gemm_skinny_shortconv: taps and state must be contiguous")
+    if _fusable_rows(x, w_in) and H % 8 == 0 and y.stride(0) % 8 == 0 and y.data_ptr() % 16 == 0:
+        # in the fused kernel: in_proj as a product of its own, then the convolution over its output
+        bcx = torch.empty((M, 3 * H), dtype=torch.bfloat16, device=x.device)
+        _fuser.add((bcx, x, w_in), kind=FD_GEMV, mode=FD_PLAIN, M=M, N=3 * H, K=K, ksplit=1, ldx=x.stride(0),
+                   ldw=w_in.stride(0), ldy=3 * H, x=_ptr(x), w=_ptr(w_in), y=_ptr(bcx))
+        _fuser.add((y, taps, state, seq_slot), kind=FD_CONV, M=M, N=H, taps=KT, ldx=3 * H, ldy=y.stride(0), x=_ptr(bcx),
+                   y=_ptr(y), aux0=_ptr(taps), aux3=_ptr(state), idx=_ptr(seq_slot))
+        return
     _check(lib().cm_gemm_skinny_shortconv(_ptr(y), _ptr(x), _ptr(w_in), _ptr(taps), _ptr(state), _ptr(seq_slot), M, H,
                                           K, KT, x.stride(0), w_in.stride(0), y.stride(0), _stream()),
            "gemm_skinny_shortconv",

@@ -30,6 +30,7 @@ from .linear import Linear
 
 class GQAttention(Mixer):
     prompt_capturable = True
+    fused_decode_ok = True
     supports_append = True
 
     def __init__(self, prefix, hidden, heads, kv_heads, head_dim, window, position, qk_norm_eps,

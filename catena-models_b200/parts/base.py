@@ -73,6 +73,12 @@ class Part:
     # forward() reads what is older than the step from its state.  A model with a part that cannot
     # is stepped with whole prompts and single tokens only.
     supports_append = False
+    # True for a part whose decode steps (one token per sequence) launch nothing but this library's
+    # kernels, in program order, on tensors that stay alive until the step ends: its products, residual
+    # sums and convolution may then be collected and run inside one persistent kernel
+    # (kernels.FusedDecode).  A part that runs torch operations of its own between kernels must leave
+    # this False: those would overtake the collected calls.
+    fused_decode_ok = False
 
     def tensor_specs(self):
         return []
@@ -97,6 +103,9 @@ class Part:
 
     def all_capturable(self):
         return self.capturable and all(c.all_capturable() for c in self.children())
+
+    def all_fused_decode_ok(self):
+        return self.fused_decode_ok and all(c.all_fused_decode_ok() for c in self.children())
 
     def all_support_append(self):
         return self.supports_append and all(c.all_support_append() for c in self.children())

@@ -14,6 +14,7 @@ from .base import Block, register_part
 
 class SandwichBlock(Block):
     prompt_capturable = True
+    fused_decode_ok = True
     supports_append = True
 
     def __init__(self, mixer, feed_forward, input_norm, ffn_norm, post_mixer_norm=None, post_ffn_norm=None):

@@ -11,6 +11,7 @@ from .linear import Linear
 
 class SwiGLU(FeedForward):
     prompt_capturable = True
+    fused_decode_ok = True
     supports_append = True
 
     def __init__(self, prefix, hidden, intermediate, names=None):

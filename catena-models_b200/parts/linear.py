@@ -15,6 +15,7 @@ from .base import Part
 
 class Linear(Part):
     prompt_capturable = True
+    fused_decode_ok = True
     supports_append = True
 
     def __init__(self, names, rows, in_features, role="matrix"):

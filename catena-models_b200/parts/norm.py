@@ -15,6 +15,7 @@ from .base import Norm, register_part
 
 class RMSNorm(Norm):
     prompt_capturable = True
+    fused_decode_ok = True
     supports_append = True
     fused_kind = "rms"          # what the fused residual kernel can absorb
 

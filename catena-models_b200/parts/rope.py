@@ -17,6 +17,7 @@ from .base import Position, register_part
 
 class Rotary(Position):
     prompt_capturable = True
+    fused_decode_ok = True
     supports_append = True
 
     def __init__(self, head_dim, theta, factors_name=None):
@@ -43,6 +44,7 @@ class Rotary(Position):
 class NoPosition(Position):
     """No position encoding: the head vectors are left unrotated."""
     prompt_capturable = True
+    fused_decode_ok = True
     supports_append = True
 
 

@@ -17,6 +17,7 @@ from .linear import Linear
 
 class ShortConv(Mixer):
     prompt_capturable = True
+    fused_decode_ok = True
     supports_append = True
 
     def __init__(self, prefix, hidden, taps, names=None):

@@ -261,3 +261,37 @@ def test_tokens_are_taken_from_the_step_before_only_if_it_sampled(tmp_path):
     logits, toks = eng.step(slots, [[9], [10]], sampling=samp(5))
     assert toks == logits.argmax(-1).tolist()
     eng.release(slots)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "L"])
+def test_decode_through_the_persistent_kernel(tmp_path, name):
+    """The opt-in decode path that collects a step's products, residual sums and convolutions into a
+    few persistent launches: the same logits as the plain model, replayed from a recording, over
+    page borders and a wrapping ring, for one and for several sequences; far fewer launches."""
+    from catena_models_b200.api import Model
+
+    folder = tiny.make_folder(tmp_path, name, seed=6)
+    cfg = tiny.ALL[name][0]
+    seqs = [tiny.random_prompt(n, cfg["vocab_size"], seed=n) for n in (150, 40, 71)]
+    launches = {}
+    for fused in (False, True):
+        model = Model.load(folder, dtype="bfloat16", max_tokens=1024)
+        model.decoder.rt.fused_decode = fused
+        eng = model.engine
+        slots = eng.admit(3)
+        got = [eng.step(slots, [s[:-90] if len(s) > 100 else s[:-30] for s in seqs]).clone()]
+        heads = [len(s) - 90 if len(s) > 100 else len(s) - 30 for s in seqs]
+        from catena_models_b200 import kernels
+        before = kernels.launches
+        for t in range(30):
+            got.append(eng.step(slots, [[s[h + t]] for s, h in zip(seqs, heads)]).clone())
+        launches[fused] = kernels.launches - before
+        for t in range(30, 90):                                  # the longest sequence alone
+            got.append(eng.step(slots[:1], [[seqs[0][heads[0] + t]]]).clone())
+        eng.release(slots)
+        eng.check_errors()
+        for i, (s, h) in enumerate(zip(seqs, heads)):
+            exact, same = _plain(folder, s, "bfloat16")
+            rows = [g[i:i + 1] for g in got[:31]] + ([g[:1] for g in got[31:]] if i == 0 else [])
+            check(torch.cat(rows), exact[h - 1:h - 1 + len(rows)], "bfloat16", same[h - 1:h - 1 + len(rows)])
+    assert launches[True] < launches[False] / 2

@@ -828,3 +828,71 @@ def test_zero_slots_clears_the_named_rows_of_every_layer(K, dtype):
     assert torch.equal(store[:, keep], before[:, keep])
     with pytest.raises(K.KernelError):
         K.zero_slots(store, [90])
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 16])
+def test_fused_decode_segment_runs_collected_calls_in_order(K, M):
+    """Products in all four output forms at sizes that fill no tile or stage, the residual + norm
+    operation over partial sums and over a finished product, and the short convolution's decode form,
+    collected and run by the persistent kernel in one launch; every result against the same call
+    launched on its own.  More calls than the kernel's table holds make it launch twice."""
+    bar = torch.zeros(4, dtype=torch.int32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    H, F, taps = 200, 136, 3
+
+    def run(fused):
+        g = lambda *shape, seed, dtype=torch.bfloat16, scale=1.0: rnd(*shape, dtype=dtype, seed=seed, scale=scale)
+        out = {}
+        x = g(M, H, seed=1)
+        w_in, w_out = g(3 * H, H, seed=2, scale=0.1), g(H, H, seed=3, scale=0.1)
+        w_gu, w_down, w_head = g(2 * F, H, seed=4, scale=0.1), g(H, F, seed=5, scale=0.1), g(1000, H, seed=6, scale=0.1)
+        conv_w = g(H, taps, seed=7, dtype=torch.float32)
+        state = g(M + 2, taps - 1, H, seed=8, dtype=torch.float32)
+        slots = torch.arange(1, M + 1, dtype=torch.int32, device=DEV)
+        post, nxt = g(H, seed=9, dtype=torch.float32), g(H, seed=10, dtype=torch.float32)
+        h = g(M, H, seed=11)
+        ctx = K.FusedDecode(bar, err) if fused else None
+        if ctx:
+            ctx.__enter__()
+        launches0 = K.launches
+        y = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+        K.gemm_skinny_shortconv(y, x, w_in, conv_w, state, slots)                 # in_proj + convolution
+        parts = torch.empty(4, M, H, dtype=torch.float32, device=DEV)
+        K.gemm_skinny_parts(parts, y, w_out)                                      # out_proj as partial sums
+        n = torch.empty_like(h)
+        K.add_norm(h, n, K.PartialSums(parts, torch.bfloat16), h, post, nxt, 1e-5, 1e-6)
+        a = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
+        K.gemm_skinny(a, n, w_gu, swiglu=True)
+        d = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+        K.gemm_skinny(d, a, w_down)
+        n2 = torch.empty_like(h)
+        K.add_norm(h, n2, d, h, None, nxt, 0.0, 1e-6)
+        logits = torch.empty(M, 1000, dtype=torch.float32, device=DEV)
+        K.gemm_skinny(logits, n2, w_head)
+        h2 = torch.empty_like(h)
+        for i in range(30):                                                       # past the table's 24 entries
+            K.add_norm(h2, n2, d, h, post, nxt, 1e-5, 1e-6)
+        if ctx:
+            ctx.__exit__(None, None, None)
+        out.update(y=y, parts=parts.sum(0), n=n, a=a, d=d, h=h, h2=h2, n2=n2, logits=logits, state=state)
+        return out, K.launches - launches0
+
+    one, n_one = run(False)
+    fused, n_fused = run(True)
+    assert n_fused == 2 and n_one > 30
+    assert int(err) == 0 and int(bar[0]) == 0
+    for name in one:
+        close(fused[name], one[name], torch.bfloat16 if one[name].dtype == torch.bfloat16 else torch.float32,
+              **(dict(rtol=3e-2, atol=3e-2) if name in ("h", "h2", "n2", "logits", "d", "a", "n") else {}))
+
+
+def test_fused_decode_refuses_what_it_cannot_run(K):
+    bar = torch.zeros(4, dtype=torch.int32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x = rnd(17, 64, dtype=torch.bfloat16)
+    w = rnd(32, 64, dtype=torch.bfloat16)
+    y = torch.empty(17, 32, dtype=torch.bfloat16, device=DEV)
+    with K.FusedDecode(bar, err) as f:
+        K.gemm_skinny(y, x, w)                       # 17 rows: not collected, launched on its own
+        assert not f.ops
+    close(y, x.float() @ w.float().T, torch.bfloat16)

@@ -38,7 +38,7 @@ def rel(got, ref):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
-def test_replay_three_ways(tmp_path, name, dtype):
+def test_replay_four_ways(tmp_path, name, dtype):
     folder = tiny.make_folder(tmp_path, name, seed=7)
     cfg, tensors = plain_lfm3.load_folder(folder)
     V = cfg["vocab_size"]
