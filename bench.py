@@ -285,7 +285,9 @@ def prompt_flops(cfg, lengths, wanted_rows):
     return flops
 
 
-def prefill_run(model, lengths, vocab, cfg, peak_tflops, repeats=3):
+def prefill_run(model, lengths, vocab, cfg, peak_tflops, repeats=3, chunk=0):
+    """One prompt step over sequences of the given lengths; with `chunk`, steps of that many tokens a
+    sequence, each on top of the ones before (append steps, which read the older keys from the cache)."""
     import torch
 
     eng = model.engine
@@ -300,7 +302,12 @@ def prefill_run(model, lengths, vocab, cfg, peak_tflops, repeats=3):
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        eng.step(slots, prompts)
+        if chunk > 0:
+            for at in range(0, max(lengths), chunk):
+                part = [(s, p[at:at + chunk]) for s, p in zip(slots, prompts) if at < len(p)]
+                eng.step([s for s, _ in part], [p for _, p in part])
+        else:
+            eng.step(slots, prompts)
         b.record()
         torch.cuda.synchronize()
         eng.release(slots)
@@ -441,6 +448,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the further decode points")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison with the 32-bit engine")
     ap.add_argument("--prefill-tokens", type=int, default=None, help="prompt length of `--only prefill`")
+    ap.add_argument("--prefill-chunk", type=int, default=0,
+                    help="with `--only prefill`: run the prompt in steps of this many tokens (append steps)")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only (small captures under a profiler); prints that part's facts")
     ap.add_argument("--kernel-table", action="store_true",
@@ -497,7 +506,7 @@ def main():
         print(json.dumps({k: v for k, v in run.items() if k != "rows"}))
         return 0
     if args.only == "prefill":
-        print(json.dumps(prefill_run(model, prefill_lengths, vocab, cfg, pk["bf16_tflops"])))
+        print(json.dumps(prefill_run(model, prefill_lengths, vocab, cfg, pk["bf16_tflops"], chunk=args.prefill_chunk)))
         return 0
 
     def frac_of(run, b):

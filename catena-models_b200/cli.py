@@ -53,6 +53,9 @@ def parser():
     ap.add_argument("--tg-context", type=_positive, default=1, help="prompt context of the decode benchmark")
     ap.add_argument("--bench-runs", type=_positive, default=1, help="measured runs per benchmark test")
     ap.add_argument("--batch", type=_positive, default=1, help="sequences per step in --bench")
+    ap.add_argument("--pp-chunk", type=int, default=0,
+                    help="run the prompt-processing test in steps of this many tokens, each on top of the ones before "
+                         "(the reference's server fills its cache in blocks of 1,024, src/server/prefix_cache.rs:4); 0: one step")
     return ap
 
 
@@ -70,9 +73,10 @@ def _rate_stats(samples):
     return statistics.mean(rates), (statistics.stdev(rates) if len(rates) > 1 else None)
 
 
-def run_benchmark(model, pp, tg, tg_context, runs, batch):
-    """`pp N`: a fresh cache slot and one prompt step; `tg N / ctx C`: a C-token prompt, two
-    untimed decode steps, N timed ones (src/main.rs:393-445), for `batch` sequences at once."""
+def run_benchmark(model, pp, tg, tg_context, runs, batch, pp_chunk=0):
+    """`pp N`: a fresh cache slot and one prompt step (or steps of `pp_chunk` tokens); `tg N / ctx C`:
+    a C-token prompt, two untimed decode steps, N timed ones (src/main.rs:393-445), for `batch`
+    sequences at once."""
     import torch
 
     vocab = model.decoder.vocab_size
@@ -85,11 +89,15 @@ def run_benchmark(model, pp, tg, tg_context, runs, batch):
             slots = eng.admit(batch)
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            eng.step(slots, [toks] * batch)
+            step = pp_chunk if pp_chunk > 0 else pp
+            for at in range(0, pp, step):
+                eng.step(slots, [toks[at:at + step]] * batch)
             torch.cuda.synchronize()
             samples.append((pp * batch, time.perf_counter() - t0))
             eng.release(slots)
-        rows.append((f"pp{pp}" + (f"x{batch}" if batch > 1 else ""), *_rate_stats(samples[1:])))
+        eng.check_errors()
+        rows.append((f"pp{pp}" + (f"/{pp_chunk}" if pp_chunk > 0 else "") + (f"x{batch}" if batch > 1 else ""),
+                     *_rate_stats(samples[1:])))
     if tg > 0:
         toks = _synthetic(tg_context + tg + 2, vocab)
         samples = []
@@ -105,6 +113,7 @@ def run_benchmark(model, pp, tg, tg_context, runs, batch):
             torch.cuda.synchronize()
             samples.append((tg * batch, time.perf_counter() - t0))
             eng.release(slots)
+        eng.check_errors()
         rows.append((f"tg{tg}/ctx{tg_context}" + (f"x{batch}" if batch > 1 else ""), *_rate_stats(samples)))
     params = model.parameter_count()
     size = model.decoder.weight_bytes_per_step()
@@ -152,9 +161,10 @@ def main(argv=None):
     else:
         with open(args.random) as fh:
             model = Model.random(json.load(fh), seed=args.weights_seed, dtype=args.dtype, max_tokens=max_tokens)
-    print(f"loaded {model.parameter_count() / 1e6:.2f} M parameters in {time.perf_counter() - t0:.2f}s", file=sys.stderr)
+    print(f"loaded {model.parameter_count() / 1e6:.2f} M parameters in {time.perf_counter() - t0:.2f}s; "
+          f"cache of {max_tokens} tokens: {model.engine.cache.bytes() / 2**20:.1f} MiB", file=sys.stderr)
     if args.bench:
-        run_benchmark(model, args.pp, args.tg, args.tg_context, args.bench_runs, args.batch)
+        run_benchmark(model, args.pp, args.tg, args.tg_context, args.bench_runs, args.batch, args.pp_chunk)
         return 0
 
     import torch
