@@ -356,8 +356,8 @@ def kernel_table(model, cfg, pk, batch, context, prompt_lengths, graph_ms):
     from catena_models_b200.engine.engine import Engine
 
     vocab = cfg["vocab_size"]
-    eng = Engine(model.decoder, max(batch * (context + 64), sum(prompt_lengths) + 64 * len(prompt_lengths)),
-                 max(batch, len(prompt_lengths)), use_graphs=False)
+    tokens_held = max(batch * (context + 64), sum(prompt_lengths) + 64 * len(prompt_lengths))
+    eng = Engine(model.decoder, tokens_held, max(batch, len(prompt_lengths)), use_graphs=False)
     KVH, HD, QS = cfg["num_key_value_heads"], cfg["head_dim"], cfg["num_attention_heads"] * cfg["head_dim"]
     window = cfg["sliding_window"]
     out = {}
@@ -379,35 +379,43 @@ def kernel_table(model, cfg, pk, batch, context, prompt_lengths, graph_ms):
                 r["flops"] = r["calls"] * 4 * QS * keys
                 r["bytes"] = r["calls"] * sum(lengths) * (2 * QS + 2 * KVH * HD) * 2
 
-    # ---- decode
-    slots = eng.admit(batch)
+    # ---- decode: the calls are timed inside the recorded step (events that a captured graph may hold),
+    # so that every kernel follows its predecessor as in production; the event nodes between the kernels
+    # make this replay a little slower than the step without them, which is timed too
+    geng = Engine(model.decoder, batch * (context + 64), batch, use_graphs=True)
+    slots = geng.admit(batch)
     state = 0x9E3779B97F4A7C15
     for s in slots:
         toks, state = synthetic_tokens(context, vocab, state)
-        eng.step([s], [toks], [[]])
-    feed, state = synthetic_tokens(4 * batch, vocab, state)
-    for i in range(3):
-        eng.step(slots, [[t] for t in feed[i * batch:(i + 1) * batch]])
-    torch.cuda.synchronize()
+        geng.step([s], [toks], [[]])
+    feed, state = synthetic_tokens(8 * batch, vocab, state)
+    step = lambda i: geng.step(slots, [[t] for t in feed[i * batch:(i + 1) * batch]])
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with kernels.Timeline() as tl:
-        a.record()
-        eng.step(slots, [[t] for t in feed[3 * batch:]])
-        b.record()
+    with kernels.Timeline(in_graph=True) as tl:
+        step(0)                                            # runs kernel by kernel, then records: both are collected
+    tl.keep_last(len(tl.calls) // 2)                       # the recording's events
+    for i in range(1, 4):
+        step(i)
+    torch.cuda.synchronize()
+    a.record()
+    step(4)
+    b.record()
+    torch.cuda.synchronize()
     rows = tl.rows()
-    attention_costs(rows, [context + 4] * batch, True)
-    out["decode"] = (rows, a.elapsed_time(b) * 1e3, f"decode step, {batch} sequences at {context} tokens "
-                     f"(recorded graph: {graph_ms * 1e3:.0f} us a step)" if graph_ms else
-                     f"decode step, {batch} sequences at {context} tokens")
-    eng.release(slots)
+    attention_costs(rows, [context + 5] * batch, True)
+    out["decode"] = (rows, a.elapsed_time(b) * 1e3, f"decode step, {batch} sequences at {context} tokens, replayed from its "
+                     f"recording with an event pair around every kernel")
+    geng.release(slots)
+    del geng
     # ---- prompt
     prompts = []
     for n in prompt_lengths:
         toks, state = synthetic_tokens(n, vocab, state)
         prompts.append(toks)
-    for rep in range(2):
+    for rep in range(3):
         slots = eng.admit(len(prompts))
         torch.cuda.synchronize()
+        time.sleep(SETTLE_SECONDS)
         with kernels.Timeline() as tl:
             a.record()
             eng.step(slots, prompts)
@@ -422,8 +430,8 @@ def kernel_table(model, cfg, pk, batch, context, prompt_lengths, graph_ms):
         rows, step_us, title = out[key]
         total = sum(r["us"] for r in rows)
         print(f"\n### {title}\n")
-        print(f"kernel by kernel the step takes {step_us:.0f} us on the stream; the kernels' own times add up to "
-              f"{total:.0f} us ({total / step_us:.2f} of it; the rest is the host between launches).  Peaks "
+        print(f"the step takes {step_us:.0f} us on the stream; the kernels' own times add up to "
+              f"{total:.0f} us ({total / step_us:.2f} of it; the rest lies between the kernels).  Peaks "
               f"({pk['source']}): {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s.\n")
         print("| kernel | operands | calls | us | share | GB/s | of peak | TFLOP/s | of peak |")
         print("|---|---|---|---|---|---|---|---|---|")

@@ -66,11 +66,21 @@ class Timeline:
     operation needs by its definition (each operand once).  `rows()` adds the calls up by name
     and shape.  catena-models prints its own phase timers on request (CATENA_COMPILE_TIMINGS,
     src/catena.rs:82-87; per-phase rates, src/main.rs:364-371); this is that habit for kernels.
-    Off unless entered: an ordinary run records no events."""
+    Off unless entered: an ordinary run records no events.
 
-    def __init__(self):
+    `in_graph=True` makes the events of a kind that may be recorded while a CUDA graph is captured and
+    read after the graph has been replayed: the calls of a decode step are then timed inside the
+    recorded step (`keep_last(n)` drops what was collected before the capture), where a kernel follows
+    its predecessor as it does in production, instead of after the host's pause between two launches."""
+
+    def __init__(self, in_graph=False):
         self.calls = []            # [name, shape, bytes, flops, start event, end event, launches]
         self._start = None
+        self._event = ((lambda: torch.cuda.Event(enable_timing=True, external=True)) if in_graph
+                       else (lambda: torch.cuda.Event(enable_timing=True)))
+
+    def keep_last(self, n):
+        self.calls = self.calls[-n:]
 
     def __enter__(self):
         global _timeline
@@ -82,13 +92,13 @@ class Timeline:
         _timeline = self._before
 
     def begin(self):
-        self._start = torch.cuda.Event(enable_timing=True)
+        self._start = self._event()
         self._start.record()
 
     def end(self, name, n, cost):
         if self._start is None:
             return
-        stop = torch.cuda.Event(enable_timing=True)
+        stop = self._event()
         stop.record()
         shape, nbytes, flops = cost() if cost is not None else ("", 0, 0)
         self.calls.append([name, shape, nbytes, flops, self._start, stop, n])
