@@ -33,6 +33,7 @@ __device__ __forceinline__ void load8<bf16>(const bf16* p, float* out) {
 //   u = T((x * inv_rms(x)) * w)           when w is given (w_q for q heads, w_k for k heads)
 //   o_i       = u_i cos a - u_{i+HD/2} sin a
 //   o_{i+HD/2}= u_{i+HD/2} cos a + u_i sin a,   a = float(pos) * rate[i]      when rate is given
+// (pairs of the two halves; with `interleaved` the pairs are neighbours, (2i, 2i+1), instead)
 // q and k are overwritten in place; k and the raw v also go to the cache entry of (slot, pos):
 // entry = pos (growing group) or pos % ring (ring group; during a prompt longer than the ring
 // only the last `ring` positions are stored, so that no two rows meet in one entry).
@@ -44,7 +45,7 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
                                   const int* __restrict__ seq_slot, const int* __restrict__ seq_end,
                                   T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
                                   int ptab_stride, int ring, int QH, int KVH, int HD, float eps, int T_tokens,
-                                  int heads_per_warp) {
+                                  int heads_per_warp, int interleaved) {
     pdl_trigger();
     pdl_wait();
     // One warp per token and group of `heads_per_warp` heads (grid.y walks the groups: many heads
@@ -88,8 +89,8 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
             const int i = lane + 32 * p;
             lo[p] = hi[p] = 0.f;
             if (i < half) {
-                lo[p] = to_f32(x[i]);
-                hi[p] = to_f32(x[i + half]);
+                lo[p] = to_f32(x[interleaved ? 2 * i : i]);
+                hi[p] = to_f32(x[interleaved ? 2 * i + 1 : i + half]);
                 ss += lo[p] * lo[p] + hi[p] * hi[p];
             }
         }
@@ -104,16 +105,17 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
             const int i = lane + 32 * p;
             if (i >= half) continue;
             float a = lo[p], bq = hi[p];
+            const int i_lo = interleaved ? 2 * i : i, i_hi = interleaved ? 2 * i + 1 : i + half;
             if (w) {
-                a = rounded<T>((a * inv) * w[i]);
-                bq = rounded<T>((bq * inv) * w[i + half]);
+                a = rounded<T>((a * inv) * w[i_lo]);
+                bq = rounded<T>((bq * inv) * w[i_hi]);
             }
             const T at = from_f32<T>(a * cs[p] - bq * sn[p]), bt = from_f32<T>(bq * cs[p] + a * sn[p]);
-            x[i] = at;
-            x[i + half] = bt;
+            x[i_lo] = at;
+            x[i_hi] = bt;
             if (kdst) {
-                kdst[i] = at;
-                kdst[i + half] = bt;
+                kdst[i_lo] = at;
+                kdst[i_hi] = bt;
             }
         }
     }
@@ -227,7 +229,7 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
                              const float* rate, const int* tok_pos, const int* tok_seq,
                              const int* seq_slot, const int* seq_end, void* pool, long long pages,
                              const int* ptab, int ptab_stride, int ring, int T, int QH, int KVH,
-                             int HD, float eps, cudaStream_t st) {
+                             int HD, float eps, int interleaved, cudaStream_t st) {
     if (T <= 0) return CM_OK;
     if (HD % 2 || HD <= 0) CM_REFUSE("qk_prepare: head size %d is not even", HD);
     if (ring % PAGE_TOKENS) CM_REFUSE("qk_prepare: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
@@ -237,7 +239,7 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
                      (((uintptr_t)qkv | (uintptr_t)pool | (uintptr_t)wq | (uintptr_t)wk) & 15) == 0;
     // Measured on B200 (32 + 8 heads of 64): 2,048 tokens 23.4 -> 12.4 us, 8,192 tokens 81.8 -> 24.2 us;
     // a decode step of 8 or 64 tokens is quicker with a channel per lane (3.2 against 3.9 us).
-    if (vec && T >= 128 && (dt == DT_F32 || dt == DT_BF16)) {
+    if (vec && T >= 128 && !interleaved && (dt == DT_F32 || dt == DT_BF16)) {
         const int hpp = 32 / (HD / 16), passes = (QH + KVH + hpp - 1) / hpp;
         // A warp walks several passes of its token (sine and cosine are formed once per warp) when
         // the tokens alone give the SMs enough warps; with fewer tokens the passes are spread.
@@ -259,11 +261,11 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
     if (dt == DT_F32)
         cm_launch(qk_prepare_kernel<float>, grid, block, smem, st, (float*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
                                                             seq_slot, seq_end, (float*)pool, pages, ptab,
-                                                            ptab_stride, ring, QH, KVH, HD, eps, T, hpw);
+                                                            ptab_stride, ring, QH, KVH, HD, eps, T, hpw, interleaved);
     else if (dt == DT_BF16)
         cm_launch(qk_prepare_kernel<bf16>, grid, block, smem, st, (bf16*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
                                                            seq_slot, seq_end, (bf16*)pool, pages, ptab,
-                                                           ptab_stride, ring, QH, KVH, HD, eps, T, hpw);
+                                                           ptab_stride, ring, QH, KVH, HD, eps, T, hpw, interleaved);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();

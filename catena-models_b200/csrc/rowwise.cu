@@ -11,7 +11,7 @@
 template <typename T, typename TT>
 __global__ void embed_gather_kernel(T* __restrict__ out, const TT* __restrict__ table,
                                     const int* __restrict__ tokens, const int* __restrict__ sampled, int H, int V,
-                                    int* __restrict__ err) {
+                                    float scale, int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -21,21 +21,22 @@ __global__ void embed_gather_kernel(T* __restrict__ out, const TT* __restrict__ 
     if (!ok && threadIdx.x == 0 && err) atomicExch(err, 1);
     const TT* src = table + (long long)(ok ? tok : 0) * H;
     T* dst = out + (long long)t * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = from_f32<T>(ok ? to_f32(src[c]) : 0.f);
+    // scale: the factor some architectures put on their embeddings (1 leaves the row as it is)
+    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = from_f32<T>(ok ? to_f32(src[c]) * scale : 0.f);
 }
 
 extern "C" int cm_embed_gather(int dt, int dt_table, void* out, const void* table, const int* tokens,
-                               const int* sampled, int T, int H, int V, int* err, cudaStream_t st) {
+                               const int* sampled, int T, int H, int V, float scale, int* err, cudaStream_t st) {
     if (T <= 0) return CM_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (dt == DT_F32 && dt_table == DT_F32)
-        cm_launch(embed_gather_kernel<float, float>, T, threads, 0, st, (float*)out, (const float*)table, tokens, sampled, H, V, err);
+        cm_launch(embed_gather_kernel<float, float>, T, threads, 0, st, (float*)out, (const float*)table, tokens, sampled, H, V, scale, err);
     else if (dt == DT_BF16 && dt_table == DT_BF16)
-        cm_launch(embed_gather_kernel<bf16, bf16>, T, threads, 0, st, (bf16*)out, (const bf16*)table, tokens, sampled, H, V, err);
+        cm_launch(embed_gather_kernel<bf16, bf16>, T, threads, 0, st, (bf16*)out, (const bf16*)table, tokens, sampled, H, V, scale, err);
     else if (dt == DT_BF16 && dt_table == DT_F32)
-        cm_launch(embed_gather_kernel<bf16, float>, T, threads, 0, st, (bf16*)out, (const float*)table, tokens, sampled, H, V, err);
+        cm_launch(embed_gather_kernel<bf16, float>, T, threads, 0, st, (bf16*)out, (const float*)table, tokens, sampled, H, V, scale, err);
     else if (dt == DT_F32 && dt_table == DT_BF16)
-        cm_launch(embed_gather_kernel<float, bf16>, T, threads, 0, st, (float*)out, (const bf16*)table, tokens, sampled, H, V, err);
+        cm_launch(embed_gather_kernel<float, bf16>, T, threads, 0, st, (float*)out, (const bf16*)table, tokens, sampled, H, V, scale, err);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
@@ -282,6 +283,25 @@ extern "C" int cm_swiglu(int dt, void* a, const void* gu, int rows, int F, cudaS
         cm_launch(swiglu_kernel<bf16>, blocks, threads, 0, st, (bf16*)a, (const bf16*)gu, total, F);
     else
         return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// ------------------------------------------------------------ logit scale and soft cap
+// x <- cap * tanh((x * scale) / cap), or x * scale when cap is 0: what some architectures do to
+// their logits before sampling.  Float logits, in place.
+__global__ void scale_softcap_kernel(float* __restrict__ x, long long total, float scale, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float v = x[i] * scale;
+    x[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+}
+
+extern "C" int cm_scale_softcap(float* x, long long total, float scale, float cap, cudaStream_t st) {
+    if (total <= 0) return CM_OK;
+    cm_launch(scale_softcap_kernel, (unsigned)((total + 255) / 256), 256, 0, st, x, total, scale, cap);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }

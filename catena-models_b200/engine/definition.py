@@ -38,6 +38,10 @@ class ModelDefinition:
     # Other names the same tensors may carry in a file: (prefix, other prefix) pairs; a tensor whose
     # name starts with `prefix` is also looked for under the name with `other prefix` in its place.
     alias_prefixes: tuple = ()
+    # Constants that some architectures put around the stack of blocks; the defaults leave it as LFM3 has it.
+    embedding_scale: float = 1.0     # factor on every embedding row
+    logit_scale: float = 1.0         # factor on the logits
+    logit_softcap: float = 0.0       # logits <- cap * tanh(logits / cap) after the scale; 0: none
 
     def parts(self):
         out = list(self.blocks) + [self.final_norm]

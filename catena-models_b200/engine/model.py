@@ -92,9 +92,11 @@ class DecoderModel:
         if batch.layout.U:
             kernels.scatter_i32(cache.ptab_all, batch.upd_index, batch.upd_value, batch.upd_count, batch.layout.U)
         h = torch.empty((batch.T, self.hidden_size), dtype=rt.dtype, device=rt.device)
-        kernels.embed_gather(h, self.embedding, batch.tokens, self.token_error, sampled=batch.prev_sampled)
+        kernels.embed_gather(h, self.embedding, batch.tokens, self.token_error, sampled=batch.prev_sampled,
+                             scale=self.definition.embedding_scale)
         plan = self.plan
-        n = self.blocks[plan[0].block].input_norm.apply(rt, h)
+        first_norm = self.blocks[plan[0].block].input_norm
+        n = first_norm.apply(rt, h) if first_norm is not None else None
         # when every row is wanted in order (a decode step), the last block's fused residual kernel
         # applies the final norm too and no rows need gathering
         whole = batch.wants_every_row and batch.n_want == batch.T
@@ -106,11 +108,18 @@ class DecoderModel:
             if state is not None:
                 state.owned, state.unit = entry.owns_state, entry.state
             h, n = block.forward(rt, batch, h, n, state, next_norm)
+            if n is None and next_norm is not None and i + 1 < len(plan):
+                n = next_norm.apply(rt, h)             # the block left the next block's norm to its caller
         if batch.n_want == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=rt.device)
         if whole and n is not None:
-            return rt.linear(n, self.head_weight, out_dtype=torch.float32)
-        rows = torch.empty((batch.n_want, self.hidden_size), dtype=rt.dtype, device=rt.device)
-        kernels.gather_rows(rows, h, batch.want_rows)
-        normed = self.final_norm.apply(rt, rows)
-        return rt.linear(normed, self.head_weight, out_dtype=torch.float32)
+            logits = rt.linear(n, self.head_weight, out_dtype=torch.float32)
+        else:
+            rows = torch.empty((batch.n_want, self.hidden_size), dtype=rt.dtype, device=rt.device)
+            kernels.gather_rows(rows, h, batch.want_rows)
+            normed = self.final_norm.apply(rt, rows)
+            logits = rt.linear(normed, self.head_weight, out_dtype=torch.float32)
+        d = self.definition
+        if d.logit_scale != 1.0 or d.logit_softcap > 0.0:
+            kernels.scale_softcap(logits, d.logit_scale, d.logit_softcap)
+        return logits

@@ -20,7 +20,8 @@ DT_F32, DT_BF16 = 0, 1
 _vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 
 _SIGNATURES = {
-    "cm_embed_gather": [_i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],
+    "cm_embed_gather": [_i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _vp],
+    "cm_scale_softcap": [_vp, _ll, _f, _f, _vp],
     "cm_rmsnorm": [_i, _vp, _vp, _vp, _i, _i, _f, _ll, _ll, _vp],
     "cm_add_norm": [_i, _vp, _vp, _vp, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
     "cm_gemm_tc_few_rows_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp],
@@ -32,7 +33,7 @@ _SIGNATURES = {
     "cm_gemm_tc": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp],
     "cm_gemm_tc_few_rows": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp],
     "cm_qk_prepare": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i,
-                      _i, _f, _vp],
+                      _i, _f, _i, _vp],
     "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "cm_attn_prefill_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "cm_attn_prefill_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _ll, _i, _i, _i, _i, _f, _vp, _vp],
@@ -298,13 +299,13 @@ def _need_cuda(*tensors):
 
 
 # ---------------------------------------------------------------------------- row-wise
-def embed_gather(out, table, tokens, err=None, sampled=None):
-    """out[t] = table[tokens[t]]; with `sampled` (int32 device tensor) an entry -(1 + i) of tokens
-    stands for sampled[i]."""
+def embed_gather(out, table, tokens, err=None, sampled=None, scale=1.0):
+    """out[t] = table[tokens[t]] * scale; with `sampled` (int32 device tensor) an entry -(1 + i) of
+    tokens stands for sampled[i]."""
     _need_cuda(out, table, tokens)
     T, H = out.shape
     _check(lib().cm_embed_gather(dtype_code(out.dtype), dtype_code(table.dtype), _ptr(out), _ptr(table), _ptr(tokens),
-                                 _ptr(sampled), T, H, table.shape[0], _ptr(err), _stream()), "embed_gather",
+                                 _ptr(sampled), T, H, table.shape[0], scale, _ptr(err), _stream()), "embed_gather",
            cost=lambda: (f"{T}x{H}", T * H * table.element_size() + _nbytes(out, tokens), 0))
 
 
@@ -363,6 +364,13 @@ def add_norm(h_out, n_out, m, h_in, w_post, w_next, eps_post, eps_next):
     _check(lib().cm_add_norm(dtype_code(m.dtype), _ptr(h_out), _ptr(n_out), _ptr(m), None, 0, 0, _ptr(h_in), _ptr(w_post),
                              _ptr(w_next), rows, H, eps_post, eps_next, _stream()), "add_norm",
            cost=lambda: (f"{rows}x{H}", _nbytes(m, h_in, h_out, n_out, w_post, w_next), 8 * rows * H))
+
+
+def scale_softcap(logits, scale=1.0, cap=0.0):
+    """logits <- cap * tanh(logits * scale / cap) (cap > 0) or logits * scale, in place; float32."""
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise KernelError("scale_softcap takes contiguous float32 logits")
+    _check(lib().cm_scale_softcap(_ptr(logits), logits.numel(), scale, cap, _stream()), "scale_softcap")
 
 
 def swiglu(out, gate_up):
@@ -483,14 +491,15 @@ def gemm_tc_few_rows(y, x, w, swiglu=False, err=None, splits=0):
 
 # -------------------------------------------------------------------------- attention
 def qk_prepare(qkv, wq, wk, rate, tok_pos, tok_seq, seq_slot, seq_end, pool, pages, ptab, ring,
-               QH, KVH, HD, eps):
+               QH, KVH, HD, eps, interleaved=False):
     """Head norm + rotation in place on the q and k columns of qkv; k and v go to the cache
-    (pool: this layer's [2, pages, KVH, 64, HD] storage, or None to write no cache)."""
+    (pool: this layer's [2, pages, KVH, 64, HD] storage, or None to write no cache).  The rotation
+    pairs element i with i + HD/2, or, with `interleaved`, 2i with 2i + 1."""
     T = qkv.shape[0]
     _check(lib().cm_qk_prepare(dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(wq), _ptr(wk), _ptr(rate),
                                _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(seq_end), _ptr(pool), pages,
                                _ptr(ptab), 0 if ptab is None else ptab.stride(0), ring, T, QH, KVH, HD, eps,
-                               _stream()), "qk_prepare",
+                               int(interleaved), _stream()), "qk_prepare",
            cost=lambda: (f"{T} tokens, {QH}+{KVH} heads of {HD}",
                          T * HD * qkv.element_size() * (2 * QH + (2 * KVH if pool is None else 4 * KVH)), 0))
 

@@ -88,17 +88,19 @@ class GQAttention(Mixer):
             raise ValueError("a layer that shares keys and values must be given another layer's state unit "
                              "by the plan (owns_state=False), and only such a layer")
         proj = self.qkvg.apply(rt, x)                  # [T, QS + 2 KVS (+ QH)], or [T, QS (+ QH)] when sharing
+        interleaved = self.position.pairing == "interleaved"
         if self.shares_kv:
             # q only: head norm and rotation over the q heads, nothing written to the cache
             kernels.qk_prepare(proj, self.q_norm_w, None, self.position.rate_table(), batch.tok_pos, batch.tok_seq,
-                               batch.seq_slot, batch.seq_end, None, 0, None, 0, QH, 0, HD, self.qk_norm_eps or 0.0)
+                               batch.seq_slot, batch.seq_end, None, 0, None, 0, QH, 0, HD, self.qk_norm_eps or 0.0,
+                               interleaved=interleaved)
             gate = proj[:, QS:] if self.output_gate else None
         else:
             # an append step keeps the cache as it is until its attention has run
             pool = None if batch.append else state.pool
             kernels.qk_prepare(proj, self.q_norm_w, self.k_norm_w, self.position.rate_table(), batch.tok_pos,
                                batch.tok_seq, batch.seq_slot, batch.seq_end, pool, state.pages, state.ptab,
-                               state.ring, QH, KVH, HD, self.qk_norm_eps or 0.0)
+                               state.ring, QH, KVH, HD, self.qk_norm_eps or 0.0, interleaved=interleaved)
             gate = proj[:, QS + 2 * KVS:] if self.output_gate else None
         q = proj[:, :QS]
         ctx = torch.empty((batch.T, QS), dtype=x.dtype, device=x.device)

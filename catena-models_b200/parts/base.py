@@ -17,10 +17,12 @@ Interfaces (x, h, n are [tokens, width] activations of the step's packed batch):
     Mixer.state_spec() -> KVStateSpec | FixedStateSpec | None
     Mixer.forward(rt, batch, x, state) -> y     state: the cache's view for this layer
     FeedForward.forward(rt, batch, x) -> y
-    Block.input_norm                            the norm applied to h before the block runs
+    Block.input_norm                            the norm applied to h before the block runs, or None
     Block.forward(rt, batch, h, n, state, next_norm) -> (h, n_next)
-        n = input_norm(h) was made by whoever ran before; n_next = next_norm(h) is made
-        here (fused with the last residual sum) when next_norm is given, else None.
+        n = input_norm(h) was made by whoever ran before (None if the block names no input_norm:
+        it then takes what it needs from h itself); n_next = next_norm(h) is made here (fused
+        with the last residual sum) when next_norm is given and the block can, else None: whoever
+        runs next then applies its norm itself.
 
 A part sets `capturable = False` if its forward() reads device data on the host,
 `prompt_capturable = True` if its prompt steps may be recorded as well, and
@@ -138,6 +140,10 @@ class Norm(Part):
 
 
 class Position(Part):
+    # which elements of a head form a rotation pair: "half" pairs i with i + head_dim/2 (the reference's
+    # rotate-half form), "interleaved" pairs 2i with 2i + 1; rate_table()[i] is pair i's rate either way
+    pairing = "half"
+
     def rate_table(self):
         return None
 

@@ -562,3 +562,159 @@ def test_toy_routed_feed_forward_and_another_position_encoding():
     eng.release([slots[0]])
     for g, (ref, _) in zip(got, refs):
         torch.testing.assert_close(torch.cat(g).double().cpu(), ref, rtol=3e-5, atol=3e-5)
+
+
+def test_a_block_without_a_pre_norm_interleaved_pairs_and_scales_around_the_stack():
+    """What an architecture may want that LFM3 does not have, added from outside the package: a block
+    arrangement in which mixer and feed-forward both read one norm of the residual stream and the block
+    names no input norm of its own (the blocks around it then neither make nor expect one), a position
+    encoding that pairs neighbouring elements (2i, 2i + 1), a factor on the embeddings, a factor and a
+    soft cap on the logits.  Prompt, decode (replayed from a recording) and append steps against plain
+    torch in float64."""
+    from catena_models_b200 import kernels, register_architecture, register_part
+    from catena_models_b200.api import Model
+    from catena_models_b200.config.base import Reader
+    from catena_models_b200.engine.definition import ModelDefinition, PlanEntry
+    from catena_models_b200.engine.model import DecoderModel
+    from catena_models_b200.parts import build_part
+    from catena_models_b200.parts.base import Block, Position
+    from catena_models_b200.weights.random_init import random_tensors
+
+    H, QH, KVH, HD, F, V, EPS, TAPS = 48, 3, 1, 16, 72, 90, 1e-5, 3
+    EMB, LSCALE, CAP, THETA = 8.0, 0.75, 4.0, 100.0
+
+    class PairTurn(Position):
+        pairing = "interleaved"
+        prompt_capturable = True
+        supports_append = True
+
+        def __init__(self, head_dim, theta):
+            self.head_dim, self.theta = head_dim, theta
+
+        def rates(self):
+            i = torch.arange(self.head_dim // 2, dtype=torch.float32)
+            return torch.pow(torch.tensor(self.theta, dtype=torch.float32), -2 * i / self.head_dim)
+
+        def bind(self, tensors, rt):
+            self._table = self.rates().to(rt.device)
+
+        def rate_table(self):
+            return self._table
+
+    class ParallelBlock(Block):
+        """h <- h + mixer(norm(h)) + feed_forward(norm(h)); no input norm that others would have to make."""
+        prompt_capturable = True
+        supports_append = True
+        input_norm = None
+
+        def __init__(self, norm, mixer, feed_forward):
+            self.norm, self.mixer, self.feed_forward = norm, mixer, feed_forward
+
+        def children(self):
+            return [self.norm, self.mixer, self.feed_forward]
+
+        def state_spec(self):
+            return self.mixer.state_spec()
+
+        def forward(self, rt, batch, h, n, state, next_norm):
+            assert n is None
+            x = self.norm.apply(rt, h)
+            m = self.mixer.forward(rt, batch, x, state)
+            f = self.feed_forward.forward(rt, batch, x)
+            kernels.add_norm(h, None, m, h, None, None, 0.0, 0.0)
+            kernels.add_norm(h, None, f, h, None, None, 0.0, 0.0)
+            return h, None
+
+    class Cfg:
+        @classmethod
+        def from_dict(cls, data, where="config.json"):
+            r = Reader(data, where)
+            r.string("architecture")
+            r.finish()
+            return cls()
+
+    def define(cfg):
+        norm = lambda name: build_part("norm", "rms", name=name, width=H, eps=EPS)
+        attn = lambda pre: build_part("mixer", "gqa_attention", prefix=pre, hidden=H, heads=QH, kv_heads=KVH, head_dim=HD,
+                                      window=0, position=build_part("position", "toy_pair_turn", head_dim=HD, theta=THETA),
+                                      qk_norm_eps=EPS, output_gate=False)
+        ffn = lambda pre: build_part("feed_forward", "swiglu", prefix=pre, hidden=H, intermediate=F)
+        blocks = [
+            build_part("block", "toy_parallel", norm=norm("l0.n"), mixer=attn("l0."), feed_forward=ffn("l0.")),
+            build_part("block", "sandwich", mixer=build_part("mixer", "short_conv", prefix="l1.", hidden=H, taps=TAPS),
+                       feed_forward=ffn("l1."), input_norm=norm("l1.n1"), ffn_norm=norm("l1.n2")),
+            build_part("block", "toy_parallel", norm=norm("l2.n"), mixer=attn("l2."), feed_forward=ffn("l2.")),
+        ]
+        return ModelDefinition("toy_parallel", V, H, "embed", blocks, [PlanEntry(i, i) for i in range(3)],
+                               norm("nf"), None, embedding_scale=EMB, logit_scale=LSCALE, logit_softcap=CAP)
+
+    register_part("position", "toy_pair_turn", PairTurn, replace=True)
+    register_part("block", "toy_parallel", ParallelBlock, replace=True)
+    register_architecture("toy_parallel", Cfg, define, replace=True)
+    raw = random_tensors(define(Cfg()).tensor_specs(), 31, std=0.3, norm_weights="random")
+    w = {k: v.double() for k, v in raw.items()}
+    rates = PairTurn(HD, THETA).rates().double()
+
+    def turn(u, positions):                                     # pairs (2i, 2i + 1)
+        ang = positions.double()[:, None, None] * rates[None, None, :]
+        a, b = u[..., 0::2], u[..., 1::2]
+        out = torch.empty_like(u)
+        out[..., 0::2] = a * torch.cos(ang) - b * torch.sin(ang)
+        out[..., 1::2] = b * torch.cos(ang) + a * torch.sin(ang)
+        return out
+
+    def attention(pre, n):
+        T = n.shape[0]
+        pos = torch.arange(T)
+        q = P.rms_norm((n @ w[pre + "attn_q.weight"].T).view(T, QH, HD), w[pre + "attn_q_norm.weight"], EPS)
+        k = P.rms_norm((n @ w[pre + "attn_k.weight"].T).view(T, KVH, HD), w[pre + "attn_k_norm.weight"], EPS)
+        q, k = turn(q, pos), turn(k, pos)
+        v = (n @ w[pre + "attn_v.weight"].T).view(T, KVH, HD)
+        ctx = torch.zeros(T, QH, HD, dtype=torch.float64)
+        for hq in range(QH):
+            s = (q[:, hq] @ k[:, 0].T) * HD ** -0.5
+            s = s.masked_fill(P.attention_mask(T, 0), float("-inf"))
+            ctx[:, hq] = torch.softmax(s, -1) @ v[:, 0]
+        return ctx.reshape(T, QH * HD) @ w[pre + "attn_output.weight"].T
+
+    def sub(pre):
+        return {k[len(pre):]: v for k, v in w.items() if k.startswith(pre)}
+
+    def plain(tokens):
+        h = w["embed"][tokens] * EMB
+        for l in (0, 2):
+            if l == 2:                                          # the sandwich block with the convolution in between
+                n1 = P.rms_norm(h, w["l1.n1"], EPS)
+                h = h + P.shortconv_mixer(n1, sub("l1."), dict(conv_L_cache=TAPS))
+                h = h + P.swiglu_ffn(P.rms_norm(h, w["l1.n2"], EPS), sub("l1."))
+            n = P.rms_norm(h, w[f"l{l}.n"], EPS)
+            h = h + attention(f"l{l}.", n) + P.swiglu_ffn(n, sub(f"l{l}."))
+        logits = (P.rms_norm(h, w["nf"], EPS) @ w["embed"].T) * LSCALE
+        return CAP * torch.tanh(logits / CAP)
+
+    seqs = [[(5 * i + 1) % V for i in range(30)], [7, 3, 80, 2, 9]]
+    refs = [plain(s) for s in seqs]
+    assert float(refs[0].abs().max()) > 0.5 * CAP               # the cap really bends the logits
+    for dtype, tol in ((torch.float32, 5e-5), (torch.bfloat16, 0.08)):
+        model = Model(DecoderModel.from_tensors(dict(architecture="toy_parallel"), raw, dtype, DEV), max_tokens=512)
+        eng = model.engine
+        assert eng.use_graphs and model.decoder.supports_append and not model.decoder.fusable_decode
+        slots = eng.admit(2)
+        got = [[], []]
+        out = eng.step(slots, [seqs[0][:12], seqs[1][:2]], [list(range(12)), [0, 1]])
+        got[0].append(out[:12].clone())
+        got[1].append(out[12:].clone())
+        out = eng.step(slots, [seqs[0][12:20], seqs[1][2:3]], [list(range(8)), [0]])        # an append step
+        got[0].append(out[:8].clone())
+        got[1].append(out[8:].clone())
+        for t in range(2):                                      # decode steps: the second one replays the recording
+            out = eng.step(slots, [[seqs[0][20 + t]], [seqs[1][3 + t]]])
+            got[0].append(out[0:1].clone())
+            got[1].append(out[1:2].clone())
+        eng.release([slots[1]])
+        for t in range(22, 30):
+            got[0].append(eng.step([slots[0]], [[seqs[0][t]]]).clone())
+        eng.release([slots[0]])
+        for g, ref in zip(got, refs):
+            err = float((torch.cat(g).double().cpu() - ref).abs().max() / ref.abs().max())
+            assert err < tol, (dtype, err)
