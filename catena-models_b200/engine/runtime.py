@@ -94,7 +94,7 @@ class Runtime:
         the caller can take `kernels.PartialSums` instead (the product cut over K, to be added by the
         fused residual kernel): used where it spares the product an exchange between its blocks."""
         kind = self._product_kernel(x, w)
-        if partial_ok and out_dtype is None and kind == "skinny":
+        if partial_ok and out_dtype is None and kind == "skinny" and x.shape[0] <= self.SKINNY_BEST_ROWS:
             slices = self._skinny_slices(w.shape[0], w.shape[1])
             if slices > 1:
                 parts = torch.empty((slices, x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
@@ -152,6 +152,8 @@ class Runtime:
 
     SKINNY_ROWS = 64          # most rows the weight-streaming kernel takes
     SKINNY_BEST_ROWS = 16     # up to here it is the fastest kernel
+    SKINNY_SHORT_K_ROWS = 32  # ... and up to here when the inner dimension is at most SKINNY_SHORT_K
+    SKINNY_SHORT_K = 1024
     FEW_ROWS = 128            # most rows of the tensor-core kernel that splits K over a cluster
 
     def _product_kernel(self, x, w):
@@ -171,13 +173,20 @@ class Runtime:
                and x.data_ptr() % 16 == 0 and w.stride(0) % 8 == 0)
         if streams and (rows <= self.SKINNY_BEST_ROWS or not tma):
             return "skinny"
+        # short inner dimensions (hidden 1,024): the tensor-memory kernel's set-up and exchange cost more
+        # than the streaming kernel's re-reading of the activations up to 32 rows (measured on B200 at 24
+        # and 32 rows, K = 1,024: 3.9 / 4.1 / 5.8 / 8.8 us against 5.1 / 5.1 / 6.4 / 11.3 us for the out,
+        # q/k/v, in and gate/up projections; at K = 2,048 the tensor-memory kernel wins from 24 rows on)
+        if streams and rows <= self.SKINNY_SHORT_K_ROWS and x.shape[1] <= self.SKINNY_SHORT_K:
+            return "skinny"
         if tma:
             return "few_rows" if rows <= self.FEW_ROWS else "tiled"
         return "simt"
 
     def streams_weights(self, x, w):
-        """True if x @ w^T goes to the weight-streaming kernel (a part may then use that kernel's fused forms)."""
-        return self._product_kernel(x, w) == "skinny"
+        """True if x @ w^T goes to the weight-streaming kernel with at most 16 rows (a part may then use
+        that kernel's fused forms, which take no more)."""
+        return x.shape[0] <= self.SKINNY_BEST_ROWS and self._product_kernel(x, w) == "skinny"
 
     def gate_up_swiglu(self, x, w_gate_up, F):
         """a = silu(x Wgate^T) * (x Wup^T) for the row-packed [Wgate; Wup]."""
