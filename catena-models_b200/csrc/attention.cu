@@ -34,6 +34,8 @@ __device__ __forceinline__ void load8<bf16>(const bf16* p, float* out) {
 //   o_i       = u_i cos a - u_{i+HD/2} sin a
 //   o_{i+HD/2}= u_{i+HD/2} cos a + u_i sin a,   a = float(pos) * rate[i]      when rate is given
 // (pairs of the two halves; with `interleaved` the pairs are neighbours, (2i, 2i+1), instead)
+// Rows whose tok_seq is negative are padding (a step recorded for a class of shapes carries some):
+// they are left alone.
 // q and k are overwritten in place; k and the raw v also go to the cache entry of (slot, pos):
 // entry = pos (growing group) or pos % ring (ring group; during a prompt longer than the ring
 // only the last `ring` positions are stored, so that no two rows meet in one entry).
@@ -55,7 +57,7 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
     constexpr int MAXP = 4;                       // pairs per lane: head sizes up to 256
     const int lane = threadIdx.x;
     const int t = blockIdx.x * blockDim.y + threadIdx.y;
-    if (t >= T_tokens) return;
+    if (t >= T_tokens || tok_seq[t] < 0) return;      // a row of padding belongs to no sequence
     const int pos = tok_pos[t];
     const int half = HD >> 1;
     float sn[MAXP], cs[MAXP];
@@ -146,7 +148,7 @@ qk_prepare_vec_kernel(T* __restrict__ qkv, long long ld, const float* __restrict
     pdl_wait();
     const int lane = threadIdx.x;
     const int t = blockIdx.x * blockDim.y + threadIdx.y;
-    if (t >= T_tokens) return;
+    if (t >= T_tokens || tok_seq[t] < 0) return;      // a row of padding belongs to no sequence
     const int half = HD >> 1, LPH = half >> 3, HPP = 32 / LPH;
     const int sub = lane % LPH, hsel = lane / LPH;          // lanes past HPP * LPH idle along
     const int pos = tok_pos[t];
@@ -476,6 +478,7 @@ __global__ void kv_store_kernel(const T* __restrict__ kv, long long ld, const in
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, b = tok_seq[t], pos = tok_pos[t];
+    if (b < 0) return;                                  // padding
     if (ring && pos + ring < seq_end[b]) return;
     const int entry = ring ? pos % ring : pos;
     const int page = ptab[(long long)seq_slot[b] * ptab_stride + entry / PAGE_TOKENS];

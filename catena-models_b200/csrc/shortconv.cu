@@ -9,7 +9,8 @@
 // A step that brings several tokens on top of a stored state (seq_pos0[b] > 0) runs in two
 // launches, because the first tokens of a sequence read the state that its last token replaces:
 // phase 1 writes the outputs only, phase 2 the state only.  With seq_pos0 given, a sequence whose
-// first position is 0 starts from an empty state whatever from_zero says.
+// first position is 0 starts from an empty state whatever from_zero says.  A row whose tok_seq is
+// negative is padding (a step recorded for a class of shapes carries some): its output is zero.
 #include "common.cuh"
 
 #define SC_MAXK CM_MAX_CONV_TAPS
@@ -26,6 +27,10 @@ __global__ void shortconv_kernel(T* __restrict__ y, const T* __restrict__ bcx, l
     const int t = blockIdx.x;                     // tokens on x: a step may carry more than 65535 of them
     if (c >= H) return;
     const int b = tok_seq[t];
+    if (b < 0) {                                  // a row of padding belongs to no sequence: zeros out
+        if (phase != 2) y[(long long)t * H + c] = from_f32<T>(0.f);
+        return;
+    }
     const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
     const int i = t - s0;
     if (phase == 2 && i != len - 1) return;
@@ -88,6 +93,13 @@ shortconv_vec_kernel(T* __restrict__ y, const T* __restrict__ bcx, long long ld,
     const int t = blockIdx.x * blockDim.y + threadIdx.y;
     if (c >= H || t >= T_tokens) return;
     const int b = tok_seq[t];
+    if (b < 0) {                                  // a row of padding belongs to no sequence: zeros out
+        if (phase != 2) {
+            const float zeros[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            store8f<T>(y + (long long)t * H + c, zeros);
+        }
+        return;
+    }
     const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
     const int i = t - s0;
     if (phase == 2 && i != len - 1) return;

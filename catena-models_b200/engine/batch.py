@@ -11,6 +11,8 @@ metadata travels in one int32 buffer, filled on the host in pinned memory and co
 
 `want_rows` are rows of the packed batch whose logits are asked for; `upd_*` are page-table
 entries that the cache allocated for this step (applied on the device before any layer runs).
+A step may carry rows of padding behind its tokens (tok_seq = -1): they belong to no sequence,
+touch no cache and change no result; recorded prompt steps use them to serve a class of shapes.
 """
 from __future__ import annotations
 
@@ -41,7 +43,7 @@ class StepBatch:
 
     KINDS = ("prefill", "decode", "append")
 
-    def __init__(self, layout, device_buf, kind, lengths, positions, n_want, n_updates):
+    def __init__(self, layout, device_buf, kind, lengths, positions, n_want, n_updates, max_len=None):
         if kind not in self.KINDS:
             raise ValueError(f"step kind {kind!r}; one of {self.KINDS}")
         self.layout = layout
@@ -59,7 +61,8 @@ class StepBatch:
         self.append = kind == "append"                         # sequences stand anywhere and bring any number of tokens
         self.lengths, self.positions = list(lengths), list(positions)    # host copies, per sequence
         self.B, self.T = layout.B, layout.T
-        self.max_len = max(lengths) if lengths else 0          # longest run of new tokens
+        # longest run of new tokens; a step recorded for a class of shapes is launched for the class's bound
+        self.max_len = max_len if max_len is not None else (max(lengths) if lengths else 0)
         self.max_end = max((p + n for p, n in zip(positions, lengths)), default=0)
         self.n_want, self.n_updates = n_want, n_updates
         self.wants_every_row = False                           # want_rows is 0, 1, ..., T-1 (set by the decode path)
@@ -125,6 +128,11 @@ def fill_host(layout, host, slots, token_lists, positions, want, updates):
             rows.append(t + w)
         t += n
     v["seq_start"][len(slots)] = t
+    if t < layout.T:
+        # rows of padding (a step recorded for a class of shapes runs layout.T rows): token 0 of no sequence
+        v["tokens"][t:layout.T] = 0
+        v["tok_seq"][t:layout.T] = -1
+        v["tok_pos"][t:layout.T] = 0
     v["want_rows"][:len(rows)] = rows
     v["upd_count"][0] = len(updates)
     for i, (idx, page) in enumerate(updates):

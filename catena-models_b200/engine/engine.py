@@ -34,7 +34,8 @@ from .batch import BatchLayout, StepBatch, clear_sampling, fill_host, fill_host_
 
 
 PROMPT_GRAPH_MAX_TOKENS = 1024     # longer prompt steps are bound by the device, not by their launches
-PROMPT_GRAPHS_KEPT = 4
+PROMPT_GRAPHS_KEPT = 8
+PROMPT_PAD = 64                    # recorded prompt steps run a multiple of this many rows, the rest as padding
 DECODE_GRAPHS_KEPT = 24            # recorded decode steps (batch size, length class) kept; the least recently used goes
 
 
@@ -310,17 +311,24 @@ class Engine:
 
     # ------------------------------------------------------------------ prompt steps
     def _prompt_step(self, slots, tokens, positions, kind, want, updates, sampling):
-        """A step with explicit tokens per sequence, launched kernel by kernel.  A prompt step whose
-        shape (the lengths, the number of wanted places) comes a second time is recorded into a graph
-        as it runs and replayed from then on: about 200 launches from Python cost more than a short
-        prompt's kernels take.  The few most recent shapes are kept."""
+        """A step with explicit tokens per sequence, launched kernel by kernel.  A short prompt step
+        whose class of shapes comes a second time is recorded into a graph as it runs and replayed
+        from then on: about 200 launches from Python cost more than a short prompt's kernels take.
+        A class is (number of sequences, tokens rounded up to PROMPT_PAD, longest prompt rounded up
+        likewise, number of wanted places): the step runs that many rows, the surplus as padding that
+        belongs to no sequence, and everything about the real lengths travels in the step's metadata,
+        so one recording serves every prompt of its class.  The few most recent classes are kept."""
         B, T = len(slots), sum(len(t) for t in tokens)
         n_want = sum(len(w) for w in want)
-        key = entry = None
+        key = entry = max_len = None
+        T_run, U_cap = T, len(updates)
         if kind == "prefill" and self.use_graphs and self.model.prompt_capturable and T <= PROMPT_GRAPH_MAX_TOKENS:
-            key = (tuple(len(t) for t in tokens), n_want, len(updates), sampling is not None)
+            T_run = -(-T // PROMPT_PAD) * PROMPT_PAD
+            max_len = -(-max(len(t) for t in tokens) // PROMPT_PAD) * PROMPT_PAD
+            U_cap = (T_run // PAGE_TOKENS + B) * max(1, self.n_kv_groups)    # no step of the class needs more pages
+            key = (B, T_run, max_len, n_want, sampling is not None)
             entry = self._prompt_graphs.get(key)
-        layout = entry.layout if entry else BatchLayout(T, B, n_want, len(updates))
+        layout = entry.layout if entry else BatchLayout(T_run, B, n_want, U_cap)
         host, idx = self._staging.take(layout.size)
         fill_host(layout, host.numpy(), slots, tokens, positions, want, updates)
         if sampling is not None:
@@ -346,7 +354,7 @@ class Engine:
         else:
             dev = host[:layout.size].to(self.rt.device, non_blocking=True)
         self._staging.mark(idx)
-        batch = StepBatch(layout, dev, kind, [len(t) for t in tokens], positions, n_want, len(updates))
+        batch = StepBatch(layout, dev, kind, [len(t) for t in tokens], positions, n_want, len(updates), max_len=max_len)
         # a decode step that wants its every row: the same launches as its recorded form
         batch.wants_every_row = kind == "decode" and all(w == [0] for w in want)
         sampled = torch.empty(B, dtype=torch.int32, device=self.rt.device) if sampling is not None else None

@@ -66,8 +66,11 @@ class Part:
     # from a captured graph.
     capturable = True
     # True for a part whose prompt steps too launch the same kernels whenever the batch has the same
-    # shape (lengths, wanted places): the engine may then record a repeated prompt shape into a graph.
-    # A part says so itself; one that does not know is not recorded.
+    # class of shape (number of sequences, rows, longest prompt as StepBatch.max_len, wanted places), that
+    # takes everything about the real lengths from the step's device metadata, and that leaves rows of
+    # padding alone (StepBatch.tok_seq is -1 there: they belong to no sequence and must touch no state):
+    # the engine may then record a prompt step of a class into a graph and replay it for every prompt
+    # of the class.  A part says so itself; one that does not know is not recorded.
     prompt_capturable = False
     # True for a part that can take a step of kind "append" (StepBatch.kind): sequences that stand at
     # any position and bring any number of tokens.  A part that works row by row (norm, feed-forward,

@@ -344,7 +344,7 @@ def test_recorded_prompt_shapes_are_bounded_and_evicted_ones_run_again(folders, 
     name, dtype = "A", "bfloat16"
     eng = engine_for(folders, name, dtype)
     vocab = plain[name][0]["vocab_size"]
-    shapes = [(n,) for n in range(40, 40 + PROMPT_GRAPHS_KEPT + 3)]
+    shapes = [(40 + 64 * i,) for i in range(PROMPT_GRAPHS_KEPT + 3)]       # one class of shapes each
     for rnd in range(2):
         for lens in shapes:
             for rep in range(3):
@@ -355,3 +355,35 @@ def test_recorded_prompt_shapes_are_bounded_and_evicted_ones_run_again(folders, 
                 exact, same = plain_logits(plain, name, prompts[0], dtype)
                 check(got, exact[-1:], dtype, same[-1:])
             assert len(eng._prompt_graphs) <= PROMPT_GRAPHS_KEPT
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "L"])
+def test_one_recording_serves_a_class_of_prompt_shapes(folders, plain, name, dtype):
+    """Prompt steps are recorded per class (sequences, tokens and longest prompt rounded up to 64, wanted
+    places): the step runs the class's rows, the surplus as padding that belongs to no sequence.  Prompts
+    of many lengths in one class, alone and in pairs of unequal lengths, each followed by a decode step,
+    must all match the plain model, whether they ran kernel by kernel (the first two of a class) or were
+    replayed; padding must leave cache and fixed-size state alone (the decode step would show it)."""
+    eng = engine_for(folders, name, dtype)
+    vocab = plain[name][0]["vocab_size"]
+    all_got, all_exact, all_same = [], [], []
+    for rep, lens in enumerate([(30, 50), (1, 100), (64, 64), (90, 20), (5, 70), (65,), (100,), (128,), (77,), (66,), (127,)]):
+        seqs = [tiny.random_prompt(n + 1, vocab, seed=500 + 10 * rep + i) for i, n in enumerate(lens)]
+        slots = eng.admit(len(lens))
+        got = eng.step(slots, [s[:-1] for s in seqs], [[0, n - 1] if n > 1 else [0] for n in lens]).clone()
+        got2 = eng.step(slots, [[s[-1]] for s in seqs]).clone()
+        eng.release(slots)
+        off = 0
+        for i, (s, n) in enumerate(zip(seqs, lens)):
+            exact, same = plain_logits(plain, name, s, dtype)
+            places = [0, n - 1] if n > 1 else [0]
+            all_got.append(torch.cat([got[off:off + len(places)], got2[i:i + 1]]))
+            off += len(places)
+            all_exact.append(exact[places + [n]])
+            if same is not None:
+                all_same.append(same[places + [n]])
+    # one comparison over all rows: the bfloat16 yardstick is a maximum and needs more than two rows to be one
+    check(torch.cat(all_got), torch.cat(all_exact), dtype, torch.cat(all_same) if all_same else None)
+    # the six single prompts are one class (128 rows, two wanted places), recorded at its second prompt
+    assert (1, 128, 128, 2, False) in eng._prompt_graphs
