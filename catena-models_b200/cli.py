@@ -2,7 +2,8 @@
 names with the same meanings where it has them (--model, --prompt, -n/--max-new-tokens,
 --ignore-eos, --bench, --pp, --tg, --tg-context, --bench-runs), a model folder in place of a
 Hub selector, token ids in place of text (this library has no tokenizer), and the options the
-reference lacks (--temperature, --seed, --dtype, --random).
+reference lacks (--temperature, --seed, --dtype, --random, --prompt-lens, --max-slots, --batch,
+--pp-chunk).  --kernels and --wmma-prefill / --no-wmma-prefill are the reference's too.
 
     python -m catena_models_b200 --model DIR --prompt "5 17 3" --prompt "9 9" -n 20
     python -m catena_models_b200 --random config.json --bench --pp 512 --tg 128 --tg-context 1024
@@ -53,6 +54,15 @@ def parser():
     ap.add_argument("--tg-context", type=_positive, default=1, help="prompt context of the decode benchmark")
     ap.add_argument("--bench-runs", type=_positive, default=1, help="measured runs per benchmark test")
     ap.add_argument("--batch", type=_positive, default=1, help="sequences per step in --bench")
+    ap.add_argument("--prompt-lens", type=_ids, metavar="LENGTHS",
+                    help="instead of --prompt: synthetic prompts of these lengths (the bench's generator of ids)")
+    ap.add_argument("--max-slots", type=_positive, default=None, help="most sequences the cache holds at once")
+    ap.add_argument("--kernels", default="fused", choices=["fused", "reference"],
+                    help="kernel family, as the reference names it; this library has the fused one only")
+    ap.add_argument("--wmma-prefill", dest="wmma_prefill", action="store_true", default=True,
+                    help="tensor-core kernels for prompt steps (the default)")
+    ap.add_argument("--no-wmma-prefill", dest="wmma_prefill", action="store_false",
+                    help="CUDA-core products and attention for prompt steps (bfloat16 activations all the same)")
     ap.add_argument("--pp-chunk", type=int, default=0,
                     help="run the prompt-processing test in steps of this many tokens, each on top of the ones before "
                          "(the reference's server fills its cache in blocks of 1,024, src/server/prefix_cache.rs:4); 0: one step")
@@ -142,9 +152,13 @@ def main(argv=None):
         with open(args.random) as fh:
             print(write_random_model(args.write_random, json.load(fh), args.weights_seed))
         return 0
-    if not args.bench and not args.prompt:
-        ap.error("--prompt is required unless --bench is given")
-    if args.bench and args.prompt:
+    if args.kernels != "fused":
+        ap.error("--kernels reference: LFM3 has the fused kernels only (as in the reference, src/lfm3.rs:15-18)")
+    if args.prompt and args.prompt_lens:
+        ap.error("--prompt and --prompt-lens exclude each other")
+    if not args.bench and not args.prompt and not args.prompt_lens:
+        ap.error("--prompt or --prompt-lens is required unless --bench is given")
+    if args.bench and (args.prompt or args.prompt_lens):
         ap.error("--bench and --prompt exclude each other")
 
     from .api import Model
@@ -153,14 +167,23 @@ def main(argv=None):
     if args.bench:
         need = args.batch * (max(args.pp, args.tg_context + args.tg + 2) + PAGE_TOKENS)
     else:
-        need = sum(-(-(len(p) + args.max_new_tokens) // PAGE_TOKENS) * PAGE_TOKENS for p in args.prompt)
+        lens = args.prompt_lens or [len(p) for p in args.prompt]
+        need = sum(-(-(n + args.max_new_tokens) // PAGE_TOKENS) * PAGE_TOKENS for n in lens)
     max_tokens = args.max_tokens or max(need, PAGE_TOKENS)
     t0 = time.perf_counter()
     if args.model:
-        model = Model.load(args.model, dtype=args.dtype, max_tokens=max_tokens)
+        model = Model.load(args.model, dtype=args.dtype, max_tokens=max_tokens, max_seqs=args.max_slots)
     else:
         with open(args.random) as fh:
-            model = Model.random(json.load(fh), seed=args.weights_seed, dtype=args.dtype, max_tokens=max_tokens)
+            model = Model.random(json.load(fh), seed=args.weights_seed, dtype=args.dtype, max_tokens=max_tokens,
+                                 max_seqs=args.max_slots)
+    model.decoder.rt.tensor_core_prompts = args.wmma_prefill
+    if args.prompt_lens:
+        ids = _synthetic(sum(args.prompt_lens), model.decoder.vocab_size)
+        args.prompt, at = [], 0
+        for n in args.prompt_lens:
+            args.prompt.append(ids[at:at + n])
+            at += n
     print(f"loaded {model.parameter_count() / 1e6:.2f} M parameters in {time.perf_counter() - t0:.2f}s; "
           f"cache of {max_tokens} tokens: {model.engine.cache.bytes() / 2**20:.1f} MiB", file=sys.stderr)
     if args.bench:

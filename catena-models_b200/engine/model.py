@@ -79,6 +79,7 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ forward
     def forward(self, batch, cache):
+        self.rt._in_prompt = batch.kind != "decode"
         with kernels.pinned_stream():
             fuse = self.rt.fused_decode_for(batch) if self.fusable_decode else None
             if fuse is None:

@@ -27,6 +27,10 @@ class Runtime:
         if self.device.type != "cuda":
             raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
         kernels.lib()                       # build and load now: fail loudly before any model work
+        # False: prompt steps (more than one row a sequence) run their products and attention on the CUDA
+        # cores, whatever the dtype: the reference's --no-wmma-prefill (src/main.rs:34-40)
+        self.tensor_core_prompts = True
+        self._in_prompt = False
         self._scratch = {}
         self._retired = []
         self._sm_count = None
@@ -166,6 +170,8 @@ class Runtime:
         aligned) fall to the streaming kernel while it takes the rows, else to the CUDA-core one,
         which is also the float32 path."""
         rows = x.shape[0]
+        if self._in_prompt and not self.tensor_core_prompts:
+            return "simt"
         bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
         streams = (bf16 and rows <= self.SKINNY_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
                    and x.data_ptr() % 16 == 0)
@@ -218,7 +224,7 @@ class Runtime:
         are multiples of 16 up to 128: mma.sync.  Everything else, and float32: CUDA cores."""
         aligned = (q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
                    and v.data_ptr() % 16 == 0)
-        bf16 = q.dtype == torch.bfloat16
+        bf16 = q.dtype == torch.bfloat16 and self.tensor_core_prompts
         span = min(batch.max_len, window) if window else batch.max_len
         if (bf16 and aligned and HD in (64, 128) and span >= self.TCGEN05_ATTENTION_MIN_LEN
                 and ctx.stride(0) % 8 == 0 and ctx.data_ptr() % 16 == 0):

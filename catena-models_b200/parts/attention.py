@@ -123,7 +123,7 @@ class GQAttention(Mixer):
             if batch.append:
                 kernels.attn_append(ctx, q, k, v, gate, batch.seq_start, batch.seq_pos0, batch.seq_slot, state.pool,
                                     state.pages, state.ptab, state.ring, batch.B, batch.max_len, QH, KVH, HD,
-                                    self.window, self.scale)
+                                    self.window, self.scale, tensor_cores=rt.tensor_core_prompts)
                 if not self.shares_kv:
                     kernels.kv_store(proj[:, QS:QS + 2 * KVS], batch.tok_pos, batch.tok_seq, batch.seq_slot,
                                      batch.seq_end, state.pool, state.pages, state.ptab, state.ring, KVH, HD)

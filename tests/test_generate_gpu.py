@@ -191,3 +191,30 @@ def test_command_line(folders, tmp_path):
                            text=True, timeout=600)
     assert bench.returncode == 0, bench.stderr
     assert "pp40x2" in bench.stdout and "tg6/ctx9x2" in bench.stdout
+
+
+def test_command_line_options_of_the_reference_and_of_the_survey(folders, tmp_path):
+    """--prompt-lens (synthetic prompts), --max-slots, --kernels, --no-wmma-prefill (CUDA-core prompt
+    steps under the bfloat16 engine: the same tokens as with tensor cores on a model this small, and
+    the plain model's in 32-bit), --pp-chunk in the bench."""
+    cfg, tensors = plain_lfm3.load_folder(folders["A"])
+    base = [sys.executable, "-m", "catena_models_b200", "--model", folders["A"], "-n", "4", "--ignore-eos",
+            "--prompt-lens", "7 19", "--max-slots", "2"]
+    outs = {}
+    for name, extra in (("f32", ["--dtype", "float32", "--kernels", "fused"]), ("f32-simt", ["--dtype", "float32", "--no-wmma-prefill"]),
+                        ("bf16", []), ("bf16-simt", ["--no-wmma-prefill"])):
+        run = subprocess.run(base + extra, cwd=ROOT, capture_output=True, text=True, timeout=600)
+        assert run.returncode == 0, run.stderr
+        outs[name] = [list(map(int, l.split())) for l in run.stdout.strip().splitlines()]
+        assert "cache of" in run.stderr and [len(o) for o in outs[name]] == [4, 4]
+    from catena_models_b200.cli import _synthetic
+    ids = _synthetic(26, cfg["vocab_size"])
+    assert outs["f32"] == outs["f32-simt"] == [plain_lfm3.generate(cfg, tensors, ids[:7], 4),
+                                                 plain_lfm3.generate(cfg, tensors, ids[7:], 4)]
+    refused = subprocess.run(base + ["--kernels", "reference"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert refused.returncode != 0 and "fused" in refused.stderr
+    conf = tmp_path / "c.json"
+    conf.write_text(json.dumps(tiny.TINY_B))
+    bench = subprocess.run([sys.executable, "-m", "catena_models_b200", "--random", str(conf), "--bench", "--pp", "100",
+                            "--pp-chunk", "30", "--tg", "0"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert bench.returncode == 0 and "pp100/30" in bench.stdout, bench.stderr
