@@ -473,8 +473,13 @@ def main():
                     help="run one part only (small captures under a profiler); prints that part's facts")
     ap.add_argument("--kernel-table", action="store_true",
                     help="time one decode step and one prompt step kernel by kernel and print the table")
+    ap.add_argument("--print-config", action="store_true",
+                    help="print the configuration's config.json (for `python -m catena_models_b200 --random FILE`) and exit")
     args = ap.parse_args()
 
+    if args.print_config:
+        print(json.dumps(model_config(args.config, args.layers), indent=1))
+        return 0
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "catena-models is a Rust crate whose kernel compiler is a network git dependency; "

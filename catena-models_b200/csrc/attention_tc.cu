@@ -1,6 +1,13 @@
 // Prefill attention on the 5th-generation tensor cores (bfloat16, head sizes 64 and 128): causal or
 // sliding-window attention of packed sequences over their own keys and values, grouped query
 // heads, optional per-head sigmoid gate.  Same result as attn_prefill_mma (attention_mma.cu).
+// PAST: the sequences may stand at seq_pos0[b] > 0 (a prompt that comes in several steps); the keys
+// and values below that position are read from the paged cache, page by page (a 128-key tile is two
+// pages of 64 entries, each one TMA box of the cache's [k|v, page, kv head, entry, head] layout),
+// before the step's own tiles.  A tile's second page that lies wholly at or above seq_pos0 is not
+// the sequence's: the first page is copied in its place, so that what the masked scores multiply is
+// the sequence's own data; the unwritten entries of the page that holds position seq_pos0 - 1 are
+// cleared by the caller (cm_kv_clear_tail), since 0 x NaN would not be 0.
 //
 // One block per (128-query tile, query head, sequence), long tiles first.  Twelve warps (the first
 // group of four gives most of its registers to the other two, setmaxnreg 40 / 232):
@@ -25,6 +32,7 @@
 #include "tc_common.cuh"
 
 #define FT_TILE 128
+static_assert(PAGE_TOKENS * 2 == FT_TILE, "a key tile of the cache is two pages");
 #define FT_THREADS 384                     // three groups of four warps: loader and issuer, softmax 0, softmax 1
 #define FT_PIECE_BYTES (128 * 64 * 2)      // 128 rows of 128 bytes
 #define FT_ERR_LOAD 111
@@ -50,10 +58,20 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t lb
     return d;
 }
 
-template <int HD, int STAGES>
+struct FtPast {                      // where the keys and values below a sequence's first row of this step lie
+    const int* seq_pos0;
+    const int* seq_slot;
+    const int* ptab;
+    long long ptab_stride;
+    long long pages;
+    int ring;
+};
+
+template <int HD, int STAGES, bool PAST>
 __global__ void __launch_bounds__(FT_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ ctx, long long ldc,
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_pool,
+                       const FtPast past, bf16* __restrict__ ctx, long long ldc,
                        const bf16* __restrict__ gate, long long ldg, const int* __restrict__ seq_start, int QH,
                        int KVH, int window, float scale_log2, int* err) {
     constexpr int KB = HD / 64;                                   // 64-column pieces of a head
@@ -79,7 +97,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kt_begin = window > 0 ? max(0, q0 - window + 1) / FT_TILE : 0;
     const int kt_end = min(q0 + FT_TILE - 1, len - 1) / FT_TILE;  // inclusive
-    const int n = kt_end - kt_begin + 1;
+    // positions: row r of this step stands at p0 + r; tiles of the cache come first, in steps of 128 positions
+    const int p0 = PAST ? past.seq_pos0[b] : 0;
+    int tp_begin = 0, n_past = 0;
+    if (PAST && p0 > 0) {
+        const int a_lo = window > 0 ? max(0, p0 + q0 - window + 1) : 0;
+        if (a_lo < p0) {
+            tp_begin = a_lo / FT_TILE;
+            n_past = (p0 - 1) / FT_TILE - tp_begin + 1;
+        }
+    }
+    const int n = n_past + kt_end - kt_begin + 1;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + STAGES * KV_BYTES, p_s = v_s + STAGES * KV_BYTES;
@@ -129,14 +157,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_expect_tx(q_full, Q_BYTES);
             for (int kb = 0; kb < KB; ++kb) tma_load_2d(q_s + kb * FT_PIECE_BYTES, &map_q, q_full, hq * HD + kb * 64, s0 + q0);
             bool ok = true;
+            // the two pages of the cache that hold positions 128 tp .. 128 tp + 127, keys (which = 0) or values
+            auto load_pages = [&](uint32_t dst, uint32_t bar, int tp, int which) {
+                const int* row = past.ptab + (long long)past.seq_slot[b] * past.ptab_stride;
+                for (int h = 0; h < 2; ++h) {
+                    int a0 = tp * FT_TILE + h * 64;
+                    if (a0 >= p0) a0 = tp * FT_TILE;                   // not this sequence's entries: the first page again
+                    const int entry = past.ring > 0 ? a0 % past.ring : a0;
+                    const long long page = row[entry >> 6];
+                    const long long r0 = ((which * past.pages + page) * KVH + hk) * 64;
+                    for (int kb = 0; kb < KB; ++kb)
+                        tma_load_2d(dst + kb * FT_PIECE_BYTES + h * 8192, &map_pool, bar, kb * 64, (int)r0);
+                }
+            };
             auto load_k = [&](int j) {
                 const int s = j % STAGES;
                 ok = mbar_wait(k_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
                 if (!ok) return;
                 mbar_expect_tx(k_full + 8 * s, KV_BYTES);
-                for (int kb = 0; kb < KB; ++kb)
-                    tma_load_2d(k_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_k, k_full + 8 * s, hk * HD + kb * 64,
-                                s0 + (kt_begin + j) * FT_TILE);
+                if (PAST && j < n_past) {
+                    load_pages(k_s + s * KV_BYTES, k_full + 8 * s, tp_begin + j, 0);
+                } else {
+                    for (int kb = 0; kb < KB; ++kb)
+                        tma_load_2d(k_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_k, k_full + 8 * s, hk * HD + kb * 64,
+                                    s0 + (kt_begin + j - n_past) * FT_TILE);
+                }
                 issued_k = j + 1;
             };
             auto load_v = [&](int j) {
@@ -144,9 +189,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 ok = mbar_wait(v_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
                 if (!ok) return;
                 mbar_expect_tx(v_full + 8 * s, KV_BYTES);
-                for (int kb = 0; kb < KB; ++kb)
-                    tma_load_2d(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_v, v_full + 8 * s, hk * HD + kb * 64,
-                                s0 + (kt_begin + j) * FT_TILE);
+                if (PAST && j < n_past) {
+                    load_pages(v_s + s * KV_BYTES, v_full + 8 * s, tp_begin + j, 1);
+                } else {
+                    for (int kb = 0; kb < KB; ++kb)
+                        tma_load_2d(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_v, v_full + 8 * s, hk * HD + kb * 64,
+                                    s0 + (kt_begin + j - n_past) * FT_TILE);
+                }
                 issued_v = j + 1;
             };
             for (int j = 0; j < n && ok; ++j) {
@@ -208,7 +257,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // ------------------------------------------------------------- softmax groups
         const int g = (warp - 4) >> 2, quarter = warp & 3;
         const int r = quarter * 32 + lane;                        // the row of the tile this thread owns
-        const int row = q0 + r;                                   // its position in the sequence
+        const int row_l = q0 + r;                                 // its row among the sequence's rows of this step
+        const int row = p0 + row_l;                               // its position in the sequence
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const uint32_t t_o = lane_base + (uint32_t)(NS * FT_TILE + g * HD);
         const uint32_t my_p = p_s + g * P_BYTES + r * 128;
@@ -234,7 +284,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_fence_before();
         };
         for (int j = g; j < n && ok; j += 2, ++t) {
-            const int k0 = (kt_begin + j) * FT_TILE;
+            // first position of the tile, and the position where its sequence's entries end
+            const bool from_cache = PAST && j < n_past;
+            const int k0 = from_cache ? (tp_begin + j) * FT_TILE : p0 + (kt_begin + j - n_past) * FT_TILE;
+            const int limit = from_cache ? p0 : p0 + len;
             // First O' of the group's previous tile: the tensor core then never waits for this group
             // to free the O' buffer, and its arrival also says that P V of that tile is done reading
             // the P buffer, which this tile's exponentials overwrite.
@@ -245,12 +298,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_fence_after();
             const uint32_t t_s = lane_base + (uint32_t)((j % NS) * FT_TILE);
             // every key of the tile is visible to this row: no comparisons needed
-            const bool all_visible = k0 + FT_TILE - 1 <= row && k0 + FT_TILE - 1 < len && (window <= 0 || k0 + window > row);
+            const bool all_visible = k0 + FT_TILE - 1 <= row && k0 + FT_TILE - 1 < limit && (window <= 0 || k0 + window > row);
             auto masked = [&](float* v, int c) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int key = k0 + c * 32 + i;
-                    const bool vis = key <= row && key < len && (window <= 0 || key + window > row);
+                    const bool vis = key <= row && key < limit && (window <= 0 || key + window > row);
                     v[i] = vis ? v[i] : -INFINITY;
                 }
             };
@@ -335,13 +388,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (lane == 0) mbar_arrive(merge_full);
         } else {
             if (ok) ok = mbar_wait(merge_full, 0, &abort_flag, err, FT_ERR_SOFTMAX);
-            if (ok && row < len) {
+            if (ok && row_l < len) {
                 const float m1 = mrg[HD * FT_TILE + r], l1 = mrg[(HD + 1) * FT_TILE + r];
                 const float m = fmaxf(m_run, m1);
                 const float f0 = m_run == -INFINITY ? 0.f : ft_exp2(m_run - m);
                 const float f1 = m1 == -INFINITY ? 0.f : ft_exp2(m1 - m);
                 float f = 1.f / (l_run * f0 + l1 * f1);
-                const long long tok = s0 + row;
+                const long long tok = s0 + row_l;
                 if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + hq]));
                 bf16* dst = ctx + tok * ldc + (long long)hq * HD;
 #pragma unroll
@@ -380,18 +433,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
-template <int HD, int STAGES>
+template <int HD, int STAGES, bool PAST>
 static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
                      const void* gate, long long ldg, const int* seq_start, int B, int max_len, long long T, int QH,
-                     int KVH, int window, float scale, int* err, cudaStream_t st) {
-    CUtensorMap map_q, map_k, map_v;
+                     int KVH, int window, float scale, const FtPast& past, const void* pool, int* err, cudaStream_t st) {
+    CUtensorMap map_q, map_k, map_v, map_pool;
     int rc = make_map(&map_q, q, T, (long long)QH * HD, ld, FT_TILE);
     if (rc == CM_OK) rc = make_map(&map_k, k, T, (long long)KVH * HD, ld, FT_TILE);
     if (rc == CM_OK) rc = make_map(&map_v, v, T, (long long)KVH * HD, ld, FT_TILE);
+    // the cache as rows of one head: [k|v, page, kv head, entry] x head size; a box is one page of one head
+    if (PAST) {
+        if (rc == CM_OK) rc = make_map(&map_pool, pool, 2 * past.pages * KVH * PAGE_TOKENS, HD, HD, PAGE_TOKENS);
+    } else {
+        map_pool = map_k;
+    }
     if (rc != CM_OK) return rc;
     constexpr int KB = HD / 64;
     const size_t smem = (size_t)KB * FT_PIECE_BYTES * (1 + 2 * STAGES) + 2 * 2 * FT_PIECE_BYTES + 1024;
-    auto kernel = attn_prefill_tc_kernel<HD, STAGES>;
+    auto kernel = attn_prefill_tc_kernel<HD, STAGES, PAST>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -401,8 +460,8 @@ static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, con
         configured = true;
     }
     dim3 grid((max_len + FT_TILE - 1) / FT_TILE, QH, B);
-    cm_launch(kernel, grid, FT_THREADS, smem, st, map_q, map_k, map_v, (bf16*)ctx, ldc, (const bf16*)gate, ldg, seq_start,
-              QH, KVH, window, scale * 1.4426950408889634f, err);
+    cm_launch(kernel, grid, FT_THREADS, smem, st, map_q, map_k, map_v, map_pool, past, (bf16*)ctx, ldc, (const bf16*)gate,
+              ldg, seq_start, QH, KVH, window, scale * 1.4426950408889634f, err);
     {
         cudaError_t e_ = cudaGetLastError();
         if (e_ != cudaSuccess) {
@@ -427,9 +486,40 @@ extern "C" int cm_attn_prefill_tc(void* ctx, long long ldc, const void* q, const
     if (QH % KVH) CM_REFUSE("attn_prefill_tc: %d query heads over %d key heads", QH, KVH);
     if (ld % 8 || ldc % 8 || (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)ctx) & 15))
         CM_REFUSE("attn_prefill_tc: row pitches %lld, %lld must be multiples of 8 and the operands 16-byte aligned", ld, ldc);
+    const FtPast none = {nullptr, nullptr, nullptr, 0, 0, 0};
     if (HD == 64)
-        return launch_ft<64, 3>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale, err, st);
+        return launch_ft<64, 3, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
+                                       none, nullptr, err, st);
     if (HD == 128)
-        return launch_ft<128, 2>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale, err, st);
+        return launch_ft<128, 2, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
+                                        none, nullptr, err, st);
     CM_REFUSE("attn_prefill_tc: head size %d (64 or 128)", HD);
+}
+
+// The same for sequences that stand at seq_pos0[b] >= 0: entries below that position come from the
+// paged bfloat16 cache `pool` [2, pages, KVH, PAGE_TOKENS, HD] through the page table (a ring of
+// `ring` entries when ring > 0), the rest from the step's own rows.  The caller clears the unwritten
+// entries of every sequence's last page first (cm_kv_clear_tail) and writes the step's keys and
+// values to the cache afterwards.  max_len: the most rows a sequence brings to this step.
+extern "C" int cm_attn_append_tc(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
+                                 const void* gate, long long ldg, const int* seq_start, const int* seq_pos0,
+                                 const int* seq_slot, const void* pool, long long pages, const int* ptab,
+                                 long long ptab_stride, int ring, int B, int max_len, long long T, int QH, int KVH,
+                                 int HD, int window, float scale, int* err, cudaStream_t st) {
+    if (B <= 0 || max_len <= 0) return CM_OK;
+    if (QH % KVH) CM_REFUSE("attn_append_tc: %d query heads over %d key heads", QH, KVH);
+    if (ring % PAGE_TOKENS) CM_REFUSE("attn_append_tc: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
+    if (!seq_pos0 || !seq_slot || !pool || !ptab)
+        CM_REFUSE("attn_append_tc: positions, slots, cache and page table are needed");
+    if (ld % 8 || ldc % 8 || (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)ctx | (uintptr_t)pool) & 15))
+        CM_REFUSE("attn_append_tc: row pitches %lld, %lld must be multiples of 8 and the operands 16-byte aligned", ld, ldc);
+    if (2 * pages * KVH * PAGE_TOKENS > 0x7fffffffLL) CM_REFUSE("attn_append_tc: a cache of %lld pages is too large", pages);
+    const FtPast past = {seq_pos0, seq_slot, ptab, ptab_stride, pages, ring};
+    if (HD == 64)
+        return launch_ft<64, 3, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
+                                      past, pool, err, st);
+    if (HD == 128)
+        return launch_ft<128, 2, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
+                                       past, pool, err, st);
+    CM_REFUSE("attn_append_tc: head size %d (64 or 128)", HD);
 }

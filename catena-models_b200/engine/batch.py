@@ -43,7 +43,7 @@ class StepBatch:
 
     KINDS = ("prefill", "decode", "append")
 
-    def __init__(self, layout, device_buf, kind, lengths, positions, n_want, n_updates, max_len=None):
+    def __init__(self, layout, device_buf, kind, lengths, positions, n_want, n_updates, max_len=None, max_end=None):
         if kind not in self.KINDS:
             raise ValueError(f"step kind {kind!r}; one of {self.KINDS}")
         self.layout = layout
@@ -63,7 +63,8 @@ class StepBatch:
         self.B, self.T = layout.B, layout.T
         # longest run of new tokens; a step recorded for a class of shapes is launched for the class's bound
         self.max_len = max_len if max_len is not None else (max(lengths) if lengths else 0)
-        self.max_end = max((p + n for p, n in zip(positions, lengths)), default=0)
+        # how far the longest sequence reaches with this step; recorded steps: the bound of its class of lengths
+        self.max_end = max_end if max_end is not None else max((p + n for p, n in zip(positions, lengths)), default=0)
         self.n_want, self.n_updates = n_want, n_updates
         self.wants_every_row = False                           # want_rows is 0, 1, ..., T-1 (set by the decode path)
         self.prev_sampled = None                               # device int32: tokens the step before chose (decode path)

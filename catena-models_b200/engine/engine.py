@@ -315,18 +315,26 @@ class Engine:
         whose class of shapes comes a second time is recorded into a graph as it runs and replayed
         from then on: about 200 launches from Python cost more than a short prompt's kernels take.
         A class is (number of sequences, tokens rounded up to PROMPT_PAD, longest prompt rounded up
-        likewise, number of wanted places): the step runs that many rows, the surplus as padding that
+        likewise, number of wanted places; for tokens on top of held ones also the class of lengths
+        that the longest sequence reaches): the step runs that many rows, the surplus as padding that
         belongs to no sequence, and everything about the real lengths travels in the step's metadata,
         so one recording serves every prompt of its class.  The few most recent classes are kept."""
         B, T = len(slots), sum(len(t) for t in tokens)
         n_want = sum(len(w) for w in want)
-        key = entry = max_len = None
+        key = entry = max_len = max_end = None
         T_run, U_cap = T, len(updates)
-        if kind == "prefill" and self.use_graphs and self.model.prompt_capturable and T <= PROMPT_GRAPH_MAX_TOKENS:
+        if (kind in ("prefill", "append") and self.use_graphs and self.model.prompt_capturable
+                and T <= PROMPT_GRAPH_MAX_TOKENS):
             T_run = -(-T // PROMPT_PAD) * PROMPT_PAD
             max_len = -(-max(len(t) for t in tokens) // PROMPT_PAD) * PROMPT_PAD
             U_cap = (T_run // PAGE_TOKENS + B) * max(1, self.n_kv_groups)    # no step of the class needs more pages
             key = (B, T_run, max_len, n_want, sampling is not None)
+            if kind == "append":
+                # tokens on top of what the sequences hold: the class also names how far the longest one
+                # reaches, in the state specs' own classes of lengths, and the step is launched for their bound
+                classes = self._length_classes(max(p + len(t) for p, t in zip(positions, tokens)))
+                key += ("append", classes)
+                max_end = max(classes) or None
             entry = self._prompt_graphs.get(key)
         layout = entry.layout if entry else BatchLayout(T_run, B, n_want, U_cap)
         host, idx = self._staging.take(layout.size)
@@ -354,7 +362,8 @@ class Engine:
         else:
             dev = host[:layout.size].to(self.rt.device, non_blocking=True)
         self._staging.mark(idx)
-        batch = StepBatch(layout, dev, kind, [len(t) for t in tokens], positions, n_want, len(updates), max_len=max_len)
+        batch = StepBatch(layout, dev, kind, [len(t) for t in tokens], positions, n_want, len(updates), max_len=max_len,
+                          max_end=max_end)
         # a decode step that wants its every row: the same launches as its recorded form
         batch.wants_every_row = kind == "decode" and all(w == [0] for w in want)
         sampled = torch.empty(B, dtype=torch.int32, device=self.rt.device) if sampling is not None else None

@@ -121,9 +121,7 @@ class GQAttention(Mixer):
                 k, v = proj[:, QS:QS + KVS], proj[:, QS + KVS:QS + 2 * KVS]
                 batch.shared[("kv", state.unit)] = (k, v)
             if batch.append:
-                kernels.attn_append(ctx, q, k, v, gate, batch.seq_start, batch.seq_pos0, batch.seq_slot, state.pool,
-                                    state.pages, state.ptab, state.ring, batch.B, batch.max_len, QH, KVH, HD,
-                                    self.window, self.scale, tensor_cores=rt.tensor_core_prompts)
+                rt.attention_append(ctx, q, k, v, gate, batch, state, QH, KVH, HD, self.window, self.scale)
                 if not self.shares_kv:
                     kernels.kv_store(proj[:, QS:QS + 2 * KVS], batch.tok_pos, batch.tok_seq, batch.seq_slot,
                                      batch.seq_end, state.pool, state.pages, state.ptab, state.ring, KVH, HD)

@@ -70,7 +70,9 @@ class Part:
     # takes everything about the real lengths from the step's device metadata, and that leaves rows of
     # padding alone (StepBatch.tok_seq is -1 there: they belong to no sequence and must touch no state):
     # the engine may then record a prompt step of a class into a graph and replay it for every prompt
-    # of the class.  A part says so itself; one that does not know is not recorded.
+    # of the class.  With supports_append this holds for steps of kind "append" too, whose class also
+    # names the class of lengths that the longest sequence reaches (StepBatch.max_end is then that
+    # class's bound, not the real end).  A part says so itself; one that does not know is not recorded.
     prompt_capturable = False
     # True for a part that can take a step of kind "append" (StepBatch.kind): sequences that stand at
     # any position and bring any number of tokens.  A part that works row by row (norm, feed-forward,

@@ -203,6 +203,61 @@ def test_attn_append_reads_the_past_from_the_pages(dtype, tensor_cores, QH, KVH,
         off += n
 
 
+@pytest.mark.parametrize("QH,KVH,HD,window", [(8, 2, 64, 0), (2, 2, 128, 100), (4, 1, 64, 300), (3, 3, 128, 0),
+                                              (2, 1, 64, 64)])
+def test_attn_append_on_tcgen05_copies_pages_and_masks_what_is_not_the_sequences(QH, KVH, HD, window):
+    """The tcgen05 form copies whole pages of the cache into a matrix operand.  Sequences that stand
+    at 0, inside a page, on a page's edge, in the second page of a 128-key tile, beyond a ring's size
+    and several tiles in; the unused entries of the cache are NaN (the step's rule for the last
+    page's unwritten entries is `kv_clear_tail`, which runs first, as in the runtime).  Against
+    float64 attention over the whole sequences, and no pipeline wait may have run out."""
+    from catena_models_b200 import kernels as K
+
+    dtype = torch.bfloat16
+    ring = (window + 63) // 64 * 64 if window else 0
+    past = [0, 5, 64, 130, 200, 257, 700]
+    new = [33, 1, 70, 150, 64, 2, 300]
+    g = torch.Generator().manual_seed(HD + window)
+    kv = [torch.randn(p + n, 2, KVH, HD, generator=g) for p, n in zip(past, new)]
+    stored = [x[:p] for x, p in zip(kv, past)]
+    pool, pages, ptab = _paged_cache(K, stored, KVH, HD, dtype, past, ring)
+    T = sum(new)
+    width = (QH * HD + 2 * KVH * HD + QH + 7) // 8 * 8
+    buf = rnd(T, width, dtype=dtype, seed=HD)
+    q = buf[:, :QH * HD]
+    k, v = buf[:, QH * HD:QH * HD + KVH * HD], buf[:, QH * HD + KVH * HD:QH * HD + 2 * KVH * HD]
+    gate = buf[:, QH * HD + 2 * KVH * HD:QH * HD + 2 * KVH * HD + QH]
+    starts, off = [0], 0
+    for b, (p, n) in enumerate(zip(past, new)):
+        k[off:off + n] = kv[b][p:, 0].reshape(n, KVH * HD).to(dtype).to(DEV)
+        v[off:off + n] = kv[b][p:, 1].reshape(n, KVH * HD).to(dtype).to(DEV)
+        off += n
+        starts.append(off)
+    starts = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    pos0 = torch.tensor(past, dtype=torch.int32, device=DEV)
+    slots = torch.arange(1, len(past) + 1, dtype=torch.int32, device=DEV)
+    ctx = torch.full((T, QH * HD), float("nan"), dtype=dtype, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = HD ** -0.5
+    held = pool.clone()
+    K.kv_clear_tail(pos0, slots, pool, pages, ptab, ring, len(past), KVH, HD)
+    # what was cleared was NaN (unwritten), never an entry that holds a position
+    changed = (pool != held) & ~(pool.isnan() & held.isnan())
+    assert bool(held[changed].isnan().all()) and bool((pool[changed] == 0).all())
+    K.attn_append_tc(ctx, q, k, v, gate, starts, pos0, slots, pool, pages, ptab, ring, len(past), max(new), QH, KVH, HD,
+                     window, scale, err=err)
+    assert int(err.item()) == 0
+    off = 0
+    for b, (p, n) in enumerate(zip(past, new)):
+        qq = torch.zeros(p + n, QH, HD)
+        qq[p:] = q[off:off + n].float().cpu().view(n, QH, HD)
+        gg = torch.zeros(p + n, QH)
+        gg[p:] = gate[off:off + n].float().cpu()
+        ref = _ref_attention(qq, kv[b][:, 0].to(dtype), kv[b][:, 1].to(dtype), window, scale, gg)[p:]
+        close(ctx[off:off + n].view(n, QH, HD), ref, dtype)
+        off += n
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("KVH,HD,ring", [(2, 16, 0), (1, 24, 64), (3, 64, 128)])
 def test_kv_store_writes_what_qk_prepare_would(dtype, KVH, HD, ring):

@@ -387,3 +387,37 @@ def test_one_recording_serves_a_class_of_prompt_shapes(folders, plain, name, dty
     check(torch.cat(all_got), torch.cat(all_exact), dtype, torch.cat(all_same) if all_same else None)
     # the six single prompts are one class (128 rows, two wanted places), recorded at its second prompt
     assert (1, 128, 128, 2, False) in eng._prompt_graphs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "L"])
+def test_one_recording_serves_a_class_of_append_steps(folders, plain, name, dtype):
+    """Tokens on top of held ones are recorded per class as well (the class also names the class of
+    lengths that the longest sequence reaches).  Requests with heads of many lengths bring second
+    pieces of 33 to 64 tokens, alone and in pairs of unequal lengths, then one more token each: the
+    first of a class runs kernel by kernel, the second is recorded, the others are replayed, and all
+    must match the plain model; the padding rows of a replay must leave cache and state alone."""
+    eng = engine_for(folders, name, dtype)
+    vocab = plain[name][0]["vocab_size"]
+    all_got, all_exact, all_same = [], [], []
+    cases = [((10, 40),), ((70, 64),), ((1, 33),), ((120, 50),), ((64, 64),), ((33, 45),),
+             ((10, 20), (50, 30)), ((64, 1), (5, 60)), ((100, 33), (3, 31)), ((20, 40), (90, 24))]
+    for rep, case in enumerate(cases):
+        seqs = [tiny.random_prompt(h + n + 1, vocab, seed=900 + 10 * rep + i) for i, (h, n) in enumerate(case)]
+        slots = eng.admit(len(case))
+        eng.step(slots, [s[:h] for s, (h, n) in zip(seqs, case)], [[] for _ in case])
+        got = eng.step(slots, [s[h:h + n] for s, (h, n) in zip(seqs, case)], [[0, n - 1] if n > 1 else [0] for h, n in case]).clone()
+        got2 = eng.step(slots, [[s[-1]] for s in seqs]).clone()
+        eng.release(slots)
+        off = 0
+        for i, (s, (h, n)) in enumerate(zip(seqs, case)):
+            exact, same = plain_logits(plain, name, s, dtype)
+            places = [h, h + n - 1] if n > 1 else [h]
+            all_got.append(torch.cat([got[off:off + len(places)], got2[i:i + 1]]))
+            off += len(places)
+            all_exact.append(exact[places + [h + n]])
+            if same is not None:
+                all_same.append(same[places + [h + n]])
+    check(torch.cat(all_got), torch.cat(all_exact), dtype, torch.cat(all_same) if all_same else None)
+    assert any(len(k) > 5 and k[5] == "append" for k in eng._prompt_graphs)
+    assert not eng.cache.book.live

@@ -247,7 +247,9 @@ def test_sixty_four_unequal_prompts_then_decode_at_other_widths(tmp_path, name):
 @pytest.mark.parametrize("name", list(WIDTHS))
 def test_a_long_prompt_in_chunks_at_other_widths(tmp_path, name):
     """A prompt of 1,300 tokens whole (tcgen05 attention and the tiled product) and in chunks of 700
-    and 600 (the append path over the cache), bfloat16, against the plain model at a few places."""
+    and 600 (the append path over the cache: tcgen05 attention that copies pages, from a position inside a
+    page), three times so that the second piece also runs from its recording, bfloat16, against the plain
+    model at a few places."""
     from catena_models_b200.api import Model
     from catena_models_b200.weights.random_init import write_random_model
 
@@ -263,10 +265,14 @@ def test_a_long_prompt_in_chunks_at_other_widths(tmp_path, name):
     (slot,) = eng.admit(1)
     whole = eng.step([slot], [seq], [places]).clone()
     eng.release([slot])
-    (slot,) = eng.admit(1)
-    cut = torch.cat([eng.step([slot], [seq[:700]], [[0, 699]]).clone(), eng.step([slot], [seq[700:]], [[0, 599]]).clone()])
-    eng.release([slot])
+    cuts = []
+    for rep in range(3):                 # kernel by kernel, recorded, replayed from the recording
+        (slot,) = eng.admit(1)
+        cuts.append(torch.cat([eng.step([slot], [seq[:700]], [[0, 699]]).clone(),
+                               eng.step([slot], [seq[700:]], [[0, 599]]).clone()]))
+        eng.release([slot])
     eng.check_errors()
-    for got in (whole, cut):
+    assert any(len(k) > 5 and k[5] == "append" for k in eng._prompt_graphs)
+    for got in [whole] + cuts:
         assert rel(got, ref) < 2.0 * rel(noise, ref)
         assert rms(got, ref) < 0.3
