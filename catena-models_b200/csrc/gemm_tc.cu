@@ -88,8 +88,8 @@ __device__ __forceinline__ void tile_origin(int tile, int m_tiles, int n_tiles, 
 template <int BLOCK_N, int STAGES, typename TC, int MODE>
 __global__ void __launch_bounds__(TCP_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_c, int tma_store, TC* __restrict__ C, int M, int N, int K,
-               long long ldc, int* err) {
+               const __grid_constant__ CUtensorMap map_c, int tma_store_ok, TC* __restrict__ C, int M, int N, int K,
+               long long ldc, int ksplit, long long part_stride, int* err) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = BLOCK_N * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -106,6 +106,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int n_tiles = (N + OUT_COLS - 1) / OUT_COLS;
     const int m_tiles = (M + TC_BM - 1) / TC_BM;
     const int num_tiles = n_tiles * m_tiles;
+    // ksplit > 1: the inner dimension is cut into ksplit runs of kb_per k-slices, every (run, tile) is an
+    // item of work of its own, and run r leaves its sums at C + r * part_stride (map_c: row r * M + ...)
+    const int kb_per = (num_kb + ksplit - 1) / ksplit;
+    const int num_items = num_tiles * ksplit;
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;                    // swizzle atoms need 1024-byte alignment
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
     const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = smem_u32(&bars[2 * STAGES + 2]);
@@ -139,11 +143,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ------------------------------------------------------------- TMA loader
         int it = 0;                               // k-slices issued so far, over all tiles
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+            const int run = item / num_tiles, tile = item - run * num_tiles;
             int m_tile, n_tile;
             tile_origin(tile, m_tiles, n_tiles, &m_tile, &n_tile);
             const int m0 = m_tile * TC_BM, n0 = n_tile * OUT_COLS;
-            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            const int kb_end = min(num_kb, (run + 1) * kb_per);
+            for (int kb = run * kb_per; kb < kb_end; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, err, TC_ERR_TIMEOUT_LOAD);
@@ -168,14 +174,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                    ((uint32_t)(TC_BM >> 4) << 24);
         int it = 0, local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++local) {
             const int acc = local & 1;
             // the epilogue must have drained this accumulator (two tiles ago)
             ok = mbar_wait(acc_empty0 + 8 * acc, ((local >> 1) & 1) ^ 1, &abort_flag, err, TC_ERR_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
-            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            const int kb_begin = (item / num_tiles) * kb_per, kb_end = min(num_kb, kb_begin + kb_per);
+            for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, err, TC_ERR_TIMEOUT_MMA);
@@ -185,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint64_t bdesc = umma_desc(tiles + s * STAGE_BYTES + A_BYTES);
 #pragma unroll
                 for (int k = 0; k < TC_BK / 16; ++k)      // 16 values of k = 32 bytes further in the row
-                    umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+                    umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((kb - kb_begin) | k) != 0);
                 umma_commit(empty0 + 8 * s);              // stage is free once these MMAs have read it
             }
             if (ok) umma_commit(acc_full0 + 8 * acc);     // accumulator complete
@@ -203,12 +210,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t sbuf = tiles + STAGES * STAGE_BYTES + (uint32_t)group * 16384u;   // the group's staging buffer
         const int r_tile = q * 32 + lane;
         int local = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+        for (int item = blockIdx.x; item < num_items; item += gridDim.x, ++local) {
             const int acc = local & 1;
+            const int run = item / num_tiles, tile = item - run * num_tiles;
             int m_tile, n_tile;
             tile_origin(tile, m_tiles, n_tiles, &m_tile, &n_tile);
             const int m0 = m_tile * TC_BM, n0 = n_tile * OUT_COLS;
             const int row = m0 + r_tile;
+            // a run's rows end at M, where the next run's begin: a row tile that crosses M is stored from registers
+            const bool tma_store = tma_store_ok && (ksplit == 1 || m0 + TC_BM <= M);
+            TC* const C_run = C + (long long)run * part_stride;
             const bool ok = mbar_wait(acc_full0 + 8 * acc, (local >> 1) & 1, &abort_flag, err, TC_ERR_TIMEOUT_EPILOGUE);
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (uint32_t)(acc * BLOCK_N) + ((uint32_t)(q * 32) << 16);
@@ -238,7 +249,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             stage_cols(sbuf, r_tile, h * (32 * (int)sizeof(TC) / 16), v, (TC*)nullptr);
                         } else {
                             const int col = n0 + c;
-                            if (row < M && col < N) store_cols<TC>(C + (long long)row * ldc + col, v, N - col, vec_ok);
+                            if (row < M && col < N) store_cols<TC>(C_run + (long long)row * ldc + col, v, N - col, vec_ok);
                         }
                     }
                 }
@@ -246,7 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
                     if (elected) {
-                        if (ok && n0 + c0 < N) tma_store_2d(&map_c, sbuf, n0 + c0, m0);   // clipped at M and N
+                        if (ok && n0 + c0 < N) tma_store_2d(&map_c, sbuf, n0 + c0, run * M + m0);   // clipped at M and N
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 }
@@ -545,7 +556,7 @@ static int make_map_c(CUtensorMap* map, void* base, long long M, long long N, lo
 
 template <int BLOCK_N, int STAGES, typename TC, int MODE>
 static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
-                     long long ldc, int* err, cudaStream_t st) {
+                     long long ldc, int* err, cudaStream_t st, int ksplit = 1, long long part_stride = 0) {
     CUtensorMap map_a, map_b;
     const long long b_rows = MODE == TC_MODE_SWIGLU ? 2LL * N : N;
     const int b_box = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
@@ -559,7 +570,7 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
     CUtensorMap map_c = map_a;
     const int tma_store = ((ldc * (long long)sizeof(TC)) % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
     if (tma_store) {
-        rc = make_map_c<TC>(&map_c, C, M, N, ldc);
+        rc = make_map_c<TC>(&map_c, C, (long long)ksplit * M, N, ldc);      // the runs of a split product lie one below the other
         if (rc != CM_OK) return rc;
     }
     const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BLOCK_N * TC_BK * 2) + 2 * 16384 + 1024;
@@ -581,8 +592,10 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count <= 0) sm_count = 1;
     }
-    dim3 grid(num_tiles < sm_count ? num_tiles : sm_count);
-    cm_launch(kernel, grid, TCP_THREADS, smem, st, map_a, map_b, map_c, tma_store, (TC*)C, M, N, K, ldc, err);
+    const int num_items = num_tiles * ksplit;
+    dim3 grid(num_items < sm_count ? num_items : sm_count);
+    cm_launch(kernel, grid, TCP_THREADS, smem, st, map_a, map_b, map_c, tma_store, (TC*)C, M, N, K, ldc, ksplit,
+              part_stride, err);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -695,6 +708,30 @@ extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M,
     if (dtc == DT_BF16) return launch_tc<128, 6, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     if (dtc == DT_F32) return launch_tc<128, 6, float, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     return CM_ERR_DTYPE;
+}
+
+// P[r][m][n] = the product over the r-th of `splits` runs of K (each a whole number of 64-wide k-slices),
+// float, the runs part_stride = M * N elements apart: the tiled product for shapes with too few output
+// tiles to occupy the device (a few hundred rows times a narrow output), with every (run, tile) a work
+// item of the persistent kernel and no exchange between blocks; whoever consumes the product adds the
+// runs in order (cm_add_norm with m_parts).  block_n as for cm_gemm_tc.
+extern "C" int cm_gemm_tc_parts(float* P, const void* A, const void* B, int M, int N, int K, long long lda,
+                                long long ldb, int splits, int block_n, int* err, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return CM_OK;
+    if (K <= 0 || K % 8 || lda % 8 || ldb % 8)
+        CM_REFUSE("gemm_tc_parts: inner size %d and row pitches %lld, %lld must be multiples of 8", K, lda, ldb);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(P)) & 15)
+        CM_REFUSE("gemm_tc_parts: operands must be 16-byte aligned");
+    if (block_n != 128 && block_n != 256) CM_REFUSE("gemm_tc_parts: tile width %d (128 or 256)", block_n);
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    if (splits < 1 || splits > 8 || (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb)
+        CM_REFUSE("gemm_tc_parts: %d runs over %d k-slices (1 to 8 runs, none empty)", splits, num_kb);
+    if (N % 4) CM_REFUSE("gemm_tc_parts: %d output columns (a multiple of 4)", N);
+    if ((long long)splits * M > 0x7fffffffLL) CM_REFUSE("gemm_tc_parts: %d runs of %d rows", splits, M);
+    const long long part_stride = (long long)M * N;
+    if (block_n == 256)
+        return launch_tc<256, 4, float, TC_MODE_PLAIN>(P, A, B, M, N, K, lda, ldb, N, err, st, splits, part_stride);
+    return launch_tc<128, 6, float, TC_MODE_PLAIN>(P, A, B, M, N, K, lda, ldb, N, err, st, splits, part_stride);
 }
 
 template <typename TC, int MODE>

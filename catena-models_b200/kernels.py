@@ -48,6 +48,7 @@ _SIGNATURES = {
     "cm_attn_append_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _ll, _i,
                           _i, _i, _i, _f, _vp, _vp],
     "cm_kv_clear_tail": [_i, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp],
+    "cm_gemm_tc_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _i, _vp, _vp],
     "cm_kv_store": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp],
     "cm_sample": [_vp, _vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "cm_scatter_i32": [_vp, _vp, _vp, _vp, _i, _vp],
@@ -452,6 +453,23 @@ def gemm_tc_few_rows_parts(parts, x, w, err=None):
     _check(lib().cm_gemm_tc_few_rows_parts(_ptr(parts), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), M * N, S,
                                            _ptr(err), _stream()), "gemm_tc_few_rows_parts",
            cost=lambda: (f"{M}x{N}x{K} in {S} slices", _nbytes(x, w, parts), 2 * M * N * K))
+
+
+def gemm_tc_parts(parts, x, w, err=None, block_n=256):
+    """parts[r] = x @ w^T over the r-th of parts.shape[0] runs of the inner dimension, float32
+    [runs, rows, width] contiguous: the tiled tcgen05 product for a few hundred rows times a narrow
+    output, cut over K so that its (run, tile) items occupy the device; no exchange between blocks,
+    the consumer adds the runs in order (`add_norm` takes them as `PartialSums`)."""
+    _need_cuda(parts, x, w)
+    S, M, N = parts.shape
+    if parts.dtype != torch.float32 or not parts.is_contiguous() or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_parts: contiguous float32 partial sums of a bfloat16 product")
+    if x.shape[0] != M or w.shape[0] != N or x.shape[1] != w.shape[1] or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemm_tc_parts: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(parts.shape)}")
+    K = x.shape[1]
+    _check(lib().cm_gemm_tc_parts(_ptr(parts), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), S, block_n, _ptr(err),
+                                  _stream()), "gemm_tc_parts",
+           cost=lambda: (f"{M}x{N}x{K} in {S} runs", _nbytes(x, w, parts), 2 * M * N * K))
 
 
 def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256):

@@ -157,6 +157,44 @@ def test_gemm_tc_few_rows_parts(K, M, N, Kin, slices):
         K.gemm_tc_few_rows_parts(torch.empty(4, M, N, device=DEV), x[:, :64].contiguous(), w[:, :64].contiguous(), err=err)
 
 
+@pytest.mark.parametrize("block_n", [128, 256])
+@pytest.mark.parametrize("M,N,Kin,slices", [(200, 2048, 2048, 4), (333, 104, 520, 3), (1024, 264, 1096, 2), (129, 516, 8192, 8),
+                                            (640, 2048, 448, 7), (300, 72, 192, 1)])
+def test_gemm_tc_parts(K, M, N, Kin, slices, block_n):
+    """The tiled tcgen05 product cut over K into float runs (work items of the persistent kernel): each
+    run against the float64 product over its own k range, with row counts that end inside a row tile
+    (the run below begins right there: such tiles are stored from registers, whole ones by TMA),
+    widths that end inside a column tile, an inner size that ends inside a 64-wide step, and
+    add_norm over the runs against add_norm over the rounded total."""
+    x = rnd(M, Kin, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, Kin, dtype=torch.bfloat16, scale=Kin ** -0.5, seed=2)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    guard = torch.full((slices * M * N + 512,), float("nan"), device=DEV)
+    parts = guard[:slices * M * N].view(slices, M, N)
+    K.gemm_tc_parts(parts, x, w, err=err, block_n=block_n)
+    assert int(err) == 0
+    assert bool(guard[slices * M * N:].isnan().all())            # nothing written past the last run
+    steps = (Kin + 63) // 64
+    per = (steps + slices - 1) // slices
+    xd, wd = x.double().cpu(), w.double().cpu()
+    for s_ in range(slices):
+        k0, k1 = min(Kin, s_ * per * 64), min(Kin, (s_ + 1) * per * 64)
+        torch.testing.assert_close(parts[s_].double().cpu(), xd[:, k0:k1] @ wd[:, k0:k1].T, rtol=1e-4, atol=1e-4)
+    if N % 8 == 0:
+        total = parts[0].clone()
+        for s_ in range(1, slices):
+            total += parts[s_]
+        m = total.to(torch.bfloat16)
+        h = rnd(M, N, dtype=torch.bfloat16, seed=3)
+        wp, wn = 1 + 0.1 * rnd(N, seed=4), 1 + 0.1 * rnd(N, seed=5)
+        h_a, n_a, h_b, n_b = (torch.empty_like(h) for _ in range(4))
+        K.add_norm(h_a, n_a, K.PartialSums(parts, torch.bfloat16), h, wp, wn, 1e-5, 1e-6)
+        K.add_norm(h_b, n_b, m, h, wp, wn, 1e-5, 1e-6)
+        assert torch.equal(h_a, h_b) and torch.equal(n_a, n_b)
+    with pytest.raises(K.KernelError):                             # a run without a k-slice
+        K.gemm_tc_parts(torch.empty(4, M, N, device=DEV), x[:, :128].contiguous(), w[:, :128].contiguous(), err=err)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu_and_gather(K, dtype):
     gu = rnd(5, 2 * 72, dtype=dtype, scale=2.0)
