@@ -264,22 +264,24 @@ class Runtime:
     TCGEN05_APPEND_MIN_ROWS = 16
     TCGEN05_APPEND_MIN_SPAN = 512
 
-    def attention_append(self, ctx, q, k, v, gate, batch, state, QH, KVH, HD, window, scale):
+    def attention_append(self, ctx, q, k, v, gate, batch, state, QH, KVH, HD, window, scale, tail_unwritten=True):
         """Attention of a step whose sequences already hold tokens: keys and values below each
         sequence's first position of the step come from the paged cache, the rest from the step's own
         rows (written to the cache by the caller afterwards).  The choice of kernel follows
         `attention_prefill`, with the span counted from the longest sequence's end and the tcgen05 kernel
         from shorter spans on (its blocks walk the past as well, so they are long enough to pipeline
         sooner); it copies whole pages, so the unwritten entries of every sequence's last page are
-        cleared first."""
+        cleared first, unless the caller says that the step's keys and values are in the cache already
+        (`tail_unwritten=False`: a layer that reads the state another layer has just written)."""
         aligned = (q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
                    and v.data_ptr() % 16 == 0 and state.pool.data_ptr() % 16 == 0)
         bf16 = q.dtype == torch.bfloat16 and state.pool.dtype == torch.bfloat16 and self.tensor_core_prompts
         span = min(batch.max_end, window) if window else batch.max_end
         if (bf16 and aligned and HD in (64, 128) and span >= self.TCGEN05_APPEND_MIN_SPAN
                 and batch.max_len >= self.TCGEN05_APPEND_MIN_ROWS and ctx.stride(0) % 8 == 0 and ctx.data_ptr() % 16 == 0):
-            kernels.kv_clear_tail(batch.seq_pos0, batch.seq_slot, state.pool, state.pages, state.ptab, state.ring,
-                                  batch.B, KVH, HD)
+            if tail_unwritten:
+                kernels.kv_clear_tail(batch.seq_pos0, batch.seq_slot, state.pool, state.pages, state.ptab, state.ring,
+                                      batch.B, KVH, HD)
             kernels.attn_append_tc(ctx, q, k, v, gate, batch.seq_start, batch.seq_pos0, batch.seq_slot, state.pool,
                                    state.pages, state.ptab, state.ring, batch.B, batch.max_len, QH, KVH, HD, window,
                                    scale, err=self.error_flag)

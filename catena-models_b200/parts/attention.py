@@ -121,7 +121,8 @@ class GQAttention(Mixer):
                 k, v = proj[:, QS:QS + KVS], proj[:, QS + KVS:QS + 2 * KVS]
                 batch.shared[("kv", state.unit)] = (k, v)
             if batch.append:
-                rt.attention_append(ctx, q, k, v, gate, batch, state, QH, KVH, HD, self.window, self.scale)
+                rt.attention_append(ctx, q, k, v, gate, batch, state, QH, KVH, HD, self.window, self.scale,
+                                    tail_unwritten=not self.shares_kv)
                 if not self.shares_kv:
                     kernels.kv_store(proj[:, QS:QS + 2 * KVS], batch.tok_pos, batch.tok_seq, batch.seq_slot,
                                      batch.seq_end, state.pool, state.pages, state.ptab, state.ring, KVH, HD)
