@@ -94,7 +94,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr uint32_t B_BYTES = BLOCK_N * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int OUT_COLS = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
-    constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;                 // two accumulators
+    constexpr uint32_t TMEM_COLS = 2 * BLOCK_N <= 256 ? 256 : 512;    // two accumulators; allocations are powers of two
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[2 * STAGES + 4];
     __shared__ uint32_t tmem_slot;
@@ -687,9 +687,9 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
 
 // A [M,K] and B [N,K] (2N rows when swiglu) bfloat16, row pitches lda/ldb multiples of 8
 // elements, bases 16-byte aligned; C bfloat16 or float.  block_n: 256 (128 x 256 tiles, four
-// stages: the most arithmetic per byte moved) or 128 (128 x 128 tiles, six stages: twice as
+// stages: the most arithmetic per byte moved), 128 (128 x 128 tiles, six stages: twice as
 // many tiles, for products with few rows where the number of tiles decides how many SMs stream
-// weights).  err: device int, raised by a block whose pipeline wait ran out; may be null.
+// weights) or 192 (plain bfloat16 products whose tiles then fill their rounds over the SMs better).  err: device int, raised by a block whose pipeline wait ran out; may be null.
 extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M, int N, int K, long long lda,
                           long long ldb, long long ldc, int swiglu, int block_n, int* err, cudaStream_t st) {
     if (M <= 0 || N <= 0) return CM_OK;
@@ -697,7 +697,8 @@ extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M,
         CM_REFUSE("gemm_tc: inner size %d and row pitches %lld, %lld must be multiples of 8", K, lda, ldb);
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15)
         CM_REFUSE("gemm_tc: operands must be 16-byte aligned");
-    if (block_n != 128 && block_n != 256) CM_REFUSE("gemm_tc: tile width %d (128 or 256)", block_n);
+    if (block_n != 128 && block_n != 192 && block_n != 256) CM_REFUSE("gemm_tc: tile width %d (128, 192 or 256)", block_n);
+    if (block_n == 192 && (swiglu || dtc != DT_BF16)) CM_REFUSE("gemm_tc: 192-wide tiles are for plain bfloat16 products");
     if (swiglu) {
         if (dtc != DT_BF16) return CM_ERR_DTYPE;
         if (block_n == 256) return launch_tc<256, 4, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
@@ -705,6 +706,8 @@ extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M,
     }
     if (dtc == DT_BF16 && block_n == 256)
         return launch_tc<256, 4, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
+    if (dtc == DT_BF16 && block_n == 192)
+        return launch_tc<192, 4, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     if (dtc == DT_BF16) return launch_tc<128, 6, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     if (dtc == DT_F32) return launch_tc<128, 6, float, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     return CM_ERR_DTYPE;

@@ -122,7 +122,8 @@ class Runtime:
         elif kind == "few_rows":
             kernels.gemm_tc_few_rows(y, x, w, err=self.error_flag)
         elif kind == "tiled":
-            kernels.gemm_tc(y, x, w, err=self.error_flag, block_n=self._tile_width(x.shape[0], w.shape[0]))
+            widths = (256, 192, 128) if y.dtype == torch.bfloat16 else (256, 128)
+            kernels.gemm_tc(y, x, w, err=self.error_flag, block_n=self._tile_width(x.shape[0], w.shape[0], widths))
         else:
             kernels.gemm_simt(y, x, w)
         return y
@@ -168,15 +169,21 @@ class Runtime:
             return 1
         return slices
 
-    def _tile_width(self, rows, out_columns):
-        """128 x 256 tiles move the fewest bytes per product, but a product with few of them leaves
-        SMs idle (512 rows x 2,048 columns: 32 tiles for 148 SMs).  128 x 128 tiles are used when
-        all of them still run at once, one per SM; with more than that the wide tiles win again
-        (measured at 512 to 1,536 rows)."""
+    # time of one 64-wide step of K on one tile, us, measured on B200 over 72 shapes (256 to 4,096 rows):
+    # a product takes about 4.5 us + rounds of tiles over the SMs x steps x this, whatever the width
+    TILE_STEP_US = {128: 0.30, 192: 0.33, 256: 0.35}
+
+    def _tile_width(self, rows, out_columns, widths=(256, 192, 128)):
+        """The tile width of the tiled product: the one whose tiles need the fewest rounds over the SMs,
+        weighted by what a step of K costs at that width (a 128 x 128 tile is bound by the operands'
+        way from L2, not by the tensor core, so it is not half the price of a 128 x 256 one).  Measured:
+        1,024 x 6,144 x 2,048 34.6 / 26.0 / 27.2 us at 128 / 192 / 256, 512 x 6,144 x 2,048 23.8 / 15.4 /
+        16.3, 2,048 x 2,048 x 8,192 81.6 / 83.0 / 50.6, 256 x 6,144 x 2,048 14.0 / 14.9 / 15.6."""
         if self._sm_count is None:
             self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
-        narrow_tiles = -(-rows // 128) * -(-out_columns // 128)
-        return 128 if narrow_tiles <= self._sm_count else 256
+        row_tiles = -(-rows // 128)
+        cost = {w: -(-(row_tiles * -(-out_columns // w)) // self._sm_count) * self.TILE_STEP_US[w] for w in widths}
+        return min(widths, key=lambda w: (cost[w], -w))
 
     SKINNY_ROWS = 64          # most rows the weight-streaming kernel takes
     SKINNY_BEST_ROWS = 16     # up to here it is the fastest kernel
@@ -231,7 +238,7 @@ class Runtime:
         if kind == "tiled":
             # a 256-wide tile of the packed matrix gives 128 output columns
             kernels.gemm_tc(a, x, w_gate_up, swiglu=True, err=self.error_flag,
-                            block_n=self._tile_width(x.shape[0], 2 * F))
+                            block_n=self._tile_width(x.shape[0], 2 * F, widths=(256, 128)))
             return a
         gu = self.linear(x, w_gate_up)
         kernels.swiglu(a, gu)

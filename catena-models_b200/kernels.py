@@ -476,7 +476,8 @@ def gemm_tc(y, x, w, swiglu=False, err=None, block_n=256):
     """y = x @ w^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory), any
     number of bfloat16 rows.  swiglu: w is [gate; up] with 2F rows and y[M, F] = silu(g) * u.
     err: device int32 that a block raises if one of its bounded pipeline waits runs out.
-    block_n: 256 (128 x 256 tiles) or 128 (twice as many 128 x 128 tiles, for few rows)."""
+    block_n: 256 (128 x 256 tiles), 128 (twice as many 128 x 128 tiles, for few rows) or 192 (plain
+    bfloat16 products only)."""
     _need_cuda(y, x, w)
     M, K = x.shape
     N = y.shape[1]

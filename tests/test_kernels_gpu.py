@@ -648,7 +648,8 @@ def test_refusals_are_errors_not_wrong_results(K):
 
 @pytest.mark.parametrize("M,N,Kd", [(128, 128, 64), (100, 70, 72), (1, 8, 8), (257, 384, 520), (2048, 2048, 2048),
                                      (65, 3104, 2048), (300, 200, 1000)])
-@pytest.mark.parametrize("dty,block_n", [(torch.bfloat16, 256), (torch.bfloat16, 128), (torch.float32, 128)])
+@pytest.mark.parametrize("dty,block_n", [(torch.bfloat16, 256), (torch.bfloat16, 192), (torch.bfloat16, 128),
+                                         (torch.float32, 128)])
 def test_gemm_tc(K, M, N, Kd, dty, block_n):
     """tcgen05/TMA GEMM: shapes that fill no tile in any dimension, K with a ragged last k-slice."""
     x, w = rnd(M, Kd, dtype=torch.bfloat16, seed=1), rnd(N, Kd, dtype=torch.bfloat16, scale=0.1, seed=2)
