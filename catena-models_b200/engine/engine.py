@@ -36,7 +36,11 @@ from .batch import BatchLayout, StepBatch, clear_sampling, fill_host, fill_host_
 PROMPT_GRAPH_MAX_TOKENS = 1024     # longer prompt steps are bound by the device, not by their launches
 PROMPT_GRAPHS_KEPT = 8
 PROMPT_PAD = 64                    # recorded prompt steps run a multiple of this many rows, the rest as padding
-DECODE_GRAPHS_KEPT = 24            # recorded decode steps (batch size, length class) kept; the least recently used goes
+# Recorded decode steps (batch size, length class) kept; the least recently used goes.  A batch whose
+# sequences end one by one walks through every batch size below its first, and a step of a new size costs 6
+# to 8 ms (1.7B-class: kernel by kernel, then the capture) where a replay costs 1.1 to 1.8 ms; a recording
+# holds about 22 MiB of its own (the allocator's block for its activations), so 96 of them are 2 GiB at most.
+DECODE_GRAPHS_KEPT = 96
 
 
 class StepError(ValueError):
