@@ -310,14 +310,12 @@ static int launch_fa_bq(void* ctx, long long ldc, const void* q, const void* k, 
 // Query tile: 128 rows (8 warps) for long sequences, where halving the key/value copies per unit
 // of work outweighs the coarser grid (measured: +6% at 16,384 tokens, -5% at 2,048); 64 rows
 // (4 warps) otherwise.
-static int g_fa_bq = 0;                       // 0: by length; 64 or 128: forced (experiments)
-extern "C" void cm_attn_prefill_set_tile(int bq) { g_fa_bq = bq; }
 
 template <int HD, bool PAST>
 static int launch_fa(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
                      const void* gate, long long ldg, const int* seq_start, int B, int max_len, int QH, int KVH,
                      int window, float scale, const FaPast& past, cudaStream_t st) {
-    const int bq = g_fa_bq ? g_fa_bq : (max_len >= 4096 ? 128 : 64);
+    const int bq = max_len >= 4096 ? 128 : 64;
     if (bq == 128)
         return launch_fa_bq<HD, 128, PAST>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, window, scale,
                                            past, st);

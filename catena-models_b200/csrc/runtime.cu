@@ -15,8 +15,6 @@ void cm_set_error(const char* fmt, ...) {
 
 extern "C" const char* cm_last_error() { return g_last_error; }
 
-extern "C" int cm_abi_version() { return 3; }
-
 // The compiled value of a limit of cm_limits.h by its name without the CM_ prefix; -1 if unknown.
 extern "C" long long cm_limit(const char* name) {
     struct Entry { const char* name; long long value; };
