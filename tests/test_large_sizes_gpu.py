@@ -276,3 +276,43 @@ def test_a_long_prompt_in_chunks_at_other_widths(tmp_path, name):
     for got in [whole] + cuts:
         assert rel(got, ref) < 2.0 * rel(noise, ref)
         assert rms(got, ref) < 0.3
+
+
+def test_several_tokens_on_top_in_a_mixed_schedule_at_full_width(big):
+    """Three requests of 580 to 700 tokens at the 1.7B-class widths (heads of 64: the tcgen05 attention
+    over the paged cache, from positions inside pages, on page borders and beside a request that starts
+    in the same step; the tiled product cut over K for the pieces of a few hundred rows): pieces of 16
+    to 300 tokens, single tokens in between, each piece a second time after its first run so that
+    recordings are replayed too, bfloat16 against the plain model."""
+    from catena_models_b200.api import Model
+
+    folder, (cfg, tensors) = big
+    V = cfg["vocab_size"]
+    seqs = [tiny.random_prompt(n, V, seed=70 + i) for i, n in enumerate((650, 700, 580))]
+    exact = [plain_lfm3.forward(cfg, tensors, s) for s in seqs]
+    noise = [plain_lfm3.forward(cfg, tensors, s, bf16=True) for s in seqs]
+    # (request -> tokens it brings) per step; a request absent from a step sits it out
+    plan = [{0: 100, 1: 300}, {0: 200, 1: 150, 2: 64}, {0: 1, 1: 1, 2: 1}, {0: 16, 2: 192}, {1: 64, 2: 130},
+            {0: 1, 1: 1, 2: 1}, {0: 300, 1: 100, 2: 100}, {0: 32, 1: 84, 2: 92}]
+    assert [sum(p.get(i, 0) for p in plan) for i in range(3)] == [650, 700, 580]
+    eng = Model.load(folder, dtype="bfloat16", max_tokens=4096).engine
+    for rep in range(3):
+        slots = eng.admit(3)
+        at, got, places = [0, 0, 0], [[], [], []], [[], [], []]
+        for step in plan:
+            ids = sorted(step)
+            want = [[0, step[i] - 1] if step[i] > 1 else [0] for i in ids]
+            out = eng.step([slots[i] for i in ids], [seqs[i][at[i]:at[i] + step[i]] for i in ids], want)
+            off = 0
+            for i, w in zip(ids, want):
+                got[i].append(out[off:off + len(w)].clone())
+                places[i] += [at[i] + x for x in w]
+                off += len(w)
+                at[i] += step[i]
+        eng.release(slots)
+        eng.check_errors()
+        for i in range(3):
+            g, ref = torch.cat(got[i]), exact[i][places[i]]
+            assert rel(g, ref) < 2.0 * rel(noise[i][places[i]], ref), (rep, i)
+            assert torch.equal(g.argmax(-1).cpu(), ref.argmax(-1)) or rel(g, ref) < 0.02
+    assert any(len(k) > 5 and k[5] == "append" for k in eng._prompt_graphs)
