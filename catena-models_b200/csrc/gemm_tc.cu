@@ -671,7 +671,11 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
                 break;
             }
         }
-        if (splits == 1) return 1;
+        // One block per tile then: the persistent kernel's job, except below 32 rows, where that kernel is a
+        // third slower than this one with a single slice (measured on B200, us: SwiGLU over 16,384 x 2,048
+        // weights at 24 rows 19.7 against 16.0, the 65,536 x 2,048 head at 17 to 31 rows 66 to 70 against 47
+        // to 49; from 32 rows on the two are level or the persistent kernel is ahead).
+        if (splits == 1 && M >= 32) return 1;
     }
     CUtensorMap map_a, map_b;
     int rc = make_map(&map_a, A, M, K, lda, A_ROWS);
@@ -788,5 +792,15 @@ extern "C" int cm_gemm_tc_few_rows(int dtc, void* C, const void* A, const void* 
         return CM_ERR_DTYPE;
     }
     if (rc != 1) return rc;
-    return cm_gemm_tc(dtc, C, A, B, M, N, K, lda, ldb, ldc, swiglu, 128, err, st);
+    // The persistent kernel with 128-wide tiles, which put the most SMs to streaming weights, unless they
+    // make one round and a fraction: the few tiles of the second round then stream alone, each at one SM's
+    // pace.  256-wide tiles run in one round instead (measured on B200, SwiGLU over 21,504 x 2,048 weights,
+    // 168 tiles for 148 SMs, 64 rows: 26.3 us against 22.0 us; 40 to 128 rows alike).
+    int sm_count = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    const int out_cols = swiglu ? 64 : 128;
+    const int tiles = (N + out_cols - 1) / out_cols;
+    const int width = (dtc == DT_BF16 && sm_count > 0 && tiles > sm_count && tiles <= 2 * sm_count) ? 256 : 128;
+    return cm_gemm_tc(dtc, C, A, B, M, N, K, lda, ldb, ldc, swiglu, width, err, st);
 }

@@ -98,6 +98,12 @@ class Runtime:
         the caller can take `kernels.PartialSums` instead (the product cut over K, to be added by the
         fused residual kernel): used where it spares the product an exchange between its blocks."""
         kind = self._product_kernel(x, w)
+        # Partial sums at 9 to 16 rows: the tcgen05 kernel's eight slices beat the streaming kernel's four
+        # (measured on B200 at 16 rows, us: 2,048 x 2,048 5.0 -> 4.0, 2,048 x 8,192 10.4 -> 8.9, 2,048 x 10,752
+        # 13.1 -> 10.1, 1,024 x 4,608 6.1 -> 5.3; at 8 rows the streaming kernel is level or ahead)
+        if (partial_ok and out_dtype is None and kind == "skinny" and 8 < x.shape[0] <= self.SKINNY_BEST_ROWS
+                and self._tma_operands(x, w) and self._few_rows_slices(w.shape[0], w.shape[1]) > 1):
+            kind = "few_rows"
         if partial_ok and out_dtype is None and kind == "skinny" and x.shape[0] <= self.SKINNY_BEST_ROWS:
             slices = self._skinny_slices(w.shape[0], w.shape[1])
             if slices > 1:
@@ -206,8 +212,7 @@ class Runtime:
         bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
         streams = (bf16 and rows <= self.SKINNY_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
                    and x.data_ptr() % 16 == 0)
-        tma = (bf16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
-               and x.data_ptr() % 16 == 0 and w.stride(0) % 8 == 0)
+        tma = self._tma_operands(x, w)
         if streams and (rows <= self.SKINNY_BEST_ROWS or not tma):
             return "skinny"
         # short inner dimensions (hidden 1,024): the tensor-memory kernel's set-up and exchange cost more
@@ -219,6 +224,12 @@ class Runtime:
         if tma:
             return "few_rows" if rows <= self.FEW_ROWS else "tiled"
         return "simt"
+
+    @staticmethod
+    def _tma_operands(x, w):
+        """True if TMA can fetch both operands of x @ w^T (bfloat16, 16-byte aligned bases and row pitches)."""
+        return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+                and x.stride(1) == 1 and x.data_ptr() % 16 == 0 and w.stride(0) % 8 == 0)
 
     def streams_weights(self, x, w):
         """True if x @ w^T goes to the weight-streaming kernel with at most 16 rows (a part may then use
