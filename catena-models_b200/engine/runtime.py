@@ -117,10 +117,10 @@ class Runtime:
                 kernels.gemm_tc_few_rows_parts(parts, x, w, err=self.error_flag)
                 return kernels.PartialSums(parts, x.dtype)
         if partial_ok and out_dtype is None and kind == "tiled":
-            slices = self._tiled_slices(x.shape[0], w.shape[0], w.shape[1])
+            slices, width = self._tiled_slices(x.shape[0], w.shape[0], w.shape[1])
             if slices > 1:
                 parts = torch.empty((slices, x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
-                kernels.gemm_tc_parts(parts, x, w, err=self.error_flag, block_n=256)
+                kernels.gemm_tc_parts(parts, x, w, err=self.error_flag, block_n=width)
                 return kernels.PartialSums(parts, x.dtype)
         y = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
         if kind == "skinny":
@@ -158,22 +158,37 @@ class Runtime:
         return 1
 
     def _tiled_slices(self, rows, out_columns, inner):
-        """Runs of K for the tiled product when its consumer adds them: a few hundred rows times a narrow
-        output are a few dozen 128 x 256 tiles for 148 SMs, and the kernel takes (run, tile) items, so as
-        many runs as keep the items within one round of the SMs, each of eight 64-wide steps at least.
-        Measured on B200 (us, unsplit -> split, cuBLAS beside it): 1,024 x 2,048 x 8,192 44.0 -> 30.2 (25.4),
-        512 rows 41.5 -> 19.2 (18.5), 256 rows 40.0 -> 14.4 (14.4), 256 x 2,048 x 2,048 12.8 -> 8.8 (5.5);
-        the residual kernel then reads float runs (1,024 rows: 5.1 -> 9.6 us, 512 rows: 3.6 -> 5.6), which
-        two runs of a short inner dimension do not repay (1,024 x 2,048 x 2,048: 13.7 -> 11.7)."""
+        """(runs of K, tile width) for the tiled product when its consumer adds the runs.  A few hundred rows
+        times a narrow output are a few dozen tiles for 148 SMs, and the kernel takes (run, tile) items: the
+        pair with the least estimated time, which is rounds of items over the SMs x k-steps of an item x the
+        measured cost of a k-step at that width (TILE_STEP_US), plus, for more than one run, what the float
+        runs cost on their way through the residual kernel (about 1 us per run and 1.5 us once, per million
+        outputs).  Measured on B200 (us, with the residual kernel, best pair first): 256 x 2,048 x 2,048
+        (4, 128) 11.1, (8, 256) 12.3, unsplit 12.8+; 256 x 2,048 x 8,192 (8, 256) 18.6, (4, 128) 19.2;
+        1,024 x 2,048 x 8,192 (2, 256) 40.1, (4, 256) 44.0, unsplit 49.9; 1,024 x 2,048 x 2,048 unsplit 19.6,
+        (2, 256) 21.7; whole steps at 1.7B-class sizes: 256 tokens 2.57 -> 2.00 ms, 512 tokens 3.08 -> 2.64."""
         if self._sm_count is None:
             self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
-        if out_columns % 4:
-            return 1
-        tiles = -(-rows // 128) * -(-out_columns // 256)
-        slices = min(8, self._sm_count // tiles, -(-inner // 64) // 8)
-        if slices < 2 or (slices < 4 and inner < 4096):
-            return 1
-        return slices
+        steps = -(-inner // 64)
+        row_tiles = -(-rows // 128)
+        outputs = rows * out_columns / 1e6
+
+        def estimate(width, runs):
+            items = row_tiles * -(-out_columns // width) * runs
+            time = -(-items // self._sm_count) * -(-steps // runs) * self.TILE_STEP_US[width]
+            return time + (outputs * (runs + 1.5) if runs > 1 else 0.0)
+
+        best = (min(estimate(w, 1) for w in (128, 192, 256)), 1, 256)
+        if out_columns % 4 == 0:
+            for width in (256, 128):
+                for runs in range(2, 9):
+                    per = -(-steps // runs)
+                    if per < 2 or per * (runs - 1) >= steps:
+                        continue
+                    t = estimate(width, runs)
+                    if t < 0.95 * best[0]:                  # a split has to pay clearly
+                        best = (t, runs, width)
+        return best[1], best[2]
 
     # time of one 64-wide step of K on one tile, us, measured on B200 over 72 shapes (256 to 4,096 rows):
     # a product takes about 4.5 us + rounds of tiles over the SMs x steps x this, whatever the width

@@ -103,7 +103,8 @@ class GQAttention(Mixer):
                                state.ring, QH, KVH, HD, self.qk_norm_eps or 0.0, interleaved=interleaved)
             gate = proj[:, QS + 2 * KVS:] if self.output_gate else None
         q = proj[:, :QS]
-        ctx = torch.empty((batch.T, QS), dtype=x.dtype, device=x.device)
+        # the attention kernels write the rows of sequences only; rows of padding must still be finite
+        ctx = (torch.zeros if batch.padded else torch.empty)((batch.T, QS), dtype=x.dtype, device=x.device)
         if batch.prefill or batch.append:
             if self.shares_kv and batch.append and state.ring:
                 raise NotImplementedError("an append step of a layer that shares the keys and values of a sliding "

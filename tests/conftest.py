@@ -22,3 +22,22 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture
+def nan_filled_allocations(monkeypatch):
+    """Every floating-point CUDA tensor that the code under test allocates without a value
+    (torch.empty, torch.empty_like) starts as NaN, also inside recorded steps, where the fill is
+    recorded with them: a row that nothing writes, but that something reads as an operand, then
+    shows in the logits whatever the allocator happened to hand out."""
+    import torch
+
+    empty, empty_like = torch.empty, torch.empty_like
+
+    def poison(t):
+        if t.is_cuda and t.is_floating_point() and t.numel():
+            t.fill_(float("nan"))
+        return t
+
+    monkeypatch.setattr(torch, "empty", lambda *a, **k: poison(empty(*a, **k)))
+    monkeypatch.setattr(torch, "empty_like", lambda *a, **k: poison(empty_like(*a, **k)))
