@@ -24,12 +24,15 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
-@pytest.fixture
-def nan_filled_allocations(monkeypatch):
-    """Every floating-point CUDA tensor that the code under test allocates without a value
+@pytest.fixture(autouse=True)
+def nan_filled_allocations(request, monkeypatch):
+    """In every GPU test, every floating-point CUDA tensor that is allocated without a value
     (torch.empty, torch.empty_like) starts as NaN, also inside recorded steps, where the fill is
     recorded with them: a row that nothing writes, but that something reads as an operand, then
     shows in the logits whatever the allocator happened to hand out."""
+    if "gpu" not in request.keywords:
+        yield
+        return
     import torch
 
     empty, empty_like = torch.empty, torch.empty_like
@@ -41,3 +44,4 @@ def nan_filled_allocations(monkeypatch):
 
     monkeypatch.setattr(torch, "empty", lambda *a, **k: poison(empty(*a, **k)))
     monkeypatch.setattr(torch, "empty_like", lambda *a, **k: poison(empty_like(*a, **k)))
+    yield

@@ -359,7 +359,7 @@ def test_recorded_prompt_shapes_are_bounded_and_evicted_ones_run_again(folders, 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "L"])
-def test_one_recording_serves_a_class_of_prompt_shapes(folders, plain, name, dtype, nan_filled_allocations):
+def test_one_recording_serves_a_class_of_prompt_shapes(folders, plain, name, dtype):
     """Prompt steps are recorded per class (sequences, tokens and longest prompt rounded up to 64, wanted
     places): the step runs the class's rows, the surplus as padding that belongs to no sequence.  Prompts
     of many lengths in one class, alone and in pairs of unequal lengths, each followed by a decode step,
@@ -391,7 +391,7 @@ def test_one_recording_serves_a_class_of_prompt_shapes(folders, plain, name, dty
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "L"])
-def test_one_recording_serves_a_class_of_append_steps(folders, plain, name, dtype, nan_filled_allocations):
+def test_one_recording_serves_a_class_of_append_steps(folders, plain, name, dtype):
     """Tokens on top of held ones are recorded per class as well (the class also names the class of
     lengths that the longest sequence reaches).  Requests with heads of many lengths bring second
     pieces of 33 to 64 tokens, alone and in pairs of unequal lengths, then one more token each: the

@@ -245,7 +245,7 @@ def test_sixty_four_unequal_prompts_then_decode_at_other_widths(tmp_path, name):
 
 
 @pytest.mark.parametrize("name", list(WIDTHS))
-def test_a_long_prompt_in_chunks_at_other_widths(tmp_path, name, nan_filled_allocations):
+def test_a_long_prompt_in_chunks_at_other_widths(tmp_path, name):
     """A prompt of 1,300 tokens whole (tcgen05 attention and the tiled product) and in chunks of 700
     and 600 (the append path over the cache: tcgen05 attention that copies pages, from a position inside a
     page), three times so that the second piece also runs from its recording, bfloat16, against the plain
@@ -278,7 +278,7 @@ def test_a_long_prompt_in_chunks_at_other_widths(tmp_path, name, nan_filled_allo
         assert rms(got, ref) < 0.3
 
 
-def test_several_tokens_on_top_in_a_mixed_schedule_at_full_width(big, nan_filled_allocations):
+def test_several_tokens_on_top_in_a_mixed_schedule_at_full_width(big):
     """Three requests of 580 to 700 tokens at the 1.7B-class widths (heads of 64: the tcgen05 attention
     over the paged cache, from positions inside pages, on page borders and beside a request that starts
     in the same step; the tiled product cut over K for the pieces of a few hundred rows): pieces of 16
