@@ -508,45 +508,6 @@ extern "C" int cm_kv_store(int dt, const void* kv, long long ld, const int* tok_
     return CM_OK;
 }
 
-// Zeroes the entries that a sequence has not written yet in the page that holds its position
-// seq_pos0[b] - 1 (entries seq_pos0 % PAGE_TOKENS .. of that page), keys and values of every kv head.
-// A kernel that copies whole pages into an operand of a matrix product (cm_attn_append_tc) multiplies
-// these entries by probabilities that are exactly zero, which needs them finite.  Nothing to do for a
-// sequence that stands on a page border, and nothing for a ring that has gone round (seq_pos0 >=
-// ring): those entries hold earlier positions that the window may still need.
-template <typename T>
-__global__ void kv_clear_tail_kernel(const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot,
-                                     T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
-                                     int ptab_stride, int ring, int KVH, int HD) {
-    pdl_trigger();
-    pdl_wait();
-    const int b = blockIdx.x, plane = blockIdx.y / KVH, kvh = blockIdx.y - plane * KVH;
-    const int p0 = seq_pos0[b];
-    const int first = p0 % PAGE_TOKENS;
-    if (p0 <= 0 || first == 0 || (ring && p0 >= ring)) return;
-    const int page = ptab[(long long)seq_slot[b] * ptab_stride + p0 / PAGE_TOKENS];      // p0 < ring: entry = position
-    T* tile = kv_tile(pool, plane, pages, page, kvh, KVH, HD) + (long long)first * HD;
-    const int count = (PAGE_TOKENS - first) * HD;
-    for (int e = threadIdx.x; e < count; e += blockDim.x) tile[e] = from_f32<T>(0.f);
-}
-
-extern "C" int cm_kv_clear_tail(int dt, const int* seq_pos0, const int* seq_slot, void* pool, long long pages,
-                                const int* ptab, long long ptab_stride, int ring, int B, int KVH, int HD,
-                                cudaStream_t st) {
-    if (B <= 0) return CM_OK;
-    if (ring % PAGE_TOKENS) CM_REFUSE("kv_clear_tail: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
-    if (dt == DT_F32)
-        cm_launch(kv_clear_tail_kernel<float>, dim3(B, 2 * KVH), 128, 0, st, seq_pos0, seq_slot, (float*)pool, pages, ptab,
-                  (int)ptab_stride, ring, KVH, HD);
-    else if (dt == DT_BF16)
-        cm_launch(kv_clear_tail_kernel<bf16>, dim3(B, 2 * KVH), 128, 0, st, seq_pos0, seq_slot, (bf16*)pool, pages, ptab,
-                  (int)ptab_stride, ring, KVH, HD);
-    else
-        return CM_ERR_DTYPE;
-    CM_CHECK_LAUNCH();
-    return CM_OK;
-}
-
 // =========================================================================================
 // Decode attention over the paged cache.  One new query token per sequence.
 // Grid (chunk, kv head, sequence); a chunk is AD_CHUNK cache entries (4 pages), one page per

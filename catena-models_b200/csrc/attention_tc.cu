@@ -5,9 +5,11 @@
 // and values below that position are read from the paged cache, page by page (a 128-key tile is two
 // pages of 64 entries, each one TMA box of the cache's [k|v, page, kv head, entry, head] layout),
 // before the step's own tiles.  A tile's second page that lies wholly at or above seq_pos0 is not
-// the sequence's: the first page is copied in its place, so that what the masked scores multiply is
-// the sequence's own data; the unwritten entries of the page that holds position seq_pos0 - 1 are
-// cleared by the caller (cm_kv_clear_tail), since 0 x NaN would not be 0.
+// the sequence's and may not be allocated: the first page is copied in its place.
+// Rows of a key/value tile that are not the sequence's (beyond its end: the next sequence's rows of
+// the step, padding, unwritten entries of a page) get scores of -inf by selection, so whatever the
+// keys hold does not matter, and their rows of the value tile are cleared in shared memory before the
+// product over them is issued, because a probability of exactly zero times NaN would not be zero.
 //
 // One block per (128-query tile, query head, sequence), long tiles first.  Twelve warps (the first
 // group of four gives most of its registers to the other two, setmaxnreg 40 / 232):
@@ -362,6 +364,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int h = 0; h < CW / 32; ++h) exp_and_stage(v + 32 * h, c * (CW / 32) + h, m_use, rs4);
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            if (k0 + FT_TILE > limit) {
+                // The tile holds rows that are not this sequence's entries (the next sequence's rows of the step,
+                // padding, unwritten entries of a page).  Their probabilities are exactly zero, but zero times a
+                // value that is not finite is not zero: thread r clears row r of the value tile before the
+                // product over it may be issued (that waits for p_full below).
+                const int s = j % STAGES;
+                ok = mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_SOFTMAX);
+                if (!ok) break;
+                if (k0 + r >= limit) {
+#pragma unroll
+                    for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            st_shared16(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES + r * 128 + c * 16, 0u, 0u, 0u, 0u);
+                }
+            }
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -498,9 +516,8 @@ extern "C" int cm_attn_prefill_tc(void* ctx, long long ldc, const void* q, const
 
 // The same for sequences that stand at seq_pos0[b] >= 0: entries below that position come from the
 // paged bfloat16 cache `pool` [2, pages, KVH, PAGE_TOKENS, HD] through the page table (a ring of
-// `ring` entries when ring > 0), the rest from the step's own rows.  The caller clears the unwritten
-// entries of every sequence's last page first (cm_kv_clear_tail) and writes the step's keys and
-// values to the cache afterwards.  max_len: the most rows a sequence brings to this step.
+// `ring` entries when ring > 0), the rest from the step's own rows.  The caller writes the step's keys
+// and values to the cache afterwards.  max_len: the most rows a sequence brings to this step.
 extern "C" int cm_attn_append_tc(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
                                  const void* gate, long long ldg, const int* seq_start, const int* seq_pos0,
                                  const int* seq_slot, const void* pool, long long pages, const int* ptab,

@@ -63,11 +63,6 @@ class StepBatch:
         self.B, self.T = layout.B, layout.T
         # longest run of new tokens; a step recorded for a class of shapes is launched for the class's bound
         self.max_len = max_len if max_len is not None else (max(lengths) if lengths else 0)
-        # True for a step that runs a class's rows (a recorded prompt step, or the run it is recorded from): rows
-        # beyond the real ones are padding, now or in a later replay.  What a part computes for such rows is
-        # never used, but it must be finite: kernels that copy whole tiles into a matrix operand multiply those
-        # rows by weights that are exactly zero, and 0 x NaN is NaN.
-        self.padded = max_len is not None
         # how far the longest sequence reaches with this step; recorded steps: the bound of its class of lengths
         self.max_end = max_end if max_end is not None else max((p + n for p, n in zip(positions, lengths)), default=0)
         self.n_want, self.n_updates = n_want, n_updates

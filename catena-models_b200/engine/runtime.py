@@ -291,30 +291,25 @@ class Runtime:
         fn = kernels.attn_prefill_mma if (bf16 and aligned and HD % 16 == 0 and HD <= 128) else kernels.attn_prefill_simt
         fn(ctx, q, k, v, gate, batch.seq_start, batch.B, batch.max_len, QH, KVH, HD, window, scale)
 
-    # Measured on B200, 32 heads of 64 over 8 kv heads, mma.sync against tcgen05 (with its clearing kernel):
+    # Measured on B200, 32 heads of 64 over 8 kv heads, mma.sync against tcgen05:
     # 128 rows on 512 held tokens 20.9 / 15.1 us, 16 rows x 8 sequences on 4,096 146 / 95 us, 1,024 rows on 8,192
     # 427 / 182 us (with a window of 512: 38 / 33 us); 64 rows x 16 sequences on 2,048 108 / 113 us.
     TCGEN05_APPEND_MIN_ROWS = 16
     TCGEN05_APPEND_MIN_SPAN = 512
 
-    def attention_append(self, ctx, q, k, v, gate, batch, state, QH, KVH, HD, window, scale, tail_unwritten=True):
+    def attention_append(self, ctx, q, k, v, gate, batch, state, QH, KVH, HD, window, scale):
         """Attention of a step whose sequences already hold tokens: keys and values below each
         sequence's first position of the step come from the paged cache, the rest from the step's own
         rows (written to the cache by the caller afterwards).  The choice of kernel follows
         `attention_prefill`, with the span counted from the longest sequence's end and the tcgen05 kernel
         from shorter spans on (its blocks walk the past as well, so they are long enough to pipeline
-        sooner); it copies whole pages, so the unwritten entries of every sequence's last page are
-        cleared first, unless the caller says that the step's keys and values are in the cache already
-        (`tail_unwritten=False`: a layer that reads the state another layer has just written)."""
+        sooner)."""
         aligned = (q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
                    and v.data_ptr() % 16 == 0 and state.pool.data_ptr() % 16 == 0)
         bf16 = q.dtype == torch.bfloat16 and state.pool.dtype == torch.bfloat16 and self.tensor_core_prompts
         span = min(batch.max_end, window) if window else batch.max_end
         if (bf16 and aligned and HD in (64, 128) and span >= self.TCGEN05_APPEND_MIN_SPAN
                 and batch.max_len >= self.TCGEN05_APPEND_MIN_ROWS and ctx.stride(0) % 8 == 0 and ctx.data_ptr() % 16 == 0):
-            if tail_unwritten:
-                kernels.kv_clear_tail(batch.seq_pos0, batch.seq_slot, state.pool, state.pages, state.ptab, state.ring,
-                                      batch.B, KVH, HD)
             kernels.attn_append_tc(ctx, q, k, v, gate, batch.seq_start, batch.seq_pos0, batch.seq_slot, state.pool,
                                    state.pages, state.ptab, state.ring, batch.B, batch.max_len, QH, KVH, HD, window,
                                    scale, err=self.error_flag)

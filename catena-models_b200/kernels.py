@@ -47,7 +47,6 @@ _SIGNATURES = {
                            _i, _i, _f, _vp],
     "cm_attn_append_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _ll, _i,
                           _i, _i, _i, _f, _vp, _vp],
-    "cm_kv_clear_tail": [_i, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp],
     "cm_gemm_tc_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _i, _vp, _vp],
     "cm_kv_store": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp],
     "cm_sample": [_vp, _vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp],
@@ -569,8 +568,7 @@ def attn_append(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, 
 def attn_append_tc(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, ptab, ring, B, max_len, QH, KVH, HD,
                    window, scale, err=None):
     """`attn_append` on the tcgen05 tensor cores: bfloat16, head size 64 or 128, the cache read page by
-    page with TMA.  The entries that a sequence has not written yet in its last page must be finite
-    (`kv_clear_tail`).  err: device int32 that a block raises if a bounded pipeline wait runs out."""
+    page with TMA.  err: device int32 that a block raises if a bounded pipeline wait runs out."""
     if (not (q.stride(0) == k.stride(0) == v.stride(0)) or q.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16
             or q.shape[0] != k.shape[0]):
         raise KernelError("attn_append_tc: bfloat16 q, k, v and cache; q, k and v share rows and a row stride")
@@ -581,14 +579,6 @@ def attn_append_tc(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, page
                                    _ptr(seq_slot), _ptr(pool), pages, _ptr(ptab), ptab.stride(0), ring, B, max_len,
                                    q.shape[0], QH, KVH, HD, window, scale, _ptr(err), _stream()), "attn_append_tc",
            cost=lambda: (f"{B} sequences of up to {max_len} rows, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
-
-
-def kv_clear_tail(seq_pos0, seq_slot, pool, pages, ptab, ring, B, KVH, HD):
-    """Zeroes, in the page that holds position seq_pos0[b] - 1 of every sequence, the entries from
-    seq_pos0[b] on (keys and values), unless the sequence stands on a page border or its ring has gone
-    round: for kernels that copy whole pages."""
-    _check(lib().cm_kv_clear_tail(dtype_code(pool.dtype), _ptr(seq_pos0), _ptr(seq_slot), _ptr(pool), pages, _ptr(ptab),
-                                  ptab.stride(0), ring, B, KVH, HD, _stream()), "kv_clear_tail")
 
 
 def kv_store(kv, tok_pos, tok_seq, seq_slot, seq_end, pool, pages, ptab, ring, KVH, HD):

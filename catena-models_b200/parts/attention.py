@@ -103,8 +103,7 @@ class GQAttention(Mixer):
                                state.ring, QH, KVH, HD, self.qk_norm_eps or 0.0, interleaved=interleaved)
             gate = proj[:, QS + 2 * KVS:] if self.output_gate else None
         q = proj[:, :QS]
-        # the attention kernels write the rows of sequences only; rows of padding must still be finite
-        ctx = (torch.zeros if batch.padded else torch.empty)((batch.T, QS), dtype=x.dtype, device=x.device)
+        ctx = torch.empty((batch.T, QS), dtype=x.dtype, device=x.device)
         if batch.prefill or batch.append:
             if self.shares_kv and batch.append and state.ring:
                 raise NotImplementedError("an append step of a layer that shares the keys and values of a sliding "
@@ -122,8 +121,7 @@ class GQAttention(Mixer):
                 k, v = proj[:, QS:QS + KVS], proj[:, QS + KVS:QS + 2 * KVS]
                 batch.shared[("kv", state.unit)] = (k, v)
             if batch.append:
-                rt.attention_append(ctx, q, k, v, gate, batch, state, QH, KVH, HD, self.window, self.scale,
-                                    tail_unwritten=not self.shares_kv)
+                rt.attention_append(ctx, q, k, v, gate, batch, state, QH, KVH, HD, self.window, self.scale)
                 if not self.shares_kv:
                     kernels.kv_store(proj[:, QS:QS + 2 * KVS], batch.tok_pos, batch.tok_seq, batch.seq_slot,
                                      batch.seq_end, state.pool, state.pages, state.ptab, state.ring, KVH, HD)

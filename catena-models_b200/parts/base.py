@@ -69,7 +69,7 @@ class Part:
     # class of shape (number of sequences, rows, longest prompt as StepBatch.max_len, wanted places), that
     # takes everything about the real lengths from the step's device metadata, and that leaves rows of
     # padding alone (StepBatch.tok_seq is -1 there: they belong to no sequence and must touch no state; what
-    # the part returns for them is never used but must be finite, see StepBatch.padded):
+    # the part returns for them is never used):
     # the engine may then record a prompt step of a class into a graph and replay it for every prompt
     # of the class.  With supports_append this holds for steps of kind "append" too, whose class also
     # names the class of lengths that the longest sequence reaches (StepBatch.max_end is then that
