@@ -780,6 +780,39 @@ def test_attn_prefill_tc_varlen(K, QH, KVH, HD, window, gated):
         close(ctx[sl].view(n, QH, HD), ref, torch.bfloat16)
 
 
+@pytest.mark.parametrize("impl", ["tc", "mma", "simt"])
+@pytest.mark.parametrize("HD", [64, 128])
+def test_attn_prefill_is_not_spoilt_by_a_batch_mate(K, HD, impl):
+    """The tcgen05 kernel copies whole 128-row tiles of keys and values, so the last tile of a sequence
+    holds rows of the sequence packed behind it (the other kernels read no row that no query sees).  That
+    one's keys and values are NaN and infinite here; the sequences before it must come out as if it
+    were not there (its own rows may be anything)."""
+    QH, KVH = 4, 2
+    lens = [70, 200, 129, 60]
+    T = sum(lens)
+    buf = rnd(T, QH * HD + 2 * KVH * HD, dtype=torch.bfloat16, seed=HD)
+    q, k = buf[:, :QH * HD], buf[:, QH * HD:QH * HD + KVH * HD]
+    v = buf[:, QH * HD + KVH * HD:]
+    bounds = [0, 70, 270, 399, 459]
+    bad = slice(bounds[2], bounds[3])                  # the third sequence is broken
+    k[bad] = float("inf")
+    v[bad] = float("nan")
+    starts = torch.tensor(bounds, dtype=torch.int32, device=DEV)
+    ctx = torch.full((T, QH * HD), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    if impl == "tc":
+        K.attn_prefill_tc(ctx, q, k, v, None, starts, len(lens), max(lens), QH, KVH, HD, 0, HD ** -0.5, err=err)
+    else:
+        fn = K.attn_prefill_mma if impl == "mma" else K.attn_prefill_simt
+        fn(ctx, q, k, v, None, starts, len(lens), max(lens), QH, KVH, HD, 0, HD ** -0.5)
+    assert int(err) == 0
+    for b in (0, 1, 3):
+        n, sl = lens[b], slice(bounds[b], bounds[b + 1])
+        ref = _ref_attention(q[sl].cpu().view(n, QH, HD), k[sl].cpu().view(n, KVH, HD), v[sl].cpu().view(n, KVH, HD),
+                             0, HD ** -0.5, None)
+        close(ctx[sl].view(n, QH, HD), ref, torch.bfloat16)
+
+
 @pytest.mark.parametrize("window", [0, 100])
 def test_attn_prefill_tc_far_key_and_window_edge(K, window):
     """One key is made to dominate and must be seen by exactly the queries whose window holds it."""
