@@ -32,6 +32,7 @@ class Runtime:
         self.tensor_core_prompts = True
         self._in_prompt = False
         self._scratch = {}
+        self._choices = {}                  # kernel choices by shape, so that a step from Python does not redo them
         self._retired = []
         self._sm_count = None
         # Two flags that kernels raise on the device (0 otherwise), side by side so that one copy
@@ -167,6 +168,9 @@ class Runtime:
         (4, 128) 11.1, (8, 256) 12.3, unsplit 12.8+; 256 x 2,048 x 8,192 (8, 256) 18.6, (4, 128) 19.2;
         1,024 x 2,048 x 8,192 (2, 256) 40.1, (4, 256) 44.0, unsplit 49.9; 1,024 x 2,048 x 2,048 unsplit 19.6,
         (2, 256) 21.7; whole steps at 1.7B-class sizes: 256 tokens 2.57 -> 2.00 ms, 512 tokens 3.08 -> 2.64."""
+        known = self._choices.get(("slices", rows, out_columns, inner))
+        if known is not None:
+            return known
         if self._sm_count is None:
             self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         steps = -(-inner // 64)
@@ -188,6 +192,7 @@ class Runtime:
                     t = estimate(width, runs)
                     if t < 0.95 * best[0]:                  # a split has to pay clearly
                         best = (t, runs, width)
+        self._choices[("slices", rows, out_columns, inner)] = best[1:]
         return best[1], best[2]
 
     # time of one 64-wide step of K on one tile, us, measured on B200 over 72 shapes (256 to 4,096 rows):
@@ -200,11 +205,16 @@ class Runtime:
         way from L2, not by the tensor core, so it is not half the price of a 128 x 256 one).  Measured:
         1,024 x 6,144 x 2,048 34.6 / 26.0 / 27.2 us at 128 / 192 / 256, 512 x 6,144 x 2,048 23.8 / 15.4 /
         16.3, 2,048 x 2,048 x 8,192 81.6 / 83.0 / 50.6, 256 x 6,144 x 2,048 14.0 / 14.9 / 15.6."""
+        known = self._choices.get(("width", rows, out_columns, widths))
+        if known is not None:
+            return known
         if self._sm_count is None:
             self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         row_tiles = -(-rows // 128)
         cost = {w: -(-(row_tiles * -(-out_columns // w)) // self._sm_count) * self.TILE_STEP_US[w] for w in widths}
-        return min(widths, key=lambda w: (cost[w], -w))
+        best = min(widths, key=lambda w: (cost[w], -w))
+        self._choices[("width", rows, out_columns, widths)] = best
+        return best
 
     SKINNY_ROWS = 64          # most rows the weight-streaming kernel takes
     SKINNY_BEST_ROWS = 16     # up to here it is the fastest kernel
