@@ -219,6 +219,7 @@ class Runtime:
     SKINNY_ROWS = 64          # most rows the weight-streaming kernel takes
     SKINNY_BEST_ROWS = 16     # up to here it is the fastest kernel
     SKINNY_SHORT_K_ROWS = 32  # ... and up to here when the inner dimension is at most SKINNY_SHORT_K
+    SKINNY_SWIGLU_MAX_WEIGHTS = 36 * 1024 * 1024   # packed gate/up elements beyond which 9 to 16 rows leave it
     SKINNY_SHORT_K = 1024
     FEW_ROWS = 128            # most rows of the tensor-core kernel that splits K over a cluster
 
@@ -265,6 +266,13 @@ class Runtime:
         """a = silu(x Wgate^T) * (x Wup^T) for the row-packed [Wgate; Wup]."""
         a = torch.empty((x.shape[0], F), dtype=x.dtype, device=x.device)
         kind = self._product_kernel(x, w_gate_up)
+        # The streaming kernel re-reads the activations once per 16 weight rows, which shows from 9 rows on when
+        # the matrix is large (measured on B200 at 16 rows, us, streaming / tcgen05 few-rows: 21,504 x 2,048
+        # weights 25.5 / 21.3, 16,384 x 2,048 15.5 / 15.6, 9,216 x 1,024 7.6 / 8.7; at 8 rows the streaming
+        # kernel leads everywhere).
+        if (kind == "skinny" and x.shape[0] > 8 and w_gate_up.numel() > self.SKINNY_SWIGLU_MAX_WEIGHTS
+                and self._tma_operands(x, w_gate_up)):
+            kind = "few_rows"
         if kind == "skinny":
             kernels.gemm_skinny(a, x, w_gate_up, swiglu=True)
             return a
