@@ -193,7 +193,7 @@ def test_command_line(folders, tmp_path):
     assert "pp40x2" in bench.stdout and "tg6/ctx9x2" in bench.stdout
 
 
-def test_command_line_options_of_the_reference_and_of_the_survey(folders, tmp_path):
+def test_command_line_options_of_the_reference_and_this_library(folders, tmp_path):
     """--prompt-lens (synthetic prompts), --max-slots, --kernels, --no-wmma-prefill (CUDA-core prompt
     steps under the bfloat16 engine: the same tokens as with tensor cores on a model this small, and
     the plain model's in 32-bit), --pp-chunk in the bench."""
