@@ -38,8 +38,8 @@ PROMPT_GRAPHS_KEPT = 8
 PROMPT_PAD = 64                    # recorded prompt steps run a multiple of this many rows, the rest as padding
 # Recorded decode steps (batch size, length class) kept; the least recently used goes.  A batch whose
 # sequences end one by one walks through every batch size below its first, and a step of a new size costs 6
-# to 8 ms (1.7B-class: kernel by kernel, then the capture) where a replay costs 1.1 to 1.8 ms; a recording
-# holds about 22 MiB of its own (the allocator's block for its activations), so 96 of them are 2 GiB at most.
+# to 8 ms (1.7B-class: kernel by kernel, then the capture) where a replay costs 1.1 to 1.8 ms; the recordings
+# share one memory pool, in which a recording keeps about 10 MiB of its own, so 96 of them are 1 GiB at most.
 DECODE_GRAPHS_KEPT = 96
 
 
@@ -114,6 +114,11 @@ class Engine:
         self._staging = _Staging()
         self._graphs = {}
         self._prompt_graphs = {}                               # shape of a prompt step -> its recorded graph
+        # One memory pool for every recording of this engine: a recording's scratch (what it allocates and
+        # frees while it is captured) is handed on to the next capture instead of being taken from the
+        # device anew, which is most of what a capture costs; what a recording still holds (its logits)
+        # stays its own.  Recordings of one engine replay one after another on one stream.
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         self._prompt_seen = {}
         self._sampled_host = None
         # the tokens the last sampling step chose, by position in that step's batch: the next step may
@@ -385,7 +390,7 @@ class Engine:
             entry = _RecordedStep(layout, dev, torch.cuda.CUDAGraph(), None, batch)
             entry.sampled = sampled
             before = _kernels.launches
-            with torch.cuda.graph(entry.graph):
+            with torch.cuda.graph(entry.graph, pool=self._graph_pool):
                 entry.logits = run()
             entry.launches = _kernels.launches - before
             _kernels.launches = before
@@ -447,7 +452,7 @@ class Engine:
             logits = run()
             graph = torch.cuda.CUDAGraph()
             before = _kernels.launches
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, pool=self._graph_pool):
                 entry.logits = run()
             entry.launches = _kernels.launches - before       # kernels one replay runs
             _kernels.launches = before                         # the capture itself ran nothing
