@@ -318,3 +318,63 @@ def test_several_tokens_on_top_in_a_mixed_schedule_at_full_width(big):
             assert rel(g, ref) < 2.0 * rel(noise[i][places[i]], ref), (rep, i)
             assert torch.equal(g.argmax(-1).cpu(), ref.argmax(-1)) or rel(g, ref) < 0.02
     assert any(len(k) > 5 and k[5] == "append" for k in eng._prompt_graphs)
+
+
+@pytest.mark.parametrize("change", [{}, {"sliding_window": 512},
+                                    {"hidden_size": 1024, "intermediate_size": 4608, "num_attention_heads": 16}])
+def test_how_a_prompt_is_cut_changes_nothing_at_full_width(tmp_path, change):
+    """Seeded random schedules at the widths where the tcgen05 kernels run (1.7B-class; with a window of
+    512, so that rings wrap inside the prompts; 350M-class): one to four requests of 200 to 1,500 tokens
+    brought in single tokens, pieces of 3 to 257 and pieces of 300 to 700, some sitting a step out, each
+    plan twice so that the second run meets recordings.  The logits at every 37th position must agree
+    with those of the same request brought whole and alone by the same bfloat16 engine to within
+    bfloat16's noise (1.1 % of the largest logit was the most seen over 96 such runs; the bound is 3 %),
+    which a wrong row, page or slot exceeds by far; the plain model is the judge elsewhere in this file."""
+    import random
+
+    from catena_models_b200.api import Model
+    from catena_models_b200.weights.random_init import write_random_model
+
+    cfg = dict(BIG, **change)
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=5, std=0.02, norm_weights="random", rope_factors="uniform")
+    eng = Model.load(folder, dtype="bfloat16", max_tokens=8192).engine
+    V = cfg["vocab_size"]
+    for seed in range(5):
+        rng = random.Random(seed)
+        lens = [rng.randint(200, 1500) for _ in range(rng.randint(1, 4))]
+        seqs = [tiny.random_prompt(n, V, seed=seed * 10 + i) for i, n in enumerate(lens)]
+        places = [list(range(0, n, 37)) + [n - 1] for n in lens]
+        whole = []
+        for s, p in zip(seqs, places):
+            (slot,) = eng.admit(1)
+            whole.append(eng.step([slot], [s], [p]).clone())
+            eng.release([slot])
+        for rep in range(2):
+            plan = random.Random(seed)
+            slots = eng.admit(len(seqs))
+            at, got = [0] * len(seqs), [dict() for _ in seqs]
+            while any(a < n for a, n in zip(at, lens)):
+                ids = [i for i in range(len(seqs)) if at[i] < lens[i] and plan.random() < 0.8]
+                if not ids:
+                    continue
+                kind = plan.choice(["one", "piece", "piece", "big"])
+                toks, want = [], []
+                for i in ids:
+                    n = 1 if kind == "one" else plan.choice([3, 16, 64, 100, 130, 257] if kind == "piece" else [300, 512, 700])
+                    n = min(n, lens[i] - at[i])
+                    toks.append(seqs[i][at[i]:at[i] + n])
+                    want.append([w for w in range(n) if at[i] + w in places[i]])
+                out = eng.step([slots[i] for i in ids], toks, want)
+                off = 0
+                for i, t, w in zip(ids, toks, want):
+                    for k, x in enumerate(w):
+                        got[i][at[i] + x] = out[off + k].clone()
+                    off += len(w)
+                    at[i] += len(t)
+            eng.release(slots)
+            eng.check_errors()
+            for i, p in enumerate(places):
+                g = torch.stack([got[i][x] for x in p])
+                assert not bool(g.isnan().any()), (seed, rep, i)
+                assert rel(g, whole[i].cpu()) < 0.03, (seed, rep, i)
+    assert not eng.cache.book.live
