@@ -321,10 +321,11 @@ def test_several_tokens_on_top_in_a_mixed_schedule_at_full_width(big):
 
 
 @pytest.mark.parametrize("change", [{}, {"sliding_window": 512},
-                                    {"hidden_size": 1024, "intermediate_size": 4608, "num_attention_heads": 16}])
+                                    {"hidden_size": 1024, "intermediate_size": 4608, "num_attention_heads": 16},
+                                    {"num_attention_heads": 16, "num_key_value_heads": 4, "head_dim": 128}])
 def test_how_a_prompt_is_cut_changes_nothing_at_full_width(tmp_path, change):
     """Seeded random schedules at the widths where the tcgen05 kernels run (1.7B-class; with a window of
-    512, so that rings wrap inside the prompts; 350M-class): one to four requests of 200 to 1,500 tokens
+    512, so that rings wrap inside the prompts; 350M-class; heads of 128): one to four requests of 200 to 1,500 tokens
     brought in single tokens, pieces of 3 to 257 and pieces of 300 to 700, some sitting a step out, each
     plan twice so that the second run meets recordings.  The logits at every 37th position must agree
     with those of the same request brought whole and alone by the same bfloat16 engine to within
