@@ -34,7 +34,11 @@ from .batch import BatchLayout, StepBatch, clear_sampling, fill_host, fill_host_
 
 
 PROMPT_GRAPH_MAX_TOKENS = 1024     # longer prompt steps are bound by the device, not by their launches
-PROMPT_GRAPHS_KEPT = 8
+# Recorded prompt steps kept.  A class is 64 tokens wide, so prompts of up to 1,024 tokens that come alone make 16
+# classes (times the numbers of wanted places in use); were fewer kept than a workload cycles through, every
+# class would be recorded again and again (about twice a step's cost each time) and never replayed.  The
+# recordings share the engine's memory pool and keep little of their own.
+PROMPT_GRAPHS_KEPT = 48
 PROMPT_PAD = 64                    # recorded prompt steps run a multiple of this many rows, the rest as padding
 # Recorded decode steps (batch size, length class) kept; the least recently used goes.  A batch whose
 # sequences end one by one walks through every batch size below its first, and a step of a new size costs 6

@@ -336,13 +336,17 @@ def test_prompt_steps_of_a_repeated_shape(folders, plain, name, dtype):
     eng.release(held)
 
 
-def test_recorded_prompt_shapes_are_bounded_and_evicted_ones_run_again(folders, plain):
-    """More repeated prompt shapes than the engine keeps graphs for: the oldest recording is dropped,
-    and a dropped shape that comes back runs kernel by kernel again with the same result."""
-    from catena_models_b200.engine.engine import PROMPT_GRAPHS_KEPT
+def test_recorded_prompt_shapes_are_bounded_and_evicted_ones_run_again(folders, plain, monkeypatch):
+    """More repeated prompt shapes than the engine keeps graphs for (eight here): the oldest recording is
+    dropped, and a dropped shape that comes back runs kernel by kernel again with the same result."""
+    from catena_models_b200.engine import engine as engine_module
 
+    PROMPT_GRAPHS_KEPT = 8
+    monkeypatch.setattr(engine_module, "PROMPT_GRAPHS_KEPT", PROMPT_GRAPHS_KEPT)
     name, dtype = "A", "bfloat16"
-    eng = engine_for(folders, name, dtype)
+    from catena_models_b200.api import Model
+
+    eng = Model.load(folders[name], dtype=dtype, max_tokens=2048).engine       # an engine without recordings
     vocab = plain[name][0]["vocab_size"]
     shapes = [(40 + 64 * i,) for i in range(PROMPT_GRAPHS_KEPT + 3)]       # one class of shapes each
     for rnd in range(2):
