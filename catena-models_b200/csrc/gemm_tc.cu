@@ -442,19 +442,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.f;
                 }
-                if (row < M && parts) {
-                    // no exchange: this k-slice's sums go to where the consumer of the product adds the slices
-                    float* dst = parts + (long long)rank * part_stride + (long long)row * ldc + n0 + c * 32;
-                    if ((ldc & 3) == 0 && n0 + c * 32 + 31 < N) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (n0 + c * 32 + i < N) dst[i] = v[i];
-                    }
-                } else if (row < M) {
+                if (row < M) {
                     float4* dst = reinterpret_cast<float4*>(stage + (size_t)row * TCS_PITCH + c * 32);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -469,25 +457,57 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (exchange) cluster.sync(); else __syncthreads();
 
     // ------------------------------------------------------------------ sum over the cluster, epilogue
-    if (!parts) {
+    if (parts) {
+        // no exchange: this k-slice's sums go to where the consumer of the product adds the slices, a row of the
+        // tile per warp and instruction (512 consecutive bytes; stored straight from the registers that hold a
+        // row per thread, 16 bytes of 32 different rows an instruction, the same rows took longer: 64 rows
+        // 4.8 -> 4.4 and 9.8 -> 9.4 us for the 2,048 x 2,048 and 2,048 x 8,192 matrices, 128 rows 6.2 -> 5.3 and
+        // 11.7 -> 10.8)
+        float* base = parts + (long long)rank * part_stride + n0;
+        const bool vec_ok = (ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(parts) | (uintptr_t)(part_stride * 4)) & 15) == 0 &&
+                            (n0 & 3) == 0;
+        for (int row = warp; row < M; row += TC_THREADS / 32) {
+            const float4 v = *reinterpret_cast<const float4*>(stage + (size_t)row * TCS_PITCH + lane * 4);
+            float* dst = base + (long long)row * ldc + lane * 4;
+            if (vec_ok && n0 + lane * 4 + 3 < N) {
+                *reinterpret_cast<float4*>(dst) = v;
+            } else {
+                const float o[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (n0 + lane * 4 + i < N) dst[i] = o[i];
+            }
+        }
+    } else {
         const int col = n0 + (MODE == TC_MODE_SWIGLU ? (lane & 15) * 4 : lane * 4);
         const bool vec_ok = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
-        for (int row = rank + splits * warp; row < M; row += splits * (TC_THREADS / 32)) {
-            // all ranks' pieces are requested before any is added: one round trip through distributed
-            // shared memory instead of one per rank; the sum still runs in rank order
-            float4 part[8];
+        constexpr int ROW_STEP = TC_THREADS / 32;
+        for (int row0 = rank + splits * warp; row0 < M; row0 += 2 * splits * ROW_STEP) {
+          // Two rows' pieces of all ranks are requested before any is added: one round trip through
+          // distributed shared memory for both instead of one per row (measured on B200 at 64 rows: q/k/v
+          // 9.5 -> 8.3 us, in_proj 10.6 -> 10.1; every row of the warp in one trip needs 168 registers and
+          // was slower than the start: 9.9 and 11.4 us); the sums still run in rank order.
+          float4 part[2][8];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                if (r < splits) {
-                    const float* src = exchange ? cluster.map_shared_rank(stage, r) : stage;
-                    part[r] = *reinterpret_cast<const float4*>(src + (size_t)row * TCS_PITCH + lane * 4);
-                }
-            }
+          for (int h = 0; h < 2; ++h) {
+              const int row = row0 + h * splits * ROW_STEP;
+#pragma unroll
+              for (int r = 0; r < 8; ++r) {
+                  if (r < splits && row < M) {
+                      const float* src = exchange ? cluster.map_shared_rank(stage, r) : stage;
+                      part[h][r] = *reinterpret_cast<const float4*>(src + (size_t)row * TCS_PITCH + lane * 4);
+                  }
+              }
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int row = row0 + h * splits * ROW_STEP;
+            if (row >= M) break;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
                 if (r < splits) {
-                    acc.x += part[r].x; acc.y += part[r].y; acc.z += part[r].z; acc.w += part[r].w;
+                    acc.x += part[h][r].x; acc.y += part[h][r].y; acc.z += part[h][r].z; acc.w += part[h][r].w;
                 }
             }
             float o[4] = {acc.x, acc.y, acc.z, acc.w};
@@ -508,6 +528,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 for (int i = 0; i < 4; ++i)
                     if (col + i < N) dst[i] = from_f32<TC>(o[i]);
             }
+          }
         }
     }
     if (exchange) cluster.sync();
