@@ -531,7 +531,13 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           }
         }
     }
-    if (exchange) cluster.sync();
+    // A block's shared memory must outlive its peers' reads of it.  Nothing is handed over here, so the arrival
+    // needs no release (which would wait for this block's stores to the product to be performed): every
+    // thread arrives once its own reads have been added up, and waits for the others'.
+    if (exchange) {
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    }
 
     // ------------------------------------------------------------------ teardown
     tc_fence_before();
@@ -672,7 +678,8 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
     } else {
         // As many blocks as 1.4 per SM (two share an SM; measured on B200 at 64 rows: 16 tiles are
         // fastest split 8 ways, 48 tiles 4 ways, 128 tiles not at all); every block keeps at least
-        // two k-slices, and the device must have room for such a cluster.
+        // four k-slices (with an inner dimension of 1,024, 24 and 17 tiles take 5.6 and 5.3 us split 4 ways,
+        // 6.4 and 6.1 us split 8 ways), and the device must have room for such a cluster.
         static int sm_count = 0;
         if (!sm_count) {
             int dev = 0;
@@ -680,13 +687,13 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
             cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
             if (sm_count <= 0) sm_count = 1;
         }
-        // With the SwiGLU epilogue the exchange moves gate and up sums (twice the data per output) and the
-        // split did not pay in any case measured: 72 tiles of a 9,216 x 1,024 matrix at 64 rows take
-        // 15.0 us split two ways and 9.5 us unsplit in the persistent kernel (128 rows: 22.6 against
-        // 9.7 us); it is only used when the tiles would leave three quarters of the SMs idle.
-        const int budget = MODE == TC_MODE_SWIGLU ? sm_count / 4 : 7 * sm_count / 5;
-        for (int s = 8; s >= 2; --s) {
-            if (2 * s > num_kb || n_tiles * s > budget) continue;
+        // With the SwiGLU epilogue the exchange moves gate and up sums (twice the data per output), which pays
+        // for fewer rows and blocks only (us, split two ways / unsplit in the persistent kernel): 72 tiles of a
+        // 9,216 x 1,024 matrix 8.1 / 9.9 at 32 rows, 9.1 / 10.0 at 64, 12.1 / 10.1 at 128; 128 tiles of a
+        // 16,384 x 2,048 matrix 14.6 / 16.0 at 32 rows, 21.4 / 16.2 at 64.
+        const int budget = MODE != TC_MODE_SWIGLU ? 7 * sm_count / 5 : M <= 32 ? 2 * sm_count : M <= 64 ? sm_count : sm_count / 4;
+        for (int s = MODE == TC_MODE_SWIGLU ? 2 : 8; s >= 2; --s) {       // SwiGLU: two ways at most (four: 10.7 against 7.4 us)
+            if (4 * s > num_kb || n_tiles * s > budget) continue;
             if (splitk_active_clusters<TC, MODE, A_ROWS, STAGES>(s, smem) > 0) {
                 splits = s;
                 break;
@@ -696,7 +703,9 @@ static int launch_splitk_rows(void* C, const void* A, const void* B, int M, int 
         // third slower than this one with a single slice (measured on B200, us: SwiGLU over 16,384 x 2,048
         // weights at 24 rows 19.7 against 16.0, the 65,536 x 2,048 head at 17 to 31 rows 66 to 70 against 47
         // to 49; from 32 rows on the two are level or the persistent kernel is ahead).
-        if (splits == 1 && M >= 32) return 1;
+        // With more tiles than SMs (168 for 148) this kernel's two blocks per SM still lead at 32 to 48 rows
+        // (2.6B-class gate/up: 18.9 and 20.2 us against 21.2 and 22.0 in the persistent kernel's wide tiles).
+        if (splits == 1 && M >= 32 && (n_tiles <= sm_count || M >= 64)) return 1;
     }
     CUtensorMap map_a, map_b;
     int rc = make_map(&map_a, A, M, K, lda, A_ROWS);

@@ -103,7 +103,12 @@ class Runtime:
         # (measured on B200 at 16 rows, us: 2,048 x 2,048 5.0 -> 4.0, 2,048 x 8,192 10.4 -> 8.9, 2,048 x 10,752
         # 13.1 -> 10.1, 1,024 x 4,608 6.1 -> 5.3; at 8 rows the streaming kernel is level or ahead)
         if (partial_ok and out_dtype is None and kind == "skinny" and 8 < x.shape[0] <= self.SKINNY_BEST_ROWS
-                and self._tma_operands(x, w) and self._few_rows_slices(w.shape[0], w.shape[1]) > 1):
+                and w.shape[1] >= 2048 and self._tma_operands(x, w) and self._few_rows_slices(w.shape[0], w.shape[1]) > 1):
+            kind = "few_rows"
+        # ... and so does a finished product of that size (q/k/v at 16 rows: 7.0 -> 6.0 us; in_proj keeps the
+        # streaming kernel, which takes the convolution along)
+        if (not partial_ok and out_dtype is None and kind == "skinny" and 8 < x.shape[0] <= self.SKINNY_BEST_ROWS
+                and w.shape[1] >= 2048 and self._tma_operands(x, w)):
             kind = "few_rows"
         if partial_ok and out_dtype is None and kind == "skinny" and x.shape[0] <= self.SKINNY_BEST_ROWS:
             slices = self._skinny_slices(w.shape[0], w.shape[1])
@@ -218,9 +223,6 @@ class Runtime:
 
     SKINNY_ROWS = 64          # most rows the weight-streaming kernel takes
     SKINNY_BEST_ROWS = 16     # up to here it is the fastest kernel
-    SKINNY_SHORT_K_ROWS = 32  # ... and up to here when the inner dimension is at most SKINNY_SHORT_K
-    SKINNY_SWIGLU_MAX_WEIGHTS = 36 * 1024 * 1024   # packed gate/up elements beyond which 9 to 16 rows leave it
-    SKINNY_SHORT_K = 1024
     FEW_ROWS = 128            # most rows of the tensor-core kernel that splits K over a cluster
 
     def _product_kernel(self, x, w):
@@ -241,12 +243,6 @@ class Runtime:
         tma = self._tma_operands(x, w)
         if streams and (rows <= self.SKINNY_BEST_ROWS or not tma):
             return "skinny"
-        # short inner dimensions (hidden 1,024): the tensor-memory kernel's set-up and exchange cost more
-        # than the streaming kernel's re-reading of the activations up to 32 rows (measured on B200 at 24
-        # and 32 rows, K = 1,024: 3.9 / 4.1 / 5.8 / 8.8 us against 5.1 / 5.1 / 6.4 / 11.3 us for the out,
-        # q/k/v, in and gate/up projections; at K = 2,048 the tensor-memory kernel wins from 24 rows on)
-        if streams and rows <= self.SKINNY_SHORT_K_ROWS and x.shape[1] <= self.SKINNY_SHORT_K:
-            return "skinny"
         if tma:
             return "few_rows" if rows <= self.FEW_ROWS else "tiled"
         return "simt"
@@ -266,12 +262,10 @@ class Runtime:
         """a = silu(x Wgate^T) * (x Wup^T) for the row-packed [Wgate; Wup]."""
         a = torch.empty((x.shape[0], F), dtype=x.dtype, device=x.device)
         kind = self._product_kernel(x, w_gate_up)
-        # The streaming kernel re-reads the activations once per 16 weight rows, which shows from 9 rows on when
-        # the matrix is large (measured on B200 at 16 rows, us, streaming / tcgen05 few-rows: 21,504 x 2,048
-        # weights 25.5 / 21.3, 16,384 x 2,048 15.5 / 15.6, 9,216 x 1,024 7.6 / 8.7; at 8 rows the streaming
-        # kernel leads everywhere).
-        if (kind == "skinny" and x.shape[0] > 8 and w_gate_up.numel() > self.SKINNY_SWIGLU_MAX_WEIGHTS
-                and self._tma_operands(x, w_gate_up)):
+        # From 9 rows on the tcgen05 few-rows kernel leads (measured on B200 at 16 rows, us, streaming /
+        # few-rows: 21,504 x 2,048 weights 25.5 / 20.2, 16,384 x 2,048 15.6 / 14.2, 9,216 x 1,024 7.7 / 7.4; at 8
+        # rows the streaming kernel leads everywhere).
+        if kind == "skinny" and x.shape[0] > 8 and self._tma_operands(x, w_gate_up):
             kind = "few_rows"
         if kind == "skinny":
             kernels.gemm_skinny(a, x, w_gate_up, swiglu=True)
