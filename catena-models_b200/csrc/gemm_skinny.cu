@@ -182,7 +182,12 @@ gemm_skinny_kernel(TY* __restrict__ Y, const bf16* __restrict__ X, const bf16* _
             }
         }
     }
-    if (ksplit > 1) cluster.sync();          // the others' shared memory must outlive the reads
+    // The others' shared memory must outlive the reads.  Nothing is handed over here, so the arrival needs no
+    // release (which would wait for this block's stores to Y): each thread arrives after its own reads.
+    if (ksplit > 1) {
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    }
 }
 
 template <int NT, typename TY, int MODE>
