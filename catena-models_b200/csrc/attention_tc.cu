@@ -15,18 +15,26 @@
 // group of four gives most of its registers to the other two, setmaxnreg 40 / 232):
 //   warp 0   one thread: TMA loads of the Q tile and of 128-key K and V tiles into shared-memory
 //            rings (128-byte rows, 128-byte swizzle; a head of 128 is two 64-column pieces);
-//   warp 1   allocates tensor memory; one thread issues S = Q K^T (128 x 128, K-major operands)
-//            into one of two S buffers, and O' = P V (128 x HD, V as the MN-major B operand:
-//            its rows are keys) into one of two O' buffers, committing to mbarriers;
+//   warp 1   allocates tensor memory;
+//   warps 1-2  one thread each (only warp 1's with a head of 128) issues products and commits them to
+//            mbarriers: S = Q K^T (128 x 128, K-major operands from shared memory) into one of the score
+//            buffers, and O += P V (128 x HD; P from tensor memory, V from shared memory as the MN-major
+//            B operand: its rows are keys) into the O buffer of the tile's softmax group;
 //   warps 4-7 and 8-11  two softmax groups of 128 threads, one query row per thread.  Group g takes
-//            the key tiles g, g+2, ...: reads its S buffer from tensor memory (maximum first,
-//            then exponentials), writes P as bfloat16 into its shared-memory buffer in the A
-//            operand's layout, and adds the finished O' of its previous tile into float
-//            registers, rescaled by the change of its running maximum.  Each group keeps its own
-//            (maximum, sum, O); the two are merged at the end through shared memory, normalised,
-//            gated and stored.
-// So the tensor core forms the scores of the next tile while a group is busy with exponentials, and
-// the instructions per score drop to the softmax itself.
+//            the key tiles g, g+2, ...: reads the row's 128 scores from tensor memory into registers
+//            once, takes their maximum, and writes the exponentials as bfloat16 back over the scores,
+//            where the product reads them.  Each group keeps its own (reference maximum, sum) in
+//            registers and its own O in tensor memory; the two are merged at the end through shared
+//            memory, normalised, gated and stored.
+// O is never read between tiles: the exponentials are taken relative to a reference that follows the
+// row's maximum only when that has grown by more than a factor of 256 since the reference was set; then
+// the group waits for its products so far, scales its O in tensor memory and goes on.  Maxima settle
+// after the first tiles of a row, so this is rare (and it changes no result beyond rounding: the sums
+// are float, and a bfloat16 probability of up to 256 is as exact as one below 1).
+// What bounds a tile's time is the softmax groups (about 128 exponentials per thread and tile on the
+// SM's 16 special-function lanes) and what stands between a group's P and the scores it reads three
+// tiles later; every look at an mbarrier and every commit costs the thread that makes it a hundred cycles
+// and more, so they are kept off that path (asked early, read late; two issuing threads).
 //
 // Maximum, sum, exponent arguments and the rescaling are float; probabilities enter the second
 // product as bfloat16.  Every wait on an mbarrier is bounded; a wait that runs out raises *err, all
@@ -37,15 +45,68 @@
 static_assert(PAGE_TOKENS * 2 == FT_TILE, "a key tile of the cache is two pages");
 #define FT_THREADS 384                     // three groups of four warps: loader and issuer, softmax 0, softmax 1
 #define FT_PIECE_BYTES (128 * 64 * 2)      // 128 rows of 128 bytes
+#define FT_STAGES_64 4                     // K and V tiles in flight with heads of 64 (16 KB each) ...
+#define FT_STAGES_128 2                    // ... and of 128 (32 KB each)
 #define FT_ERR_LOAD 111
 #define FT_ERR_MMA 112
 #define FT_ERR_SOFTMAX 113
 
+__device__ __forceinline__ float ft_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// Has the phase completed?  Does not block; the answer can be asked for early and read late.
+__device__ __forceinline__ uint32_t ft_mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
 __device__ __forceinline__ float ft_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+// 32 columns of this warp's 32 lanes of tensor memory written from registers (the reverse of tmem_load32_issue)
+__device__ __forceinline__ void tmem_store32_issue(uint32_t taddr, const float* v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+// 16 columns (32 bfloat16 of a row, two to a column) of this warp's 32 lanes
+__device__ __forceinline__ void tmem_store16_issue(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// D (tensor memory) (+)= A (tensor memory: a row per lane, two bfloat16 of K per column) x B (shared memory)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Descriptor of an MN-major operand tile with 128-byte rows and 128-byte swizzle: 64 contiguous
 // elements along N, groups of 8 rows along K 1024 bytes apart, further 64-element blocks along N
@@ -77,13 +138,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const bf16* __restrict__ gate, long long ldg, const int* __restrict__ seq_start, int QH,
                        int KVH, int window, float scale_log2, int* err) {
     constexpr int KB = HD / 64;                                   // 64-column pieces of a head
-    constexpr uint32_t Q_BYTES = KB * FT_PIECE_BYTES, KV_BYTES = KB * FT_PIECE_BYTES, P_BYTES = 2 * FT_PIECE_BYTES;
+    constexpr uint32_t Q_BYTES = KB * FT_PIECE_BYTES, KV_BYTES = KB * FT_PIECE_BYTES;
+    constexpr int NP = 2;                                         // mbarriers per group for P and for O, in turns
     // tensor memory: NS score buffers of 128 columns in rotation (three when the head leaves room:
-    // the scores of a group's next tile are then formed while the group is still busy), then one O'
+    // the scores of a group's next tile are then formed while the group is still busy), then one O
     // buffer of HD columns per softmax group
     constexpr int NS = HD == 64 ? 3 : 2;
+    // Threads that issue products.  Two where three score buffers tie the groups to one another (a group's
+    // next scores follow the other group's product, which keeps the groups half a tile apart); one where each
+    // group has a buffer of its own, and only the single thread's order keeps the groups from running in step,
+    // both busy with exponentials at the same time and both away from them at the same time.
+    constexpr int ISSUERS = NS == 3 ? 2 : 1;
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr int NBARS = 1 + 4 * STAGES + NS + 6;
+    constexpr int NBARS = 1 + 4 * STAGES + NS + 4 * NP + 2;
+    // a stage of V is waited for by one group's threads only: a wait that skips a phase of an mbarrier reads the wrong one
+    static_assert(STAGES % 2 == 0, "tiles of one stage belong to one softmax group");
     static_assert(NS * FT_TILE + 2 * HD <= 512, "tensor memory holds the S and O' buffers");
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[NBARS];
@@ -112,13 +181,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int n = n_past + kt_end - kt_begin + 1;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + STAGES * KV_BYTES, p_s = v_s + STAGES * KV_BYTES;
+    const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + STAGES * KV_BYTES;
     const uint32_t bar0 = smem_u32(&bars[0]);
     const uint32_t q_full = bar0;
     const uint32_t k_full = bar0 + 8, k_empty = k_full + 8 * STAGES, v_full = k_empty + 8 * STAGES,
                    v_empty = v_full + 8 * STAGES;
-    const uint32_t s_full = v_empty + 8 * STAGES, p_full = s_full + 8 * NS, o_full = p_full + 16, all_done = o_full + 16,
-                   merge_full = all_done + 8;
+    const uint32_t s_full = v_empty + 8 * STAGES, p_full = s_full + 8 * NS, o_full = p_full + 16 * NP,
+                   all_done = o_full + 16 * NP, merge_full = all_done + 8;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -129,9 +198,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(v_empty + 8 * s, 1);
         }
         for (int i = 0; i < NS; ++i) mbar_init(s_full + 8 * i, 1);
-        for (int g = 0; g < 2; ++g) {
-            mbar_init(p_full + 8 * g, 4);                         // one arrival per warp of the group
-            mbar_init(o_full + 8 * g, 1);
+        // per group and P buffer: a waiter may lag one phase behind an mbarrier, not two
+        for (int i = 0; i < 2 * NP; ++i) {
+            mbar_init(p_full + 8 * i, 4);                         // one arrival per warp of the group
+            mbar_init(o_full + 8 * i, 1);
         }
         mbar_init(all_done, 8);
         mbar_init(merge_full, 4);
@@ -206,52 +276,63 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             if (ok) load_v(n - 1);
             pdl_trigger();                            // every tile is requested: the next kernel may start up
-        } else if (warp == 1 && lane == 0) {
-            // ------------------------------------------------------------- MMA issuer
-            // float accumulator, bf16 operands; S: both K-major, N = 128; O': B (V) MN-major, N = HD
+        } else if (warp >= 1 && warp <= ISSUERS && lane == 0) {
+            // ------------------------------------------------------------- issuers of products
+            // For a tile j: O += P V of tile j, then S = Q K^T of tile j + NS, whose scores go where P of tile j
+            // lies: both from one thread, so the tensor core takes them in that order.  With two issuers thread g
+            // has the tiles of softmax group g: a look at an mbarrier or a commit costs the issuing thread a
+            // hundred cycles and more, and what one thread spends on them then runs beside the other's products.
+            // S: float accumulator, bf16 operands, both K-major, N = 128.  O: A (P) from tensor memory, B (V)
+            // MN-major (its rows are keys), N = HD.
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FT_TILE >> 3) << 17) |
                                          ((uint32_t)(FT_TILE >> 4) << 24);
             constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
                                          ((uint32_t)(FT_TILE >> 4) << 24);
+            const int me = warp - 1;
             bool ok = mbar_wait(q_full, 0, &abort_flag, err, FT_ERR_MMA);
-            auto issue_s = [&](int j) {
+            auto await_k = [&](int j) {
+                ok = mbar_wait(k_full + 8 * (j % STAGES), (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+            };
+            auto products_s = [&](int j) {
                 const int s = j % STAGES;
-                // The S buffer is free: tile j - NS, which used it, had its P announced (p_full) before
-                // P V of that tile was issued, and this call comes after that.
-                ok = mbar_wait(k_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
-                if (!ok) return;
-                tc_fence_after();
-    #pragma unroll
+#pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint64_t a = umma_desc(q_s + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
                     const uint64_t bd = umma_desc(k_s + s * KV_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
                     umma_bf16(tmem_base + (uint32_t)((j % NS) * FT_TILE), a, bd, idesc_s, k != 0);
                 }
-                umma_commit(k_empty + 8 * s);
                 umma_commit(s_full + 8 * (j % NS));
+                umma_commit(k_empty + 8 * s);
             };
-            auto issue_o = [&](int j) {
-                const int g = j & 1, t = j >> 1, s = j % STAGES;
-                // V first: it has long been loaded, and P is what this thread really waits for.
-                ok = mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
-                if (ok) ok = mbar_wait(p_full + 8 * g, t & 1, &abort_flag, err, FT_ERR_MMA);
-                // The group's O' buffer is free as well: the group adds the O' of its previous tile before it
-                // touches the scores of this one, so before the p_full that was just awaited.
-                if (!ok) return;
+            // the first NS tiles' scores wait for nothing; tile i is issued by the thread that has tile i + NS after its product
+            for (int i = 0; i < NS && i < n && ok; ++i) {
+                if (ISSUERS == 2 && ((i + NS) & 1) != me) continue;
+                await_k(i);
+                if (!ok) break;
                 tc_fence_after();
-    #pragma unroll
+                products_s(i);
+            }
+            for (int j = ISSUERS == 2 ? me : 0; j < n && ok; j += ISSUERS) {
+                const int g = j & 1, t = j >> 1, s = j % STAGES, pb = g * NP + t % NP;
+                // V and the next K first: they have long been loaded, and P is what this thread really waits
+                // for; what follows P's arrival is on the path of the group that will read the next scores.
+                ok = mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+                if (ok && j + NS < n) await_k(j + NS);
+                if (ok) ok = mbar_wait(p_full + 8 * pb, (t / NP) & 1, &abort_flag, err, FT_ERR_MMA);
+                // The group's O is in order as well: when the group rescales it, it does so before it
+                // announces the P of the tile (p_full), with every earlier product finished.
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
                 for (int k = 0; k < FT_TILE / 16; ++k) {                // 16 keys per instruction
-                    const uint64_t a = umma_desc(p_s + g * P_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
+                    // P lies where the tile's scores lay: 16 keys are 8 columns
                     const uint64_t bd = umma_desc_mn(v_s + s * KV_BYTES + k * 2048, FT_PIECE_BYTES);
-                    umma_bf16(tmem_base + (uint32_t)(NS * FT_TILE + g * HD), a, bd, idesc_o, k != 0);
+                    umma_bf16_ts(tmem_base + (uint32_t)(NS * FT_TILE + g * HD), tmem_base + (uint32_t)((j % NS) * FT_TILE + 8 * k), bd,
+                                 idesc_o, k != 0 || t != 0);
                 }
+                if (j + NS < n) products_s(j + NS);
+                umma_commit(o_full + 8 * pb);                            // also behind the scores just issued: nobody waits long for it
                 umma_commit(v_empty + 8 * s);
-                umma_commit(o_full + 8 * g);
-            };
-            for (int j = 0; j < NS && j < n && ok; ++j) issue_s(j);
-            for (int j = 0; j < n && ok; ++j) {
-                issue_o(j);
-                if (ok && j + NS < n) issue_s(j + NS);
             }
         }
     } else {
@@ -263,106 +344,106 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int row = p0 + row_l;                               // its position in the sequence
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const uint32_t t_o = lane_base + (uint32_t)(NS * FT_TILE + g * HD);
-        const uint32_t my_p = p_s + g * P_BYTES + r * 128;
-        float o_acc[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+        const uint32_t full = 0xffffffffu;
+        // The group's O stays in tensor memory: every product of the group adds to it.  The exponentials are
+        // taken relative to m_ref, which follows the row's running maximum only when that has grown by more
+        // than RESCALE (a factor of 256 in the probabilities; bfloat16 and the float sums have the range for
+        // it): then, and only then, O is read, scaled and written back, after the group's products so far are
+        // done.  With maxima that settle after the first tiles a tile costs no round trip through O at all.
+        constexpr float RESCALE = 8.f;
+        float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
-        int t = 0;
-        auto add_previous = [&](int tt) {                         // O += O' of this group's tile tt, which is finished
-            ok = mbar_wait(o_full + 8 * g, tt & 1, &abort_flag, err, FT_ERR_SOFTMAX);
-            if (!ok) return;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < HD / 64; ++c) {
-                float v[64];
-                tmem_load32_issue(t_o + (uint32_t)(c * 64), v);
-                tmem_load32_issue(t_o + (uint32_t)(c * 64 + 32), v + 32);
-                tmem_load_wait();
-#pragma unroll
-                for (int i = 0; i < 64; ++i) o_acc[c * 64 + i] = fmaf(o_acc[c * 64 + i], alpha_prev, v[i]);
+        int t = 0, products_done = 0;                             // products 0 .. products_done - 1 of this group are finished
+        auto await_products = [&](int upto) {
+            if (products_done >= upto) return;                    // warp-uniform: every lane counts alike
+            while (ok && products_done < upto) {
+                ok = mbar_wait(o_full + 8 * (g * NP + products_done % NP), (products_done / NP) & 1, &abort_flag, err,
+                               FT_ERR_SOFTMAX);
+                ++products_done;
             }
-            tc_fence_before();
+            ok = __all_sync(full, ok);                            // what follows is warp-wide
         };
         for (int j = g; j < n && ok; j += 2, ++t) {
             // first position of the tile, and the position where its sequence's entries end
             const bool from_cache = PAST && j < n_past;
             const int k0 = from_cache ? (tp_begin + j) * FT_TILE : p0 + (kt_begin + j - n_past) * FT_TILE;
             const int limit = from_cache ? p0 : p0 + len;
-            // First O' of the group's previous tile: the tensor core then never waits for this group
-            // to free the O' buffer, and its arrival also says that P V of that tile is done reading
-            // the P buffer, which this tile's exponentials overwrite.
-            if (t > 0) add_previous(t - 1);
-            if (!ok) break;
-            ok = mbar_wait(s_full + 8 * (j % NS), (j / NS) & 1, &abort_flag, err, FT_ERR_SOFTMAX);
+            ok = __all_sync(full, mbar_wait(s_full + 8 * (j % NS), (j / NS) & 1, &abort_flag, err, FT_ERR_SOFTMAX));
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_s = lane_base + (uint32_t)((j % NS) * FT_TILE);
+            float v[FT_TILE];                                     // the row's 128 scores, read once
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_load32_issue(t_s + (uint32_t)(32 * c), v + 32 * c);
+            // Asked now, read after the maxima: has the product of two tiles ago finished?  (It has, long ago; the
+            // question keeps this group within one phase of its O barriers, and a look at an mbarrier costs about
+            // a hundred cycles when it stands in the way.)
+            uint32_t early = 1;
+            if (t >= 2 && products_done == t - 2)
+                early = ft_mbar_test(o_full + 8 * (g * NP + (t - 2) % NP), (uint32_t)(((t - 2) / NP) & 1));
+            tmem_load_wait();
             // every key of the tile is visible to this row: no comparisons needed
             const bool all_visible = k0 + FT_TILE - 1 <= row && k0 + FT_TILE - 1 < limit && (window <= 0 || k0 + window > row);
-            auto masked = [&](float* v, int c) {
+            if (!all_visible) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = k0 + c * 32 + i;
+                for (int i = 0; i < FT_TILE; ++i) {
+                    const int key = k0 + i;
                     const bool vis = key <= row && key < limit && (window <= 0 || key + window > row);
                     v[i] = vis ? v[i] : -INFINITY;
                 }
-            };
-            // four partial sums and four partial maxima: chains of 128 dependent adds or maxima would
-            // leave the thread waiting on arithmetic latency
-            auto exp_and_stage = [&](const float* v, int c, float m_use, float* rs) {
+            }
+            // four partial maxima and four partial sums: chains of 128 dependent operations would leave the
+            // thread waiting on arithmetic latency
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < FT_TILE; i += 2) mx4[(i >> 1) & 3] = ft_max3(mx4[(i >> 1) & 3], v[i], v[i + 1]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const float m_cand = fmaxf(m_ref, mx * scale_log2);   // scale > 0 keeps the order of the scores
+            // A row that has seen no key yet has O = 0 and l = 0 whatever m_ref is: it takes the maximum as it is.
+            if (m_ref == -INFINITY) m_ref = m_cand;
+            const bool grown = m_cand - m_ref > RESCALE;
+            if (t > 0 && __any_sync(full, grown)) {
+                // The warp owns its 32 lanes of tensor memory, so the warp decides; rows that have not grown
+                // much move to their own maximum as well (a factor below one).
+                await_products(t);
+                if (!ok) break;
+                const float alpha = ft_exp2(m_ref - (m_cand == -INFINITY ? 0.f : m_cand));
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < HD / 32; ++c) {
+                    float o[32];
+                    tmem_load32_issue(t_o + (uint32_t)(32 * c), o);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                    tmem_store32_issue(t_o + (uint32_t)(32 * c), o);
+                }
+                tmem_store_wait();
+                l_run *= alpha;
+                m_ref = m_cand;
+            }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            // Keeps this group within one phase of its O barriers (a wait that lags two phases behind an
+            // mbarrier never returns); the product of two tiles ago is long done.
+            if (t >= 2 && products_done == t - 2 && __all_sync(full, early)) products_done = t - 1;
+            await_products(t - 1);
+            if (!ok) break;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
                 uint32_t w[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = ft_exp2(fmaf(v[2 * i], scale_log2, -m_use));
-                    const float p1 = ft_exp2(fmaf(v[2 * i + 1], scale_log2, -m_use));
-                    rs[i & 3] += p0 + p1;
-                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    const float e0 = ft_exp2(fmaf(v[32 * c + 2 * i], scale_log2, -m_use));
+                    const float e1 = ft_exp2(fmaf(v[32 * c + 2 * i + 1], scale_log2, -m_use));
+                    rs4[i & 3] += e0 + e1;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
                     w[i] = *reinterpret_cast<uint32_t*>(&h);
                 }
-                // 32 probabilities = four 16-byte pieces of this row; keys 64.. go to the second 64-key block
-                const uint32_t dst = my_p + (uint32_t)(c >> 1) * FT_PIECE_BYTES;
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    st_shared16(dst + ((((c & 1) * 4 + i) ^ (r & 7)) << 4), w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-            };
-            // Two passes over the row (maximum, then exponentials), CW columns per wait on tensor
-            // memory: 64 with the 64 output registers of a head of 64, 32 with the 128 of a head of 128.
-            constexpr int CW = HD == 64 ? 64 : 32;
-            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-            for (int c = 0; c < 128 / CW; ++c) {
-                float v[CW];
-#pragma unroll
-                for (int h = 0; h < CW / 32; ++h) tmem_load32_issue(t_s + (uint32_t)(c * CW + 32 * h), v + 32 * h);
-                tmem_load_wait();
-                if (!all_visible) {
-#pragma unroll
-                    for (int h = 0; h < CW / 32; ++h) masked(v + 32 * h, c * (CW / 32) + h);
-                }
-#pragma unroll
-                for (int i = 0; i < CW; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
+                // over the scores, which are in registers: 32 probabilities of the row are 16 columns
+                tmem_store16_issue(t_s + (uint32_t)(16 * c), w);
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float m_new = fmaxf(m_run, mx * scale_log2);    // scale > 0 keeps the order of the scores
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = ft_exp2(m_run - m_use);
-            m_run = m_new;
-#pragma unroll 1
-            for (int c = 0; c < 128 / CW; ++c) {
-                float v[CW];
-#pragma unroll
-                for (int h = 0; h < CW / 32; ++h) tmem_load32_issue(t_s + (uint32_t)(c * CW + 32 * h), v + 32 * h);
-                tmem_load_wait();
-                if (!all_visible) {
-#pragma unroll
-                    for (int h = 0; h < CW / 32; ++h) masked(v + 32 * h, c * (CW / 32) + h);
-                }
-#pragma unroll
-                for (int h = 0; h < CW / 32; ++h) exp_and_stage(v + 32 * h, c * (CW / 32) + h, m_use, rs4);
-            }
+            tmem_store_wait();
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             if (k0 + FT_TILE > limit) {
                 // The tile holds rows that are not this sequence's entries (the next sequence's rows of the step,
@@ -370,7 +451,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // value that is not finite is not zero: thread r clears row r of the value tile before the
                 // product over it may be issued (that waits for p_full below).
                 const int s = j % STAGES;
-                ok = mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_SOFTMAX);
+                ok = __all_sync(full, mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_SOFTMAX));
                 if (!ok) break;
                 if (k0 + r >= limit) {
 #pragma unroll
@@ -379,15 +460,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         for (int c = 0; c < 8; ++c)
                             st_shared16(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES + r * 128 + c * 16, 0u, 0u, 0u, 0u);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the cleared rows, for the tensor core
             }
             tc_fence_before();
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full + 8 * g);         // P is in shared memory; S and the old O' are read out
-            l_run = l_run * alpha + rs;
-            alpha_prev = alpha;
+            if (lane == 0) mbar_arrive(p_full + 8 * (g * NP + t % NP));   // P is in tensor memory and O is in order
+            l_run += rs;
         }
-        if (ok && t > 0) add_previous(t - 1);
+        // the group's O, once its last product is done (a group without a tile has none)
+        float o_acc[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+        if (ok) await_products(t);
+        if (ok && t > 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) tmem_load32_issue(t_o + (uint32_t)(32 * c), o_acc + 32 * c);
+            tmem_load_wait();
+            tc_fence_before();
+        }
+        const float m_run = m_ref;
         // ---- both groups done with the tensor core: every buffer in shared memory is free
         __syncwarp();
         if (lane == 0) mbar_arrive(all_done);
@@ -467,7 +559,7 @@ static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, con
     }
     if (rc != CM_OK) return rc;
     constexpr int KB = HD / 64;
-    const size_t smem = (size_t)KB * FT_PIECE_BYTES * (1 + 2 * STAGES) + 2 * 2 * FT_PIECE_BYTES + 1024;
+    const size_t smem = (size_t)KB * FT_PIECE_BYTES * (1 + 2 * STAGES) + 1024;
     auto kernel = attn_prefill_tc_kernel<HD, STAGES, PAST>;
     static bool configured = false;
     if (!configured) {
@@ -506,10 +598,10 @@ extern "C" int cm_attn_prefill_tc(void* ctx, long long ldc, const void* q, const
         CM_REFUSE("attn_prefill_tc: row pitches %lld, %lld must be multiples of 8 and the operands 16-byte aligned", ld, ldc);
     const FtPast none = {nullptr, nullptr, nullptr, 0, 0, 0};
     if (HD == 64)
-        return launch_ft<64, 3, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
+        return launch_ft<64, FT_STAGES_64, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
                                        none, nullptr, err, st);
     if (HD == 128)
-        return launch_ft<128, 2, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
+        return launch_ft<128, FT_STAGES_128, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
                                         none, nullptr, err, st);
     CM_REFUSE("attn_prefill_tc: head size %d (64 or 128)", HD);
 }
@@ -533,10 +625,10 @@ extern "C" int cm_attn_append_tc(void* ctx, long long ldc, const void* q, const 
     if (2 * pages * KVH * PAGE_TOKENS > 0x7fffffffLL) CM_REFUSE("attn_append_tc: a cache of %lld pages is too large", pages);
     const FtPast past = {seq_pos0, seq_slot, ptab, ptab_stride, pages, ring};
     if (HD == 64)
-        return launch_ft<64, 3, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
+        return launch_ft<64, FT_STAGES_64, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
                                       past, pool, err, st);
     if (HD == 128)
-        return launch_ft<128, 2, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
+        return launch_ft<128, FT_STAGES_128, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
                                        past, pool, err, st);
     CM_REFUSE("attn_append_tc: head size %d (64 or 128)", HD);
 }

@@ -837,6 +837,28 @@ def test_attn_prefill_tc_far_key_and_window_edge(K, window):
     assert torch.equal(hit, expect)
 
 
+@pytest.mark.parametrize("HD", [64, 128])
+@pytest.mark.parametrize("slope", [0.004, 0.012, 0.035])
+def test_attn_prefill_tc_maxima_that_grow_tile_after_tile(K, HD, slope):
+    """The kernel keeps its sums in tensor memory relative to a reference maximum that it moves only when
+    a row's maximum has grown by more than a factor of 256, rescaling the sums then.  Scores that rise
+    with the key's position make every row's maximum grow from tile to tile: slowly (the reference is
+    moved every few tiles), faster (every other tile) or by more than the threshold in every tile."""
+    QH, KVH, T = 2, 1, 1500
+    buf = rnd(T, QH * HD + 2 * KVH * HD, dtype=torch.bfloat16, scale=0.3, seed=HD)
+    buf[:, 0] = HD ** 0.5                                          # query component 0, so that the score is k[p, 0] + noise
+    buf[:, HD] = HD ** 0.5
+    buf[:, QH * HD] = (slope * torch.arange(T, device=DEV)).to(torch.bfloat16)
+    q, k, v = buf[:, :QH * HD], buf[:, QH * HD:QH * HD + HD], buf[:, QH * HD + HD:]
+    starts = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    ctx = torch.empty(T, QH * HD, dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.attn_prefill_tc(ctx, q, k, v, None, starts, 1, T, QH, KVH, HD, 0, HD ** -0.5, err=err)
+    assert int(err) == 0
+    ref = _ref_attention(q.cpu().view(T, QH, HD), k.cpu().view(T, KVH, HD), v.cpu().view(T, KVH, HD), 0, HD ** -0.5)
+    close(ctx.view(T, QH, HD), ref, torch.bfloat16)
+
+
 def test_attn_prefill_tc_refuses_other_head_sizes(K):
     x = torch.empty(4, 96, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(K.KernelError, match="head size"):
