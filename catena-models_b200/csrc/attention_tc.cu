@@ -150,7 +150,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // both busy with exponentials at the same time and both away from them at the same time.
     constexpr int ISSUERS = NS == 3 ? 2 : 1;
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr int NBARS = 1 + 4 * STAGES + NS + 4 * NP + 2;
+    constexpr int NBARS = 1 + 4 * STAGES + NS + 4 * NP;
+    static_assert(NBARS <= 32, "one lane of the first warp sets up each mbarrier");
     // a stage of V is waited for by one group's threads only: a wait that skips a phase of an mbarrier reads the wrong one
     static_assert(STAGES % 2 == 0, "tiles of one stage belong to one softmax group");
     static_assert(NS * FT_TILE + 2 * HD <= 512, "tensor memory holds the S and O' buffers");
@@ -159,6 +160,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ int issued_k, issued_v;
+    __shared__ float2 group_ml[2][FT_TILE];                       // each group's (reference maximum, sum) per row, for the end
 
     pdl_wait();
     const int b = blockIdx.z, hq = blockIdx.y, hk = hq / (QH / KVH);
@@ -186,29 +188,72 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t q_full = bar0;
     const uint32_t k_full = bar0 + 8, k_empty = k_full + 8 * STAGES, v_full = k_empty + 8 * STAGES,
                    v_empty = v_full + 8 * STAGES;
-    const uint32_t s_full = v_empty + 8 * STAGES, p_full = s_full + 8 * NS, o_full = p_full + 16 * NP,
-                   all_done = o_full + 16 * NP, merge_full = all_done + 8;
+    const uint32_t s_full = v_empty + 8 * STAGES, p_full = s_full + 8 * NS, o_full = p_full + 16 * NP;
 
-    if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(k_full + 8 * s, 1);
-            mbar_init(k_empty + 8 * s, 1);
-            mbar_init(v_full + 8 * s, 1);
-            mbar_init(v_empty + 8 * s, 1);
+    // ---- the loader's state and its two kinds of copies (used by thread 0 only)
+    bool ld_ok = true;
+    // the two pages of the cache that hold positions 128 tp .. 128 tp + 127, keys (which = 0) or values
+    auto load_pages = [&](uint32_t dst, uint32_t bar, int tp, int which) {
+        const int* row = past.ptab + (long long)past.seq_slot[b] * past.ptab_stride;
+        for (int h = 0; h < 2; ++h) {
+            int a0 = tp * FT_TILE + h * 64;
+            if (a0 >= p0) a0 = tp * FT_TILE;                   // not this sequence's entries: the first page again
+            const int entry = past.ring > 0 ? a0 % past.ring : a0;
+            const long long page = row[entry >> 6];
+            const long long r0 = ((which * past.pages + page) * KVH + hk) * 64;
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_2d(dst + kb * FT_PIECE_BYTES + h * 8192, &map_pool, bar, kb * 64, (int)r0);
         }
-        for (int i = 0; i < NS; ++i) mbar_init(s_full + 8 * i, 1);
-        // per group and P buffer: a waiter may lag one phase behind an mbarrier, not two
-        for (int i = 0; i < 2 * NP; ++i) {
-            mbar_init(p_full + 8 * i, 4);                         // one arrival per warp of the group
-            mbar_init(o_full + 8 * i, 1);
+    };
+    auto load_k = [&](int j) {
+        const int s = j % STAGES;
+        ld_ok = mbar_wait(k_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
+        if (!ld_ok) return;
+        mbar_expect_tx(k_full + 8 * s, KV_BYTES);
+        if (PAST && j < n_past) {
+            load_pages(k_s + s * KV_BYTES, k_full + 8 * s, tp_begin + j, 0);
+        } else {
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_2d(k_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_k, k_full + 8 * s, hk * HD + kb * 64,
+                            s0 + (kt_begin + j - n_past) * FT_TILE);
         }
-        mbar_init(all_done, 8);
-        mbar_init(merge_full, 4);
-        abort_flag = 0;
-        issued_k = 0;
-        issued_v = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        issued_k = j + 1;
+    };
+    auto load_v = [&](int j) {
+        const int s = j % STAGES;
+        ld_ok = mbar_wait(v_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
+        if (!ld_ok) return;
+        mbar_expect_tx(v_full + 8 * s, KV_BYTES);
+        if (PAST && j < n_past) {
+            load_pages(v_s + s * KV_BYTES, v_full + 8 * s, tp_begin + j, 1);
+        } else {
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_2d(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_v, v_full + 8 * s, hk * HD + kb * 64,
+                            s0 + (kt_begin + j - n_past) * FT_TILE);
+        }
+        issued_v = j + 1;
+    };
+    // ---- set-up: the first warp's lanes set up one mbarrier each, and its first lane starts the copies of Q
+    // and of the first K and V tiles at once, while the others allocate tensor memory and gather at the barrier
+    if (warp == 0) {
+        if (lane < NBARS) {
+            const int first_p = 1 + 4 * STAGES + NS;              // p_full: one arrival per warp of the group; all others one
+            mbar_init(bar0 + 8 * lane, lane >= first_p && lane < first_p + 2 * NP ? 4 : 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+        if (lane == 0) {
+            abort_flag = 0;
+            issued_k = 0;
+            issued_v = 0;
+            mbar_expect_tx(q_full, Q_BYTES);
+            for (int kb = 0; kb < KB; ++kb) tma_load_2d(q_s + kb * FT_PIECE_BYTES, &map_q, q_full, hq * HD + kb * 64, s0 + q0);
+            // the first round of the rings waits for nobody
+            for (int j = 0; j < n && j < STAGES; ++j) {
+                load_k(j);
+                if (j >= 1) load_v(j - 1);
+            }
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
@@ -225,56 +270,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (warp == 0 && lane == 0) {
-            // ------------------------------------------------------------- TMA loader
-            mbar_expect_tx(q_full, Q_BYTES);
-            for (int kb = 0; kb < KB; ++kb) tma_load_2d(q_s + kb * FT_PIECE_BYTES, &map_q, q_full, hq * HD + kb * 64, s0 + q0);
-            bool ok = true;
-            // the two pages of the cache that hold positions 128 tp .. 128 tp + 127, keys (which = 0) or values
-            auto load_pages = [&](uint32_t dst, uint32_t bar, int tp, int which) {
-                const int* row = past.ptab + (long long)past.seq_slot[b] * past.ptab_stride;
-                for (int h = 0; h < 2; ++h) {
-                    int a0 = tp * FT_TILE + h * 64;
-                    if (a0 >= p0) a0 = tp * FT_TILE;                   // not this sequence's entries: the first page again
-                    const int entry = past.ring > 0 ? a0 % past.ring : a0;
-                    const long long page = row[entry >> 6];
-                    const long long r0 = ((which * past.pages + page) * KVH + hk) * 64;
-                    for (int kb = 0; kb < KB; ++kb)
-                        tma_load_2d(dst + kb * FT_PIECE_BYTES + h * 8192, &map_pool, bar, kb * 64, (int)r0);
-                }
-            };
-            auto load_k = [&](int j) {
-                const int s = j % STAGES;
-                ok = mbar_wait(k_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
-                if (!ok) return;
-                mbar_expect_tx(k_full + 8 * s, KV_BYTES);
-                if (PAST && j < n_past) {
-                    load_pages(k_s + s * KV_BYTES, k_full + 8 * s, tp_begin + j, 0);
-                } else {
-                    for (int kb = 0; kb < KB; ++kb)
-                        tma_load_2d(k_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_k, k_full + 8 * s, hk * HD + kb * 64,
-                                    s0 + (kt_begin + j - n_past) * FT_TILE);
-                }
-                issued_k = j + 1;
-            };
-            auto load_v = [&](int j) {
-                const int s = j % STAGES;
-                ok = mbar_wait(v_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
-                if (!ok) return;
-                mbar_expect_tx(v_full + 8 * s, KV_BYTES);
-                if (PAST && j < n_past) {
-                    load_pages(v_s + s * KV_BYTES, v_full + 8 * s, tp_begin + j, 1);
-                } else {
-                    for (int kb = 0; kb < KB; ++kb)
-                        tma_load_2d(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_v, v_full + 8 * s, hk * HD + kb * 64,
-                                    s0 + (kt_begin + j - n_past) * FT_TILE);
-                }
-                issued_v = j + 1;
-            };
-            for (int j = 0; j < n && ok; ++j) {
+            // ------------------------------------------------------------- TMA loader: the tiles after the first round
+            for (int j = STAGES; j < n && ld_ok; ++j) {
                 load_k(j);
-                if (ok && j >= 1) load_v(j - 1);
+                if (ld_ok) load_v(j - 1);
             }
-            if (ok) load_v(n - 1);
+            if (ld_ok) load_v(n - 1);
             pdl_trigger();                            // every tile is requested: the next kernel may start up
         } else if (warp >= 1 && warp <= ISSUERS && lane == 0) {
             // ------------------------------------------------------------- issuers of products
@@ -467,58 +468,51 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (lane == 0) mbar_arrive(p_full + 8 * (g * NP + t % NP));   // P is in tensor memory and O is in order
             l_run += rs;
         }
-        // the group's O, once its last product is done (a group without a tile has none)
-        float o_acc[HD];
+        // ---- the end.  Each group leaves its rows' (reference maximum, sum) in shared memory; then every
+        // thread reads half of the row's O columns of BOTH groups from tensor memory (a warp reaches its 32
+        // lanes in every column), merges, normalises, gates and stores them: group 0 the lower half of the
+        // head, group 1 the upper.
+        if (ok) await_products(t);                                // the group's last product is done
+        group_ml[g][r] = make_float2(m_ref, l_run);
+        tc_fence_before();
+        asm volatile("bar.sync 1, 256;" ::: "memory");            // the eight softmax warps; every one of them gets here
+        tc_fence_after();
+        constexpr int HALF = HD / 2;
+        const bool other_has_tiles = n > 1 - g;                   // group 1 has none when there is one tile only
+        float mine[HALF], theirs[HALF];
 #pragma unroll
-        for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
-        if (ok) await_products(t);
-        if (ok && t > 0) {
-            tc_fence_after();
+        for (int i = 0; i < HALF; ++i) theirs[i] = 0.f;
+        if (ok) {                                                 // the same in every lane of the warp
 #pragma unroll
-            for (int c = 0; c < HD / 32; ++c) tmem_load32_issue(t_o + (uint32_t)(32 * c), o_acc + 32 * c);
+            for (int c = 0; c < HALF / 32; ++c) tmem_load32_issue(t_o + (uint32_t)(g * HALF + 32 * c), mine + 32 * c);
+            if (other_has_tiles) {
+                const uint32_t t_other = lane_base + (uint32_t)(NS * FT_TILE + (g ^ 1) * HD);
+#pragma unroll
+                for (int c = 0; c < HALF / 32; ++c) tmem_load32_issue(t_other + (uint32_t)(g * HALF + 32 * c), theirs + 32 * c);
+            }
             tmem_load_wait();
             tc_fence_before();
         }
-        const float m_run = m_ref;
-        // ---- both groups done with the tensor core: every buffer in shared memory is free
-        __syncwarp();
-        if (lane == 0) mbar_arrive(all_done);
-        if (ok) ok = mbar_wait(all_done, 0, &abort_flag, err, FT_ERR_SOFTMAX);
-        float* mrg = reinterpret_cast<float*>(smem_raw + (k_s - smem_u32(smem_raw)));   // [HD + 2][128] over the K and V rings
-        static_assert((size_t)(HD + 2) * FT_TILE * sizeof(float) <= (size_t)2 * STAGES * KV_BYTES, "merge rows fit the rings");
-        if (g == 1) {
-            if (ok) {
+        if (ok && row_l < len) {
+            const float2 other = group_ml[g ^ 1][r];
+            const float m = fmaxf(m_ref, other.x);
+            const float f_mine = m_ref == -INFINITY ? 0.f : ft_exp2(m_ref - m);
+            const float f_theirs = other.x == -INFINITY ? 0.f : ft_exp2(other.x - m);
+            float f = 1.f / (l_run * f_mine + other.y * f_theirs);
+            const long long tok = s0 + row_l;
+            if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + hq]));
+            bf16* dst = ctx + tok * ldc + (long long)hq * HD + g * HALF;
 #pragma unroll
-                for (int i = 0; i < HD; ++i) mrg[i * FT_TILE + r] = o_acc[i];
-                mrg[HD * FT_TILE + r] = m_run;
-                mrg[(HD + 1) * FT_TILE + r] = l_run;
-            }
-            __syncwarp();
-            __threadfence_block();
-            if (lane == 0) mbar_arrive(merge_full);
-        } else {
-            if (ok) ok = mbar_wait(merge_full, 0, &abort_flag, err, FT_ERR_SOFTMAX);
-            if (ok && row_l < len) {
-                const float m1 = mrg[HD * FT_TILE + r], l1 = mrg[(HD + 1) * FT_TILE + r];
-                const float m = fmaxf(m_run, m1);
-                const float f0 = m_run == -INFINITY ? 0.f : ft_exp2(m_run - m);
-                const float f1 = m1 == -INFINITY ? 0.f : ft_exp2(m1 - m);
-                float f = 1.f / (l_run * f0 + l1 * f1);
-                const long long tok = s0 + row_l;
-                if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + hq]));
-                bf16* dst = ctx + tok * ldc + (long long)hq * HD;
+            for (int c = 0; c < HALF / 8; ++c) {
+                uint4 raw;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
-                for (int c = 0; c < HD / 8; ++c) {
-                    uint4 raw;
-                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int d = 8 * c + 2 * i;
-                        h[i] = __floats2bfloat162_rn((o_acc[d] * f0 + mrg[d * FT_TILE + r] * f1) * f,
-                                                     (o_acc[d + 1] * f0 + mrg[(d + 1) * FT_TILE + r] * f1) * f);
-                    }
-                    *reinterpret_cast<uint4*>(dst + 8 * c) = raw;
+                for (int i = 0; i < 4; ++i) {
+                    const int d = 8 * c + 2 * i;
+                    h[i] = __floats2bfloat162_rn((mine[d] * f_mine + theirs[d] * f_theirs) * f,
+                                                 (mine[d + 1] * f_mine + theirs[d + 1] * f_theirs) * f);
                 }
+                *reinterpret_cast<uint4*>(dst + 8 * c) = raw;
             }
         }
     }
