@@ -130,13 +130,61 @@ struct FtPast {                      // where the keys and values below a sequen
     int ring;
 };
 
+// One work item: a 128-query tile of one query head of one sequence, and the key tiles it takes.
+struct FtItem {
+    int b, hq, hk, s0, len, q0, p0, kt_begin, tp_begin, n_past, n;
+};
+// Item w of the launch, long rows first (the query tile falls as w rises).  n = 0: nothing to do (the
+// sequence is shorter than this tile's first row).
+template <bool PAST>
+__device__ __forceinline__ void ft_item(int w, int tiles_x, int QH, int KVH, int B, int window,
+                                        const int* __restrict__ seq_start, const FtPast& past, FtItem& it) {
+    const int per_x = QH * B, x = w / per_x, rest = w - x * per_x;
+    it.b = rest / QH;
+    it.hq = rest - it.b * QH;
+    it.hk = it.hq / (QH / KVH);
+    it.s0 = seq_start[it.b];
+    it.len = seq_start[it.b + 1] - it.s0;
+    it.q0 = (tiles_x - 1 - x) * FT_TILE;
+    it.n = 0;
+    it.p0 = 0;
+    it.kt_begin = it.tp_begin = it.n_past = 0;
+    if (it.q0 >= it.len) return;
+    it.kt_begin = window > 0 ? max(0, it.q0 - window + 1) / FT_TILE : 0;
+    const int kt_end = min(it.q0 + FT_TILE - 1, it.len - 1) / FT_TILE;   // inclusive
+    // positions: row r of this step stands at p0 + r; tiles of the cache come first, in steps of 128 positions
+    it.p0 = PAST ? past.seq_pos0[it.b] : 0;
+    if (PAST && it.p0 > 0) {
+        const int a_lo = window > 0 ? max(0, it.p0 + it.q0 - window + 1) : 0;
+        if (a_lo < it.p0) {
+            it.tp_begin = a_lo / FT_TILE;
+            it.n_past = (it.p0 - 1) / FT_TILE - it.tp_begin + 1;
+        }
+    }
+    it.n = it.n_past + kt_end - it.kt_begin + 1;
+}
+// The item that block `bx` of `G` takes in its round `r`: rounds run to and fro over the blocks, so that the
+// block with the longest item of one round has the shortest of the next (items are sorted by length).  -1: none.
+__device__ __forceinline__ int ft_item_of_round(int r, int bx, int G, int total) {
+    const int w = r * G + ((r & 1) ? G - 1 - bx : bx);
+    return w < total ? w : -1;
+}
+// The number of key tiles alone, for the roles that need no more.
+template <bool PAST>
+__device__ __forceinline__ int ft_item_tiles(int w, int tiles_x, int QH, int KVH, int B, int window,
+                                             const int* __restrict__ seq_start, const FtPast& past) {
+    FtItem it;
+    ft_item<PAST>(w, tiles_x, QH, KVH, B, window, seq_start, past, it);
+    return it.n;
+}
+
 template <int HD, int STAGES, bool PAST>
 __global__ void __launch_bounds__(FT_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_pool,
                        const FtPast past, bf16* __restrict__ ctx, long long ldc,
                        const bf16* __restrict__ gate, long long ldg, const int* __restrict__ seq_start, int QH,
-                       int KVH, int window, float scale_log2, int* err) {
+                       int KVH, int B, int tiles_x, int window, float scale_log2, int* err) {
     constexpr int KB = HD / 64;                                   // 64-column pieces of a head
     constexpr uint32_t Q_BYTES = KB * FT_PIECE_BYTES, KV_BYTES = KB * FT_PIECE_BYTES;
     constexpr int NP = 2;                                         // mbarriers per group for P and for O, in turns
@@ -150,109 +198,48 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // both busy with exponentials at the same time and both away from them at the same time.
     constexpr int ISSUERS = NS == 3 ? 2 : 1;
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr int NBARS = 1 + 4 * STAGES + NS + 4 * NP;
-    static_assert(NBARS <= 32, "one lane of the first warp sets up each mbarrier");
-    // a stage of V is waited for by one group's threads only: a wait that skips a phase of an mbarrier reads the wrong one
+    constexpr int NBARS = 4 + 4 * STAGES + NS + 4 * NP + 2;
+    // a stage of K or V is waited for by one issuing thread and one group only: a wait that skips a phase
+    // of an mbarrier reads the wrong one
     static_assert(STAGES % 2 == 0, "tiles of one stage belong to one softmax group");
-    static_assert(NS * FT_TILE + 2 * HD <= 512, "tensor memory holds the S and O' buffers");
+    static_assert(NS * FT_TILE + 2 * HD <= 512, "tensor memory holds the S and O buffers");
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[NBARS];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ int issued_k, issued_v;
-    __shared__ float2 group_ml[2][FT_TILE];                       // each group's (reference maximum, sum) per row, for the end
+    __shared__ int issued_q, issued_k, issued_v;
+    __shared__ float2 group_ml[2][2][FT_TILE];                    // [item parity][group][row]: (reference maximum, sum), for an item's end
 
     pdl_wait();
-    const int b = blockIdx.z, hq = blockIdx.y, hk = hq / (QH / KVH);
-    const int s0 = seq_start[b], len = seq_start[b + 1] - s0;
-    const int q0 = (gridDim.x - 1 - blockIdx.x) * FT_TILE;        // long rows first
-    if (q0 >= len) return;                                        // the whole block, before anything is set up
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kt_begin = window > 0 ? max(0, q0 - window + 1) / FT_TILE : 0;
-    const int kt_end = min(q0 + FT_TILE - 1, len - 1) / FT_TILE;  // inclusive
-    // positions: row r of this step stands at p0 + r; tiles of the cache come first, in steps of 128 positions
-    const int p0 = PAST ? past.seq_pos0[b] : 0;
-    int tp_begin = 0, n_past = 0;
-    if (PAST && p0 > 0) {
-        const int a_lo = window > 0 ? max(0, p0 + q0 - window + 1) : 0;
-        if (a_lo < p0) {
-            tp_begin = a_lo / FT_TILE;
-            n_past = (p0 - 1) / FT_TILE - tp_begin + 1;
-        }
-    }
-    const int n = n_past + kt_end - kt_begin + 1;
+    const int total = tiles_x * QH * B, G = gridDim.x;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + STAGES * KV_BYTES;
+    const uint32_t q_s = base, k_s = q_s + 2 * Q_BYTES, v_s = k_s + STAGES * KV_BYTES;
     const uint32_t bar0 = smem_u32(&bars[0]);
-    const uint32_t q_full = bar0;
-    const uint32_t k_full = bar0 + 8, k_empty = k_full + 8 * STAGES, v_full = k_empty + 8 * STAGES,
+    const uint32_t q_full = bar0, q_empty = q_full + 16;
+    const uint32_t k_full = q_empty + 16, k_empty = k_full + 8 * STAGES, v_full = k_empty + 8 * STAGES,
                    v_empty = v_full + 8 * STAGES;
-    const uint32_t s_full = v_empty + 8 * STAGES, p_full = s_full + 8 * NS, o_full = p_full + 16 * NP;
+    const uint32_t s_full = v_empty + 8 * STAGES, p_full = s_full + 8 * NS, o_full = p_full + 16 * NP,
+                   merge_ready = o_full + 16 * NP, o_free = merge_ready + 8;
 
-    // ---- the loader's state and its two kinds of copies (used by thread 0 only)
-    bool ld_ok = true;
-    // the two pages of the cache that hold positions 128 tp .. 128 tp + 127, keys (which = 0) or values
-    auto load_pages = [&](uint32_t dst, uint32_t bar, int tp, int which) {
-        const int* row = past.ptab + (long long)past.seq_slot[b] * past.ptab_stride;
-        for (int h = 0; h < 2; ++h) {
-            int a0 = tp * FT_TILE + h * 64;
-            if (a0 >= p0) a0 = tp * FT_TILE;                   // not this sequence's entries: the first page again
-            const int entry = past.ring > 0 ? a0 % past.ring : a0;
-            const long long page = row[entry >> 6];
-            const long long r0 = ((which * past.pages + page) * KVH + hk) * 64;
-            for (int kb = 0; kb < KB; ++kb)
-                tma_load_2d(dst + kb * FT_PIECE_BYTES + h * 8192, &map_pool, bar, kb * 64, (int)r0);
-        }
-    };
-    auto load_k = [&](int j) {
-        const int s = j % STAGES;
-        ld_ok = mbar_wait(k_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
-        if (!ld_ok) return;
-        mbar_expect_tx(k_full + 8 * s, KV_BYTES);
-        if (PAST && j < n_past) {
-            load_pages(k_s + s * KV_BYTES, k_full + 8 * s, tp_begin + j, 0);
-        } else {
-            for (int kb = 0; kb < KB; ++kb)
-                tma_load_2d(k_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_k, k_full + 8 * s, hk * HD + kb * 64,
-                            s0 + (kt_begin + j - n_past) * FT_TILE);
-        }
-        issued_k = j + 1;
-    };
-    auto load_v = [&](int j) {
-        const int s = j % STAGES;
-        ld_ok = mbar_wait(v_empty + 8 * s, ((j / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
-        if (!ld_ok) return;
-        mbar_expect_tx(v_full + 8 * s, KV_BYTES);
-        if (PAST && j < n_past) {
-            load_pages(v_s + s * KV_BYTES, v_full + 8 * s, tp_begin + j, 1);
-        } else {
-            for (int kb = 0; kb < KB; ++kb)
-                tma_load_2d(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES, &map_v, v_full + 8 * s, hk * HD + kb * 64,
-                            s0 + (kt_begin + j - n_past) * FT_TILE);
-        }
-        issued_v = j + 1;
-    };
-    // ---- set-up: the first warp's lanes set up one mbarrier each, and its first lane starts the copies of Q
-    // and of the first K and V tiles at once, while the others allocate tensor memory and gather at the barrier
     if (warp == 0) {
-        if (lane < NBARS) {
-            const int first_p = 1 + 4 * STAGES + NS;              // p_full: one arrival per warp of the group; all others one
-            mbar_init(bar0 + 8 * lane, lane >= first_p && lane < first_p + 2 * NP ? 4 : 1);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // one lane per mbarrier.  Arrivals: q_empty one per issuing thread; p_full, merge_ready and o_free one per
+        // warp of a group (four, eight, eight); all others one.
+        for (int i = lane; i < NBARS; i += 32) {
+            const int first_p = 4 + 4 * STAGES + NS;
+            int count = 1;
+            if (i == 2 || i == 3) count = ISSUERS;
+            if (i >= first_p && i < first_p + 2 * NP) count = 4;
+            if (i >= NBARS - 2) count = 8;
+            mbar_init(bar0 + 8 * i, count);
         }
-        __syncwarp();
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (lane == 0) {
             abort_flag = 0;
+            issued_q = 0;
             issued_k = 0;
             issued_v = 0;
-            mbar_expect_tx(q_full, Q_BYTES);
-            for (int kb = 0; kb < KB; ++kb) tma_load_2d(q_s + kb * FT_PIECE_BYTES, &map_q, q_full, hq * HD + kb * 64, s0 + q0);
-            // the first round of the rings waits for nobody
-            for (int j = 0; j < n && j < STAGES; ++j) {
-                load_k(j);
-                if (j >= 1) load_v(j - 1);
-            }
         }
     }
     if (warp == 1) {
@@ -265,21 +252,76 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
+    // Every role walks the same items (ft_item_of_round), skipping those without key tiles, and
+    // counts items (i) and key tiles (J) from the block's start: rings, score buffers, the two softmax groups
+    // (tile J is group J & 1's) and all mbarrier phases go by these counts, so that nothing starts over at an
+    // item's border and the copies and scores of the next item are under way while this one's rows are stored.
     // 384 threads x 168 registers fill the register file; the first four warps keep 40 each and the
     // eight softmax warps take 232 (4 x 32 x 40 + 8 x 32 x 232 = 64,512 of 65,536)
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-        if (warp == 0 && lane == 0) {
-            // ------------------------------------------------------------- TMA loader: the tiles after the first round
-            for (int j = STAGES; j < n && ld_ok; ++j) {
-                load_k(j);
-                if (ld_ok) load_v(j - 1);
+        if ((warp == 0 || warp == 3) && lane == 0) {
+            // ------------------------------------------------------------- TMA loaders: warp 0 for Q and K, warp 3 for V,
+            // so that a V tile that waits for its place in the ring holds no K tile back
+            const bool values = warp == 3;
+            bool ok = true;
+            int J = 0, i = 0;
+            FtItem it = {};
+            // the two pages of the cache that hold positions 128 tp .. 128 tp + 127, keys (which = 0) or values
+            auto load_pages = [&](uint32_t dst, uint32_t bar, int tp, int which) {
+                const int* row = past.ptab + (long long)past.seq_slot[it.b] * past.ptab_stride;
+                for (int h = 0; h < 2; ++h) {
+                    int a0 = tp * FT_TILE + h * 64;
+                    if (a0 >= it.p0) a0 = tp * FT_TILE;               // not this sequence's entries: the first page again
+                    const int entry = past.ring > 0 ? a0 % past.ring : a0;
+                    const long long page = row[entry >> 6];
+                    const long long r0 = ((which * past.pages + page) * KVH + it.hk) * 64;
+                    for (int kb = 0; kb < KB; ++kb)
+                        tma_load_2d(dst + kb * FT_PIECE_BYTES + h * 8192, &map_pool, bar, kb * 64, (int)r0);
+                }
+            };
+            auto load_tile = [&](int j, uint32_t ring_s, uint32_t full, uint32_t empty, const CUtensorMap* map, int which) {
+                const int s = J % STAGES;
+                ok = mbar_wait(empty + 8 * s, ((J / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
+                if (!ok) return;
+                mbar_expect_tx(full + 8 * s, KV_BYTES);
+                if (PAST && j < it.n_past) {
+                    load_pages(ring_s + s * KV_BYTES, full + 8 * s, it.tp_begin + j, which);
+                } else {
+                    for (int kb = 0; kb < KB; ++kb)
+                        tma_load_2d(ring_s + s * KV_BYTES + kb * FT_PIECE_BYTES, map, full + 8 * s, it.hk * HD + kb * 64,
+                                    it.s0 + (it.kt_begin + j - it.n_past) * FT_TILE);
+                }
+            };
+            for (int rnd = 0; rnd * G < total && ok; ++rnd) {
+                const int w = ft_item_of_round(rnd, blockIdx.x, G, total);
+                if (w < 0) continue;
+                ft_item<PAST>(w, tiles_x, QH, KVH, B, window, seq_start, past, it);
+                if (it.n == 0) continue;
+                if (!values) {
+                    ok = mbar_wait(q_empty + 8 * (i & 1), ((i >> 1) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
+                    if (!ok) break;
+                    mbar_expect_tx(q_full + 8 * (i & 1), Q_BYTES);
+                    for (int kb = 0; kb < KB; ++kb)
+                        tma_load_2d(q_s + (i & 1) * Q_BYTES + kb * FT_PIECE_BYTES, &map_q, q_full + 8 * (i & 1), it.hq * HD + kb * 64,
+                                    it.s0 + it.q0);
+                    issued_q = ++i;
+                }
+                for (int j = 0; j < it.n && ok; ++j) {
+                    if (values) {
+                        load_tile(j, v_s, v_full, v_empty, &map_v, 1);
+                        if (ok) issued_v = J + 1;
+                    } else {
+                        load_tile(j, k_s, k_full, k_empty, &map_k, 0);
+                        if (ok) issued_k = J + 1;
+                    }
+                    ++J;
+                }
             }
-            if (ld_ok) load_v(n - 1);
             pdl_trigger();                            // every tile is requested: the next kernel may start up
         } else if (warp >= 1 && warp <= ISSUERS && lane == 0) {
             // ------------------------------------------------------------- issuers of products
-            // For a tile j: O += P V of tile j, then S = Q K^T of tile j + NS, whose scores go where P of tile j
+            // For a tile J: O (+)= P V of tile J, then S = Q K^T of tile J + NS, whose scores go where P of tile J
             // lies: both from one thread, so the tensor core takes them in that order.  With two issuers thread g
             // has the tiles of softmax group g: a look at an mbarrier or a commit costs the issuing thread a
             // hundred cycles and more, and what one thread spends on them then runs beside the other's products.
@@ -290,50 +332,100 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
                                          ((uint32_t)(FT_TILE >> 4) << 24);
             const int me = warp - 1;
-            bool ok = mbar_wait(q_full, 0, &abort_flag, err, FT_ERR_MMA);
-            auto await_k = [&](int j) {
-                ok = mbar_wait(k_full + 8 * (j % STAGES), (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+            bool ok = true;
+            // Two walks over the tiles: the one whose scores are issued (sw, sn, sj, si: item, its tiles, the tile,
+            // the count of items; global tile J + NS) runs NS tiles ahead of the one whose product is (pw, ...; J).
+            int sr = -1, sn = 0, sj = 0, si = -1;                   // round, the item's tiles, the tile, the count of items
+            int pr = -1, pn = 0, pj = 0, pi = -1;
+            bool s_valid = true;
+            int T0 = 0, T1 = 0;                                     // products issued per group
+            // moves the score walk to the next tile; at an item's border the item just left gives its Q buffer
+            // back and the next one's Q is awaited
+            auto advance_s = [&]() {
+                if (++sj < sn) return;
+                if (si >= 0) umma_commit(q_empty + 8 * (si & 1));    // this thread's scores of the item are all issued
+                do {
+                    ++sr;
+                    if (sr * G >= total) { s_valid = false; return; }
+                    const int w = ft_item_of_round(sr, blockIdx.x, G, total);
+                    sn = w < 0 ? 0 : ft_item_tiles<PAST>(w, tiles_x, QH, KVH, B, window, seq_start, past);
+                } while (sn == 0);
+                sj = 0;
+                ++si;
+                ok = mbar_wait(q_full + 8 * (si & 1), (si >> 1) & 1, &abort_flag, err, FT_ERR_MMA);
             };
-            auto products_s = [&](int j) {
-                const int s = j % STAGES;
+            auto products_s = [&](int Js) {
+                const int s = Js % STAGES;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
-                    const uint64_t a = umma_desc(q_s + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
+                    const uint64_t a = umma_desc(q_s + (si & 1) * Q_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
                     const uint64_t bd = umma_desc(k_s + s * KV_BYTES + (k >> 2) * FT_PIECE_BYTES) + 2 * (k & 3);
-                    umma_bf16(tmem_base + (uint32_t)((j % NS) * FT_TILE), a, bd, idesc_s, k != 0);
+                    umma_bf16(tmem_base + (uint32_t)((Js % NS) * FT_TILE), a, bd, idesc_s, k != 0);
                 }
-                umma_commit(s_full + 8 * (j % NS));
+                umma_commit(s_full + 8 * (Js % NS));
                 umma_commit(k_empty + 8 * s);
             };
-            // the first NS tiles' scores wait for nothing; tile i is issued by the thread that has tile i + NS after its product
-            for (int i = 0; i < NS && i < n && ok; ++i) {
-                if (ISSUERS == 2 && ((i + NS) & 1) != me) continue;
-                await_k(i);
-                if (!ok) break;
-                tc_fence_after();
-                products_s(i);
-            }
-            for (int j = ISSUERS == 2 ? me : 0; j < n && ok; j += ISSUERS) {
-                const int g = j & 1, t = j >> 1, s = j % STAGES, pb = g * NP + t % NP;
-                // V and the next K first: they have long been loaded, and P is what this thread really waits
-                // for; what follows P's arrival is on the path of the group that will read the next scores.
-                ok = mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
-                if (ok && j + NS < n) await_k(j + NS);
-                if (ok) ok = mbar_wait(p_full + 8 * pb, (t / NP) & 1, &abort_flag, err, FT_ERR_MMA);
-                // The group's O is in order as well: when the group rescales it, it does so before it
-                // announces the P of the tile (p_full), with every earlier product finished.
-                if (!ok) break;
-                tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < FT_TILE / 16; ++k) {                // 16 keys per instruction
-                    // P lies where the tile's scores lay: 16 keys are 8 columns
-                    const uint64_t bd = umma_desc_mn(v_s + s * KV_BYTES + k * 2048, FT_PIECE_BYTES);
-                    umma_bf16_ts(tmem_base + (uint32_t)(NS * FT_TILE + g * HD), tmem_base + (uint32_t)((j % NS) * FT_TILE + 8 * k), bd,
-                                 idesc_o, k != 0 || t != 0);
+            auto mine = [&](int J) { return ISSUERS == 1 || (J & 1) == me; };
+            sj = -1;                                                // so that the first advance enters the first item
+            sn = 0;
+            advance_s();
+            // the first NS tiles' scores wait for no product; tile Js is issued by the thread that has tile Js - NS ... + NS after its product
+            int Js = 0;
+            for (; Js < NS && s_valid && ok; ++Js) {
+                if (mine(Js + NS)) {
+                    ok = mbar_wait(k_full + 8 * (Js % STAGES), (Js / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+                    if (!ok) break;
+                    tc_fence_after();
+                    products_s(Js);
                 }
-                if (j + NS < n) products_s(j + NS);
-                umma_commit(o_full + 8 * pb);                            // also behind the scores just issued: nobody waits long for it
-                umma_commit(v_empty + 8 * s);
+                advance_s();
+            }
+            // Js = J + NS from here on, as long as there are tiles left to score
+            int J = 0;
+            while (ok) {
+                // the product walk's next tile
+                if (++pj >= pn) {
+                    do {
+                        ++pr;
+                        if (pr * G >= total) break;
+                        const int w = ft_item_of_round(pr, blockIdx.x, G, total);
+                        pn = w < 0 ? 0 : ft_item_tiles<PAST>(w, tiles_x, QH, KVH, B, window, seq_start, past);
+                    } while (pn == 0);
+                    if (pr * G >= total) break;
+                    pj = 0;
+                    ++pi;
+                    // the O buffers hold the item before until both groups have read them
+                    if (pi >= 1) ok = mbar_wait(o_free, (pi - 1) & 1, &abort_flag, err, FT_ERR_MMA);
+                    if (!ok) break;
+                }
+                if (mine(J)) {
+                    const int g = J & 1, s = J % STAGES, Tg = g ? T1 : T0, pb = g * NP + Tg % NP;
+                    // V and the next K first: they have long been loaded, and P is what this thread really waits
+                    // for; what follows P's arrival is on the path of the group that will read the next scores.
+                    ok = mbar_wait(v_full + 8 * s, (J / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+                    if (ok && s_valid) ok = mbar_wait(k_full + 8 * (Js % STAGES), (Js / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+                    if (ok) ok = mbar_wait(p_full + 8 * pb, (Tg / NP) & 1, &abort_flag, err, FT_ERR_MMA);
+                    // The group's O is in order as well: when the group rescales it, it does so before it
+                    // announces the P of the tile (p_full), with every earlier product finished.
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < FT_TILE / 16; ++k) {            // 16 keys per instruction
+                        // P lies where the tile's scores lay: 16 keys are 8 columns.  The item's first product of a group starts O anew.
+                        const uint64_t bd = umma_desc_mn(v_s + s * KV_BYTES + k * 2048, FT_PIECE_BYTES);
+                        umma_bf16_ts(tmem_base + (uint32_t)(NS * FT_TILE + g * HD), tmem_base + (uint32_t)((J % NS) * FT_TILE + 8 * k), bd,
+                                     idesc_o, k != 0 || pj >= 2);
+                    }
+                    if (s_valid) products_s(Js);
+                    umma_commit(o_full + 8 * pb);                        // also behind the scores just issued: nobody waits long for it
+                    umma_commit(v_empty + 8 * s);
+                    if (g) ++T1; else ++T0;
+                }
+                ++J;
+                if (s_valid) {
+                    ++Js;
+                    advance_s();
+                }
             }
         }
     } else {
@@ -341,8 +433,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // ------------------------------------------------------------- softmax groups
         const int g = (warp - 4) >> 2, quarter = warp & 3;
         const int r = quarter * 32 + lane;                        // the row of the tile this thread owns
-        const int row_l = q0 + r;                                 // its row among the sequence's rows of this step
-        const int row = p0 + row_l;                               // its position in the sequence
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const uint32_t t_o = lane_base + (uint32_t)(NS * FT_TILE + g * HD);
         const uint32_t full = 0xffffffffu;
@@ -352,9 +442,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // it): then, and only then, O is read, scaled and written back, after the group's products so far are
         // done.  With maxima that settle after the first tiles a tile costs no round trip through O at all.
         constexpr float RESCALE = 8.f;
-        float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
-        int t = 0, products_done = 0;                             // products 0 .. products_done - 1 of this group are finished
+        int J = 0, i = 0;                                         // key tiles and items so far (both groups' tiles count)
+        int T = 0, products_done = 0;                             // this group's products so far; products 0 .. products_done - 1 are finished
         auto await_products = [&](int upto) {
             if (products_done >= upto) return;                    // warp-uniform: every lane counts alike
             while (ok && products_done < upto) {
@@ -364,127 +454,148 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             ok = __all_sync(full, ok);                            // what follows is warp-wide
         };
-        for (int j = g; j < n && ok; j += 2, ++t) {
-            // first position of the tile, and the position where its sequence's entries end
-            const bool from_cache = PAST && j < n_past;
-            const int k0 = from_cache ? (tp_begin + j) * FT_TILE : p0 + (kt_begin + j - n_past) * FT_TILE;
-            const int limit = from_cache ? p0 : p0 + len;
-            ok = __all_sync(full, mbar_wait(s_full + 8 * (j % NS), (j / NS) & 1, &abort_flag, err, FT_ERR_SOFTMAX));
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t t_s = lane_base + (uint32_t)((j % NS) * FT_TILE);
-            float v[FT_TILE];                                     // the row's 128 scores, read once
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_load32_issue(t_s + (uint32_t)(32 * c), v + 32 * c);
-            // Asked now, read after the maxima: has the product of two tiles ago finished?  (It has, long ago; the
-            // question keeps this group within one phase of its O barriers, and a look at an mbarrier costs about
-            // a hundred cycles when it stands in the way.)
-            uint32_t early = 1;
-            if (t >= 2 && products_done == t - 2)
-                early = ft_mbar_test(o_full + 8 * (g * NP + (t - 2) % NP), (uint32_t)(((t - 2) / NP) & 1));
-            tmem_load_wait();
-            // every key of the tile is visible to this row: no comparisons needed
-            const bool all_visible = k0 + FT_TILE - 1 <= row && k0 + FT_TILE - 1 < limit && (window <= 0 || k0 + window > row);
-            if (!all_visible) {
-#pragma unroll
-                for (int i = 0; i < FT_TILE; ++i) {
-                    const int key = k0 + i;
-                    const bool vis = key <= row && key < limit && (window <= 0 || key + window > row);
-                    v[i] = vis ? v[i] : -INFINITY;
-                }
-            }
-            // four partial maxima and four partial sums: chains of 128 dependent operations would leave the
-            // thread waiting on arithmetic latency
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int i = 0; i < FT_TILE; i += 2) mx4[(i >> 1) & 3] = ft_max3(mx4[(i >> 1) & 3], v[i], v[i + 1]);
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float m_cand = fmaxf(m_ref, mx * scale_log2);   // scale > 0 keeps the order of the scores
-            // A row that has seen no key yet has O = 0 and l = 0 whatever m_ref is: it takes the maximum as it is.
-            if (m_ref == -INFINITY) m_ref = m_cand;
-            const bool grown = m_cand - m_ref > RESCALE;
-            if (t > 0 && __any_sync(full, grown)) {
-                // The warp owns its 32 lanes of tensor memory, so the warp decides; rows that have not grown
-                // much move to their own maximum as well (a factor below one).
-                await_products(t);
+        for (int rnd = 0; rnd * G < total && ok; ++rnd) {
+            const int w = ft_item_of_round(rnd, blockIdx.x, G, total);
+            if (w < 0) continue;
+            FtItem it;
+            ft_item<PAST>(w, tiles_x, QH, KVH, B, window, seq_start, past, it);
+            if (it.n == 0) continue;
+            const int row_l = it.q0 + r;                          // this thread's row among the sequence's rows of this step
+            const int row = it.p0 + row_l;                        // its position in the sequence
+            const int J0 = J;
+            float m_ref = -INFINITY, l_run = 0.f;
+            int t = 0;                                            // this group's tiles of the item so far
+            for (int j = 0; j < it.n && ok; ++j, ++J) {
+                if ((J & 1) != g) continue;
+                // first position of the tile, and the position where its sequence's entries end
+                const bool from_cache = PAST && j < it.n_past;
+                const int k0 = from_cache ? (it.tp_begin + j) * FT_TILE : it.p0 + (it.kt_begin + j - it.n_past) * FT_TILE;
+                const int limit = from_cache ? it.p0 : it.p0 + it.len;
+                ok = __all_sync(full, mbar_wait(s_full + 8 * (J % NS), (J / NS) & 1, &abort_flag, err, FT_ERR_SOFTMAX));
                 if (!ok) break;
-                const float alpha = ft_exp2(m_ref - (m_cand == -INFINITY ? 0.f : m_cand));
                 tc_fence_after();
+                const uint32_t t_s = lane_base + (uint32_t)((J % NS) * FT_TILE);
+                float v[FT_TILE];                                     // the row's 128 scores, read once
 #pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
-                    float o[32];
-                    tmem_load32_issue(t_o + (uint32_t)(32 * c), o);
-                    tmem_load_wait();
+                for (int c = 0; c < 4; ++c) tmem_load32_issue(t_s + (uint32_t)(32 * c), v + 32 * c);
+                // Asked now, read after the maxima: has the product of two tiles ago finished?  (It has, long ago; the
+                // question keeps this group within one phase of its O barriers, and a look at an mbarrier costs about
+                // a hundred cycles when it stands in the way.)
+                uint32_t early = 1;
+                if (T >= 2 && products_done == T - 2)
+                    early = ft_mbar_test(o_full + 8 * (g * NP + (T - 2) % NP), (uint32_t)(((T - 2) / NP) & 1));
+                tmem_load_wait();
+                // every key of the tile is visible to this row: no comparisons needed
+                const bool all_visible = k0 + FT_TILE - 1 <= row && k0 + FT_TILE - 1 < limit && (window <= 0 || k0 + window > row);
+                if (!all_visible) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] *= alpha;
-                    tmem_store32_issue(t_o + (uint32_t)(32 * c), o);
+                    for (int c = 0; c < FT_TILE; ++c) {
+                        const int key = k0 + c;
+                        const bool vis = key <= row && key < limit && (window <= 0 || key + window > row);
+                        v[c] = vis ? v[c] : -INFINITY;
+                    }
+                }
+                // four partial maxima and four partial sums: chains of 128 dependent operations would leave the
+                // thread waiting on arithmetic latency
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < FT_TILE; c += 2) mx4[(c >> 1) & 3] = ft_max3(mx4[(c >> 1) & 3], v[c], v[c + 1]);
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                const float m_cand = fmaxf(m_ref, mx * scale_log2);   // scale > 0 keeps the order of the scores
+                // A row that has seen no key yet has O = 0 and l = 0 whatever m_ref is: it takes the maximum as it is.
+                if (m_ref == -INFINITY) m_ref = m_cand;
+                const bool grown = m_cand - m_ref > RESCALE;
+                if (t > 0 && __any_sync(full, grown)) {
+                    // The warp owns its 32 lanes of tensor memory, so the warp decides; rows that have not grown
+                    // much move to their own maximum as well (a factor below one).
+                    await_products(T);
+                    if (!ok) break;
+                    const float alpha = ft_exp2(m_ref - (m_cand == -INFINITY ? 0.f : m_cand));
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < HD / 32; ++c) {
+                        float o[32];
+                        tmem_load32_issue(t_o + (uint32_t)(32 * c), o);
+                        tmem_load_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] *= alpha;
+                        tmem_store32_issue(t_o + (uint32_t)(32 * c), o);
+                    }
+                    tmem_store_wait();
+                    l_run *= alpha;
+                    m_ref = m_cand;
+                }
+                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                // Keeps this group within one phase of its O barriers (a wait that lags two phases behind an
+                // mbarrier never returns); the product of two tiles ago is long done.
+                if (T >= 2 && products_done == T - 2 && __all_sync(full, early)) products_done = T - 1;
+                await_products(T - 1);
+                if (!ok) break;
+                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const float e0 = ft_exp2(fmaf(v[32 * c + 2 * e], scale_log2, -m_use));
+                        const float e1 = ft_exp2(fmaf(v[32 * c + 2 * e + 1], scale_log2, -m_use));
+                        rs4[e & 3] += e0 + e1;
+                        __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+                        pk[e] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    // over the scores, which are in registers: 32 probabilities of the row are 16 columns
+                    tmem_store16_issue(t_s + (uint32_t)(16 * c), pk);
                 }
                 tmem_store_wait();
-                l_run *= alpha;
-                m_ref = m_cand;
+                const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+                if (k0 + FT_TILE > limit) {
+                    // The tile holds rows that are not this sequence's entries (the next sequence's rows of the step,
+                    // padding, unwritten entries of a page).  Their probabilities are exactly zero, but zero times a
+                    // value that is not finite is not zero: thread r clears row r of the value tile before the
+                    // product over it may be issued (that waits for p_full below).
+                    const int s = J % STAGES;
+                    ok = __all_sync(full, mbar_wait(v_full + 8 * s, (J / STAGES) & 1, &abort_flag, err, FT_ERR_SOFTMAX));
+                    if (!ok) break;
+                    if (k0 + r >= limit) {
+#pragma unroll
+                        for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                            for (int c = 0; c < 8; ++c)
+                                st_shared16(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES + r * 128 + c * 16, 0u, 0u, 0u, 0u);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the cleared rows, for the tensor core
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full + 8 * (g * NP + T % NP));   // P is in tensor memory and O is in order
+                l_run += rs;
+                ++T;
+                ++t;
             }
-            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            // Keeps this group within one phase of its O barriers (a wait that lags two phases behind an
-            // mbarrier never returns); the product of two tiles ago is long done.
-            if (t >= 2 && products_done == t - 2 && __all_sync(full, early)) products_done = t - 1;
-            await_products(t - 1);
             if (!ok) break;
-            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t w[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float e0 = ft_exp2(fmaf(v[32 * c + 2 * i], scale_log2, -m_use));
-                    const float e1 = ft_exp2(fmaf(v[32 * c + 2 * i + 1], scale_log2, -m_use));
-                    rs4[i & 3] += e0 + e1;
-                    __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-                    w[i] = *reinterpret_cast<uint32_t*>(&h);
-                }
-                // over the scores, which are in registers: 32 probabilities of the row are 16 columns
-                tmem_store16_issue(t_s + (uint32_t)(16 * c), w);
-            }
-            tmem_store_wait();
-            const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-            if (k0 + FT_TILE > limit) {
-                // The tile holds rows that are not this sequence's entries (the next sequence's rows of the step,
-                // padding, unwritten entries of a page).  Their probabilities are exactly zero, but zero times a
-                // value that is not finite is not zero: thread r clears row r of the value tile before the
-                // product over it may be issued (that waits for p_full below).
-                const int s = j % STAGES;
-                ok = __all_sync(full, mbar_wait(v_full + 8 * s, (j / STAGES) & 1, &abort_flag, err, FT_ERR_SOFTMAX));
-                if (!ok) break;
-                if (k0 + r >= limit) {
-#pragma unroll
-                    for (int kb = 0; kb < KB; ++kb)
-#pragma unroll
-                        for (int c = 0; c < 8; ++c)
-                            st_shared16(v_s + s * KV_BYTES + kb * FT_PIECE_BYTES + r * 128 + c * 16, 0u, 0u, 0u, 0u);
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the cleared rows, for the tensor core
-            }
+            // ---- the item's end.  Each group leaves its rows' (reference maximum, sum) in shared memory; then every
+            // thread reads half of the row's O columns of BOTH groups from tensor memory (a warp reaches its 32
+            // lanes in every column), merges, normalises, gates and stores them: group 0 the lower half of the
+            // head, group 1 the upper.  Once both groups have read, the O buffers are the next item's.
+            await_products(T);                                    // the group's last product is done
+            if (!ok) break;
+            group_ml[i & 1][g][r] = make_float2(m_ref, l_run);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full + 8 * (g * NP + t % NP));   // P is in tensor memory and O is in order
-            l_run += rs;
-        }
-        // ---- the end.  Each group leaves its rows' (reference maximum, sum) in shared memory; then every
-        // thread reads half of the row's O columns of BOTH groups from tensor memory (a warp reaches its 32
-        // lanes in every column), merges, normalises, gates and stores them: group 0 the lower half of the
-        // head, group 1 the upper.
-        if (ok) await_products(t);                                // the group's last product is done
-        group_ml[g][r] = make_float2(m_ref, l_run);
-        tc_fence_before();
-        asm volatile("bar.sync 1, 256;" ::: "memory");            // the eight softmax warps; every one of them gets here
-        tc_fence_after();
-        constexpr int HALF = HD / 2;
-        const bool other_has_tiles = n > 1 - g;                   // group 1 has none when there is one tile only
-        float mine[HALF], theirs[HALF];
+            if (lane == 0) mbar_arrive(merge_ready);
+            ok = __all_sync(full, mbar_wait(merge_ready, i & 1, &abort_flag, err, FT_ERR_SOFTMAX));
+            if (!ok) break;
+            tc_fence_after();
+            constexpr int HALF = HD / 2;
+            // the other group's tiles of this item: those of the other parity among J0 .. J0 + n - 1
+            const bool other_has_tiles = (it.n + (((J0 & 1) == (g ^ 1)) ? 1 : 0)) / 2 > 0;
+            float mine[HALF], theirs[HALF];
 #pragma unroll
-        for (int i = 0; i < HALF; ++i) theirs[i] = 0.f;
-        if (ok) {                                                 // the same in every lane of the warp
+            for (int c = 0; c < HALF; ++c) mine[c] = theirs[c] = 0.f;
+            if (t > 0) {
 #pragma unroll
-            for (int c = 0; c < HALF / 32; ++c) tmem_load32_issue(t_o + (uint32_t)(g * HALF + 32 * c), mine + 32 * c);
+                for (int c = 0; c < HALF / 32; ++c) tmem_load32_issue(t_o + (uint32_t)(g * HALF + 32 * c), mine + 32 * c);
+            }
             if (other_has_tiles) {
                 const uint32_t t_other = lane_base + (uint32_t)(NS * FT_TILE + (g ^ 1) * HD);
 #pragma unroll
@@ -492,28 +603,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             tmem_load_wait();
             tc_fence_before();
-        }
-        if (ok && row_l < len) {
-            const float2 other = group_ml[g ^ 1][r];
-            const float m = fmaxf(m_ref, other.x);
-            const float f_mine = m_ref == -INFINITY ? 0.f : ft_exp2(m_ref - m);
-            const float f_theirs = other.x == -INFINITY ? 0.f : ft_exp2(other.x - m);
-            float f = 1.f / (l_run * f_mine + other.y * f_theirs);
-            const long long tok = s0 + row_l;
-            if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + hq]));
-            bf16* dst = ctx + tok * ldc + (long long)hq * HD + g * HALF;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_free);
+            if (row_l < it.len) {
+                const float2 other = group_ml[i & 1][g ^ 1][r];
+                const float m = fmaxf(m_ref, other.x);
+                const float f_mine = m_ref == -INFINITY ? 0.f : ft_exp2(m_ref - m);
+                const float f_theirs = other.x == -INFINITY ? 0.f : ft_exp2(other.x - m);
+                float f = 1.f / (l_run * f_mine + other.y * f_theirs);
+                const long long tok = it.s0 + row_l;
+                if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + it.hq]));
+                bf16* dst = ctx + tok * ldc + (long long)it.hq * HD + g * HALF;
 #pragma unroll
-            for (int c = 0; c < HALF / 8; ++c) {
-                uint4 raw;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+                for (int c = 0; c < HALF / 8; ++c) {
+                    uint4 raw;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int d = 8 * c + 2 * i;
-                    h[i] = __floats2bfloat162_rn((mine[d] * f_mine + theirs[d] * f_theirs) * f,
-                                                 (mine[d + 1] * f_mine + theirs[d + 1] * f_theirs) * f);
+                    for (int e = 0; e < 4; ++e) {
+                        const int d = 8 * c + 2 * e;
+                        h[e] = __floats2bfloat162_rn((mine[d] * f_mine + theirs[d] * f_theirs) * f,
+                                                     (mine[d + 1] * f_mine + theirs[d + 1] * f_theirs) * f);
+                    }
+                    *reinterpret_cast<uint4*>(dst + 8 * c) = raw;
                 }
-                *reinterpret_cast<uint4*>(dst + 8 * c) = raw;
             }
+            ++i;
         }
     }
     // ------------------------------------------------------------------ teardown
@@ -521,13 +635,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     if (abort_flag && threadIdx.x == 0) {
         // copies that were issued but never consumed must land before shared memory is given up
-        for (int i = 0; i < TC_SPIN_LIMIT; ++i)
-            if (mbar_try_wait(q_full, 0)) break;
+        for (int q = max(0, issued_q - 2); q < issued_q; ++q)
+            for (int c = 0; c < TC_SPIN_LIMIT; ++c)
+                if (mbar_try_wait(q_full + 8 * (q & 1), (q >> 1) & 1)) break;
         for (int j = max(0, issued_k - STAGES); j < issued_k; ++j)
-            for (int i = 0; i < TC_SPIN_LIMIT; ++i)
+            for (int c = 0; c < TC_SPIN_LIMIT; ++c)
                 if (mbar_try_wait(k_full + 8 * (j % STAGES), (j / STAGES) & 1)) break;
         for (int j = max(0, issued_v - STAGES); j < issued_v; ++j)
-            for (int i = 0; i < TC_SPIN_LIMIT; ++i)
+            for (int c = 0; c < TC_SPIN_LIMIT; ++c)
                 if (mbar_try_wait(v_full + 8 * (j % STAGES), (j / STAGES) & 1)) break;
     }
     __syncthreads();
@@ -553,7 +668,7 @@ static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, con
     }
     if (rc != CM_OK) return rc;
     constexpr int KB = HD / 64;
-    const size_t smem = (size_t)KB * FT_PIECE_BYTES * (1 + 2 * STAGES) + 1024;
+    const size_t smem = (size_t)KB * FT_PIECE_BYTES * (2 + 2 * STAGES) + 1024;   // two Q tiles, the K and V rings
     auto kernel = attn_prefill_tc_kernel<HD, STAGES, PAST>;
     static bool configured = false;
     if (!configured) {
@@ -563,9 +678,20 @@ static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, con
         }
         configured = true;
     }
-    dim3 grid((max_len + FT_TILE - 1) / FT_TILE, QH, B);
+    // one block per SM walks the items (query tile, head, sequence), long rows first
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 1;
+    }
+    const int tiles_x = (max_len + FT_TILE - 1) / FT_TILE;
+    const long long items = (long long)tiles_x * QH * B;
+    if (items > 0x7fffffffLL) CM_REFUSE("attn_prefill_tc: %lld items", items);
+    dim3 grid((unsigned)(items < sm_count ? items : sm_count));
     cm_launch(kernel, grid, FT_THREADS, smem, st, map_q, map_k, map_v, map_pool, past, (bf16*)ctx, ldc, (const bf16*)gate,
-              ldg, seq_start, QH, KVH, window, scale * 1.4426950408889634f, err);
+              ldg, seq_start, QH, KVH, B, tiles_x, window, scale * 1.4426950408889634f, err);
     {
         cudaError_t e_ = cudaGetLastError();
         if (e_ != cudaSuccess) {
