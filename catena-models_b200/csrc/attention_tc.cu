@@ -11,30 +11,32 @@
 // keys hold does not matter, and their rows of the value tile are cleared in shared memory before the
 // product over them is issued, because a probability of exactly zero times NaN would not be zero.
 //
-// One block per (128-query tile, query head, sequence), long tiles first.  Twelve warps (the first
-// group of four gives most of its registers to the other two, setmaxnreg 40 / 232):
-//   warp 0   one thread: TMA loads of the Q tile and of 128-key K and V tiles into shared-memory
-//            rings (128-byte rows, 128-byte swizzle; a head of 128 is two 64-column pieces);
-//   warp 1   allocates tensor memory;
-//   warps 1-2  one thread each (only warp 1's with a head of 128) issues products and commits them to
-//            mbarriers: S = Q K^T (128 x 128, K-major operands from shared memory) into one of the score
-//            buffers, and O += P V (128 x HD; P from tensor memory, V from shared memory as the MN-major
-//            B operand: its rows are keys) into the O buffer of the tile's softmax group;
-//   warps 4-7 and 8-11  two softmax groups of 128 threads, one query row per thread.  Group g takes
-//            the key tiles g, g+2, ...: reads the row's 128 scores from tensor memory into registers
-//            once, takes their maximum, and writes the exponentials as bfloat16 back over the scores,
-//            where the product reads them.  Each group keeps its own (reference maximum, sum) in
-//            registers and its own O in tensor memory; the two are merged at the end through shared
-//            memory, normalised, gated and stored.
-// O is never read between tiles: the exponentials are taken relative to a reference that follows the
-// row's maximum only when that has grown by more than a factor of 256 since the reference was set; then
-// the group waits for its products so far, scales its O in tensor memory and goes on.  Maxima settle
-// after the first tiles of a row, so this is rare (and it changes no result beyond rounding: the sums
-// are float, and a bfloat16 probability of up to 256 is as exact as one below 1).
-// What bounds a tile's time is the softmax groups (about 128 exponentials per thread and tile on the
-// SM's 16 special-function lanes) and what stands between a group's P and the scores it reads three
-// tiles later; every look at an mbarrier and every commit costs the thread that makes it a hundred cycles
-// and more, so they are kept off that path (asked early, read late; two issuing threads).
+// Work items are (128-query tile, query head, sequence), long rows first; one block per SM walks its share
+// of them, to and fro over the blocks so that the shares come out even, and keeps its rings, its tensor-memory
+// buffers and all mbarrier phases running across an item's border: the copies and first scores of the next
+// item are under way while this one's rows are stored.  Twelve warps (the first group of four gives most of
+// its registers to the other two, setmaxnreg 40 / 232): threads that copy with TMA (Q tiles, 128-key K and V
+// tiles into shared-memory rings; 128-byte rows, 128-byte swizzle; a head of 128 is two 64-column pieces),
+// threads that issue products and commit them to mbarriers (S = Q K^T, 128 x 128, K-major operands from
+// shared memory; O += P V, 128 x HD, P from tensor memory, V from shared memory as the MN-major B operand:
+// its rows are keys), and two softmax groups of 128 threads, one query row a thread: a thread reads its
+// row's 128 scores from tensor memory into registers once, takes their maximum, and writes the exponentials
+// as bfloat16 back into tensor memory, where the product reads them.
+// O is never read between tiles: the exponentials are taken relative to a reference that follows the row's
+// maximum only when that has grown by more than a factor of 256 since the reference was set; then the group
+// waits for its products so far, scales its O in tensor memory and goes on.  Maxima settle after the first
+// tiles of a row, so this is rare (and it changes no result beyond rounding: the sums are float, and a
+// bfloat16 probability of up to 256 is as exact as one below 1).
+// Two forms.  In this file, for heads of 128: the two groups share an item and take its key tiles in turns
+// (group g the tiles g, g + 2, ...), each with its own (reference, sum) and its own O, merged at the item's
+// end; P lies over the scores it came from, and one thread issues, for a tile, the product and then the
+// scores of the tile that takes the buffer over, which also keeps the groups half a tile apart.  In
+// attention_tc_solo.cuh, for heads of 64, where tensor memory has room for it: each group has items of its
+// own, with its own copying and issuing thread, rings, and S, P and O columns.
+// What bounds a tile's time is the softmax (128 exponentials a thread and tile on the SM's 16
+// special-function lanes, which the two groups share) and what stands between one tile's P and the next
+// tile's scores; every look at an mbarrier and every commit costs the thread that makes it a hundred cycles
+// and more, so they are kept off that path (asked early, read late).
 //
 // Maximum, sum, exponent arguments and the rescaling are float; probabilities enter the second
 // product as bfloat16.  Every wait on an mbarrier is bounded; a wait that runs out raises *err, all
@@ -45,7 +47,7 @@
 static_assert(PAGE_TOKENS * 2 == FT_TILE, "a key tile of the cache is two pages");
 #define FT_THREADS 384                     // three groups of four warps: loader and issuer, softmax 0, softmax 1
 #define FT_PIECE_BYTES (128 * 64 * 2)      // 128 rows of 128 bytes
-#define FT_STAGES_64 4                     // K and V tiles in flight with heads of 64 (16 KB each) ...
+#define FT_STAGES_64 3                     // K and V tiles in flight with heads of 64 (16 KB each), per pipeline ...
 #define FT_STAGES_128 2                    // ... and of 128 (32 KB each)
 #define FT_ERR_LOAD 111
 #define FT_ERR_MMA 112
@@ -188,15 +190,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     constexpr int KB = HD / 64;                                   // 64-column pieces of a head
     constexpr uint32_t Q_BYTES = KB * FT_PIECE_BYTES, KV_BYTES = KB * FT_PIECE_BYTES;
     constexpr int NP = 2;                                         // mbarriers per group for P and for O, in turns
-    // tensor memory: NS score buffers of 128 columns in rotation (three when the head leaves room:
-    // the scores of a group's next tile are then formed while the group is still busy), then one O
-    // buffer of HD columns per softmax group
-    constexpr int NS = HD == 64 ? 3 : 2;
-    // Threads that issue products.  Two where three score buffers tie the groups to one another (a group's
-    // next scores follow the other group's product, which keeps the groups half a tile apart); one where each
-    // group has a buffer of its own, and only the single thread's order keeps the groups from running in step,
-    // both busy with exponentials at the same time and both away from them at the same time.
-    constexpr int ISSUERS = NS == 3 ? 2 : 1;
+    // tensor memory: a score buffer of 128 columns per softmax group (tile J's is buffer J % NS), then an O
+    // buffer of HD columns per group: 512 columns with a head of 128
+    constexpr int NS = 2;
     constexpr uint32_t TMEM_COLS = 512;
     constexpr int NBARS = 4 + 4 * STAGES + NS + 4 * NP + 2;
     // a stage of K or V is waited for by one issuing thread and one group only: a wait that skips a phase
@@ -224,12 +220,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                    merge_ready = o_full + 16 * NP, o_free = merge_ready + 8;
 
     if (warp == 0) {
-        // one lane per mbarrier.  Arrivals: q_empty one per issuing thread; p_full, merge_ready and o_free one per
-        // warp of a group (four, eight, eight); all others one.
+        // one lane per mbarrier.  Arrivals: p_full, merge_ready and o_free one per warp of a group (four, eight,
+        // eight); all others one.
         for (int i = lane; i < NBARS; i += 32) {
             const int first_p = 4 + 4 * STAGES + NS;
             int count = 1;
-            if (i == 2 || i == 3) count = ISSUERS;
             if (i >= first_p && i < first_p + 2 * NP) count = 4;
             if (i >= NBARS - 2) count = 8;
             mbar_init(bar0 + 8 * i, count);
@@ -319,19 +314,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
             pdl_trigger();                            // every tile is requested: the next kernel may start up
-        } else if (warp >= 1 && warp <= ISSUERS && lane == 0) {
-            // ------------------------------------------------------------- issuers of products
+        } else if (warp == 1 && lane == 0) {
+            // ------------------------------------------------------------- issuer of products
             // For a tile J: O (+)= P V of tile J, then S = Q K^T of tile J + NS, whose scores go where P of tile J
-            // lies: both from one thread, so the tensor core takes them in that order.  With two issuers thread g
-            // has the tiles of softmax group g: a look at an mbarrier or a commit costs the issuing thread a
-            // hundred cycles and more, and what one thread spends on them then runs beside the other's products.
+            // lies: both from one thread, so the tensor core takes them in that order; and the one thread's order,
+            // group after group, keeps the two groups half a tile apart, not both at their exponentials at once.
             // S: float accumulator, bf16 operands, both K-major, N = 128.  O: A (P) from tensor memory, B (V)
             // MN-major (its rows are keys), N = HD.
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FT_TILE >> 3) << 17) |
                                          ((uint32_t)(FT_TILE >> 4) << 24);
             constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
                                          ((uint32_t)(FT_TILE >> 4) << 24);
-            const int me = warp - 1;
             bool ok = true;
             // Two walks over the tiles: the one whose scores are issued (sw, sn, sj, si: item, its tiles, the tile,
             // the count of items; global tile J + NS) runs NS tiles ahead of the one whose product is (pw, ...; J).
@@ -365,19 +358,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 umma_commit(s_full + 8 * (Js % NS));
                 umma_commit(k_empty + 8 * s);
             };
-            auto mine = [&](int J) { return ISSUERS == 1 || (J & 1) == me; };
             sj = -1;                                                // so that the first advance enters the first item
             sn = 0;
             advance_s();
-            // the first NS tiles' scores wait for no product; tile Js is issued by the thread that has tile Js - NS ... + NS after its product
+            // the first NS tiles' scores wait for no product
             int Js = 0;
             for (; Js < NS && s_valid && ok; ++Js) {
-                if (mine(Js + NS)) {
-                    ok = mbar_wait(k_full + 8 * (Js % STAGES), (Js / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
-                    if (!ok) break;
-                    tc_fence_after();
-                    products_s(Js);
-                }
+                ok = mbar_wait(k_full + 8 * (Js % STAGES), (Js / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+                if (!ok) break;
+                tc_fence_after();
+                products_s(Js);
                 advance_s();
             }
             // Js = J + NS from here on, as long as there are tiles left to score
@@ -398,7 +388,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (pi >= 1) ok = mbar_wait(o_free, (pi - 1) & 1, &abort_flag, err, FT_ERR_MMA);
                     if (!ok) break;
                 }
-                if (mine(J)) {
+                {
                     const int g = J & 1, s = J % STAGES, Tg = g ? T1 : T0, pb = g * NP + Tg % NP;
                     // V and the next K first: they have long been loaded, and P is what this thread really waits
                     // for; what follows P's arrival is on the path of the group that will read the next scores.
@@ -652,6 +642,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
+#include "attention_tc_solo.cuh"
+
+template <int HD, int STAGES, bool PAST>
+static auto ft_kernel() {
+    if constexpr (HD == 64)
+        return attn_prefill_tc_solo_kernel<HD, STAGES, PAST>;
+    else
+        return attn_prefill_tc_kernel<HD, STAGES, PAST>;
+}
+
 template <int HD, int STAGES, bool PAST>
 static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
                      const void* gate, long long ldg, const int* seq_start, int B, int max_len, long long T, int QH,
@@ -668,8 +668,12 @@ static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, con
     }
     if (rc != CM_OK) return rc;
     constexpr int KB = HD / 64;
-    const size_t smem = (size_t)KB * FT_PIECE_BYTES * (2 + 2 * STAGES) + 1024;   // two Q tiles, the K and V rings
-    auto kernel = attn_prefill_tc_kernel<HD, STAGES, PAST>;
+    // Heads of 64: two pipelines a block, each with its own query tile, Q and rings (STAGES is a pipeline's).
+    // Heads of 128: one query tile a block at a time, its key tiles dealt to the two groups (two Q tiles, shared rings).
+    constexpr bool SOLO = HD == 64;
+    const size_t smem = SOLO ? (size_t)2 * KB * FT_PIECE_BYTES * (1 + 2 * STAGES) + 1024
+                             : (size_t)KB * FT_PIECE_BYTES * (2 + 2 * STAGES) + 1024;
+    auto kernel = ft_kernel<HD, STAGES, PAST>();
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -689,7 +693,8 @@ static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, con
     const int tiles_x = (max_len + FT_TILE - 1) / FT_TILE;
     const long long items = (long long)tiles_x * QH * B;
     if (items > 0x7fffffffLL) CM_REFUSE("attn_prefill_tc: %lld items", items);
-    dim3 grid((unsigned)(items < sm_count ? items : sm_count));
+    const long long blocks = SOLO ? (items + 1) / 2 : items;
+    dim3 grid((unsigned)(blocks < sm_count ? blocks : sm_count));
     cm_launch(kernel, grid, FT_THREADS, smem, st, map_q, map_k, map_v, map_pool, past, (bf16*)ctx, ldc, (const bf16*)gate,
               ldg, seq_start, QH, KVH, B, tiles_x, window, scale * 1.4426950408889634f, err);
     {
