@@ -281,15 +281,13 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_read);
-                // every key of the tile is visible to this row: no comparisons needed
-                const bool all_visible = k0 + FT_TILE - 1 <= row && k0 + FT_TILE - 1 < limit && (window <= 0 || k0 + window > row);
-                if (!all_visible) {
+                // the keys of the tile that this row sees are the columns lo .. hi - 1; all of them: no comparisons needed
+                const int lo = window > 0 ? max(0, row - window + 1 - k0) : 0;
+                const int hi = min(FT_TILE, min(row, limit - 1) - k0 + 1);
+                if (lo > 0 || hi < FT_TILE) {
+                    const unsigned span = (unsigned)max(hi - lo, 0);
 #pragma unroll
-                    for (int c = 0; c < FT_TILE; ++c) {
-                        const int key = k0 + c;
-                        const bool vis = key <= row && key < limit && (window <= 0 || key + window > row);
-                        v[c] = vis ? v[c] : -INFINITY;
-                    }
+                    for (int c = 0; c < FT_TILE; ++c) v[c] = (unsigned)(c - lo) < span ? v[c] : -INFINITY;
                 }
                 // four partial maxima and four partial sums: chains of 128 dependent operations would leave the
                 // thread waiting on arithmetic latency
