@@ -70,6 +70,26 @@ __device__ __forceinline__ uint32_t ft_mbar_test(uint32_t bar, uint32_t parity) 
         : "memory");
     return ok;
 }
+// Two floats in one 64-bit register and arithmetic on both at once (fma and add as for single floats, round to
+// nearest): half the instructions for the softmax's multiply-adds and sums.
+__device__ __forceinline__ uint64_t ft_pack2(float a, float b) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(a), "f"(b));
+    return d;
+}
+__device__ __forceinline__ void ft_unpack2(uint64_t d, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(d));
+}
+__device__ __forceinline__ uint64_t ft_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t ft_add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ float ft_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -475,15 +495,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (T >= 2 && products_done == T - 2)
                     early = ft_mbar_test(o_full + 8 * (g * NP + (T - 2) % NP), (uint32_t)(((T - 2) / NP) & 1));
                 tmem_load_wait();
-                // every key of the tile is visible to this row: no comparisons needed
-                const bool all_visible = k0 + FT_TILE - 1 <= row && k0 + FT_TILE - 1 < limit && (window <= 0 || k0 + window > row);
-                if (!all_visible) {
+                // the keys of the tile that this row sees are the columns lo .. hi - 1; all of them: no comparisons needed
+                const int lo = window > 0 ? max(0, row - window + 1 - k0) : 0;
+                const int hi = min(FT_TILE, min(row, limit - 1) - k0 + 1);
+                if (lo > 0 || hi < FT_TILE) {
+                    const unsigned span = (unsigned)max(hi - lo, 0);
 #pragma unroll
-                    for (int c = 0; c < FT_TILE; ++c) {
-                        const int key = k0 + c;
-                        const bool vis = key <= row && key < limit && (window <= 0 || key + window > row);
-                        v[c] = vis ? v[c] : -INFINITY;
-                    }
+                    for (int c = 0; c < FT_TILE; ++c) v[c] = (unsigned)(c - lo) < span ? v[c] : -INFINITY;
                 }
                 // four partial maxima and four partial sums: chains of 128 dependent operations would leave the
                 // thread waiting on arithmetic latency
@@ -521,15 +539,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (T >= 2 && products_done == T - 2 && __all_sync(full, early)) products_done = T - 1;
                 await_products(T - 1);
                 if (!ok) break;
-                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+                // two partial sums of pairs: a chain of 64 dependent additions would leave the thread waiting on their latency
+                const uint64_t scale2 = ft_pack2(scale_log2, scale_log2), minus_m2 = ft_pack2(-m_use, -m_use);
+                uint64_t rs2[2] = {ft_pack2(0.f, 0.f), ft_pack2(0.f, 0.f)};
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
-                        const float e0 = ft_exp2(fmaf(v[32 * c + 2 * e], scale_log2, -m_use));
-                        const float e1 = ft_exp2(fmaf(v[32 * c + 2 * e + 1], scale_log2, -m_use));
-                        rs4[e & 3] += e0 + e1;
+                        float x0, x1;
+                        ft_unpack2(ft_fma2(ft_pack2(v[32 * c + 2 * e], v[32 * c + 2 * e + 1]), scale2, minus_m2), x0, x1);
+                        const float e0 = ft_exp2(x0), e1 = ft_exp2(x1);
+                        rs2[e & 1] = ft_add2(rs2[e & 1], ft_pack2(e0, e1));
                         __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
                         pk[e] = *reinterpret_cast<uint32_t*>(&h);
                     }
@@ -537,7 +558,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tmem_store16_issue(t_s + (uint32_t)(16 * c), pk);
                 }
                 tmem_store_wait();
-                const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+                float rs_a, rs_b;
+                ft_unpack2(ft_add2(rs2[0], rs2[1]), rs_a, rs_b);
+                const float rs = rs_a + rs_b;
                 if (k0 + FT_TILE > limit) {
                     // The tile holds rows that are not this sequence's entries (the next sequence's rows of the step,
                     // padding, unwritten entries of a page).  Their probabilities are exactly zero, but zero times a

@@ -330,13 +330,16 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     for (int c = 0; c < EXP_TURN_POLLS && !my_turn; ++c) my_turn = atomicCAS(&exp_turn[quarter], 0, 1) == 0;
                 }
                 __syncwarp();
-                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+                // two partial sums of pairs: a chain of 64 dependent additions would leave the thread waiting on their latency
+                const uint64_t scale2 = ft_pack2(scale_log2, scale_log2), minus_m2 = ft_pack2(-m_use, -m_use);
+                uint64_t rs2[2] = {ft_pack2(0.f, 0.f), ft_pack2(0.f, 0.f)};
                 uint32_t pk[FT_TILE / 2];                             // the row's probabilities, two bfloat16 a word
 #pragma unroll
                 for (int e = 0; e < FT_TILE / 2; ++e) {
-                    const float e0 = ft_exp2(fmaf(v[2 * e], scale_log2, -m_use));
-                    const float e1 = ft_exp2(fmaf(v[2 * e + 1], scale_log2, -m_use));
-                    rs4[e & 3] += e0 + e1;
+                    float x0, x1;
+                    ft_unpack2(ft_fma2(ft_pack2(v[2 * e], v[2 * e + 1]), scale2, minus_m2), x0, x1);
+                    const float e0 = ft_exp2(x0), e1 = ft_exp2(x1);
+                    rs2[e & 1] = ft_add2(rs2[e & 1], ft_pack2(e0, e1));
                     __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
                     pk[e] = *reinterpret_cast<uint32_t*>(&h);
                 }
@@ -349,7 +352,9 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 // asked now, read at the top of the next tile: are its scores there?
                 s_early = ft_mbar_test(s_full, (uint32_t)((J + 1) & 1));
                 tmem_store_wait();
-                const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+                float rs_a, rs_b;
+                ft_unpack2(ft_add2(rs2[0], rs2[1]), rs_a, rs_b);
+                const float rs = rs_a + rs_b;
                 if (k0 + FT_TILE > limit) {
                     // The tile holds rows that are not this sequence's entries (the next sequence's rows of the step,
                     // padding, unwritten entries of a page).  Their probabilities are exactly zero, but zero times a
