@@ -40,7 +40,6 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ int issued_q[2], issued_k[2], issued_v[2];
-    __shared__ int exp_turn[4];                                   // per quarter of the SM: a warp is at its exponentials
 
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -66,7 +65,6 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (lane == 0) {
             abort_flag = 0;
-            for (int p = 0; p < 4; ++p) exp_turn[p] = 0;
             for (int p = 0; p < 2; ++p) issued_q[p] = issued_k[p] = issued_v[p] = 0;
         }
     }
@@ -104,7 +102,7 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             };
             auto load_tile = [&](int j, uint32_t ring_s, uint32_t full, uint32_t empty, const CUtensorMap* map, int which) {
                 const int s = J % STAGES;
-                ok = mbar_wait(empty + 8 * s, ((J / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
+                ok = ft_mbar_wait(empty + 8 * s, ((J / STAGES) & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
                 if (!ok) return;
                 mbar_expect_tx(full + 8 * s, KV_BYTES);
                 if (PAST && j < it.n_past) {
@@ -121,7 +119,7 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ft_item<PAST>(w, tiles_x, QH, KVH, B, window, seq_start, past, it);
                 if (it.n == 0) continue;
                 // Q's place is free once the scores of the item before are all formed
-                ok = mbar_wait(q_empty, (i & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
+                ok = ft_mbar_wait(q_empty, (i & 1) ^ 1, &abort_flag, err, FT_ERR_LOAD);
                 if (!ok) break;
                 mbar_expect_tx(q_full, Q_BYTES);
                 for (int kb = 0; kb < KB; ++kb)
@@ -166,8 +164,8 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // S of the score walk's tile; the S columns are free (nothing was in them yet, or s_read said so)
             auto scores = [&]() {
                 const int s = Js % STAGES;
-                if (sj == 0) ok = mbar_wait(q_full, si & 1, &abort_flag, err, FT_ERR_MMA);
-                if (ok) ok = mbar_wait(k_full + 8 * s, (Js / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+                if (sj == 0) ok = ft_mbar_wait(q_full, si & 1, &abort_flag, err, FT_ERR_MMA);
+                if (ok) ok = ft_mbar_wait(k_full + 8 * s, (Js / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
                 if (!ok) return;
                 tc_fence_after();
 #pragma unroll
@@ -198,12 +196,12 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     pj = 0;
                     ++pi;
                     // O holds the item before until the group has read it
-                    if (pi >= 1) ok = mbar_wait(o_free, (pi - 1) & 1, &abort_flag, err, FT_ERR_MMA);
+                    if (pi >= 1) ok = ft_mbar_wait(o_free, (pi - 1) & 1, &abort_flag, err, FT_ERR_MMA);
                     if (!ok) break;
                 }
                 // the next tile's scores as soon as this tile's are read out ...
                 if (s_valid) {
-                    ok = mbar_wait(s_read, J & 1, &abort_flag, err, FT_ERR_MMA);
+                    ok = ft_mbar_wait(s_read, J & 1, &abort_flag, err, FT_ERR_MMA);
                     if (!ok) break;
                     scores();
                     if (!ok) break;
@@ -211,8 +209,8 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 // ... and this tile's product once P is there.  V first: it has long been loaded.
                 const int s = J % STAGES;
-                ok = mbar_wait(v_full + 8 * s, (J / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
-                if (ok) ok = mbar_wait(p_full, J & 1, &abort_flag, err, FT_ERR_MMA);
+                ok = ft_mbar_wait(v_full + 8 * s, (J / STAGES) & 1, &abort_flag, err, FT_ERR_MMA);
+                if (ok) ok = ft_mbar_wait(p_full, J & 1, &abort_flag, err, FT_ERR_MMA);
                 // O is in order as well: when the group rescales it, it does so before it announces P, with every
                 // earlier product finished.
                 if (!ok) break;
@@ -236,8 +234,6 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t t_s = lane_base, t_p = lane_base + COL_P, t_o = lane_base + COL_O;
         const uint32_t full = 0xffffffffu;
         constexpr float RESCALE = 8.f;                            // the reference follows the maximum after a factor of 256
-        constexpr int EXP_TURN_POLLS = 48;
-        constexpr int EXP_TURN_TILES = 24;                        // ... for items long enough for the distance to last
         bool ok = true;
         int J = 0, i = 0;                                         // key tiles and items of this pipeline so far
         int products_done = 0;                                    // products 0 .. products_done - 1 are finished
@@ -245,7 +241,7 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         auto await_products = [&](int upto) {
             if (products_done >= upto) return;                    // warp-uniform: every lane counts alike
             while (ok && products_done < upto) {
-                ok = mbar_wait(o_full, products_done & 1, &abort_flag, err, FT_ERR_SOFTMAX);
+                ok = ft_mbar_wait(o_full, products_done & 1, &abort_flag, err, FT_ERR_SOFTMAX);
                 ++products_done;
             }
             ok = __all_sync(full, ok);                            // what follows is warp-wide
@@ -265,7 +261,7 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const int k0 = from_cache ? (it.tp_begin + j) * FT_TILE : it.p0 + (it.kt_begin + j - it.n_past) * FT_TILE;
                 const int limit = from_cache ? it.p0 : it.p0 + it.len;
                 // (asked at the end of the tile before: the scores are formed while the group is at its exponentials)
-                if (!__all_sync(full, s_early)) ok = __all_sync(full, mbar_wait(s_full, J & 1, &abort_flag, err, FT_ERR_SOFTMAX));
+                if (!__all_sync(full, s_early)) ok = __all_sync(full, ft_mbar_wait(s_full, J & 1, &abort_flag, err, FT_ERR_SOFTMAX));
                 if (!ok) break;
                 tc_fence_after();
                 float v[FT_TILE];                                     // the row's 128 scores, read once
@@ -321,15 +317,6 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     m_ref = m_cand;
                 }
                 const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-                // The two warps of a quarter of the SM (one of each group) share its 4 special-function lanes.
-                // Taking turns at the exponentials keeps them half a tile apart, each at its other work while the
-                // other is here; in step they would both wait on the lanes, and then leave them idle together.
-                // Only a hint: after EXP_TURN_POLLS looks the warp goes ahead anyway.
-                bool my_turn = false;
-                if (lane == 0 && it.n >= EXP_TURN_TILES) {
-                    for (int c = 0; c < EXP_TURN_POLLS && !my_turn; ++c) my_turn = atomicCAS(&exp_turn[quarter], 0, 1) == 0;
-                }
-                __syncwarp();
                 // two partial sums of pairs: a chain of 64 dependent additions would leave the thread waiting on their latency
                 const uint64_t scale2 = ft_pack2(scale_log2, scale_log2), minus_m2 = ft_pack2(-m_use, -m_use);
                 uint64_t rs2[2] = {ft_pack2(0.f, 0.f), ft_pack2(0.f, 0.f)};
@@ -343,7 +330,6 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
                     pk[e] = *reinterpret_cast<uint32_t*>(&h);
                 }
-                if (my_turn) atomicExch(&exp_turn[quarter], 0);
                 // The product of the tile before reads the P columns: it has had the time of the exponentials to finish.
                 await_products(J);
                 if (!ok) break;
@@ -361,7 +347,7 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     // value that is not finite is not zero: thread r clears row r of the value tile before the
                     // product over it may be issued (that waits for p_full below).
                     const int s = J % STAGES;
-                    ok = __all_sync(full, mbar_wait(v_full + 8 * s, (J / STAGES) & 1, &abort_flag, err, FT_ERR_SOFTMAX));
+                    ok = __all_sync(full, ft_mbar_wait(v_full + 8 * s, (J / STAGES) & 1, &abort_flag, err, FT_ERR_SOFTMAX));
                     if (!ok) break;
                     if (k0 + r >= limit) {
 #pragma unroll

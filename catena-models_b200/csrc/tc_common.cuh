@@ -35,9 +35,6 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Waits for the phase of `parity` to complete.  Gives up after TC_SPIN_LIMIT polls or when
 // another role has raised *abort; on its own timeout it raises *abort and *err itself.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, int* err, int code) {
-    // not unrolled: a kernel waits in dozens of places, nearly always with success at the first look, and every
-    // copy of the loop is so much less instruction cache for the code that does the work
-#pragma unroll 1
     for (int i = 0; i < TC_SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255) == 255 && *abort) return false;
