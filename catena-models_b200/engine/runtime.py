@@ -283,18 +283,19 @@ class Runtime:
         return a
 
     # ------------------------------------------------------------------ attention
-    TCGEN05_ATTENTION_MIN_LEN = 1024     # shorter prompts (or windows) give an item too few key tiles to pipeline ...
-    TCGEN05_ATTENTION_MIN_LEN_BATCH = 512    # ... unless there are many of them:
+    TCGEN05_ATTENTION_MIN_LEN = 768      # shorter prompts (or windows) give an item too few key tiles to pipeline ...
+    TCGEN05_ATTENTION_MIN_LEN_BATCH = 256    # ... unless there are many of them:
     TCGEN05_ATTENTION_MIN_TOKENS = 2048      # this many rows in the step
 
     def attention_prefill(self, ctx, q, k, v, gate, batch, QH, KVH, HD, window, scale):
         """Attention of a prompt step over the step's own keys and values.  bfloat16 with head size
         64 or 128 and long sequences: the tcgen05 kernel (measured on B200, 32 heads of 64, tcgen05 against
-        mma.sync: 26 / 35 us at 1,024 tokens, 49 / 96 at 2,048, 604 against 264 TFLOP/s at 16,384; heads of
-        128: 802 against 286; 8 prompts of 512: 49 / 53 us, 16 of 1,100: 267 / 376; a window of 512 on
-        4,096 tokens: 81 / 87.  The mma.sync kernel is ahead below that: one prompt of 512 14 / 17 us, 64
-        prompts of 300 160 / 213, a window of 256 56 / 65).  Other bfloat16 head sizes that are
-        multiples of 16 up to 128: mma.sync.  Everything else, and float32: CUDA cores."""
+        mma.sync: 18 / 25 us at 768 tokens, 22 / 35 at 1,024, 40 / 96 at 2,048, 664 against 264 TFLOP/s at
+        16,384; heads of 128: 871 against 286; 8 prompts of 256: 17 / 20 us, 8 of 512: 37 / 52, 16 of
+        1,100: 205 / 376, 64 of 300: 155 / 160; a window of 512 on 4,096 tokens: 57 / 87, of 256: 43 / 56.
+        The mma.sync kernel is ahead for a single short prompt: 512 tokens 14.2 / 14.4 us, 256 tokens 7 /
+        11, 128 tokens 4 / 9).  Other bfloat16 head sizes that are multiples of 16 up to 128: mma.sync.
+        Everything else, and float32: CUDA cores."""
         aligned = (q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
                    and v.data_ptr() % 16 == 0)
         bf16 = q.dtype == torch.bfloat16 and self.tensor_core_prompts
@@ -310,9 +311,9 @@ class Runtime:
         fn(ctx, q, k, v, gate, batch.seq_start, batch.B, batch.max_len, QH, KVH, HD, window, scale)
 
     # Measured on B200, 32 heads of 64 over 8 kv heads, mma.sync against tcgen05:
-    # 128 rows on 512 held tokens 20.8 / 19.9 us, on 256 held 13.4 / 15.9; 16 rows x 8 sequences on 4,096 146 / 85 us,
-    # 8 rows x 8 on 4,096 146 / 83; 1,024 rows on 8,192 429 / 164 us (with a window of 512: 38 / 24 us); 64 rows x 16
-    # sequences on 2,048 108 / 90 us, on 192 held 17 / 38; 16 rows x 8 on 300 held 16 / 23.
+    # 128 rows on 512 held tokens 20.9 / 17.0 us, on 256 held 13.4 / 13.3; 64 rows on 256 held 12.1 / 13.2; 16 rows x 8
+    # sequences on 4,096 146 / 74 us, 8 rows x 8 on 4,096 146 / 73; 1,024 rows on 8,192 429 / 149 us (with a window of
+    # 512: 38 / 19 us); 64 rows x 16 sequences on 2,048 108 / 79 us, on 192 held 17 / 27; 16 rows x 8 on 300 held 16 / 17.
     TCGEN05_APPEND_MIN_ROWS = 8
     TCGEN05_APPEND_MIN_SPAN = 512
 
