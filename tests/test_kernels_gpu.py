@@ -87,6 +87,28 @@ def test_add_norm(K, dtype, post, nxt, rows, H):
     assert torch.equal(h2, h_out)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,H,slices", [(3, 64, 1), (700, 1544, 3), (1500, 2048, 2), (2500, 264, 8), (600, 4104, 4)])
+def test_add_norm_over_partial_sums_with_more_rows_than_blocks(K, dtype, rows, H, slices):
+    """Over partial sums the kernel's blocks walk rows, a fixed number of blocks per SM, with the next row's
+    loads in flight: fewer rows than blocks, about as many, and several rows a block; the result must be the
+    bits of add_norm over the rounded total."""
+    parts = rnd(slices, rows, H, seed=5)
+    h = rnd(rows, H, dtype=dtype, seed=6)
+    wp, wn = 1 + 0.1 * rnd(H, seed=3), 1 + 0.1 * rnd(H, seed=4)
+    total = torch.zeros(rows, H, device=DEV)
+    for r in range(slices):
+        total += parts[r]                                            # index order, in float
+    m = total.to(dtype)
+    h_a, n_a, h_b, n_b = (torch.empty_like(h) for _ in range(4))
+    K.add_norm(h_a, n_a, K.PartialSums(parts, dtype), h, wp, wn, 1e-5, 1e-6)
+    K.add_norm(h_b, n_b, m, h, wp, wn, 1e-5, 1e-6)
+    assert torch.equal(h_a, h_b) and torch.equal(n_a, n_b)
+    h2 = h.clone()                                                   # in place on the residual stream, no norms
+    K.add_norm(h2, None, K.PartialSums(parts, dtype), h2, None, None, 0.0, 0.0)
+    assert torch.equal(h2, (h.float() + m.float()).to(dtype))
+
+
 @pytest.mark.parametrize("M,N,Kin,slices", [(1, 48, 256, 4), (8, 2048, 2048, 4), (13, 200, 1000, 3), (16, 72, 8192, 8),
                                             (5, 40, 64, 2)])
 def test_gemm_skinny_parts_and_add_norm_over_them(K, M, N, Kin, slices):
