@@ -235,7 +235,7 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t full = 0xffffffffu;
         constexpr float RESCALE = 8.f;                            // the reference follows the maximum after a factor of 256
         bool ok = true;
-        int J = 0, i = 0;                                         // key tiles and items of this pipeline so far
+        int J = 0;                                                // key tiles of this pipeline so far
         int products_done = 0;                                    // products 0 .. products_done - 1 are finished
         uint32_t s_early = 0;                                     // the next tile's scores were seen to be there
         auto await_products = [&](int upto) {
@@ -389,7 +389,6 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     *reinterpret_cast<uint4*>(dst + 8 * c) = raw;
                 }
             }
-            ++i;
         }
     }
     // ------------------------------------------------------------------ teardown
