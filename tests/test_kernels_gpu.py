@@ -881,6 +881,39 @@ def test_attn_prefill_tc_maxima_that_grow_tile_after_tile(K, HD, slope):
     close(ctx.view(T, QH, HD), ref, torch.bfloat16)
 
 
+@pytest.mark.parametrize("seed,QH,KVH,HD,window", [(1, 8, 2, 64, 0), (2, 6, 3, 64, 200), (3, 4, 1, 128, 0), (4, 4, 2, 128, 64),
+                                                   (5, 16, 8, 64, 64)])
+def test_attn_prefill_tc_many_short_and_long_items(K, seed, QH, KVH, HD, window):
+    """The kernel's blocks walk items (query tile, head, sequence) one after another with rings, tensor-memory
+    buffers and barrier phases that run on across their borders.  Batches of 30 to 60 sequences of 1 to 700
+    rows give every block dozens of items of one to six key tiles in a row, among them many of a single tile
+    and sequences that are over before a block's share begins; compared with the float64 reference."""
+    import random
+    rng = random.Random(seed)
+    lens = [rng.choice([1, 2, 63, 64, 65, 127, 128, 129, 130, rng.randint(1, 700)]) for _ in range(rng.randint(30, 60))]
+    T = sum(lens)
+    width = (QH * HD + 2 * KVH * HD + QH + 7) // 8 * 8
+    buf = rnd(T, width, dtype=torch.bfloat16, seed=seed)
+    q, k = buf[:, :QH * HD], buf[:, QH * HD:QH * HD + KVH * HD]
+    v = buf[:, QH * HD + KVH * HD:QH * HD + 2 * KVH * HD]
+    gate = buf[:, QH * HD + 2 * KVH * HD:QH * HD + 2 * KVH * HD + QH]
+    bounds = [0]
+    for n in lens:
+        bounds.append(bounds[-1] + n)
+    starts = torch.tensor(bounds, dtype=torch.int32, device=DEV)
+    ctx = torch.full((T, QH * HD), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = HD ** -0.5
+    for _ in range(3):                                  # the same launch again: nothing may be left over from the last
+        K.attn_prefill_tc(ctx, q, k, v, gate, starts, len(lens), max(lens), QH, KVH, HD, window, scale, err=err)
+    assert int(err) == 0
+    qc, kc, vc, gc = q.cpu(), k.cpu(), v.cpu(), gate.cpu()
+    for b, n in enumerate(lens):
+        sl = slice(bounds[b], bounds[b] + n)
+        ref = _ref_attention(qc[sl].view(n, QH, HD), kc[sl].view(n, KVH, HD), vc[sl].view(n, KVH, HD), window, scale, gc[sl])
+        close(ctx[sl].view(n, QH, HD), ref, torch.bfloat16)
+
+
 def test_attn_prefill_tc_refuses_other_head_sizes(K):
     x = torch.empty(4, 96, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(K.KernelError, match="head size"):
