@@ -212,12 +212,27 @@ def test_attn_append_on_tcgen05_copies_pages_and_masks_what_is_not_the_sequences
     buffer behind the last sequence's (the kernel clears what is not the sequence's in its copy of a
     value tile).  Against float64 attention over the whole sequences; no pipeline wait may have run
     out, and the cache is left as it was."""
+    _append_on_tcgen05([0, 5, 64, 130, 200, 257, 700], [33, 1, 70, 150, 64, 2, 300], QH, KVH, HD, window)
+
+
+@pytest.mark.parametrize("seed,QH,KVH,HD,window", [(1, 8, 2, 64, 0), (2, 4, 2, 128, 0), (3, 6, 3, 64, 192), (4, 2, 1, 128, 64)])
+def test_attn_append_on_tcgen05_with_many_sequences(seed, QH, KVH, HD, window):
+    """The same with 24 to 40 sequences at positions 0 to 900 that bring 1 to 260 rows each: every block of the
+    kernel walks many (query tile, head, sequence) items, of one key tile and of eight, from the cache and from
+    the step, one after another."""
+    import random
+    rng = random.Random(seed)
+    n_seq = rng.randint(24, 40)
+    past = [rng.choice([0, 1, 63, 64, 65, 128, 129, rng.randint(0, 900)]) for _ in range(n_seq)]
+    new = [rng.choice([1, 2, 16, 64, 65, 128, 129, rng.randint(1, 260)]) for _ in range(n_seq)]
+    _append_on_tcgen05(past, new, QH, KVH, HD, window)
+
+
+def _append_on_tcgen05(past, new, QH, KVH, HD, window):
     from catena_models_b200 import kernels as K
 
     dtype = torch.bfloat16
     ring = (window + 63) // 64 * 64 if window else 0
-    past = [0, 5, 64, 130, 200, 257, 700]
-    new = [33, 1, 70, 150, 64, 2, 300]
     g = torch.Generator().manual_seed(HD + window)
     kv = [torch.randn(p + n, 2, KVH, HD, generator=g) for p, n in zip(past, new)]
     stored = [x[:p] for x, p in zip(kv, past)]
