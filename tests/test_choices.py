@@ -42,3 +42,41 @@ def test_runs_of_k_fill_one_round_and_shrink_with_the_rows():
 
 def test_fewer_sms_fewer_runs():
     assert _runtime(32)._tiled_slices(512, 2048, 8192)[0] <= _runtime(148)._tiled_slices(512, 2048, 8192)[0]
+
+
+def _attention_choice(monkeypatch, lens, window, dtype="bfloat16", HD=64):
+    """Which prompt-attention kernel the runtime calls for a step of sequences of these lengths."""
+    import types
+    import torch
+    from catena_models_b200.engine import runtime as R
+
+    called = []
+    for name in ("attn_prefill_tc", "attn_prefill_mma", "attn_prefill_simt"):
+        monkeypatch.setattr(R.kernels, name, lambda *a, _n=name, **k: called.append(_n))
+    rt = _runtime()
+    rt.tensor_core_prompts, rt.error_flag = True, None
+    T, QH, KVH = sum(lens), 4, 2
+    buf = torch.zeros(T, (QH + 2 * KVH) * HD, dtype=getattr(torch, dtype))
+    q, k, v = buf[:, :QH * HD], buf[:, QH * HD:(QH + KVH) * HD], buf[:, (QH + KVH) * HD:]
+    ctx = torch.zeros(T, QH * HD, dtype=buf.dtype)
+    batch = types.SimpleNamespace(max_len=max(lens), B=len(lens), seq_start=None)
+    rt.attention_prefill(ctx, q, k, v, None, batch, QH, KVH, HD, window, 1.0)
+    assert len(called) == 1
+    return called[0]
+
+
+def test_prompt_attention_goes_to_tcgen05_from_768_tokens_or_with_many_rows(monkeypatch):
+    assert _attention_choice(monkeypatch, [767], 0) == "attn_prefill_mma"
+    assert _attention_choice(monkeypatch, [768], 0) == "attn_prefill_tc"
+    assert _attention_choice(monkeypatch, [1500], 512) == "attn_prefill_mma"          # the window is what a row sees
+    assert _attention_choice(monkeypatch, [1500], 768) == "attn_prefill_tc"
+    assert _attention_choice(monkeypatch, [4096], 512) == "attn_prefill_tc"           # ... unless the step has 2,048 rows
+    assert _attention_choice(monkeypatch, [4096], 192) == "attn_prefill_mma"
+    assert _attention_choice(monkeypatch, [256] * 8, 0) == "attn_prefill_tc"          # 2,048 rows of 256 and more
+    assert _attention_choice(monkeypatch, [256] * 7, 0) == "attn_prefill_mma"
+    assert _attention_choice(monkeypatch, [255] * 64, 0) == "attn_prefill_mma"
+    assert _attention_choice(monkeypatch, [2048] * 4, 256) == "attn_prefill_tc"
+    assert _attention_choice(monkeypatch, [2048], 0, HD=128) == "attn_prefill_tc"
+    assert _attention_choice(monkeypatch, [2048], 0, HD=96) == "attn_prefill_mma"     # other multiples of 16 up to 128
+    assert _attention_choice(monkeypatch, [2048], 0, HD=192) == "attn_prefill_simt"
+    assert _attention_choice(monkeypatch, [2048], 0, dtype="float32") == "attn_prefill_simt"
