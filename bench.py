@@ -2,7 +2,7 @@
 """Decode and prefill throughput of LFM3-class models with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--config 1.7b|350m|2.6b] [--batch B]
-                    [--layers L] [--impl reference] [--kernel-table]
+                    [--layers L] [--impl reference] [--kernel-table] [--attention-table]
 
 A step is one decode step of the whole batch.  Prints one JSON line: decoded tokens per second
 on the device (`value`), the same through the Python entry point with host tokens in and out
@@ -17,7 +17,8 @@ decode towards a context of 4,096; decode points at batch 1, 8 and 64 at three c
 16,384-token prompt alone, then decode of 64 sequences on a cache sized for 64 x 32,768 tokens).
 `--kernel-table` runs one decode step and one prompt step kernel by kernel with a pair of CUDA
 events around each launch and prints what each kernel took against its roofline, instead of the
-JSON line.  This engine runs on one GPU; for --gpus above 1 it says so and exits with 2.
+JSON line.  `--attention-table` times the prompt-attention kernels alone (the configuration's heads, one
+sequence of 2,048, 4,096 and 16,384 tokens, launches back to back in a recorded graph).  This engine runs on one GPU; for --gpus above 1 it says so and exits with 2.
 """
 import argparse
 import json
@@ -105,6 +106,63 @@ def peaks():
         except (OSError, ValueError):
             pass
     return out
+
+
+def _graph_time_us(torch, fn, launches=10, replays=5):
+    """Median time of one call of fn, in microseconds, over `replays` replays of a recorded graph of
+    `launches` calls back to back (CUDA events around each replay; three calls first)."""
+    for _ in range(3):
+        fn()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(launches):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(replays):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) / launches * 1e3)
+    return statistics.median(times)
+
+
+def attention_table(cfg, pk, device="cuda:0", lengths=(2048, 4096, 16384), time_us=None):
+    """The two tensor-core prompt-attention kernels alone, for the configuration's heads: one sequence of each
+    length with a full causal mask, random bfloat16 q, k and v as column blocks of one buffer (as the q/k/v
+    product leaves them), no gate.  FLOPs are counted over the causal half: 4 * heads * head size * T (T + 1) / 2."""
+    import torch
+
+    from catena_models_b200 import kernels as K
+
+    time_us = time_us or (lambda fn: _graph_time_us(torch, fn))
+    QH, KVH, HD = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    print(f"\n### prompt attention alone, {QH} query heads over {KVH} kv heads of {HD}, bfloat16, causal\n")
+    print(f"| tokens | tcgen05 us | TFLOP/s | of peak ({pk['bf16_tflops']:.0f}) | mma.sync us | TFLOP/s |")
+    print("|---|---|---|---|---|---|")
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    for T in lengths:
+        width = QH * HD + 2 * KVH * HD
+        buf = torch.randn(T, width, device=device).to(torch.bfloat16)
+        q, k, v = buf[:, :QH * HD], buf[:, QH * HD:QH * HD + KVH * HD], buf[:, QH * HD + KVH * HD:]
+        starts = torch.tensor([0, T], dtype=torch.int32, device=device)
+        ctx = torch.empty(T, QH * HD, dtype=torch.bfloat16, device=device)
+        scale = HD ** -0.5
+        flops = 4.0 * QH * HD * T * (T + 1) / 2
+        cells = []
+        if HD in (64, 128):
+            t = time_us(lambda: K.attn_prefill_tc(ctx, q, k, v, None, starts, 1, T, QH, KVH, HD, 0, scale, err=err))
+            if int(err.item()) != 0:
+                raise RuntimeError(f"attn_prefill_tc raised its error flag ({int(err.item())})")
+            cells += [f"{t:.1f}", f"{flops / t / 1e6:.0f}", f"{flops / t / 1e6 / pk['bf16_tflops']:.3f}"]
+        else:
+            cells += ["", "", ""]
+        t = time_us(lambda: K.attn_prefill_mma(ctx, q, k, v, None, starts, 1, T, QH, KVH, HD, 0, scale))
+        cells += [f"{t:.1f}", f"{flops / t / 1e6:.0f}"]
+        print(f"| {T:,} | " + " | ".join(cells) + " |", flush=True)
 
 
 class ClockSampler:
@@ -473,6 +531,8 @@ def main():
                     help="run one part only (small captures under a profiler); prints that part's facts")
     ap.add_argument("--kernel-table", action="store_true",
                     help="time one decode step and one prompt step kernel by kernel and print the table")
+    ap.add_argument("--attention-table", action="store_true",
+                    help="time the prompt-attention kernels alone at 2,048, 4,096 and 16,384 tokens and print the table")
     ap.add_argument("--print-config", action="store_true",
                     help="print the configuration's config.json (for `python -m catena_models_b200 --random FILE`) and exit")
     args = ap.parse_args()
@@ -504,6 +564,9 @@ def main():
 
     pk = peaks()
     cfg = model_config(args.config, args.layers)
+    if args.attention_table:
+        attention_table(cfg, pk)
+        return 0
     vocab = cfg["vocab_size"]
     headline = args.config == "1.7b"
     point_batches = (1, 8, 64) if headline and not args.no_points and args.only == "all" and not args.kernel_table else ()
